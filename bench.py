@@ -1,0 +1,355 @@
+"""Benchmark of the MoE block: tokens/s of one layer pass.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload c2|c3]
+
+A step is one pass of the block (router -> top-4 -> permutation -> grouped
+gate_up + SwiGLU -> grouped down -> combine + residual) over one batch of
+seeded synthetic tokens.  One JSON line is printed by rank 0.
+
+N=1 runs the gpt-oss-20b-shape layer at T=7168 ("c2"), the configuration the
+single-GPU metric is quoted on.  N>1 runs one such replica per GPU (the
+reference serves the 20b shape as data-parallel replicas, getp_run.cpp:1035-1060),
+so per-GPU work is fixed ("weak") and no data-path collective is involved.
+--workload c3 runs the 120b-shape layer (T=6144, 128 experts) instead.
+
+--impl reference times the reference's own CPU code (oracle/_ref when it was
+built from the reference tree, else the C port in oracle/) on the host cores, on
+a bounded sample of the same workload per step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import pathlib
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = pathlib.Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+import __graft_entry__ as entry  # noqa: E402
+
+METRIC = "moe_layer_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def read_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs
+    (read-only queries)."""
+
+    def __init__(self, index, period=0.02):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period
+        self.samples, self.reasons, self.stop_flag = [], set(), False
+        self.max_mhz = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.dev = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.dev, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if not self.nv:
+            return
+        nv = self.nv
+        names = {
+            nv.nvmlClocksEventReasonHwSlowdown: "hw_slowdown",
+            nv.nvmlClocksEventReasonHwThermalSlowdown: "hw_thermal_slowdown",
+            nv.nvmlClocksEventReasonSwThermalSlowdown: "sw_thermal_slowdown",
+            nv.nvmlClocksEventReasonSwPowerCap: "sw_power_cap",
+        }
+        while not self.stop_flag:
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.dev, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.dev)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def result(self):
+        self.stop_flag = True
+        self.join(timeout=2)
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable"]}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons)}
+
+
+def workload_shape(name):
+    from gpt_oss_b200 import synth
+
+    return synth.SHAPES[name]
+
+
+def device_weights(shape, dev, dtype_out="bf16"):
+    """Seeded bf16 weights generated on the device (N(0,0.02); biases N(0,0.01))."""
+    import torch
+
+    g = torch.Generator(device=dev)
+    g.manual_seed(shape.seed)
+    H, IM, E = shape.hidden_dim, shape.intermediate_dim, shape.n_experts
+
+    def normal(size, std, dtype=torch.bfloat16):
+        return (torch.randn(size, generator=g, device=dev, dtype=torch.float32) * std).to(dtype)
+
+    w = {
+        "w_router": normal((E, H), 0.02),
+        "b_router": normal((E,), 0.02).float(),
+        "w_mlp1": torch.empty((E, 2 * IM, H), device=dev, dtype=torch.bfloat16),
+        "b_mlp1": normal((E, 2 * IM), 0.01).float(),
+        "w_mlp2": torch.empty((E, H, IM), device=dev, dtype=torch.bfloat16),
+        "b_mlp2": normal((E, H), 0.01).float(),
+    }
+    for e in range(E):  # per expert, to bound the fp32 temporary
+        w["w_mlp1"][e] = normal((2 * IM, H), 0.02)
+        w["w_mlp2"][e] = normal((H, IM), 0.02)
+    return w
+
+
+def host_weights_f32(w):
+    return {k: v.float().cpu().numpy() for k, v in w.items()}
+
+
+def cpu_sample(shape, w_host, t_host, x_host, n_tokens, kind):
+    """Times the CPU implementation on the first n_tokens of the batch."""
+    oracle = entry.load_oracle()
+    d = dict(w_host)
+    d["t"], d["x"], d["pos"] = t_host[:n_tokens], x_host[:n_tokens], None
+    t0 = time.perf_counter()
+    oracle.moe_layer(d, shape, which=("ref" if kind == "reference" else "oracle"), taps=False)
+    return time.perf_counter() - t0
+
+
+def run_reference_arm(args, shape):
+    """The reference's CPU implementation on the host cores (rank 0 only)."""
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    oracle = entry.load_oracle()
+    if not oracle.ORACLE_LIB.exists():
+        oracle.build(native=True)
+    kind = "reference" if oracle.have_ref() else "port"
+    cores = oracle.num_threads("ref" if kind == "reference" else "oracle")
+    g = torch.Generator().manual_seed(shape.seed)
+    # weights drawn on the CPU here (same distributions); the sample is what matters
+    H, IM, E = shape.hidden_dim, shape.intermediate_dim, shape.n_experts
+
+    def normal(size, std):
+        return (torch.randn(size, generator=g) * std).bfloat16().float().numpy()
+
+    w = {"w_router": normal((E, H), 0.02), "b_router": normal((E,), 0.02),
+         "w_mlp1": normal((E, 2 * IM, H), 0.02), "b_mlp1": normal((E, 2 * IM), 0.01),
+         "w_mlp2": normal((E, H, IM), 0.02), "b_mlp2": normal((E, H), 0.01)}
+    n_sample = args.cpu_tokens
+    t = normal((n_sample, H), 1.0)
+    x = normal((n_sample, H), 1.0)
+    for _ in range(min(args.warmup, 1)):
+        cpu_sample(shape, w, t, x, n_sample, kind)
+    times = [cpu_sample(shape, w, t, x, n_sample, kind) for _ in range(args.steps)]
+    total = sum(times)
+    value = n_sample * args.steps / total
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": shape.name, "tokens_per_step": n_sample,
+                   "note": "CPU path of the reference on a bounded sample per step"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind,
+                         "sample": f"{n_sample} tokens x {shape.experts_per_token} experts per step"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, shape):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    pkg = entry.load_package()
+    T, H, IM, E, K = (shape.n_tokens, shape.hidden_dim, shape.intermediate_dim, shape.n_experts,
+                      shape.experts_per_token)
+    eng = pkg.MoeEngine(H, IM, E, K, n_layers=1, max_tokens=T, swiglu_limit=shape.swiglu_limit,
+                        device=local_rank)
+    w = device_weights(shape, dev)
+    eng.load_layer_bf16(0, w["w_router"], w["b_router"], w["w_mlp1"], w["b_mlp1"], w["w_mlp2"],
+                        w["b_mlp2"], on_device=True)
+    g = torch.Generator(device=dev)
+    g.manual_seed(shape.seed + 1000 + rank)
+    t = torch.randn((T, H), generator=g, device=dev).bfloat16()
+    x0 = torch.randn((T, H), generator=g, device=dev).bfloat16()
+    x = x0.clone()
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        eng.forward(0, t, x, None, T, stream)
+    barrier()
+    if eng.device_status() != 0:
+        raise SystemExit("device status non-zero after warm-up")
+    x.copy_(x0)
+    eng.set_option("time_stages", 1)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    barrier()
+    launches0 = eng.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        eng.forward(0, t, x, None, T, stream)
+    ev1.record()
+    barrier()
+    clocks = sampler.result()
+    elapsed_ms = ev0.elapsed_time(ev1)
+    launches = eng.launch_count() - launches0
+    stage_ms = {s: eng.stage_ms(s) for s in ("route", "permute", "gate_up", "down", "combine")}
+    eng.set_option("time_stages", 0)
+    if world > 1:
+        tt = torch.tensor([elapsed_ms], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(tt.item())
+    value = world * T * args.steps / (elapsed_ms * 1e-3)
+
+    # end to end through the host-buffer entry point: pinned host inputs copied in,
+    # result copied out, every step
+    t_h = t.cpu().pin_memory()
+    x_h = x0.cpu().pin_memory()
+    for _ in range(2):
+        eng.forward_host(0, t_h, x_h, None, T)
+    barrier()
+    t0 = time.perf_counter()
+    e2e_steps = max(3, min(args.steps, 20))
+    for _ in range(e2e_steps):
+        eng.forward_host(0, t_h, x_h, None, T)
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        tt = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e2e_s = float(tt.item())
+    e2e_value = world * T * e2e_steps / e2e_s
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = read_peaks()
+    n_assign = T * K
+    flops_gate_up = 2.0 * n_assign * 2 * IM * H
+    timed_s = elapsed_ms * 1e-3
+    peak_kind = "bf16_tflops" if timed_s < 1.0 else "bf16_tflops_sustained"
+    achieved = flops_gate_up / (stage_ms["gate_up"] * 1e-3) / 1e12
+    roofline = {
+        "kernel": "grouped_gemm_tc_kernel<240, swiglu> (gate_up)", "bound": "tensor",
+        "achieved": achieved, "peak": peaks[peak_kind], "unit": "TFLOP/s",
+        "frac": achieved / peaks[peak_kind], "peak_source": f"{peaks['source']} {peak_kind}",
+        "traffic": None, "kernel_ms": stage_ms["gate_up"],
+        "stage_ms": stage_ms,
+        "down_tflops": 2.0 * n_assign * H * IM / (stage_ms["down"] * 1e-3) / 1e12,
+        "route_gbs": (T * H * 2 + E * H * 2 + T * K * 8) / (stage_ms["route"] * 1e-3) / 1e9,
+        "combine_gbs": (n_assign * H * 2 + 2 * T * H * 2) / (stage_ms["combine"] * 1e-3) / 1e9,
+        "hbm_peak_gbs": peaks["hbm_gbs"],
+    }
+
+    cpu_baseline = None
+    if not args.no_cpu_baseline:
+        oracle = entry.load_oracle()
+        if not oracle.ORACLE_LIB.exists():
+            oracle.build(native=True)
+        kind = "reference" if oracle.have_ref() else "port"
+        n_cpu = args.cpu_tokens
+        w_host = host_weights_f32(w)
+        t_host = t[:n_cpu].float().cpu().numpy()
+        x_host = x0[:n_cpu].float().cpu().numpy()
+        sec = cpu_sample(shape, w_host, t_host, x_host, n_cpu, kind)
+        cpu_baseline = {"value": n_cpu / sec, "unit": UNIT,
+                        "cores": oracle.num_threads("ref" if kind == "reference" else "oracle"),
+                        "kind": kind,
+                        "sample": f"first {n_cpu} tokens of the batch, {K} experts each, {sec:.1f} s"}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": shape.name, "tokens_per_gpu": T, "hidden": H, "intermediate": IM,
+                   "experts": E, "top_k": K, "parallelism": f"replicas x{world}",
+                   "l2": "inputs larger than L2 (expert weights %.2f GB streamed every step)"
+                         % ((E * 3 * IM * H * 2) / 1e9)},
+        "roofline": roofline, "cpu_baseline": cpu_baseline,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 2 * T * H * 2,
+                "d2h_bytes_per_step": T * H * 2, "steps": e2e_steps},
+        "gpu_launches": launches, "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "tiny"])
+    ap.add_argument("--cpu-tokens", type=int, default=None,
+                    help="tokens in the CPU sample (default 256 for ours, 64 for reference)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    entry.load_package()
+    shape = workload_shape(args.workload)
+    if args.impl == "reference":
+        args.steps = args.steps if args.steps is not None else 5
+        args.warmup = args.warmup if args.warmup is not None else 1
+        args.cpu_tokens = args.cpu_tokens or 64
+        run_reference_arm(args, shape)
+    else:
+        args.steps = args.steps if args.steps is not None else 100
+        args.warmup = max(3, args.warmup if args.warmup is not None else 10)
+        args.cpu_tokens = args.cpu_tokens or 256
+        run_ours(args, shape)
+
+
+if __name__ == "__main__":
+    main()

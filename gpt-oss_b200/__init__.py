@@ -1,0 +1,268 @@
+"""B200 (sm_100a) engine for the GPT-OSS MoE block: Python binding of the C ABI.
+
+The product is ``libgptoss_moe_b200.so`` (CUDA kernels + ``extern "C"`` layer,
+declared in ``include/gptoss_moe_b200.h``).  This module only loads it through
+``ctypes`` and wraps the handle in :class:`MoeEngine`, whose methods map one to
+one onto the C entry points.  There is no CPU fallback: loading fails loudly
+when the library has not been built, and every compute call fails with
+``GPTOSS_E_CUDA`` when no sm_100 GPU is present.
+"""
+from __future__ import annotations
+
+import ctypes
+import pathlib
+
+import numpy as np
+
+PKG_DIR = pathlib.Path(__file__).resolve().parent
+LIB_PATH = PKG_DIR / "libgptoss_moe_b200.so"
+HEADER_PATH = PKG_DIR.parent / "include" / "gptoss_moe_b200.h"
+
+GPTOSS_OK = 0
+GPTOSS_E_INVALID = -1
+GPTOSS_E_CUDA = -2
+GPTOSS_E_CAPACITY = -3
+GPTOSS_E_DEVICE = -4
+GPTOSS_E_STATE = -5
+GPTOSS_E_COMM = -6
+
+WEIGHTS_BF16 = 0
+WEIGHTS_MXFP4 = 1
+GEMM_TCGEN05 = 0
+GEMM_SIMT = 1
+
+STAGES = ("route", "permute", "gate_up", "down", "combine", "dispatch", "return")
+
+
+class MoeConfig(ctypes.Structure):
+    """Mirror of gptoss_moe_config_t."""
+
+    _fields_ = [
+        ("hidden_dim", ctypes.c_int),
+        ("intermediate_dim", ctypes.c_int),
+        ("n_experts", ctypes.c_int),
+        ("experts_per_token", ctypes.c_int),
+        ("n_layers", ctypes.c_int),
+        ("max_tokens", ctypes.c_int),
+        ("swiglu_limit", ctypes.c_float),
+        ("ep_rank", ctypes.c_int),
+        ("ep_size", ctypes.c_int),
+        ("weight_format", ctypes.c_int),
+        ("device", ctypes.c_int),
+    ]
+
+
+class MoeError(RuntimeError):
+    def __init__(self, code: int, text: str):
+        super().__init__(f"gptoss_moe error {code}: {text}")
+        self.code = code
+
+
+_lib = None
+
+
+def load_library() -> ctypes.CDLL:
+    """Load the native library (once).  Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -c 'import __graft_entry__ as g; "
+            "g.build()'` (there is no fallback path)"
+        )
+    lib = ctypes.CDLL(str(LIB_PATH))
+    vp, ip, fp = ctypes.c_void_p, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_float)
+    c_int, c_char_p = ctypes.c_int, ctypes.c_char_p
+    sigs = {
+        "gptoss_moe_create": (c_int, [ctypes.POINTER(MoeConfig), ctypes.POINTER(vp)]),
+        "gptoss_moe_destroy": (c_int, [vp]),
+        "gptoss_moe_last_error": (c_char_p, [vp]),
+        "gptoss_moe_load_layer_f32": (c_int, [vp, c_int, vp, vp, vp, vp, vp, vp]),
+        "gptoss_moe_load_layer_bf16": (c_int, [vp, c_int, vp, vp, vp, vp, vp, vp, c_int]),
+        "gptoss_moe_load_layer_mxfp4": (
+            c_int,
+            [vp, c_int, vp, vp, vp, vp, vp, vp, vp, vp, c_int],
+        ),
+        "gptoss_moe_forward": (c_int, [vp, c_int, vp, vp, vp, c_int, vp]),
+        "gptoss_moe_forward_host": (c_int, [vp, c_int, vp, vp, vp, c_int]),
+        "gptoss_moe_route": (c_int, [vp, c_int, vp, vp, c_int, vp]),
+        "gptoss_moe_permute": (c_int, [vp, vp, c_int, vp]),
+        "gptoss_moe_experts": (c_int, [vp, c_int, vp]),
+        "gptoss_moe_combine": (c_int, [vp, vp, c_int, vp]),
+        "gptoss_moe_rmsnorm": (c_int, [vp, vp, vp, vp, vp, c_int, vp]),
+        "gptoss_moe_get_routing": (c_int, [vp, c_int, vp, vp, vp, vp, vp]),
+        "gptoss_moe_get_activations": (c_int, [vp, vp, ctypes.c_size_t]),
+        "gptoss_moe_set_option": (c_int, [vp, c_char_p, c_int]),
+        "gptoss_moe_launch_count": (ctypes.c_longlong, [vp]),
+        "gptoss_moe_device_status": (c_int, [vp]),
+        "gptoss_moe_stage_ms": (c_int, [vp, c_int, fp]),
+        "gptoss_moe_ep_unique_id": (c_int, [vp]),
+        "gptoss_moe_ep_init": (c_int, [vp, vp]),
+        "gptoss_moe_version": (c_char_p, []),
+    }
+    for name, (res, args) in sigs.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def _ptr(obj):
+    """Raw address of a torch tensor, numpy array, int or None."""
+    if obj is None:
+        return None
+    if isinstance(obj, int):
+        return ctypes.c_void_p(obj)
+    if isinstance(obj, np.ndarray):
+        if not obj.flags["C_CONTIGUOUS"]:
+            raise ValueError("array must be C-contiguous")
+        return ctypes.c_void_p(obj.ctypes.data)
+    if hasattr(obj, "data_ptr"):
+        if not obj.is_contiguous():
+            raise ValueError("tensor must be contiguous")
+        return ctypes.c_void_p(obj.data_ptr())
+    raise TypeError(f"cannot take the address of {type(obj)}")
+
+
+class MoeEngine:
+    """One engine = one gptoss_moe_t handle.  Method names follow the C ABI."""
+
+    def __init__(
+        self,
+        hidden_dim,
+        intermediate_dim,
+        n_experts,
+        experts_per_token,
+        n_layers=1,
+        max_tokens=1024,
+        swiglu_limit=7.0,
+        ep_rank=0,
+        ep_size=1,
+        weight_format=WEIGHTS_BF16,
+        device=0,
+    ):
+        self.lib = load_library()
+        self.cfg = MoeConfig(
+            hidden_dim, intermediate_dim, n_experts, experts_per_token, n_layers, max_tokens,
+            swiglu_limit, ep_rank, ep_size, weight_format, device,
+        )
+        self.handle = ctypes.c_void_p()
+        rc = self.lib.gptoss_moe_create(ctypes.byref(self.cfg), ctypes.byref(self.handle))
+        if rc != GPTOSS_OK:
+            text = self.lib.gptoss_moe_last_error(None).decode()
+            self.handle = None
+            raise MoeError(rc, text)
+
+    # -- plumbing
+    def _check(self, rc):
+        if rc != GPTOSS_OK:
+            raise MoeError(rc, self.lib.gptoss_moe_last_error(self.handle).decode())
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.lib.gptoss_moe_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def local_experts(self):
+        return self.cfg.n_experts // max(1, self.cfg.ep_size)
+
+    # -- weights
+    def load_layer_f32(self, layer, w_router, b_router, w_mlp1, b_mlp1, w_mlp2, b_mlp2):
+        arrs = [np.ascontiguousarray(a, dtype=np.float32)
+                for a in (w_router, b_router, w_mlp1, b_mlp1, w_mlp2, b_mlp2)]
+        self._check(self.lib.gptoss_moe_load_layer_f32(self.handle, layer, *[_ptr(a) for a in arrs]))
+
+    def load_layer_bf16(self, layer, w_router, b_router, w_mlp1, b_mlp1, w_mlp2, b_mlp2,
+                        on_device):
+        args = [_ptr(a) for a in (w_router, b_router, w_mlp1, b_mlp1, w_mlp2, b_mlp2)]
+        self._check(self.lib.gptoss_moe_load_layer_bf16(self.handle, layer, *args,
+                                                        1 if on_device else 0))
+
+    # -- compute
+    def forward(self, layer, t, x, pos, n_tokens, stream=0):
+        self._check(self.lib.gptoss_moe_forward(self.handle, layer, _ptr(t), _ptr(x), _ptr(pos),
+                                                n_tokens, ctypes.c_void_p(stream)))
+
+    def forward_host(self, layer, t_host, x_host, pos_host, n_tokens):
+        self._check(self.lib.gptoss_moe_forward_host(self.handle, layer, _ptr(t_host),
+                                                     _ptr(x_host), _ptr(pos_host), n_tokens))
+
+    def route(self, layer, t, pos, n_tokens, stream=0):
+        self._check(self.lib.gptoss_moe_route(self.handle, layer, _ptr(t), _ptr(pos), n_tokens,
+                                              ctypes.c_void_p(stream)))
+
+    def permute(self, t, n_tokens, stream=0):
+        self._check(self.lib.gptoss_moe_permute(self.handle, _ptr(t), n_tokens,
+                                                ctypes.c_void_p(stream)))
+
+    def experts(self, layer, stream=0):
+        self._check(self.lib.gptoss_moe_experts(self.handle, layer, ctypes.c_void_p(stream)))
+
+    def combine(self, x, n_tokens, stream=0):
+        self._check(self.lib.gptoss_moe_combine(self.handle, _ptr(x), n_tokens,
+                                                ctypes.c_void_p(stream)))
+
+    def rmsnorm(self, out, x, w_dev, pos, n_tokens, stream=0):
+        self._check(self.lib.gptoss_moe_rmsnorm(self.handle, _ptr(out), _ptr(x), _ptr(w_dev),
+                                                _ptr(pos), n_tokens, ctypes.c_void_p(stream)))
+
+    # -- taps
+    def get_routing(self, n_tokens, want_logits=False):
+        K, El, E = self.cfg.experts_per_token, self.local_experts, self.cfg.n_experts
+        topk_i = np.empty((n_tokens, K), dtype=np.int32)
+        topk_v = np.empty((n_tokens, K), dtype=np.float32)
+        offsets = np.empty((El + 1,), dtype=np.int32)
+        sorted_token = np.full((max(1, n_tokens * K * max(1, self.cfg.ep_size)),), -1,
+                               dtype=np.int32)
+        logits = np.empty((n_tokens, E), dtype=np.float32) if want_logits else None
+        self._check(self.lib.gptoss_moe_get_routing(self.handle, n_tokens, _ptr(topk_i),
+                                                    _ptr(topk_v), _ptr(offsets),
+                                                    _ptr(sorted_token), _ptr(logits)))
+        out = {"topk_i": topk_i, "topk_v": topk_v, "expert_offsets": offsets,
+               "sorted_token": sorted_token[: int(offsets[-1])]}
+        if want_logits:
+            out["logits"] = logits
+        return out
+
+    def get_activations(self, n_rows):
+        buf = np.empty((n_rows, self.cfg.intermediate_dim), dtype=np.uint16)
+        self._check(self.lib.gptoss_moe_get_activations(self.handle, _ptr(buf), buf.nbytes))
+        return buf
+
+    def set_option(self, name, value):
+        self._check(self.lib.gptoss_moe_set_option(self.handle, name.encode(), int(value)))
+
+    def launch_count(self):
+        return int(self.lib.gptoss_moe_launch_count(self.handle))
+
+    def device_status(self):
+        return int(self.lib.gptoss_moe_device_status(self.handle))
+
+    def stage_ms(self, stage):
+        ms = ctypes.c_float()
+        idx = STAGES.index(stage) if isinstance(stage, str) else stage
+        self._check(self.lib.gptoss_moe_stage_ms(self.handle, idx, ctypes.byref(ms)))
+        return float(ms.value)
+
+    # -- expert parallelism
+    @staticmethod
+    def ep_unique_id():
+        lib = load_library()
+        buf = (ctypes.c_ubyte * 128)()
+        rc = lib.gptoss_moe_ep_unique_id(ctypes.cast(buf, ctypes.c_void_p))
+        if rc != GPTOSS_OK:
+            raise MoeError(rc, "gptoss_moe_ep_unique_id failed")
+        return bytes(buf)
+
+    def ep_init(self, unique_id: bytes):
+        buf = (ctypes.c_ubyte * 128).from_buffer_copy(unique_id)
+        self._check(self.lib.gptoss_moe_ep_init(self.handle, ctypes.cast(buf, ctypes.c_void_p)))

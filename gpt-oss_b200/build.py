@@ -1,0 +1,58 @@
+"""Build steps for the native code: one nvcc command for the CUDA library.
+
+Kept as plain command lines (no JIT cache): the .so lands beside this file so
+that it is what every process loads.
+"""
+from __future__ import annotations
+
+import os
+import pathlib
+import shutil
+import subprocess
+
+PKG_DIR = pathlib.Path(__file__).resolve().parent
+CSRC = PKG_DIR / "csrc"
+LIB = PKG_DIR / "libgptoss_moe_b200.so"
+
+CU_SOURCES = ["moe_api.cu", "router.cu", "permute.cu", "grouped_gemm.cu", "weights.cu", "ep.cu"]
+HEADERS = ["common.cuh", "engine.h", "ep.h"]
+
+NVCC_FLAGS = [
+    "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+    "-Xcompiler", "-fPIC,-fvisibility=default", "-shared",
+]
+
+
+def _nvcc() -> str:
+    for cand in ("/usr/local/cuda/bin/nvcc", shutil.which("nvcc")):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found")
+
+
+def _stale(target: pathlib.Path, deps) -> bool:
+    if not target.exists():
+        return True
+    t = target.stat().st_mtime
+    return any(pathlib.Path(d).stat().st_mtime > t for d in deps)
+
+
+def build_library(force: bool = False, verbose: bool = False) -> pathlib.Path:
+    """Compile every CUDA source for sm_100a into libgptoss_moe_b200.so."""
+    srcs = [CSRC / s for s in CU_SOURCES]
+    deps = srcs + [CSRC / h for h in HEADERS] + [PKG_DIR.parent / "include" / "gptoss_moe_b200.h"]
+    if not force and not _stale(LIB, deps):
+        return LIB
+    cmd = [_nvcc(), *NVCC_FLAGS, "-o", str(LIB), *map(str, srcs), "-ldl"]
+    if verbose:
+        cmd.insert(1, "-Xptxas=-v")
+    env = dict(os.environ)
+    # the image exports CC/CXX that point at a wrapper; let nvcc pick the system g++
+    if os.path.exists("/usr/bin/g++"):
+        cmd[1:1] = ["-ccbin", "/usr/bin/g++"]
+    res = subprocess.run(cmd, cwd=str(CSRC), env=env, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
+    if verbose:
+        print(res.stdout + res.stderr)
+    return LIB

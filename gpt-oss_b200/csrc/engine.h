@@ -1,0 +1,132 @@
+// Internal declarations shared by the translation units of the MoE library:
+// the engine object behind the opaque C handle and the kernel launchers.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/gptoss_moe_b200.h"
+
+namespace gptoss {
+
+typedef __nv_bfloat16 bf16;
+
+// Rows of one M tile of the grouped GEMMs (UMMA M) and the K extent of one
+// pipeline stage (one 128-byte swizzle row of bf16).
+constexpr int kTileM = 128;
+constexpr int kTileK = 64;
+// Tokens handled by one CTA of the permutation kernels.
+constexpr int kPermTokens = 128;
+
+struct LayerWeights {
+  bf16 *w_router = nullptr;   // [E, H]
+  float *b_router = nullptr;  // [E]
+  bf16 *w1 = nullptr;         // [E_local, 2*IM, H]
+  float *b1 = nullptr;        // [E_local, 2*IM]
+  bf16 *w2 = nullptr;         // [E_local, H, IM]
+  float *b2 = nullptr;        // [E_local, H]
+  uint8_t *w1_blocks = nullptr, *w1_scales = nullptr;  // MXFP4 storage
+  uint8_t *w2_blocks = nullptr, *w2_scales = nullptr;
+  CUtensorMap tmap_w1, tmap_w2;
+  bool loaded = false;
+};
+
+// CUDA-event pairs recorded around one stage on the launching stream; one pair
+// per call while stage timing is on, averaged by gptoss_moe_stage_ms.
+struct StageTimer {
+  std::vector<cudaEvent_t> beg, end;
+  size_t used = 0;
+};
+
+}  // namespace gptoss
+
+struct gptoss_moe {
+  gptoss_moe_config_t cfg;
+  int H, IM, E, K, L, El;  // El = experts owned by this rank
+  int ep_rank, ep_size;
+  int max_tokens;
+  int rows_cap;     // rows that can enter the expert stage (T, or ep_size*T)
+  int assign_cap;   // (row, slot) pairs that can enter the expert stage
+  int mtiles_cap;   // M tiles of the grouped GEMMs
+  int perm_blocks_cap;
+  int num_sms;
+
+  std::vector<gptoss::LayerWeights> layers;
+
+  // home-side routing results for the rank's own tokens
+  int *topk_i = nullptr;      // [T, K] global expert ids, -1 on inactive rows
+  float *topk_v = nullptr;    // [T, K]
+  float *logits = nullptr;    // [T, E], only with keep_logits
+
+  // expert-stage inputs (single GPU: t / topk_i / topk_v of the caller's batch;
+  // expert parallel: the rows received from all homes)
+  const gptoss::bf16 *stage_rows = nullptr;  // [R, H]
+  const int *stage_expert = nullptr;         // [R, K] local expert id or -1
+  const float *stage_weight = nullptr;       // [R, K]
+  int stage_R = 0;
+
+  // permutation outputs
+  int *block_counts = nullptr;   // [perm_blocks_cap, El]
+  int *expert_offsets = nullptr; // [El + 1]
+  int *sorted_row = nullptr;     // [assign_cap] source row
+  float *sorted_weight = nullptr;// [assign_cap]
+  int *row_of = nullptr;         // [rows_cap * K] position in sorted order or -1
+  int *mtile_expert = nullptr;   // [mtiles_cap]
+  int *mtile_row0 = nullptr;     // [mtiles_cap] first sorted row of the tile
+  int *mtile_rows = nullptr;     // [mtiles_cap] valid rows in the tile
+  int *num_mtiles = nullptr;     // [1]
+
+  gptoss::bf16 *xs = nullptr;    // [assign_cap + pad, H]  gathered inputs
+  gptoss::bf16 *hact = nullptr;  // [assign_cap + pad, IM] SwiGLU activations
+  gptoss::bf16 *ys = nullptr;    // [assign_cap, H]        weighted expert outputs
+  CUtensorMap tmap_xs, tmap_h;
+
+  // host-call staging
+  gptoss::bf16 *t_dev = nullptr, *x_dev = nullptr;
+  int *pos_dev = nullptr;
+
+  int *status = nullptr;  // device status word
+  int opt_gemm_impl = GPTOSS_GEMM_TCGEN05;
+  int opt_keep_logits = 0;
+  int opt_exact_ties = 1;
+  int opt_time_stages = 0;
+  gptoss::StageTimer timers[8];
+  long long launches = 0;
+  mutable std::string err;
+
+  // expert parallelism (ep.cu)
+  void *ep = nullptr;
+};
+
+namespace gptoss {
+
+// router.cu
+cudaError_t launch_router_topk(const bf16 *t, const bf16 *w_router, const float *b_router,
+                               const int *pos, int T, int H, int E, int K, int *topk_i,
+                               float *topk_v, float *logits_opt, int exact_ties,
+                               cudaStream_t stream, long long *launches);
+cudaError_t launch_rmsnorm(bf16 *out, const bf16 *x, const float *w, const int *pos, int T, int H,
+                           cudaStream_t stream, long long *launches);
+
+// permute.cu
+cudaError_t launch_permute(gptoss_moe *h, cudaStream_t stream);
+cudaError_t launch_combine(gptoss_moe *h, bf16 *x, const int *topk_i_rows, int T,
+                           cudaStream_t stream);
+cudaError_t launch_reduce_rows(gptoss_moe *h, bf16 *out_rows, int R, cudaStream_t stream);
+
+// grouped_gemm.cu
+cudaError_t launch_gate_up(gptoss_moe *h, int layer, cudaStream_t stream);
+cudaError_t launch_down(gptoss_moe *h, int layer, cudaStream_t stream);
+int make_tmap_2d_bf16(CUtensorMap *map, const void *base, uint64_t inner, uint64_t outer,
+                      uint32_t box_inner, uint32_t box_outer, std::string *err);
+int gemm_tile_n(int which);  // N extent of one tile: 0 = gate_up, 1 = down
+
+// weights.cu
+cudaError_t launch_f32_to_bf16(bf16 *dst, const float *src, size_t n, cudaStream_t stream,
+                               long long *launches);
+
+}  // namespace gptoss

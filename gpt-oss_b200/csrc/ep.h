@@ -1,0 +1,12 @@
+// Expert parallelism over NCCL: declarations used by the C layer.
+#pragma once
+#include "engine.h"
+
+namespace gptoss {
+// Dispatch the routed rows of this rank's tokens to the ranks that own their
+// experts, run the local experts on everything received, send the per-row
+// partial sums back and add them to x.  Router results must already be in
+// h->topk_i / h->topk_v.
+int ep_forward(gptoss_moe *h, int layer, const void *t, void *x, int n_tokens, void *stream);
+void ep_destroy(gptoss_moe *h);
+}  // namespace gptoss

@@ -1,0 +1,315 @@
+// Token permutation into per-expert groups, and the inverse (combine).
+//
+// Replaces count_expert_assignments_kernel / exclusive_scan_small_kernel /
+// build_expert_assignments_kernel (getp-csrc/utility/utility.cpp:1058, :758,
+// :1079) and reduce_mlp2_slots_kernel + residual_add_batch_kernel
+// (utility.cpp:701-726, :158-173) of the reference.
+//
+// Input of the expert stage: R rows, each with K slots (local expert id or -1,
+// routing weight).  Output: the (row, slot) pairs sorted by expert, in flat
+// (row, slot) order inside an expert - a stable counting sort, so the result
+// is the same on every run (the reference's atomic scatter is not).
+//   count:        per-CTA histogram of 128 rows           -> block_counts
+//   scan_scatter: every CTA re-derives its own base offsets from block_counts,
+//                 ranks its items with warp match + per-warp histograms and
+//                 scatters; CTA 0 also writes expert_offsets and the M-tile
+//                 schedule of the grouped GEMMs
+//   gather:       copies the source rows into sorted order (16-byte accesses)
+// All kernels are bound by latency (<= 200k items) or HBM (gather, combine).
+#include "common.cuh"
+#include "engine.h"
+
+namespace gptoss {
+
+constexpr int kScanThreads = 512;
+
+__global__ void __launch_bounds__(256)
+perm_count_kernel(const int *__restrict__ slot_expert, int R, int K, int El,
+                  int *__restrict__ block_counts, int *status) {
+  extern __shared__ int hist[];
+  for (int e = threadIdx.x; e < El; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  const int r0 = blockIdx.x * kPermTokens;
+  const int items = kPermTokens * K;
+  for (int i = threadIdx.x; i < items; i += blockDim.x) {
+    const int row = r0 + i / K;
+    if (row < R) {
+      const int e = slot_expert[static_cast<size_t>(r0) * K + i];
+      if (e >= El) {
+        set_status(status, kStatusBadIndex);
+      } else if (e >= 0) {
+        atomicAdd(&hist[e], 1);
+      }
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < El; e += blockDim.x)
+    block_counts[static_cast<size_t>(blockIdx.x) * El + e] = hist[e];
+}
+
+__global__ void __launch_bounds__(kScanThreads)
+perm_scan_scatter_kernel(const int *__restrict__ slot_expert,
+                         const float *__restrict__ slot_weight, int R, int K, int El,
+                         const int *__restrict__ block_counts, int nblocks,
+                         int *__restrict__ expert_offsets, int *__restrict__ sorted_row,
+                         float *__restrict__ sorted_weight, int *__restrict__ row_of,
+                         int *__restrict__ mtile_expert, int *__restrict__ mtile_row0,
+                         int *__restrict__ mtile_rows, int *__restrict__ num_mtiles,
+                         int mtiles_cap, int assign_cap, int *status) {
+  extern __shared__ int sm[];
+  int *s_tot = sm;                 // [El] rows of each expert over all CTAs
+  int *s_base = sm + El;           // [El] next free position for this CTA
+  int *s_off = sm + 2 * El;        // [El + 1] exclusive scan of s_tot
+  int *s_whist = sm + 3 * El + 1;  // [warps][El]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int kWarps = kScanThreads / 32;
+
+  for (int e = tid; e < El; e += kScanThreads) {
+    int tot = 0, before = 0;
+    for (int b = 0; b < nblocks; b++) {
+      const int c = block_counts[static_cast<size_t>(b) * El + e];
+      tot += c;
+      if (b < static_cast<int>(blockIdx.x)) before += c;
+    }
+    s_tot[e] = tot;
+    s_base[e] = before;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    // exclusive scan over experts: each lane owns a run of consecutive experts
+    const int per = (El + 31) / 32;
+    int local = 0;
+    for (int j = 0; j < per; j++) {
+      const int e = lane * per + j;
+      if (e < El) local += s_tot[e];
+    }
+    int incl = local;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += v;
+    }
+    int run = incl - local;
+    for (int j = 0; j < per; j++) {
+      const int e = lane * per + j;
+      if (e < El) {
+        s_off[e] = run;
+        run += s_tot[e];
+      }
+    }
+    if (lane == 31) s_off[El] = incl;
+  }
+  __syncthreads();
+  for (int e = tid; e < El; e += kScanThreads) s_base[e] += s_off[e];
+
+  if (blockIdx.x == 0) {
+    for (int e = tid; e <= El; e += kScanThreads) expert_offsets[e] = s_off[e];
+    // M-tile schedule: expert e gets ceil(rows / kTileM) tiles, experts in order
+    if (warp == 0) {
+      const int per = (El + 31) / 32;
+      int local = 0;
+      for (int j = 0; j < per; j++) {
+        const int e = lane * per + j;
+        if (e < El) local += (s_tot[e] + kTileM - 1) / kTileM;
+      }
+      int incl = local;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += v;
+      }
+      int mt = incl - local;
+      for (int j = 0; j < per; j++) {
+        const int e = lane * per + j;
+        if (e < El) {
+          const int rows = s_tot[e];
+          for (int i = 0; i * kTileM < rows; i++, mt++) {
+            if (mt < mtiles_cap) {
+              mtile_expert[mt] = e;
+              mtile_row0[mt] = s_off[e] + i * kTileM;
+              mtile_rows[mt] = min(kTileM, rows - i * kTileM);
+            } else {
+              set_status(status, kStatusBadIndex);
+            }
+          }
+        }
+      }
+      if (lane == 31) *num_mtiles = min(incl, mtiles_cap);
+    }
+  }
+
+  const int r0 = blockIdx.x * kPermTokens;
+  const int items = kPermTokens * K;
+  for (int c0 = 0; c0 < items; c0 += kScanThreads) {
+    __syncthreads();
+    for (int i = tid; i < kWarps * El; i += kScanThreads) s_whist[i] = 0;
+    __syncthreads();
+    const int i = c0 + tid;
+    const int row = r0 + i / K;
+    int e = -1;
+    float wgt = 0.f;
+    if (i < items && row < R) {
+      e = slot_expert[static_cast<size_t>(r0) * K + i];
+      wgt = slot_weight[static_cast<size_t>(r0) * K + i];
+      if (e >= El) e = -1;
+    }
+    const uint32_t peers = __match_any_sync(0xffffffffu, e);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    if (e >= 0 && rank == 0) s_whist[warp * El + e] = __popc(peers);
+    __syncthreads();
+    if (e >= 0) {
+      int before = 0;
+      for (int w = 0; w < warp; w++) before += s_whist[w * El + e];
+      const int dst = s_base[e] + before + rank;
+      if (dst < assign_cap) {
+        sorted_row[dst] = row;
+        sorted_weight[dst] = wgt;
+        row_of[static_cast<size_t>(r0) * K + i] = dst;
+      } else {
+        set_status(status, kStatusBadIndex);
+        row_of[static_cast<size_t>(r0) * K + i] = -1;
+      }
+    } else if (i < items && row < R) {
+      row_of[static_cast<size_t>(r0) * K + i] = -1;
+    }
+    __syncthreads();
+    for (int ee = tid; ee < El; ee += kScanThreads) {
+      int add = 0;
+      for (int w = 0; w < kWarps; w++) add += s_whist[w * El + ee];
+      s_base[ee] += add;
+    }
+  }
+}
+
+// xs[r, :] = rows[sorted_row[r], :] for r < expert_offsets[El]; one warp per row.
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(bf16 *__restrict__ xs, const bf16 *__restrict__ rows,
+                   const int *__restrict__ sorted_row, const int *__restrict__ expert_offsets,
+                   int El, int H, int R, int *status) {
+  const int total = expert_offsets[El];
+  const int lane = threadIdx.x & 31;
+  const int nwarps = gridDim.x * (blockDim.x >> 5);
+  const int n4 = H >> 3;
+  for (int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < total; r += nwarps) {
+    const int src = sorted_row[r];
+    if (src < 0 || src >= R) {
+      set_status(status, kStatusBadIndex);
+      continue;
+    }
+    const uint4 *s4 = reinterpret_cast<const uint4 *>(rows + static_cast<size_t>(src) * H);
+    uint4 *d4 = reinterpret_cast<uint4 *>(xs + static_cast<size_t>(r) * H);
+    for (int p = lane; p < n4; p += 32) d4[p] = __ldg(s4 + p);
+  }
+}
+
+// RESIDUAL: x[row] = bf16(float(x[row]) + sum_k ys[row_of[row,k]]), rows without
+//           any valid slot untouched (inactive rows keep their x).
+// otherwise: out[row] = bf16(sum_k ys[row_of[row,k]]) for every row (zero when
+//           the row has no valid slot) - the owner-side pre-reduction under
+//           expert parallelism (getp-csrc/expert.cpp:394-410).
+template <bool RESIDUAL>
+__global__ void __launch_bounds__(256)
+combine_rows_kernel(bf16 *__restrict__ out, const bf16 *__restrict__ ys,
+                    const int *__restrict__ row_of, int R, int K, int H, int assign_cap,
+                    int *status) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= R) return;
+  int src[GPTOSS_MAX_TOPK];
+  int nvalid = 0;
+#pragma unroll
+  for (int k = 0; k < GPTOSS_MAX_TOPK; k++) {
+    src[k] = -1;
+    if (k < K) {
+      const int s = row_of[static_cast<size_t>(row) * K + k];
+      if (s >= assign_cap) {
+        set_status(status, kStatusBadIndex);
+      } else if (s >= 0) {
+        src[k] = s;
+        nvalid++;
+      }
+    }
+  }
+  if (RESIDUAL && nvalid == 0) return;
+  uint4 *o4 = reinterpret_cast<uint4 *>(out + static_cast<size_t>(row) * H);
+  const int n4 = H >> 3;
+  for (int p = lane; p < n4; p += 32) {
+    float a[8];
+    if (RESIDUAL) {
+      const uint4 v = o4[p];
+      a[0] = bf16_lo(v.x); a[1] = bf16_hi(v.x); a[2] = bf16_lo(v.y); a[3] = bf16_hi(v.y);
+      a[4] = bf16_lo(v.z); a[5] = bf16_hi(v.z); a[6] = bf16_lo(v.w); a[7] = bf16_hi(v.w);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; i++) a[i] = 0.f;
+    }
+    float s[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) s[i] = 0.f;
+#pragma unroll
+    for (int k = 0; k < GPTOSS_MAX_TOPK; k++) {
+      if (k < K && src[k] >= 0) {
+        const uint4 v =
+            __ldg(reinterpret_cast<const uint4 *>(ys + static_cast<size_t>(src[k]) * H) + p);
+        s[0] += bf16_lo(v.x); s[1] += bf16_hi(v.x); s[2] += bf16_lo(v.y); s[3] += bf16_hi(v.y);
+        s[4] += bf16_lo(v.z); s[5] += bf16_hi(v.z); s[6] += bf16_lo(v.w); s[7] += bf16_hi(v.w);
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16(a[0] + s[0], a[1] + s[1]);
+    o.y = pack_bf16(a[2] + s[2], a[3] + s[3]);
+    o.z = pack_bf16(a[4] + s[4], a[5] + s[5]);
+    o.w = pack_bf16(a[6] + s[6], a[7] + s[7]);
+    o4[p] = o;
+  }
+}
+
+cudaError_t launch_permute(gptoss_moe *h, cudaStream_t stream) {
+  const int R = h->stage_R, K = h->K, El = h->El;
+  const int nblocks = (R + kPermTokens - 1) / kPermTokens;
+  if (R <= 0) {
+    // nothing routed here: empty schedule
+    cudaError_t e = cudaMemsetAsync(h->expert_offsets, 0, sizeof(int) * (El + 1), stream);
+    if (e != cudaSuccess) return e;
+    return cudaMemsetAsync(h->num_mtiles, 0, sizeof(int), stream);
+  }
+  if (nblocks > h->perm_blocks_cap) return cudaErrorInvalidValue;
+  perm_count_kernel<<<nblocks, 256, El * sizeof(int), stream>>>(h->stage_expert, R, K, El,
+                                                                 h->block_counts, h->status);
+  h->launches++;
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  const size_t smem = (static_cast<size_t>(3 + kScanThreads / 32) * El + 1) * sizeof(int);
+  perm_scan_scatter_kernel<<<nblocks, kScanThreads, smem, stream>>>(
+      h->stage_expert, h->stage_weight, R, K, El, h->block_counts, nblocks, h->expert_offsets,
+      h->sorted_row, h->sorted_weight, h->row_of, h->mtile_expert, h->mtile_row0, h->mtile_rows,
+      h->num_mtiles, h->mtiles_cap, h->assign_cap, h->status);
+  h->launches++;
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  gather_rows_kernel<<<h->num_sms * 4, 256, 0, stream>>>(h->xs, h->stage_rows, h->sorted_row,
+                                                         h->expert_offsets, El, h->H, R,
+                                                         h->status);
+  h->launches++;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_combine(gptoss_moe *h, bf16 *x, const int *, int T, cudaStream_t stream) {
+  if (T <= 0) return cudaSuccess;
+  const int warps = 8;
+  combine_rows_kernel<true><<<(T + warps - 1) / warps, warps * 32, 0, stream>>>(
+      x, h->ys, h->row_of, T, h->K, h->H, h->assign_cap, h->status);
+  h->launches++;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_reduce_rows(gptoss_moe *h, bf16 *out_rows, int R, cudaStream_t stream) {
+  if (R <= 0) return cudaSuccess;
+  const int warps = 8;
+  combine_rows_kernel<false><<<(R + warps - 1) / warps, warps * 32, 0, stream>>>(
+      out_rows, h->ys, h->row_of, R, h->K, h->H, h->assign_cap, h->status);
+  h->launches++;
+  return cudaGetLastError();
+}
+
+}  // namespace gptoss

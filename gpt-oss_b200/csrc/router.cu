@@ -1,0 +1,383 @@
+// Router stage: logits = t . Wr^T + b, top-K by value (lowest index first on
+// equal values), softmax over the K selected logits.  One kernel; the logits
+// never go to HBM unless the debug tap asks for them.
+//
+// Replaces matmul_router_kernel (getp-csrc/matmul/matmul.cpp:945-1019) and
+// fused_topk_softmax_batch_kernel (getp-csrc/utility/utility.cpp:274-365) of the
+// reference.  Bound by HBM: the only large stream is t [T,H] bf16, read once.
+//
+// Layout: a CTA owns 32 consecutive tokens.  8 warps = 2 token groups of 16 x 4
+// expert slices; bf16 tensor-core MMAs (m16n8k16, fp32 accumulate) over K chunks
+// of 64 that are staged in shared memory with a 3-deep cp.async pipeline.  The
+// fp32 logits of the 32 tokens then sit in shared memory and one warp per token
+// does the selection in registers.
+//
+// Exact selection: fp32 tensor-core accumulation differs from the reference's
+// double-precision dot product by up to ~1e-5, enough to flip two near-tied
+// experts.  A token whose top-(K+1) logits contain two neighbours closer than
+// kTieGuard gets the logits of every contender (anything within 2*kTieGuard of
+// the K-th value) recomputed in fp64 by the same warp, and is re-selected.
+#include "common.cuh"
+#include "engine.h"
+
+namespace gptoss {
+
+constexpr int kRtTokens = 32;      // tokens per CTA
+constexpr int kRtKC = 64;          // K elements per pipeline stage
+constexpr int kRtStages = 3;
+constexpr int kRtRowBytes = 144;   // 128 B of data + 16 B pad: conflict-free ldmatrix
+constexpr int kRtThreads = 256;
+constexpr float kTieGuard = 1e-3f;
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src),
+               "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t &r0, uint32_t &r1,
+                                            uint32_t &r2, uint32_t &r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x2(uint32_t addr, uint32_t &r0, uint32_t &r1) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];"
+               : "=r"(r0), "=r"(r1)
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4],
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, "
+      "{%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Dot product of two bf16 rows the way the reference's CPU matmul does it
+// (run.cpp:356-369): exact float products summed in double, rounded to float
+// once at the end.  Whole warp cooperates; every lane returns the result.
+__device__ __forceinline__ float warp_exact_dot(const bf16 *a, const bf16 *b, int H, int lane) {
+  double acc = 0.0;
+  const uint4 *a4 = reinterpret_cast<const uint4 *>(a);
+  const uint4 *b4 = reinterpret_cast<const uint4 *>(b);
+  for (int p = lane; p < (H >> 3); p += 32) {
+    uint4 av = __ldg(a4 + p), bv = __ldg(b4 + p);
+    const uint32_t aw[4] = {av.x, av.y, av.z, av.w};
+    const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      acc += static_cast<double>(__fmul_rn(bf16_lo(aw[i]), bf16_lo(bw[i])));
+      acc += static_cast<double>(__fmul_rn(bf16_hi(aw[i]), bf16_hi(bw[i])));
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  return __double2float_rn(acc);
+}
+
+// NT = 8-expert MMA tiles per warp; the CTA covers EPAD = 32*NT experts.
+template <int NT>
+__global__ void __launch_bounds__(kRtThreads)
+router_topk_kernel(const bf16 *__restrict__ t, const bf16 *__restrict__ w_router,
+                   const float *__restrict__ b_router, const int *__restrict__ pos, int T, int H,
+                   int E, int K, int *__restrict__ topk_i, float *__restrict__ topk_v,
+                   float *__restrict__ logits_out, int exact_ties) {
+  constexpr int EPAD = 32 * NT;
+  constexpr int kStageBytes = (kRtTokens + EPAD) * kRtRowBytes;
+  extern __shared__ __align__(128) unsigned char smem[];
+  float *lg = reinterpret_cast<float *>(smem + kRtStages * kStageBytes);  // [32][EPAD]
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tok0 = blockIdx.x * kRtTokens;
+  const int nk = (H + kRtKC - 1) / kRtKC;
+
+  auto load_chunk = [&](int kc, int stage) {
+    unsigned char *base = smem + stage * kStageBytes;
+    const int k0 = kc * kRtKC;
+    for (int p = tid; p < (kRtTokens + EPAD) * 8; p += kRtThreads) {
+      const int row = p >> 3, c = p & 7;
+      const int k = k0 + c * 8;
+      const void *src;
+      bool ok = k < H;
+      if (row < kRtTokens) {
+        const int tok = tok0 + row;
+        ok = ok && tok < T;
+        src = ok ? static_cast<const void *>(t + static_cast<size_t>(tok) * H + k)
+                 : static_cast<const void *>(t);
+      } else {
+        const int e = row - kRtTokens;
+        ok = ok && e < E;
+        src = ok ? static_cast<const void *>(w_router + static_cast<size_t>(e) * H + k)
+                 : static_cast<const void *>(w_router);
+      }
+      cp_async16(smem_u32(base + row * kRtRowBytes + c * 16), src, ok ? 16u : 0u);
+    }
+  };
+
+  float acc[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+
+  const int tg = warp & 1;   // token group: rows tg*16 .. +15
+  const int sl = warp >> 1;  // expert slice: experts sl*NT*8 .. +NT*8-1
+
+#pragma unroll
+  for (int s = 0; s < kRtStages - 1; s++) {
+    if (s < nk) load_chunk(s, s);
+    cp_async_commit();
+  }
+  for (int kc = 0; kc < nk; kc++) {
+    cp_async_wait<kRtStages - 2>();
+    __syncthreads();
+    {
+      const int nxt = kc + kRtStages - 1;
+      if (nxt < nk) load_chunk(nxt, nxt % kRtStages);
+      cp_async_commit();
+    }
+    const uint32_t sbase = smem_u32(smem + (kc % kRtStages) * kStageBytes);
+    const uint32_t a_base = sbase + (tg * 16 + (lane & 15)) * kRtRowBytes + (lane >> 4) * 16;
+    const uint32_t w_base = sbase + kRtTokens * kRtRowBytes;
+#pragma unroll
+    for (int kk = 0; kk < kRtKC / 16; kk++) {
+      uint32_t a[4];
+      ldmatrix_x4(a_base + kk * 32, a[0], a[1], a[2], a[3]);
+      if constexpr (NT == 1) {
+        uint32_t b0, b1;
+        const int row = sl * 8 + (lane & 7);
+        ldmatrix_x2(w_base + row * kRtRowBytes + kk * 32 + ((lane >> 3) & 1) * 16, b0, b1);
+        mma_bf16_16816(acc[0], a, b0, b1);
+      } else {
+#pragma unroll
+        for (int nt = 0; nt < NT; nt += 2) {
+          uint32_t b0, b1, b2, b3;
+          const int mat = lane >> 3;
+          const int row = (sl * NT + nt + (mat >> 1)) * 8 + (lane & 7);
+          ldmatrix_x4(w_base + row * kRtRowBytes + kk * 32 + (mat & 1) * 16, b0, b1, b2, b3);
+          mma_bf16_16816(acc[nt], a, b0, b1);
+          mma_bf16_16816(acc[nt + 1], a, b2, b3);
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+
+  // accumulators -> shared logits [32][EPAD]
+#pragma unroll
+  for (int nt = 0; nt < NT; nt++) {
+    const int col = (sl * NT + nt) * 8 + (lane & 3) * 2;
+    const int r0 = tg * 16 + (lane >> 2);
+    lg[r0 * EPAD + col] = acc[nt][0];
+    lg[r0 * EPAD + col + 1] = acc[nt][1];
+    lg[(r0 + 8) * EPAD + col] = acc[nt][2];
+    lg[(r0 + 8) * EPAD + col + 1] = acc[nt][3];
+  }
+  __syncthreads();
+
+  // selection: warp w owns tokens w*4 .. w*4+3 of the CTA
+  const int rounds_sel = K;
+  const int rounds_chk = (K + 1 <= E) ? K + 1 : E;
+  for (int i = 0; i < kRtTokens / 8; i++) {
+    const int row = warp * (kRtTokens / 8) + i;
+    const int tok = tok0 + row;
+    if (tok >= T) break;
+    if (pos && pos[tok] < 0) {
+      if (lane < K) {
+        topk_i[static_cast<size_t>(tok) * K + lane] = -1;
+        topk_v[static_cast<size_t>(tok) * K + lane] = 0.f;
+      }
+      continue;
+    }
+    float v[NT];
+#pragma unroll
+    for (int j = 0; j < NT; j++) {
+      const int e = lane + 32 * j;
+      v[j] = (e < E) ? lg[row * EPAD + e] + __ldg(b_router + e) : -INFINITY;
+    }
+    float selv[GPTOSS_MAX_TOPK + 1];
+    int seli[GPTOSS_MAX_TOPK + 1];
+
+    auto select = [&](int rounds) {
+      uint32_t taken = 0;
+#pragma unroll
+      for (int r = 0; r < GPTOSS_MAX_TOPK + 1; r++) {
+        if (r < rounds) {
+          float bv = -INFINITY;
+          int bi = 0x7fffffff;
+#pragma unroll
+          for (int j = 0; j < NT; j++) {
+            const int e = lane + 32 * j;
+            if (!((taken >> j) & 1u) && e < E && (v[j] > bv || bi == 0x7fffffff)) {
+              bv = v[j];
+              bi = e;
+            }
+          }
+#pragma unroll
+          for (int off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+            if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) {
+              bv = ov;
+              bi = oi;
+            }
+          }
+          selv[r] = bv;
+          seli[r] = bi;
+          if (bi != 0x7fffffff && (bi & 31) == lane) taken |= 1u << (bi >> 5);
+        }
+      }
+    };
+
+    select(rounds_chk);
+    if (exact_ties) {
+      bool near = false;
+#pragma unroll
+      for (int r = 0; r < GPTOSS_MAX_TOPK; r++)
+        if (r + 1 < rounds_chk && selv[r] - selv[r + 1] < kTieGuard) near = true;
+      if (near) {
+        float kth = selv[0];
+#pragma unroll
+        for (int r = 1; r < GPTOSS_MAX_TOPK; r++)
+          if (r < K) kth = selv[r];
+        const float thr = kth - 2.f * kTieGuard;
+        const bf16 *trow = t + static_cast<size_t>(tok) * H;
+#pragma unroll
+        for (int j = 0; j < NT; j++) {
+          uint32_t mask = __ballot_sync(0xffffffffu, (lane + 32 * j) < E && v[j] >= thr);
+          while (mask) {
+            const int src = __ffs(mask) - 1;
+            mask &= mask - 1;
+            const int e = src + 32 * j;
+            const float ex = warp_exact_dot(trow, w_router + static_cast<size_t>(e) * H, H, lane);
+            if (lane == src) v[j] = ex + __ldg(b_router + e);
+          }
+        }
+        select(rounds_sel);
+      }
+    }
+    if (logits_out) {
+#pragma unroll
+      for (int j = 0; j < NT; j++) {
+        const int e = lane + 32 * j;
+        if (e < E) logits_out[static_cast<size_t>(tok) * E + e] = v[j];
+      }
+    }
+    // softmax over the K selected values (run.cpp:336-354: double max/sum)
+    float ev[GPTOSS_MAX_TOPK];
+    double sum = 0.0;
+    const double mx = static_cast<double>(selv[0]);
+#pragma unroll
+    for (int r = 0; r < GPTOSS_MAX_TOPK; r++) {
+      if (r < K) {
+        ev[r] = expf(static_cast<float>(static_cast<double>(selv[r]) - mx));
+        sum += static_cast<double>(ev[r]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < GPTOSS_MAX_TOPK; r++) {
+      if (r < K && lane == r) {
+        topk_i[static_cast<size_t>(tok) * K + r] = seli[r];
+        topk_v[static_cast<size_t>(tok) * K + r] =
+            static_cast<float>(static_cast<double>(ev[r]) / sum);
+      }
+    }
+  }
+}
+
+template <int NT>
+static cudaError_t launch_router_nt(const bf16 *t, const bf16 *w_router, const float *b_router,
+                                    const int *pos, int T, int H, int E, int K, int *topk_i,
+                                    float *topk_v, float *logits_opt, int exact_ties,
+                                    cudaStream_t stream) {
+  constexpr int EPAD = 32 * NT;
+  const size_t smem =
+      static_cast<size_t>(kRtStages) * (kRtTokens + EPAD) * kRtRowBytes + kRtTokens * EPAD * 4;
+  cudaError_t e = cudaFuncSetAttribute(router_topk_kernel<NT>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  const int grid = (T + kRtTokens - 1) / kRtTokens;
+  router_topk_kernel<NT><<<grid, kRtThreads, smem, stream>>>(
+      t, w_router, b_router, pos, T, H, E, K, topk_i, topk_v, logits_opt, exact_ties);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_router_topk(const bf16 *t, const bf16 *w_router, const float *b_router,
+                               const int *pos, int T, int H, int E, int K, int *topk_i,
+                               float *topk_v, float *logits_opt, int exact_ties,
+                               cudaStream_t stream, long long *launches) {
+  if (T <= 0) return cudaSuccess;
+  if (launches) ++*launches;
+  if (E <= 32)
+    return launch_router_nt<1>(t, w_router, b_router, pos, T, H, E, K, topk_i, topk_v, logits_opt,
+                               exact_ties, stream);
+  if (E <= 64)
+    return launch_router_nt<2>(t, w_router, b_router, pos, T, H, E, K, topk_i, topk_v, logits_opt,
+                               exact_ties, stream);
+  if (E <= 128)
+    return launch_router_nt<4>(t, w_router, b_router, pos, T, H, E, K, topk_i, topk_v, logits_opt,
+                               exact_ties, stream);
+  if (E <= 256)
+    return launch_router_nt<8>(t, w_router, b_router, pos, T, H, E, K, topk_i, topk_v, logits_opt,
+                               exact_ties, stream);
+  return cudaErrorInvalidValue;
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// out = w * x * rsqrt(mean(x^2) + 1e-5); one warp per token, 16-byte accesses.
+// Replaces rmsnorm_batch_kernel (getp-csrc/utility/utility.cpp:194-271).
+__global__ void __launch_bounds__(256)
+rmsnorm_rows_kernel(bf16 *__restrict__ out, const bf16 *__restrict__ x,
+                    const float *__restrict__ w, const int *__restrict__ pos, int T, int H) {
+  const int lane = threadIdx.x & 31;
+  const int tok = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (tok >= T) return;
+  if (pos && pos[tok] < 0) return;
+  const uint4 *x4 = reinterpret_cast<const uint4 *>(x + static_cast<size_t>(tok) * H);
+  uint4 *o4 = reinterpret_cast<uint4 *>(out + static_cast<size_t>(tok) * H);
+  const int n4 = H >> 3;
+  float ss = 0.f;
+  for (int p = lane; p < n4; p += 32) {
+    const uint4 v = x4[p];
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const float a = bf16_lo(u[i]), b = bf16_hi(u[i]);
+      ss = fmaf(a, a, ss);
+      ss = fmaf(b, b, ss);
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  const float inv = 1.0f / sqrtf(ss / static_cast<float>(H) + 1e-5f);
+  for (int p = lane; p < n4; p += 32) {
+    const uint4 v = x4[p];
+    const float4 w0 = __ldg(reinterpret_cast<const float4 *>(w) + 2 * p);
+    const float4 w1 = __ldg(reinterpret_cast<const float4 *>(w) + 2 * p + 1);
+    uint4 o;
+    o.x = pack_bf16(w0.x * (inv * bf16_lo(v.x)), w0.y * (inv * bf16_hi(v.x)));
+    o.y = pack_bf16(w0.z * (inv * bf16_lo(v.y)), w0.w * (inv * bf16_hi(v.y)));
+    o.z = pack_bf16(w1.x * (inv * bf16_lo(v.z)), w1.y * (inv * bf16_hi(v.z)));
+    o.w = pack_bf16(w1.z * (inv * bf16_lo(v.w)), w1.w * (inv * bf16_hi(v.w)));
+    o4[p] = o;
+  }
+}
+
+cudaError_t launch_rmsnorm(bf16 *out, const bf16 *x, const float *w, const int *pos, int T, int H,
+                           cudaStream_t stream, long long *launches) {
+  if (T <= 0) return cudaSuccess;
+  if (launches) ++*launches;
+  const int warps = 8;
+  rmsnorm_rows_kernel<<<(T + warps - 1) / warps, warps * 32, 0, stream>>>(out, x, w, pos, T, H);
+  return cudaGetLastError();
+}
+
+}  // namespace gptoss

@@ -1,0 +1,87 @@
+"""Seeded synthetic inputs for the MoE block.
+
+The reference is benchmarked on real gpt-oss checkpoints and prompt files that
+are not available offline; every workload here is random data with the shapes,
+dtypes and value distributions of those runs: activations bf16 N(0,1) (as after
+RMSNorm), weights bf16 N(0,0.02), biases N(0,0.01) (router bias N(0,0.02)).
+All values are rounded to bf16 and carried as float32, so the CPU oracle (fp32
+arithmetic) and the GPU path (bf16 storage) see identical numbers.
+"""
+from __future__ import annotations
+
+import dataclasses
+
+import numpy as np
+
+
+def bf16_bits(a: np.ndarray) -> np.ndarray:
+    """float32 -> bf16 bit patterns (uint16), round to nearest even."""
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+    rounded = u + (np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1)))
+    return (rounded >> np.uint32(16)).astype(np.uint16)
+
+
+def bf16_to_f32(bits: np.ndarray) -> np.ndarray:
+    """bf16 bit patterns (uint16) -> float32."""
+    return (np.ascontiguousarray(bits, dtype=np.uint16).astype(np.uint32) << np.uint32(16)).view(
+        np.float32
+    )
+
+
+def bf16_round(a: np.ndarray) -> np.ndarray:
+    """Round float32 values to the nearest bf16, keep float32 storage."""
+    return bf16_to_f32(bf16_bits(a))
+
+
+@dataclasses.dataclass
+class MoeShape:
+    """One MoE layer workload (names follow the reference's Config, run.cpp:26-46)."""
+
+    name: str
+    n_tokens: int
+    hidden_dim: int
+    intermediate_dim: int
+    n_experts: int
+    experts_per_token: int = 4
+    swiglu_limit: float = 7.0
+    seed: int = 0
+
+
+# The workloads of the benchmark description.  "c2" is the 20b-shape layer the
+# single-GPU metric is quoted on, "c3" the 120b-shape layer.
+SHAPES = {
+    "tiny": MoeShape("tiny", 16, 128, 128, 8, 4, 7.0, 0),
+    "c2": MoeShape("gpt-oss-20b-moe-layer-T7168", 7168, 2880, 2880, 32, 4, 7.0, 1),
+    "c3": MoeShape("gpt-oss-120b-moe-layer-T6144", 6144, 2880, 2880, 128, 4, 7.0, 2),
+}
+
+
+def make_layer(shape: MoeShape, n_tokens: int | None = None, inactive_every: int = 0):
+    """Host tensors of one layer, float32 arrays holding bf16-exact values.
+
+    Returns a dict with t, x (residual stream; a second N(0,1) draw), pos,
+    w_router, b_router, w_mlp1 (gate rows even, up rows odd), b_mlp1, w_mlp2,
+    b_mlp2.  inactive_every > 0 marks every n-th token inactive (pos = -1).
+    """
+    T = shape.n_tokens if n_tokens is None else n_tokens
+    H, IM, E = shape.hidden_dim, shape.intermediate_dim, shape.n_experts
+    rng = np.random.Generator(np.random.PCG64(shape.seed))
+
+    def normal(size, std):
+        return bf16_round((rng.standard_normal(size, dtype=np.float32) * np.float32(std)))
+
+    d = {
+        "t": normal((T, H), 1.0),
+        "x": normal((T, H), 1.0),
+        "w_router": normal((E, H), 0.02),
+        "b_router": normal((E,), 0.02),
+        "w_mlp1": normal((E, 2 * IM, H), 0.02),
+        "b_mlp1": normal((E, 2 * IM), 0.01),
+        "w_mlp2": normal((E, H, IM), 0.02),
+        "b_mlp2": normal((E, H), 0.01),
+    }
+    pos = np.arange(T, dtype=np.int32)
+    if inactive_every > 0:
+        pos[::inactive_every] = -1
+    d["pos"] = pos
+    return d

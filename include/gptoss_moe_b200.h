@@ -1,0 +1,200 @@
+/*
+ * C ABI of the B200 (sm_100a) GPT-OSS MoE engine.
+ *
+ * This is the boundary a host program binds to replace the MoE section of the
+ * reference's batched ("getp") engine.  Plain C types only: device and host
+ * pointers are void* / typed pointers, a CUDA stream is passed as void*
+ * (cudaStream_t), every call returns 0 on success or a negative GPTOSS_E_* code
+ * and gptoss_moe_last_error() gives the text.  There is no CPU fallback: every
+ * compute entry point fails with GPTOSS_E_CUDA when no sm_100 device is usable.
+ *
+ * Citations are file:line in the reference project (pmatuan/gpt-oss).
+ */
+#ifndef GPTOSS_MOE_B200_H
+#define GPTOSS_MOE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GPTOSS_OK 0
+#define GPTOSS_E_INVALID (-1)   /* bad argument / unsupported shape            */
+#define GPTOSS_E_CUDA (-2)      /* CUDA runtime or driver error                */
+#define GPTOSS_E_CAPACITY (-3)  /* more tokens than the engine was created for */
+#define GPTOSS_E_DEVICE (-4)    /* a kernel reported a status (bounded wait ran
+                                   out, index out of range); see
+                                   gptoss_moe_device_status()                  */
+#define GPTOSS_E_STATE (-5)     /* call order (weights not loaded, EP not set
+                                   up)                                         */
+#define GPTOSS_E_COMM (-6)      /* NCCL error                                  */
+
+#define GPTOSS_MAX_TOPK 8
+
+typedef struct gptoss_moe gptoss_moe_t;
+
+/* Expert weight storage on the device. */
+enum { GPTOSS_WEIGHTS_BF16 = 0, GPTOSS_WEIGHTS_MXFP4 = 1 };
+/* Grouped-GEMM implementation.  TCGEN05 is the product path; SIMT is a slow
+ * CUDA-core kernel kept only so tests can cross-check the tensor-core path on
+ * the GPU at sizes the CPU oracle cannot reach.  It is never selected
+ * automatically. */
+enum { GPTOSS_GEMM_TCGEN05 = 0, GPTOSS_GEMM_SIMT = 1 };
+
+/*
+ * Shape of one engine.  Field meanings follow the reference's Config
+ * (run.cpp:26-46): hidden_dim, intermediate_dim, n_experts,
+ * experts_per_token, n_layers, swiglu_limit.  max_tokens plays the role of
+ * MAX_BATCH_SIZE (getp-csrc/common/defines.h:30-31): all device workspaces are
+ * allocated once for it (getp_run.cpp:39-143).  ep_rank / ep_size select expert
+ * parallelism: expert e lives on rank e % ep_size with local id e / ep_size
+ * (getp-csrc/expert.cpp:18, :1191-1213); ep_size <= 1 means all experts local.
+ */
+typedef struct {
+  int hidden_dim;
+  int intermediate_dim;
+  int n_experts;
+  int experts_per_token;
+  int n_layers;
+  int max_tokens;
+  float swiglu_limit;
+  int ep_rank;
+  int ep_size;
+  int weight_format; /* GPTOSS_WEIGHTS_* */
+  int device;        /* CUDA device ordinal */
+} gptoss_moe_config_t;
+
+/* Replaces init_device_context's MoE allocations (getp_run.cpp:43-68,
+ * :126-143) and init_device_context_ep (expert.cpp:709). */
+int gptoss_moe_create(const gptoss_moe_config_t *cfg, gptoss_moe_t **out);
+/* Replaces cleanup in finish() (getp_run.cpp:315-411, expert.cpp:1234). */
+int gptoss_moe_destroy(gptoss_moe_t *h);
+/* Text of the last error on this handle (or of the last failed create when h
+ * is NULL).  Valid until the next call on the same thread. */
+const char *gptoss_moe_last_error(const gptoss_moe_t *h);
+
+/*
+ * Weight upload for one layer from the fp32 tensors of the .bin file
+ * (run.cpp:237-248: w_router [E,H], b_router [E], w_mlp1 [E,2*IM,H] with gate
+ * rows even / up rows odd, b_mlp1 [E,2*IM], w_mlp2 [E,H,IM], b_mlp2 [E,H]),
+ * host pointers.  Weights are rounded to bf16 (round-to-nearest-even, as
+ * copy_fp32_to_bf16_device does, getp-csrc/utility/utility.cpp:417-556);
+ * biases stay fp32.  Under expert parallelism only the experts this rank owns
+ * are uploaded (expert.cpp:895-930, :971-1009); pointers still address the full
+ * [E,...] tensors.
+ */
+int gptoss_moe_load_layer_f32(gptoss_moe_t *h, int layer, const float *w_router,
+                              const float *b_router, const float *w_mlp1, const float *b_mlp1,
+                              const float *w_mlp2, const float *b_mlp2);
+/*
+ * Same tensors already in bf16 (uint16 bit patterns), biases fp32.
+ * on_device != 0: all pointers are device pointers on the engine's device and
+ * are copied device-to-device.  Full [E,...] tensors as above.
+ */
+int gptoss_moe_load_layer_bf16(gptoss_moe_t *h, int layer, const void *w_router,
+                               const float *b_router, const void *w_mlp1, const float *b_mlp1,
+                               const void *w_mlp2, const float *b_mlp2, int on_device);
+/*
+ * Expert weights as MXFP4 (engine created with GPTOSS_WEIGHTS_MXFP4): blocks are
+ * packed e2m1 codes, two per byte, low nibble = even element
+ * (export_model_bin/gpt-oss-120b/export_model_bin.py:80-97, :126-131), scales
+ * are e8m0 bytes (value 2^(s-127)), one per 32 consecutive elements of the
+ * contraction dimension.  w_mlp1_blocks [E,2*IM,H/2], w_mlp1_scales
+ * [E,2*IM,H/32], w_mlp2_blocks [E,H,IM/2], w_mlp2_scales [E,H,IM/32]; router in
+ * bf16, biases fp32.  The reference stores such checkpoints dequantised; this
+ * format has no counterpart file in the reference.
+ */
+int gptoss_moe_load_layer_mxfp4(gptoss_moe_t *h, int layer, const void *w_router_bf16,
+                                const float *b_router, const uint8_t *w_mlp1_blocks,
+                                const uint8_t *w_mlp1_scales, const float *b_mlp1,
+                                const uint8_t *w_mlp2_blocks, const uint8_t *w_mlp2_scales,
+                                const float *b_mlp2, int on_device);
+
+/*
+ * One MoE block on device buffers; replaces the MoE section of
+ * gpu_forward_device_batch (getp_run.cpp:697-852: router, top-k + softmax,
+ * count / scan / build assignments, mlp1, mlp2, slot reduce, residual add) and,
+ * when the engine was set up for expert parallelism, gpu_forward_device_batch_ep
+ * (expert.cpp:1366-1607).
+ *   t   bf16 [n_tokens, H]  post-norm input (the reference's d_t)
+ *   x   bf16 [n_tokens, H]  residual stream, updated in place: x += MoE(t)
+ *   pos i32  [n_tokens] or NULL; rows with pos < 0 are skipped and their x is
+ *       left untouched (matmul.cpp:955, utility.cpp:281)
+ * All work is enqueued on `stream`; the call does not synchronise unless expert
+ * parallelism needs the per-peer row counts on the host.
+ */
+int gptoss_moe_forward(gptoss_moe_t *h, int layer, const void *t, void *x, const int *pos,
+                       int n_tokens, void *stream);
+/*
+ * Same block with HOST buffers: copies t, x (and pos) to the device, runs the
+ * block, copies x back and waits.  This is the call a host engine that keeps
+ * activations in host memory makes per layer.
+ */
+int gptoss_moe_forward_host(gptoss_moe_t *h, int layer, const void *t_host, void *x_host,
+                            const int *pos_host, int n_tokens);
+
+/* The stages of gptoss_moe_forward, individually (same order). */
+/* router linear + bias + top-k + softmax (matmul.cpp:945, utility.cpp:274). */
+int gptoss_moe_route(gptoss_moe_t *h, int layer, const void *t, const int *pos, int n_tokens,
+                     void *stream);
+/* histogram, prefix sum, scatter into per-expert groups and row gather
+ * (utility.cpp:1058, :758, :1079). */
+int gptoss_moe_permute(gptoss_moe_t *h, const void *t, int n_tokens, void *stream);
+/* grouped gate_up GEMM + bias + SwiGLU, grouped down GEMM + bias, times the
+ * routing weight (matmul.cpp:1023-1431, :1470-1874). */
+int gptoss_moe_experts(gptoss_moe_t *h, int layer, void *stream);
+/* sum of the K expert outputs per token plus residual (utility.cpp:701-726,
+ * :158-173). */
+int gptoss_moe_combine(gptoss_moe_t *h, void *x, int n_tokens, void *stream);
+
+/* ffn RMSNorm that feeds the block (rmsnorm_batch_kernel, utility.cpp:194-271):
+ * out = w * x * rsqrt(mean(x^2) + 1e-5), bf16 in/out, fp32 scale w [H]. */
+int gptoss_moe_rmsnorm(gptoss_moe_t *h, void *out, const void *x, const float *w_dev,
+                       const int *pos, int n_tokens, void *stream);
+
+/*
+ * Debug taps of the last forward (host destination buffers, any may be NULL;
+ * synchronises the device).  topk_i / topk_v [n_tokens,K] (inactive rows: -1 /
+ * 0), expert_offsets [E_local+1], sorted_token [n_assignments] (row of t, in
+ * per-expert order), logits [n_tokens,E] only when enabled with
+ * gptoss_moe_set_option("keep_logits", 1).
+ */
+int gptoss_moe_get_routing(gptoss_moe_t *h, int n_tokens, int *topk_i, float *topk_v,
+                           int *expert_offsets, int *sorted_token, float *logits);
+/* bf16 [n_assignments, IM] activations after SwiGLU, in per-expert order. */
+int gptoss_moe_get_activations(gptoss_moe_t *h, void *act_host, size_t bytes);
+
+/* Options: "gemm_impl" (GPTOSS_GEMM_*), "keep_logits" (0/1),
+ * "exact_ties" (0/1, default 1: re-evaluate near-tied router logits in fp64),
+ * "time_stages" (0/1, see gptoss_moe_stage_ms). */
+int gptoss_moe_set_option(gptoss_moe_t *h, const char *name, int value);
+/* Kernels launched by this handle since creation. */
+long long gptoss_moe_launch_count(const gptoss_moe_t *h);
+/* Reads (and clears) the device status word; 0 = no kernel reported a problem.
+ * Synchronises the device. */
+int gptoss_moe_device_status(gptoss_moe_t *h);
+/* Average duration in milliseconds of one stage, measured with CUDA events
+ * recorded on the launching stream around the stage's kernels in every call
+ * made since gptoss_moe_set_option("time_stages", 1).  stage: 0 route,
+ * 1 permute, 2 gate_up GEMM, 3 down GEMM, 4 combine, 5 dispatch, 6 return.
+ * Waits for the last recorded event. */
+int gptoss_moe_stage_ms(gptoss_moe_t *h, int stage, float *ms);
+
+/*
+ * Expert parallelism over NCCL (replaces warm_up_ep's peer setup,
+ * expert.cpp:1176-1231, and the host rendezvous, expert.cpp:67-173).
+ * Rank 0 fills a 128-byte id with gptoss_moe_ep_unique_id and hands it to the
+ * other ranks by any means; every rank then calls gptoss_moe_ep_init.
+ */
+int gptoss_moe_ep_unique_id(void *id128);
+int gptoss_moe_ep_init(gptoss_moe_t *h, const void *id128);
+
+/* Library / build information. */
+const char *gptoss_moe_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GPTOSS_MOE_B200_H */

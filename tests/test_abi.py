@@ -1,0 +1,62 @@
+"""The C-ABI library loads and exports every symbol the public header declares.
+No compute is done here (no GPU needed)."""
+import ctypes
+import re
+
+import pytest
+
+
+def _declared_functions(header_text):
+    text = re.sub(r"/\*.*?\*/", "", header_text, flags=re.S)
+    return sorted(set(re.findall(r"\b(gptoss_moe_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported(pkg):
+    lib = pkg.load_library()
+    names = _declared_functions(pkg.HEADER_PATH.read_text())
+    assert len(names) >= 20
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, f"declared in the header but not exported: {missing}"
+
+
+def test_version_string(pkg):
+    assert b"sm_100a" in pkg.load_library().gptoss_moe_version()
+
+
+def test_config_struct_matches_header(pkg):
+    # 11 four-byte fields, no padding
+    assert ctypes.sizeof(pkg.MoeConfig) == 44
+    fields = [f[0] for f in pkg.MoeConfig._fields_]
+    text = pkg.HEADER_PATH.read_text()
+    body = text[text.index("typedef struct {"):text.index("} gptoss_moe_config_t;")]
+    order = [m for m in re.findall(r"\b(?:int|float)\s+([a-z_]+);", body)]
+    assert order == fields
+
+
+def test_invalid_config_is_rejected_before_touching_cuda(pkg):
+    with pytest.raises(pkg.MoeError) as ei:
+        pkg.MoeEngine(100, 128, 8, 4)  # hidden_dim not a multiple of 8
+    assert ei.value.code == pkg.GPTOSS_E_INVALID
+    with pytest.raises(pkg.MoeError) as ei:
+        pkg.MoeEngine(128, 128, 8, 9)  # top-k larger than supported
+    assert ei.value.code == pkg.GPTOSS_E_INVALID
+    with pytest.raises(pkg.MoeError) as ei:
+        pkg.MoeEngine(128, 128, 6, 4, ep_rank=0, ep_size=4)  # experts not divisible
+    assert ei.value.code == pkg.GPTOSS_E_INVALID
+
+
+def test_no_cpu_fallback_without_gpu(pkg):
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(pkg.MoeError) as ei:
+        pkg.MoeEngine(128, 128, 8, 4)
+    assert ei.value.code == pkg.GPTOSS_E_CUDA
+
+
+def test_missing_library_fails_loudly(pkg, monkeypatch, tmp_path):
+    monkeypatch.setattr(pkg, "_lib", None)
+    monkeypatch.setattr(pkg, "LIB_PATH", tmp_path / "nope.so")
+    with pytest.raises(RuntimeError, match="no fallback"):
+        pkg.load_library()

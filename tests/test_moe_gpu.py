@@ -1,0 +1,160 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU
+oracle and the committed reference fixtures.
+
+Tolerances (from the benchmark description): expert indices bit-exact unless
+the deciding logits are within 1e-6 of a tie; activations max-abs <= 2e-2 and
+mean-rel <= 1e-2 (bf16 outputs against the fp32 oracle).
+"""
+import numpy as np
+import pytest
+
+import helpers
+from gpt_oss_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _compare(pkg, oracle, shape, d, via="forward", gemm_impl=None, want=None):
+    want = want or oracle.moe_layer(d, shape)
+    active = d["pos"] >= 0 if d.get("pos") is not None else np.ones(d["t"].shape[0], bool)
+    got = helpers.run_gpu_layer(pkg, shape, d, via=via, gemm_impl=gemm_impl)
+    r = got["routing"]
+    helpers.check_indices(r["topk_i"], want["topk_i"], want["logits"], active)
+    assert (r["topk_i"][~active] == -1).all()
+    same = (r["topk_i"] == want["topk_i"]).all(axis=1) & active
+    np.testing.assert_allclose(r["topk_v"][same], want["topk_v"][same], rtol=0, atol=2e-5)
+    np.testing.assert_allclose(r["logits"][active], want["logits"][active], rtol=0, atol=5e-5)
+    helpers.check_activations(got["x_out"][active], want["x_out"][active], "x_out")
+    # inactive rows keep their residual bit for bit
+    np.testing.assert_array_equal(got["x_out"][~active], synth.bf16_round(d["x"])[~active])
+    # pure block output (zero residual): small magnitudes, tighter check of the GEMMs
+    got0 = helpers.run_gpu_layer(pkg, shape, d, via=via, gemm_impl=gemm_impl, zero_residual=True)
+    helpers.check_activations(got0["x_out"][active], want["e_agg"][active], "e_agg",
+                              max_abs=2e-2, mean_rel=1e-2)
+    return got, want
+
+
+@pytest.mark.parametrize("name", helpers.GOLDEN_CASES)
+@pytest.mark.parametrize("via", ["forward", "stages", "host"])
+def test_reference_fixtures(pkg, oracle, name, via):
+    shape, d, ref = helpers.load_golden(name)
+    _compare(pkg, oracle, shape, d, via=via, want=ref)
+
+
+@pytest.mark.parametrize("name", helpers.GOLDEN_CASES[:2])
+def test_reference_fixtures_simt_kernel(pkg, oracle, name):
+    shape, d, ref = helpers.load_golden(name)
+    _compare(pkg, oracle, shape, d, gemm_impl=pkg.GEMM_SIMT, want=ref)
+
+
+EDGE_CASES = [
+    # T, H, IM, E, K, inactive_every
+    (1, 64, 64, 8, 4, 0),
+    (3, 72, 40, 8, 4, 0),        # H, IM not multiples of the 64-wide K tile
+    (127, 128, 128, 8, 4, 0),    # one row short of an M tile (tiny-model dims)
+    (129, 128, 128, 8, 4, 3),    # one row over, some rows inactive
+    (200, 256, 192, 32, 4, 7),
+    (96, 320, 248, 128, 4, 0),   # 128 experts, most of them with 0-5 rows; ragged N
+    (64, 128, 64, 16, 1, 0),     # top-1
+    (64, 128, 64, 16, 8, 5),     # top-8
+    (300, 2880, 2880, 8, 2, 0),  # the real hidden sizes: 45 K steps, 24 / 12 N tiles
+]
+
+
+@pytest.mark.parametrize("T,H,IM,E,K,inactive", EDGE_CASES)
+def test_layer_against_oracle(pkg, oracle, T, H, IM, E, K, inactive):
+    shape = synth.MoeShape("edge", T, H, IM, E, K, 7.0, 1000 + T + E + K)
+    d = synth.make_layer(shape, inactive_every=inactive)
+    _compare(pkg, oracle, shape, d)
+
+
+def test_empty_batch_and_all_inactive(pkg, oracle):
+    shape = synth.MoeShape("empty", 8, 64, 64, 8, 4, 7.0, 3)
+    d = synth.make_layer(shape)
+    d0 = {k: (v[:0] if k in ("t", "x", "pos") else v) for k, v in d.items()}
+    got = helpers.run_gpu_layer(pkg, shape, d0, max_tokens=8)
+    assert got["x_out"].shape == (0, 64)
+    d["pos"][:] = -1
+    got = helpers.run_gpu_layer(pkg, shape, d)
+    np.testing.assert_array_equal(got["x_out"], d["x"])
+    assert int(got["routing"]["expert_offsets"][-1]) == 0
+
+
+def test_exact_ties_pick_lowest_index(pkg, oracle):
+    shape = synth.MoeShape("ties", 40, 64, 32, 16, 4, 7.0, 9)
+    d = synth.make_layer(shape)
+    # experts 3, 7 and 12 share one router row and bias: their logits tie exactly
+    for e in (7, 12):
+        d["w_router"][e] = d["w_router"][3]
+        d["b_router"][e] = d["b_router"][3]
+    want = oracle.moe_layer(d, shape)
+    got = helpers.run_gpu_layer(pkg, shape, d)
+    np.testing.assert_array_equal(got["routing"]["topk_i"], want["topk_i"])
+    tied = np.isin(want["topk_i"], (3, 7, 12)).sum(axis=1) >= 2
+    assert tied.any()
+    helpers.check_activations(got["x_out"], want["x_out"], "x_out with ties")
+
+
+def test_capacity_and_state_errors(pkg):
+    shape = synth.MoeShape("cap", 16, 64, 64, 8, 4, 7.0, 4)
+    d = synth.make_layer(shape)
+    import torch
+
+    eng = pkg.MoeEngine(64, 64, 8, 4, max_tokens=8)
+    t = helpers.to_dev_bf16(d["t"], "cuda:0")
+    x = helpers.to_dev_bf16(d["x"], "cuda:0")
+    with pytest.raises(pkg.MoeError) as ei:
+        eng.forward(0, t, x, None, 8)
+    assert ei.value.code == pkg.GPTOSS_E_STATE  # weights not loaded
+    eng.load_layer_f32(0, d["w_router"], d["b_router"], d["w_mlp1"], d["b_mlp1"], d["w_mlp2"],
+                       d["b_mlp2"])
+    with pytest.raises(pkg.MoeError) as ei:
+        eng.forward(0, t, x, None, 16)
+    assert ei.value.code == pkg.GPTOSS_E_CAPACITY
+    with pytest.raises(pkg.MoeError) as ei:
+        eng.forward(1, t, x, None, 8)
+    assert ei.value.code == pkg.GPTOSS_E_INVALID
+    eng.forward(0, t, x, None, 8)
+    torch.cuda.synchronize()
+    assert eng.device_status() == 0
+    eng.close()
+
+
+def test_permutation_is_a_stable_counting_sort(pkg):
+    shape = synth.MoeShape("perm", 1000, 128, 64, 32, 4, 7.0, 21)
+    d = synth.make_layer(shape, inactive_every=9)
+    r = helpers.run_gpu_layer(pkg, shape, d)["routing"]
+    topk_i, off, st = r["topk_i"], r["expert_offsets"], r["sorted_token"]
+    counts = np.bincount(topk_i[topk_i >= 0], minlength=32)
+    np.testing.assert_array_equal(np.diff(off), counts)
+    assert off[0] == 0 and off[-1] == (topk_i >= 0).sum() == st.shape[0]
+    for e in range(32):
+        seg = st[off[e]:off[e + 1]]
+        assert (np.diff(seg) > 0).all(), "rows of one expert must be in ascending token order"
+        np.testing.assert_array_equal(seg, np.nonzero((topk_i == e).any(axis=1))[0])
+
+
+def test_bitwise_repeatable(pkg):
+    shape = synth.MoeShape("rep", 513, 256, 128, 32, 4, 7.0, 33)
+    d = synth.make_layer(shape)
+    a = helpers.run_gpu_layer(pkg, shape, d)
+    b = helpers.run_gpu_layer(pkg, shape, d)
+    np.testing.assert_array_equal(a["x_out"], b["x_out"])
+    np.testing.assert_array_equal(a["routing"]["sorted_token"], b["routing"]["sorted_token"])
+
+
+def test_rmsnorm_against_oracle(pkg, oracle):
+    import torch
+
+    rng = np.random.default_rng(5)
+    x = synth.bf16_round(rng.standard_normal((77, 2880)).astype(np.float32) * 3)
+    w = synth.bf16_round(1 + 0.1 * rng.standard_normal(2880).astype(np.float32))
+    want = oracle.rmsnorm_rows(x, w)
+    eng = pkg.MoeEngine(2880, 64, 8, 4, max_tokens=128)
+    xd = helpers.to_dev_bf16(x, "cuda:0")
+    out = torch.zeros_like(xd)
+    wd = torch.from_numpy(w).cuda()
+    eng.rmsnorm(out, xd, wd, None, 77, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    helpers.check_activations(out.float().cpu().numpy(), want, "rmsnorm")
+    eng.close()
