@@ -332,7 +332,7 @@ def main():
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "tiny"])
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c2s", "tiny"])
     ap.add_argument("--cpu-tokens", type=int, default=None,
                     help="tokens in the CPU sample (default 256 for ours, 64 for reference)")
     ap.add_argument("--no-cpu-baseline", action="store_true")

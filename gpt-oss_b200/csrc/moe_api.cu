@@ -321,7 +321,8 @@ struct StageScope {
 
 int gptoss_moe_route(gptoss_moe_t *h, int layer, const void *t, const int *pos, int n_tokens,
                      void *stream) {
-  if (!h || !t) return GPTOSS_E_INVALID;
+  if (!h) return GPTOSS_E_INVALID;
+  if (!t && n_tokens > 0) return fail(h, GPTOSS_E_INVALID, "null input");
   int rc = check_layer(h, layer, n_tokens);
   if (rc) return rc;
   CK(h, cudaSetDevice(h->cfg.device));
@@ -338,7 +339,8 @@ int gptoss_moe_route(gptoss_moe_t *h, int layer, const void *t, const int *pos, 
 }
 
 int gptoss_moe_permute(gptoss_moe_t *h, const void *t, int n_tokens, void *stream) {
-  if (!h || !t) return GPTOSS_E_INVALID;
+  if (!h) return GPTOSS_E_INVALID;
+  if (!t && n_tokens > 0) return fail(h, GPTOSS_E_INVALID, "null input");
   if (n_tokens < 0 || n_tokens > h->max_tokens)
     return fail(h, GPTOSS_E_CAPACITY, "n_tokens out of range");
   if (h->ep_size > 1)
@@ -372,7 +374,8 @@ int gptoss_moe_experts(gptoss_moe_t *h, int layer, void *stream) {
 }
 
 int gptoss_moe_combine(gptoss_moe_t *h, void *x, int n_tokens, void *stream) {
-  if (!h || !x) return GPTOSS_E_INVALID;
+  if (!h) return GPTOSS_E_INVALID;
+  if (!x && n_tokens > 0) return fail(h, GPTOSS_E_INVALID, "null output");
   if (n_tokens < 0 || n_tokens > h->max_tokens)
     return fail(h, GPTOSS_E_CAPACITY, "n_tokens out of range");
   if (h->ep_size > 1)
@@ -386,7 +389,8 @@ int gptoss_moe_combine(gptoss_moe_t *h, void *x, int n_tokens, void *stream) {
 
 int gptoss_moe_forward(gptoss_moe_t *h, int layer, const void *t, void *x, const int *pos,
                        int n_tokens, void *stream) {
-  if (!h || !t || !x) return GPTOSS_E_INVALID;
+  if (!h) return GPTOSS_E_INVALID;
+  if ((!t || !x) && n_tokens > 0) return fail(h, GPTOSS_E_INVALID, "null activation pointer");
   int rc = check_layer(h, layer, n_tokens);
   if (rc) return rc;
   if (n_tokens == 0 && h->ep_size <= 1) return GPTOSS_OK;
@@ -399,8 +403,12 @@ int gptoss_moe_forward(gptoss_moe_t *h, int layer, const void *t, void *x, const
 
 int gptoss_moe_forward_host(gptoss_moe_t *h, int layer, const void *t_host, void *x_host,
                             const int *pos_host, int n_tokens) {
-  if (!h || !t_host || !x_host) return GPTOSS_E_INVALID;
+  if (!h) return GPTOSS_E_INVALID;
+  if ((!t_host || !x_host) && n_tokens > 0)
+    return fail(h, GPTOSS_E_INVALID, "null activation pointer");
   int rc = check_layer(h, layer, n_tokens);
+  if (rc) return rc;
+  if (n_tokens == 0 && h->ep_size <= 1) return GPTOSS_OK;
   if (rc) return rc;
   CK(h, cudaSetDevice(h->cfg.device));
   const size_t cap = (size_t)h->max_tokens * h->H;

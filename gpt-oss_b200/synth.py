@@ -53,6 +53,10 @@ SHAPES = {
     "tiny": MoeShape("tiny", 16, 128, 128, 8, 4, 7.0, 0),
     "c2": MoeShape("gpt-oss-20b-moe-layer-T7168", 7168, 2880, 2880, 32, 4, 7.0, 1),
     "c3": MoeShape("gpt-oss-120b-moe-layer-T6144", 6144, 2880, 2880, 128, 4, 7.0, 2),
+    # c2 cut to 8 experts and a quarter of the tokens: the same 896 rows per expert
+    # and the same tiles, 0.4 GB of weights (still larger than L2); the case that
+    # profiler captures with many passes are taken on
+    "c2s": MoeShape("gpt-oss-20b-moe-layer-8experts-T1792", 1792, 2880, 2880, 8, 4, 7.0, 1),
 }
 
 

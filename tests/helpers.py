@@ -50,8 +50,14 @@ def check_indices(got_i, want_i, want_logits, active):
     assert not bad, f"expert indices differ beyond the tie exemption on tokens {bad[:10]}"
 
 
-def check_activations(got, want, what, max_abs=MAX_ABS, mean_rel=MEAN_REL):
+def check_activations(got, want, what, max_abs=MAX_ABS, mean_rel=MEAN_REL, bf16_quantum=False):
+    """max-abs / mean-rel check.  bf16_quantum=True is for the residual stream,
+    whose magnitude is set by the caller's residual and not by the block: the
+    limit on each element then grows by half a bf16 ulp of the expected value
+    (|want| * 2^-9), the part of the error the output format itself imposes."""
     err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    if bf16_quantum:
+        err = np.maximum(err - np.abs(want.astype(np.float64)) * 2.0 ** -9, 0.0)
     denom = max(float(np.abs(want).mean()), 1e-30)
     m_abs, m_rel = float(err.max()) if err.size else 0.0, float(err.mean() / denom) if err.size else 0.0
     assert m_abs <= max_abs and m_rel <= mean_rel, (

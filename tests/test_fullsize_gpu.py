@@ -1,0 +1,116 @@
+"""Parity at the benchmark's full sizes (20b-shape and 120b-shape layers).
+
+The CPU oracle needs ~4 ms per (token, expert) at these sizes, so the whole batch
+is checked through properties that do not depend on size (router on every token,
+permutation invariants, bitwise repeatability, tensor-core path against the
+CUDA-core cross-check kernel) and a seeded sample of tokens goes through the
+oracle end to end.
+"""
+import numpy as np
+import pytest
+
+import helpers
+from gpt_oss_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+N_SAMPLE = 40
+
+
+def _device_case(shape):
+    import torch
+
+    import bench
+
+    dev = torch.device("cuda:0")
+    w = bench.device_weights(shape, dev)
+    g = torch.Generator(device=dev)
+    g.manual_seed(shape.seed + 77)
+    T, H = shape.n_tokens, shape.hidden_dim
+    t = torch.randn((T, H), generator=g, device=dev).bfloat16()
+    x = torch.randn((T, H), generator=g, device=dev).bfloat16()
+    pos = torch.arange(T, device=dev, dtype=torch.int32)
+    pos[5::97] = -1  # a few finished sequences
+    return w, t, x, pos
+
+
+@pytest.mark.parametrize("workload", ["c2", "c3"])
+def test_full_size_layer(pkg, oracle, workload):
+    import torch
+
+    shape = synth.SHAPES[workload]
+    T, H, IM, E, K = (shape.n_tokens, shape.hidden_dim, shape.intermediate_dim, shape.n_experts,
+                      shape.experts_per_token)
+    w, t, x0, pos = _device_case(shape)
+    eng = pkg.MoeEngine(H, IM, E, K, max_tokens=T, swiglu_limit=shape.swiglu_limit)
+    eng.load_layer_bf16(0, w["w_router"], w["b_router"], w["w_mlp1"], w["b_mlp1"], w["w_mlp2"],
+                        w["b_mlp2"], on_device=True)
+    eng.set_option("keep_logits", 1)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def run(impl):
+        eng.set_option("gemm_impl", impl)
+        x = x0.clone()
+        eng.forward(0, t, x, pos, T, stream)
+        torch.cuda.synchronize()
+        assert eng.device_status() == 0
+        return x
+
+    x_tc = run(pkg.GEMM_TCGEN05)
+    routing = eng.get_routing(T, want_logits=True)
+    x_tc2 = run(pkg.GEMM_TCGEN05)
+    assert torch.equal(x_tc, x_tc2), "two runs on the same input must agree bit for bit"
+    x_simt = run(pkg.GEMM_SIMT)
+
+    pos_h = pos.cpu().numpy()
+    active = pos_h >= 0
+    # -- router on every token against the oracle (cheap: T*E dot products)
+    host = {"t": t.float().cpu().numpy(), "pos": pos_h,
+            "w_router": w["w_router"].float().cpu().numpy(),
+            "b_router": w["b_router"].cpu().numpy()}
+    import ctypes
+
+    lib = ctypes.CDLL(str(oracle.ORACLE_LIB))
+    fp, ip = ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_int)
+    lg = np.zeros((T, E), np.float32)
+    ti = np.full((T, K), -1, np.int32)
+    tv = np.zeros((T, K), np.float32)
+    lib.oracle_router.argtypes = [fp, ip] + [ctypes.c_int] * 4 + [fp, fp, fp, ip, fp]
+    rc = lib.oracle_router(host["t"].ctypes.data_as(fp), pos_h.ctypes.data_as(ip), T, H, E, K,
+                           host["w_router"].ctypes.data_as(fp),
+                           host["b_router"].ctypes.data_as(fp), lg.ctypes.data_as(fp),
+                           ti.ctypes.data_as(ip), tv.ctypes.data_as(fp))
+    assert rc == 0
+    helpers.check_indices(routing["topk_i"], ti, lg, active)
+    same = (routing["topk_i"] == ti).all(axis=1) & active
+    assert same.sum() >= active.sum() - 2
+    np.testing.assert_allclose(routing["topk_v"][same], tv[same], rtol=0, atol=3e-5)
+    np.testing.assert_allclose(routing["topk_v"][active].sum(axis=1), 1.0, atol=1e-5)
+    assert (routing["topk_i"][~active] == -1).all()
+
+    # -- permutation invariants
+    off, st, gi = routing["expert_offsets"], routing["sorted_token"], routing["topk_i"]
+    np.testing.assert_array_equal(np.diff(off), np.bincount(gi[gi >= 0], minlength=E))
+    assert off[-1] == active.sum() * K
+    for e in range(E):
+        seg = st[off[e]:off[e + 1]]
+        assert (np.diff(seg) > 0).all()
+
+    # -- tensor-core kernel against the CUDA-core kernel on the whole batch
+    a, b = x_tc.float().cpu().numpy(), x_simt.float().cpu().numpy()
+    helpers.check_activations(a, b, "tcgen05 vs simt", max_abs=4e-2, mean_rel=1e-3)
+    x0_h = x0.float().cpu().numpy()
+    np.testing.assert_array_equal(a[~active], x0_h[~active])
+
+    # -- a seeded sample of tokens through the oracle, end to end
+    rng = np.random.default_rng(shape.seed)
+    idx = np.sort(rng.choice(np.nonzero(active)[0], N_SAMPLE, replace=False))
+    d = {k: v.float().cpu().numpy() for k, v in w.items()}
+    d["t"], d["x"], d["pos"] = host["t"][idx], x0_h[idx], None
+    want = oracle.moe_layer(d, shape)
+    helpers.check_indices(routing["topk_i"][idx], want["topk_i"], want["logits"],
+                          np.ones(N_SAMPLE, bool))
+    helpers.check_activations(a[idx], want["x_out"], "x_out sample", bf16_quantum=True)
+    helpers.check_activations(a[idx] - x0_h[idx], want["e_agg"], "block output sample",
+                              max_abs=4e-2, mean_rel=2e-2)
+    eng.close()

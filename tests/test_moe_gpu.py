@@ -24,7 +24,8 @@ def _compare(pkg, oracle, shape, d, via="forward", gemm_impl=None, want=None):
     same = (r["topk_i"] == want["topk_i"]).all(axis=1) & active
     np.testing.assert_allclose(r["topk_v"][same], want["topk_v"][same], rtol=0, atol=2e-5)
     np.testing.assert_allclose(r["logits"][active], want["logits"][active], rtol=0, atol=5e-5)
-    helpers.check_activations(got["x_out"][active], want["x_out"][active], "x_out")
+    helpers.check_activations(got["x_out"][active], want["x_out"][active], "x_out",
+                              bf16_quantum=True)
     # inactive rows keep their residual bit for bit
     np.testing.assert_array_equal(got["x_out"][~active], synth.bf16_round(d["x"])[~active])
     # pure block output (zero residual): small magnitudes, tighter check of the GEMMs
@@ -57,7 +58,7 @@ EDGE_CASES = [
     (96, 320, 248, 128, 4, 0),   # 128 experts, most of them with 0-5 rows; ragged N
     (64, 128, 64, 16, 1, 0),     # top-1
     (64, 128, 64, 16, 8, 5),     # top-8
-    (300, 2880, 2880, 8, 2, 0),  # the real hidden sizes: 45 K steps, 24 / 12 N tiles
+    (300, 2880, 2880, 8, 4, 0),  # the real hidden sizes: 45 K steps, 24 / 12 N tiles
 ]
 
 
