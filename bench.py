@@ -210,6 +210,8 @@ def run_ours(args, shape):
     w = device_weights(shape, dev)
     eng.load_layer_bf16(0, w["w_router"], w["b_router"], w["w_mlp1"], w["b_mlp1"], w["w_mlp2"],
                         w["b_mlp2"], on_device=True)
+    if os.environ.get("GPTOSS_SKIP_EPILOGUE"):  # measurement aid: main loop only
+        eng.set_option("skip_epilogue", int(os.environ["GPTOSS_SKIP_EPILOGUE"]))
     g = torch.Generator(device=dev)
     g.manual_seed(shape.seed + 1000 + rank)
     t = torch.randn((T, H), generator=g, device=dev).bfloat16()

@@ -94,6 +94,7 @@ struct gptoss_moe {
   int opt_keep_logits = 0;
   int opt_exact_ties = 1;
   int opt_time_stages = 0;
+  int opt_skip_epilogue = 0;
   gptoss::StageTimer timers[8];
   long long launches = 0;
   mutable std::string err;

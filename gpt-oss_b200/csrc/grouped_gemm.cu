@@ -66,50 +66,72 @@ struct GemmArgs {
   int out_ld;   // leading dimension of out
   float limit;
   int *status;
+  int skip_epilogue;  // measurement aid: release the accumulator without reading it
 };
 
-template <int BN, int EPI>
-__device__ __forceinline__ void epilogue_chunk(const uint32_t *r, int ncols_chunk, int n0,
-                                               int e, int grow, bool row_ok, float wrow,
-                                               const GemmArgs &g) {
-  // r: ncols_chunk (16 or 32) fp32 accumulators of one row, columns n0 .. n0+ncols_chunk-1
+// bias add for 8 accumulator columns n .. n+7 of expert row `bias`
+__device__ __forceinline__ void add_bias8(const uint32_t *r, const float *bias, int n, float *v) {
+  const float4 b0 = __ldg(reinterpret_cast<const float4 *>(bias + n));
+  const float4 b1 = __ldg(reinterpret_cast<const float4 *>(bias + n + 4));
+  v[0] = __uint_as_float(r[0]) + b0.x;
+  v[1] = __uint_as_float(r[1]) + b0.y;
+  v[2] = __uint_as_float(r[2]) + b0.z;
+  v[3] = __uint_as_float(r[3]) + b0.w;
+  v[4] = __uint_as_float(r[4]) + b1.x;
+  v[5] = __uint_as_float(r[5]) + b1.y;
+  v[6] = __uint_as_float(r[6]) + b1.z;
+  v[7] = __uint_as_float(r[7]) + b1.w;
+}
+
+// One row's NC (16 or 32) fp32 accumulators, columns n0 .. n0+NC-1 of expert e:
+// bias, activation or routing weight, bf16, 16-byte stores.
+template <int EPI, int NC>
+__device__ __forceinline__ void epilogue_chunk(const uint32_t *r, int n0, int e, int grow,
+                                               bool row_ok, float wrow, const GemmArgs &g) {
   const float *bias = g.bias + static_cast<size_t>(e) * g.n_cols;
 #pragma unroll
-  for (int q = 0; q < 4; q++) {  // 8 accumulator columns per step
-    if (q * 8 >= ncols_chunk) break;
-    const int n = n0 + q * 8;
-    if (n + 8 > g.n_cols) break;
-    const float4 b0 = __ldg(reinterpret_cast<const float4 *>(bias + n));
-    const float4 b1 = __ldg(reinterpret_cast<const float4 *>(bias + n + 4));
-    float v[8];
-    v[0] = __uint_as_float(r[q * 8 + 0]) + b0.x;
-    v[1] = __uint_as_float(r[q * 8 + 1]) + b0.y;
-    v[2] = __uint_as_float(r[q * 8 + 2]) + b0.z;
-    v[3] = __uint_as_float(r[q * 8 + 3]) + b0.w;
-    v[4] = __uint_as_float(r[q * 8 + 4]) + b1.x;
-    v[5] = __uint_as_float(r[q * 8 + 5]) + b1.y;
-    v[6] = __uint_as_float(r[q * 8 + 6]) + b1.z;
-    v[7] = __uint_as_float(r[q * 8 + 7]) + b1.w;
+  for (int q = 0; q < NC / 16; q++) {  // 16 accumulator columns per step
+    const int n = n0 + q * 16;
+    const int valid = g.n_cols - n;  // columns of this step that exist (multiple of 8)
+    if (valid <= 0) break;
+    float v[16];
+    add_bias8(r + q * 16, bias, n, v);
+    if (valid >= 16) {
+      add_bias8(r + q * 16 + 8, bias, n + 8, v + 8);
+    } else {
+#pragma unroll
+      for (int i = 8; i < 16; i++) v[i] = 0.f;
+    }
     if (EPI == kEpiSwiglu) {
-      // 8 accumulator columns = 4 (gate, up) pairs -> 4 activations, one 8-byte store
-      const float a0 = swiglu_act(v[0], v[1], g.limit);
-      const float a1 = swiglu_act(v[2], v[3], g.limit);
-      const float a2 = swiglu_act(v[4], v[5], g.limit);
-      const float a3 = swiglu_act(v[6], v[7], g.limit);
+      // 16 columns = 8 (gate, up) pairs -> 8 activations -> one 16-byte store
+      uint4 o;
+      o.x = pack_bf16(swiglu_act(v[0], v[1], g.limit), swiglu_act(v[2], v[3], g.limit));
+      o.y = pack_bf16(swiglu_act(v[4], v[5], g.limit), swiglu_act(v[6], v[7], g.limit));
+      o.z = pack_bf16(swiglu_act(v[8], v[9], g.limit), swiglu_act(v[10], v[11], g.limit));
+      o.w = pack_bf16(swiglu_act(v[12], v[13], g.limit), swiglu_act(v[14], v[15], g.limit));
       if (row_ok) {
-        uint2 o;
-        o.x = pack_bf16(a0, a1);
-        o.y = pack_bf16(a2, a3);
-        *reinterpret_cast<uint2 *>(g.out + static_cast<size_t>(grow) * g.out_ld + (n >> 1)) = o;
+        bf16 *dst = g.out + static_cast<size_t>(grow) * g.out_ld + (n >> 1);
+        if (valid >= 16)
+          *reinterpret_cast<uint4 *>(dst) = o;
+        else
+          *reinterpret_cast<uint2 *>(dst) = make_uint2(o.x, o.y);
       }
     } else {
       if (row_ok) {
+        bf16 *dst = g.out + static_cast<size_t>(grow) * g.out_ld + n;
         uint4 o;
         o.x = pack_bf16(v[0] * wrow, v[1] * wrow);
         o.y = pack_bf16(v[2] * wrow, v[3] * wrow);
         o.z = pack_bf16(v[4] * wrow, v[5] * wrow);
         o.w = pack_bf16(v[6] * wrow, v[7] * wrow);
-        *reinterpret_cast<uint4 *>(g.out + static_cast<size_t>(grow) * g.out_ld + n) = o;
+        *reinterpret_cast<uint4 *>(dst) = o;
+        if (valid >= 16) {
+          o.x = pack_bf16(v[8] * wrow, v[9] * wrow);
+          o.y = pack_bf16(v[10] * wrow, v[11] * wrow);
+          o.z = pack_bf16(v[12] * wrow, v[13] * wrow);
+          o.w = pack_bf16(v[14] * wrow, v[15] * wrow);
+          *reinterpret_cast<uint4 *>(dst + 8) = o;
+        }
       }
     }
   }
@@ -257,18 +279,36 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kAccCols;
-#pragma unroll 1
-      for (int c = 0; c + 32 <= BN; c += 32) {
-        uint32_t r[32];
-        tmem_ld32(taddr + c, r);
-        tmem_ld_wait();
-        epilogue_chunk<BN, EPI>(r, 32, nt * BN + c, e, grow, row_ok, wrow, g);
-      }
-      if (BN % 32 != 0) {
-        uint32_t r[16];
-        tmem_ld16(taddr + (BN / 32) * 32, r);
-        tmem_ld_wait();
-        epilogue_chunk<BN, EPI>(r, 16, nt * BN + (BN / 32) * 32, e, grow, row_ok, wrow, g);
+      if (!g.skip_epilogue) {
+        // TMEM -> registers through two register buffers: the load of the next 32
+        // columns is in flight while the current 32 are processed
+        constexpr int kFull = BN / 32;
+        constexpr bool kTail = (BN % 32) != 0;  // 16 more columns
+        uint32_t ra[32], rb[32];
+        tmem_ld32(taddr, ra);
+        tmem_ld_wait32(ra);
+#pragma unroll
+        for (int c = 0; c < kFull; c += 2) {
+          if (c + 1 < kFull) {
+            tmem_ld32(taddr + (c + 1) * 32, rb);
+          } else if (kTail) {
+            tmem_ld16(taddr + kFull * 32, *reinterpret_cast<uint32_t(*)[16]>(rb));
+          }
+          epilogue_chunk<EPI, 32>(ra, nt * BN + c * 32, e, grow, row_ok, wrow, g);
+          if (c + 1 < kFull || kTail) tmem_ld_wait32(rb);
+          if (c + 1 < kFull) {
+            if (c + 2 < kFull) {
+              tmem_ld32(taddr + (c + 2) * 32, ra);
+            } else if (kTail) {
+              tmem_ld16(taddr + kFull * 32, *reinterpret_cast<uint32_t(*)[16]>(ra));
+            }
+            epilogue_chunk<EPI, 32>(rb, nt * BN + (c + 1) * 32, e, grow, row_ok, wrow, g);
+            if (c + 2 < kFull || kTail) tmem_ld_wait32(ra);
+          }
+        }
+        if (kTail)
+          epilogue_chunk<EPI, 16>((kFull & 1) ? rb : ra, nt * BN + kFull * 32, e, grow, row_ok,
+                                  wrow, g);
       }
       tc_fence_before();
       __syncwarp();
@@ -443,6 +483,7 @@ cudaError_t launch_gate_up(gptoss_moe *h, int layer, cudaStream_t stream) {
   g.out_ld = h->IM;
   g.limit = h->cfg.swiglu_limit;
   g.status = h->status;
+  g.skip_epilogue = h->opt_skip_epilogue;
   if (h->opt_gemm_impl == GPTOSS_GEMM_SIMT) {
     dim3 grid((g.n_cols + 63) / 64, h->mtiles_cap);
     grouped_gemm_simt_kernel<kEpiSwiglu><<<grid, 256, 0, stream>>>(h->xs, h->H, lw.w1, g);
@@ -467,6 +508,7 @@ cudaError_t launch_down(gptoss_moe *h, int layer, cudaStream_t stream) {
   g.out_ld = h->H;
   g.limit = h->cfg.swiglu_limit;
   g.status = h->status;
+  g.skip_epilogue = h->opt_skip_epilogue;
   if (h->opt_gemm_impl == GPTOSS_GEMM_SIMT) {
     dim3 grid((g.n_cols + 63) / 64, h->mtiles_cap);
     grouped_gemm_simt_kernel<kEpiDown><<<grid, 256, 0, stream>>>(h->hact, h->IM, lw.w2, g);
