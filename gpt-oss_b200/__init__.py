@@ -100,6 +100,7 @@ def load_library() -> ctypes.CDLL:
         "gptoss_moe_ep_unique_id": (c_int, [vp]),
         "gptoss_moe_ep_init": (c_int, [vp, vp]),
         "gptoss_moe_version": (c_char_p, []),
+        "gptoss_moe_permute_static": (c_int, [vp, vp, c_int, c_int, c_int, vp, vp, vp, vp, vp]),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(lib, name)
@@ -124,6 +125,19 @@ def _ptr(obj):
             raise ValueError("tensor must be contiguous")
         return ctypes.c_void_p(obj.data_ptr())
     raise TypeError(f"cannot take the address of {type(obj)}")
+
+
+def permute_static(slot_expert, slot_weight, n_rows, top_k, n_experts, expert_offsets, sorted_row,
+                   sorted_weight, row_of, stream=0):
+    """gptoss_moe_permute_static: the permutation stage without an engine handle and
+    without any allocation (scratch is a fixed array inside the library).  All
+    arguments are device buffers owned by the caller."""
+    lib = load_library()
+    rc = lib.gptoss_moe_permute_static(_ptr(slot_expert), _ptr(slot_weight), n_rows, top_k,
+                                       n_experts, _ptr(expert_offsets), _ptr(sorted_row),
+                                       _ptr(sorted_weight), _ptr(row_of), ctypes.c_void_p(stream))
+    if rc != GPTOSS_OK:
+        raise MoeError(rc, lib.gptoss_moe_last_error(None).decode())
 
 
 class MoeEngine:

@@ -126,6 +126,10 @@ int make_tmap_2d_bf16(CUtensorMap *map, const void *base, uint64_t inner, uint64
                       uint32_t box_inner, uint32_t box_outer, std::string *err);
 int gemm_tile_n(int which);  // N extent of one tile: 0 = gate_up, 1 = down
 
+// moe_api.cu: error text for entry points that take no handle (read back with
+// gptoss_moe_last_error(NULL)); returns `code`
+int set_global_error(int code, const char *text);
+
 // weights.cu
 cudaError_t launch_f32_to_bf16(bf16 *dst, const float *src, size_t n, cudaStream_t stream,
                                long long *launches);

@@ -28,7 +28,14 @@ static int fail(const gptoss_moe *h, int code, const char *fmt, ...) {
   return code;
 }
 
-#define CK(h, call)                                                                       \
+namespace gptoss {
+int set_global_error(int code, const char *text) {
+  g_create_err = text ? text : "";
+  return code;
+}
+}  // namespace gptoss
+
+#define CK(h, call)                                                                      \
   do {                                                                                    \
     cudaError_t e__ = (call);                                                             \
     if (e__ != cudaSuccess)                                                               \

@@ -313,3 +313,91 @@ cudaError_t launch_reduce_rows(gptoss_moe *h, bf16 *out_rows, int R, cudaStream_
 }
 
 }  // namespace gptoss
+
+// ---------------------------------------------------------------------------
+// Permutation without any allocation: gptoss_moe_permute_static.
+//
+// Same two kernels as launch_permute (count, scan + scatter), but the scratch
+// they need - the per-CTA expert histograms and the M-tile schedule - lives in a
+// fixed array in device memory that is part of the library image, so the call
+// needs neither an engine handle nor cudaMalloc.  Every GPU that loads the
+// library holds the array (kStaticInts * 4 bytes = 78 KB) until the process
+// exits.  Limits: kStaticMaxRows rows, kStaticMaxExperts experts, top-k <= 8.
+namespace gptoss {
+
+constexpr int kStaticMaxRows = 8192;
+constexpr int kStaticMaxExperts = 256;
+constexpr int kStaticBlocks = kStaticMaxRows / kPermTokens;  // 64 CTAs at most
+constexpr int kStaticMtilesPad = 1024;  // >= 8192 * 8 / 128 + 256 + 1 M tiles
+// ints: [block counts: 64 x 256][mtile_expert | mtile_row0 | mtile_rows: 3 x 1024][num_mtiles, status, pad]
+constexpr int kStaticCountsInts = kStaticBlocks * kStaticMaxExperts;
+constexpr int kStaticInts = kStaticCountsInts + 3 * kStaticMtilesPad + 64;
+
+static __device__ __align__(256) int g_perm_scratch[kStaticInts];
+
+// In host code `g_perm_scratch` is only a handle for the runtime, not an address
+// a kernel can use; the device address is looked up once per device.
+static int *g_perm_scratch_dev[64] = {nullptr};
+
+static cudaError_t static_scratch(int **out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!g_perm_scratch_dev[dev]) {
+    int *p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_perm_scratch);
+    if (e != cudaSuccess) return e;
+    g_perm_scratch_dev[dev] = p;
+  }
+  *out = g_perm_scratch_dev[dev];
+  return cudaSuccess;
+}
+
+}  // namespace gptoss
+
+extern "C" int gptoss_moe_permute_static(const int *slot_expert, const float *slot_weight,
+                                         int n_rows, int top_k, int n_experts,
+                                         int *expert_offsets, int *sorted_row,
+                                         float *sorted_weight, int *row_of, void *stream) {
+  using namespace gptoss;
+  if (n_rows < 0 || top_k <= 0 || n_experts <= 0 || !expert_offsets)
+    return set_global_error(GPTOSS_E_INVALID, "gptoss_moe_permute_static: bad argument");
+  if (n_rows > kStaticMaxRows || n_experts > kStaticMaxExperts || top_k > GPTOSS_MAX_TOPK)
+    return set_global_error(
+        GPTOSS_E_CAPACITY,
+        "gptoss_moe_permute_static: at most 8192 rows, 256 experts and top-8 fit the fixed scratch");
+  if (n_rows > 0 && (!slot_expert || !slot_weight || !sorted_row || !sorted_weight || !row_of))
+    return set_global_error(GPTOSS_E_INVALID, "gptoss_moe_permute_static: null buffer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int *scratch = nullptr;
+  cudaError_t e = static_scratch(&scratch);
+  if (e != cudaSuccess) return set_global_error(GPTOSS_E_CUDA, cudaGetErrorString(e));
+  if (n_rows == 0) {
+    e = cudaMemsetAsync(expert_offsets, 0, sizeof(int) * (n_experts + 1), st);
+    return e == cudaSuccess ? GPTOSS_OK : set_global_error(GPTOSS_E_CUDA, cudaGetErrorString(e));
+  }
+  int *block_counts = scratch;
+  int *mtile_expert = scratch + kStaticCountsInts;
+  int *mtile_row0 = mtile_expert + kStaticMtilesPad;
+  int *mtile_rows = mtile_row0 + kStaticMtilesPad;
+  int *num_mtiles = mtile_rows + kStaticMtilesPad;
+  int *status = num_mtiles + 1;
+  // the array keeps what the previous call left: the two words that are only ever
+  // OR-ed / compared start from zero again; everything else is fully rewritten
+  e = cudaMemsetAsync(num_mtiles, 0, 2 * sizeof(int), st);
+  if (e != cudaSuccess) return set_global_error(GPTOSS_E_CUDA, cudaGetErrorString(e));
+  const int nblocks = (n_rows + kPermTokens - 1) / kPermTokens;
+  perm_count_kernel<<<nblocks, 256, n_experts * sizeof(int), st>>>(slot_expert, n_rows, top_k,
+                                                                   n_experts, block_counts, status);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return set_global_error(GPTOSS_E_CUDA, cudaGetErrorString(e));
+  const size_t smem = (static_cast<size_t>(3 + kScanThreads / 32) * n_experts + 1) * sizeof(int);
+  perm_scan_scatter_kernel<<<nblocks, kScanThreads, smem, st>>>(
+      slot_expert, slot_weight, n_rows, top_k, n_experts, block_counts, nblocks, expert_offsets,
+      sorted_row, sorted_weight, row_of, mtile_expert, mtile_row0, mtile_rows, num_mtiles,
+      kStaticMtilesPad, n_rows * top_k, status);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return set_global_error(GPTOSS_E_CUDA, cudaGetErrorString(e));
+  return GPTOSS_OK;
+}

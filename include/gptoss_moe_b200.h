@@ -193,6 +193,39 @@ int gptoss_moe_stage_ms(gptoss_moe_t *h, int stage, float *ms);
 int gptoss_moe_ep_unique_id(void *id128);
 int gptoss_moe_ep_init(gptoss_moe_t *h, const void *id128);
 
+/*
+ * The permutation stage for callers that cannot allocate device memory.  (No
+ * counterpart in the reference: its count / scan / build kernels work on buffers
+ * the engine allocated at start-up.)
+ *
+ * Who needs it: a host engine that has already given every free byte of HBM to
+ * its own pool (the reference grows its KV cache until allocation fails), or a
+ * serving loop that cannot afford the device-wide synchronisation a cudaMalloc
+ * or cudaFree implies.  This call takes no engine handle and allocates nothing,
+ * neither with cudaMalloc nor through any library: its scratch (per-block expert
+ * histograms and the tile schedule) is a fixed 78 KB array inside the library
+ * image, present on every GPU that loads the library until the process exits.
+ *
+ * Same result as gptoss_moe_permute without the row gather: for n_rows rows with
+ * top_k slots each (slot_expert: expert id or -1 to skip the slot; ids >=
+ * n_experts are skipped too), a stable counting sort by expert.  All pointers
+ * are device pointers owned by the caller:
+ *   expert_offsets [n_experts+1], sorted_row / sorted_weight [n_rows*top_k]
+ *   (first expert_offsets[n_experts] entries valid), row_of [n_rows*top_k]
+ *   (position of each slot in sorted order, -1 for skipped slots).
+ * Limits: n_rows <= 8192, n_experts <= 256, top_k <= 8; anything larger is
+ * rejected with GPTOSS_E_CAPACITY (text via gptoss_moe_last_error(NULL)).
+ *
+ * The first call on each device looks up the array's device address; make that
+ * first call before starting any stream capture.  All calls on one GPU share
+ * the one array, which keeps the previous call's contents (the call clears the
+ * words that must start at zero): two calls whose kernels overlap on the GPU,
+ * from different streams or threads, race - serialise them.
+ */
+int gptoss_moe_permute_static(const int *slot_expert, const float *slot_weight, int n_rows,
+                              int top_k, int n_experts, int *expert_offsets, int *sorted_row,
+                              float *sorted_weight, int *row_of, void *stream);
+
 /* Library / build information. */
 const char *gptoss_moe_version(void);
 
