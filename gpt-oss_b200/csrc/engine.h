@@ -119,6 +119,26 @@ cudaError_t launch_combine(gptoss_moe *h, bf16 *x, const int *topk_i_rows, int T
                            cudaStream_t stream);
 cudaError_t launch_reduce_rows(gptoss_moe *h, bf16 *out_rows, int R, cudaStream_t stream);
 
+// A counting sort of (row, slot) pairs by key on caller-named buffers.
+struct PermPlan {
+  const int *slot_expert;    // [R, K] key (0 .. El-1) or -1
+  const float *slot_weight;  // [R, K]
+  int R, K, El;
+  int *block_counts;         // [blocks_cap, El]
+  int blocks_cap;
+  int *expert_offsets;       // [El + 1]
+  int *sorted_row;           // [assign_cap]
+  float *sorted_weight;      // [assign_cap]
+  int *row_of;               // [R * K]
+  int *mtile_expert, *mtile_row0, *mtile_rows, *num_mtiles;
+  int mtiles_cap, assign_cap;
+};
+cudaError_t launch_perm_plan(const PermPlan &p, int *status, cudaStream_t stream,
+                             long long *launches);
+cudaError_t launch_combine_rows(bool residual, bf16 *out, const bf16 *ys, const int *row_of, int R,
+                                int K, int H, int assign_cap, int *status, cudaStream_t stream,
+                                long long *launches);
+
 // grouped_gemm.cu
 cudaError_t launch_gate_up(gptoss_moe *h, int layer, cudaStream_t stream);
 cudaError_t launch_down(gptoss_moe *h, int layer, cudaStream_t stream);

@@ -1,12 +1,404 @@
+// Expert parallelism: dispatch -> owner experts -> return -> combine over NCCL.
+//
+// Replaces gpu_forward_device_batch_ep and run_owner_mlp of the reference
+// (getp-csrc/expert.cpp:1366-1607, :175-437), its per-owner routing / packing
+// kernels (getp-csrc/utility/utility.cpp:830-1016) and the host rendezvous
+// (expert.cpp:67-173).  Kept from the reference: owner of expert e is rank
+// e % N with local id e / N; a token travels once to an owner even when several
+// of its experts live there; the owner sums its experts' weighted outputs per
+// received row in fp32 and returns one bf16 row.  Not kept: host mutexes, one
+// routing launch per owner, per-(home, expert) copy loops and memsets.
+//
+// Every rank is a home (its own tokens) and an owner (E / N experts).  Per layer:
+//   1. home: mark for every token the owners it needs; counting sort of the
+//      (token, owner) pairs by owner with the permutation kernels -> per-owner
+//      send lists in token order; pack rows and per-row slot metadata
+//   2. counts: all-gather of the N send counts, one small D2H copy and the only
+//      host synchronisation of the layer (NCCL point-to-point sizes are host
+//      arguments)
+//   3. dispatch: grouped ncclSend / ncclRecv; received rows land in this rank's
+//      own HBM before any kernel or TMA touches them
+//   4. owner: the single-GPU expert stage on the received rows, then the
+//      per-row pre-reduction
+//   5. return: grouped send / recv the other way
+//   6. home: x += sum over owners of the returned rows (the combine kernel with
+//      one slot per owner)
+// Ranks must call the layer in lock step (also with zero tokens).
+//
+// NCCL is loaded with dlopen on first use, so single-GPU users of the library do
+// not need it; in a process that already loaded NCCL (PyTorch) the same copy is
+// picked up.
 #include "ep.h"
+
+#include <dlfcn.h>
+#include <nccl.h>
+#include <stdio.h>
+
+#include <vector>
+
+#include "common.cuh"
+
 namespace gptoss {
-int ep_forward(gptoss_moe *h, int, const void *, void *, int, void *) {
-  h->err = "expert parallelism is not set up: call gptoss_moe_ep_init first";
-  return GPTOSS_E_STATE;
+
+struct NcclApi {
+  void *lib = nullptr;
+  ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
+  ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  ncclResult_t (*Send)(const void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*Recv)(void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t,
+                            cudaStream_t) = nullptr;
+  ncclResult_t (*GroupStart)() = nullptr;
+  ncclResult_t (*GroupEnd)() = nullptr;
+  const char *(*GetErrorString)(ncclResult_t) = nullptr;
+};
+
+static NcclApi g_nccl;
+
+static bool load_nccl(std::string *err) {
+  if (g_nccl.lib) return true;
+  void *lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+  if (!lib) lib = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+  if (!lib) {
+    *err = std::string("cannot load NCCL: ") + dlerror();
+    return false;
+  }
+#define SYM(field, name)                                                  \
+  *reinterpret_cast<void **>(&g_nccl.field) = dlsym(lib, name);           \
+  if (!g_nccl.field) {                                                    \
+    *err = std::string("NCCL symbol missing: ") + name;                   \
+    return false;                                                         \
+  }
+  SYM(GetUniqueId, "ncclGetUniqueId")
+  SYM(CommInitRank, "ncclCommInitRank")
+  SYM(CommDestroy, "ncclCommDestroy")
+  SYM(Send, "ncclSend")
+  SYM(Recv, "ncclRecv")
+  SYM(AllGather, "ncclAllGather")
+  SYM(GroupStart, "ncclGroupStart")
+  SYM(GroupEnd, "ncclGroupEnd")
+  SYM(GetErrorString, "ncclGetErrorString")
+#undef SYM
+  g_nccl.lib = lib;
+  return true;
 }
-void ep_destroy(gptoss_moe *) {}
+
+struct EpState {
+  ncclComm_t comm = nullptr;
+  int N = 1, rank = 0;
+  int send_cap = 0;  // rows this rank can send: T * min(N, K)
+  // home side: (token, owner) plan
+  int *own_key = nullptr;       // [T, N] owner id or -1
+  float *own_w = nullptr;       // [T, N] unused weights (zeros)
+  int *s_block_counts = nullptr, *s_offsets = nullptr, *s_sorted_row = nullptr;
+  float *s_sorted_w = nullptr;
+  int *s_row_of = nullptr;
+  int *s_mtile = nullptr;       // dummy tile schedule (3 arrays + count)
+  int s_mtiles_cap = 0, s_blocks_cap = 0;
+  bf16 *send_rows = nullptr;    // [send_cap, H]
+  int *send_e = nullptr;        // [send_cap, K] local expert id at the owner or -1
+  float *send_w = nullptr;      // [send_cap, K]
+  bf16 *ret_rows = nullptr;     // [send_cap, H] partial sums coming back
+  // owner side
+  bf16 *recv_rows = nullptr;    // [N*T, H]
+  int *recv_e = nullptr;        // [N*T, K]
+  float *recv_w = nullptr;      // [N*T, K]
+  bf16 *out_rows = nullptr;     // [N*T, H] per-row sums over this rank's experts
+  int *counts_dev = nullptr;    // [N, N] counts_dev[src][dst]
+  int *counts_host = nullptr;   // pinned copy
+};
+
+// own_key[t, o] = o when token t has at least one selected expert on rank o.
+__global__ void __launch_bounds__(256)
+ep_owner_keys_kernel(const int *__restrict__ topk_i, int T, int K, int N,
+                     int *__restrict__ own_key, float *__restrict__ own_w) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T * N) return;
+  const int t = i / N, o = i - t * N;
+  bool has = false;
+  for (int k = 0; k < K; k++) {
+    const int e = topk_i[t * K + k];
+    if (e >= 0 && e % N == o) has = true;
+  }
+  own_key[i] = has ? o : -1;
+  own_w[i] = 0.f;
+}
+
+// One warp per send row p: copy the token's row and write its K slots as seen by
+// the owner (local expert id e / N for the experts that live there, else -1).
+__global__ void __launch_bounds__(256)
+ep_pack_kernel(const bf16 *__restrict__ t, const int *__restrict__ topk_i,
+               const float *__restrict__ topk_v, const int *__restrict__ s_offsets,
+               const int *__restrict__ s_sorted_row, int N, int K, int H, int T,
+               bf16 *__restrict__ send_rows, int *__restrict__ send_e,
+               float *__restrict__ send_w, int *__restrict__ my_counts, int *status) {
+  const int total = s_offsets[N];
+  const int lane = threadIdx.x & 31;
+  const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int nwarps = gridDim.x * (blockDim.x >> 5);
+  if (gw == 0 && lane < N) my_counts[lane] = s_offsets[lane + 1] - s_offsets[lane];
+  const int n4 = H >> 3;
+  for (int p = gw; p < total; p += nwarps) {
+    const int tok = s_sorted_row[p];
+    if (tok < 0 || tok >= T) {
+      set_status(status, kStatusBadIndex);
+      continue;
+    }
+    int owner = 0;
+    while (owner + 1 < N && s_offsets[owner + 1] <= p) owner++;
+    if (lane < K) {
+      const int e = topk_i[tok * K + lane];
+      const bool mine = e >= 0 && e % N == owner;
+      send_e[static_cast<size_t>(p) * K + lane] = mine ? e / N : -1;
+      send_w[static_cast<size_t>(p) * K + lane] = mine ? topk_v[tok * K + lane] : 0.f;
+    }
+    const uint4 *s4 = reinterpret_cast<const uint4 *>(t + static_cast<size_t>(tok) * H);
+    uint4 *d4 = reinterpret_cast<uint4 *>(send_rows + static_cast<size_t>(p) * H);
+    for (int q = lane; q < n4; q += 32) d4[q] = __ldg(s4 + q);
+  }
+}
+
+static int ep_fail(gptoss_moe *h, int code, const std::string &msg) {
+  h->err = msg;
+  return code;
+}
+
+#define EP_CUDA(h, call)                                                                 \
+  do {                                                                                   \
+    cudaError_t e__ = (call);                                                            \
+    if (e__ != cudaSuccess)                                                              \
+      return ep_fail((h), GPTOSS_E_CUDA, std::string(#call) + ": " + cudaGetErrorString(e__)); \
+  } while (0)
+#define EP_NCCL(h, call)                                                                 \
+  do {                                                                                   \
+    ncclResult_t r__ = (call);                                                           \
+    if (r__ != ncclSuccess)                                                              \
+      return ep_fail((h), GPTOSS_E_COMM, std::string(#call) + ": " + g_nccl.GetErrorString(r__)); \
+  } while (0)
+
+template <typename T>
+static cudaError_t ep_alloc(T **p, size_t n) {
+  return cudaMalloc(reinterpret_cast<void **>(p), (n ? n : 1) * sizeof(T));
+}
+
+struct EpStageScope {
+  gptoss_moe *h;
+  int id;
+  cudaStream_t st;
+  EpStageScope(gptoss_moe *h_, int id_, cudaStream_t st_) : h(h_), id(id_), st(st_) {
+    if (!h->opt_time_stages) return;
+    StageTimer &t = h->timers[id];
+    if (t.used == t.beg.size()) {
+      cudaEvent_t b, e;
+      cudaEventCreate(&b);
+      cudaEventCreate(&e);
+      t.beg.push_back(b);
+      t.end.push_back(e);
+    }
+    cudaEventRecord(t.beg[t.used], st);
+  }
+  ~EpStageScope() {
+    if (!h->opt_time_stages) return;
+    StageTimer &t = h->timers[id];
+    cudaEventRecord(t.end[t.used], st);
+    t.used++;
+  }
+};
+
+int ep_forward(gptoss_moe *h, int layer, const void *t_in, void *x_io, int T, void *stream) {
+  EpState *ep = static_cast<EpState *>(h->ep);
+  if (!ep || !ep->comm)
+    return ep_fail(h, GPTOSS_E_STATE,
+                   "expert parallelism is not set up: call gptoss_moe_ep_init first");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int N = ep->N, K = h->K, H = h->H;
+  const bf16 *t = static_cast<const bf16 *>(t_in);
+  std::vector<int> soff(N + 1, 0), roff(N + 1, 0);
+  {
+    EpStageScope sc(h, 5, st);
+    // 1. per-owner send lists
+    if (T > 0) {
+      ep_owner_keys_kernel<<<(T * N + 255) / 256, 256, 0, st>>>(h->topk_i, T, K, N, ep->own_key,
+                                                                ep->own_w);
+      h->launches++;
+      EP_CUDA(h, cudaGetLastError());
+    }
+    PermPlan p;
+    p.slot_expert = ep->own_key;
+    p.slot_weight = ep->own_w;
+    p.R = T; p.K = N; p.El = N;
+    p.block_counts = ep->s_block_counts;
+    p.blocks_cap = ep->s_blocks_cap;
+    p.expert_offsets = ep->s_offsets;
+    p.sorted_row = ep->s_sorted_row;
+    p.sorted_weight = ep->s_sorted_w;
+    p.row_of = ep->s_row_of;
+    p.mtile_expert = ep->s_mtile;
+    p.mtile_row0 = ep->s_mtile + ep->s_mtiles_cap;
+    p.mtile_rows = ep->s_mtile + 2 * ep->s_mtiles_cap;
+    p.num_mtiles = ep->s_mtile + 3 * ep->s_mtiles_cap;
+    p.mtiles_cap = ep->s_mtiles_cap;
+    p.assign_cap = ep->send_cap;
+    EP_CUDA(h, launch_perm_plan(p, h->status, st, &h->launches));
+    ep_pack_kernel<<<h->num_sms * 4, 256, 0, st>>>(t, h->topk_i, h->topk_v, ep->s_offsets,
+                                                   ep->s_sorted_row, N, K, H, T, ep->send_rows,
+                                                   ep->send_e, ep->send_w,
+                                                   ep->counts_dev + ep->rank * N, h->status);
+    h->launches++;
+    EP_CUDA(h, cudaGetLastError());
+    // 2. counts to every rank, then to the host
+    EP_NCCL(h, g_nccl.AllGather(ep->counts_dev + ep->rank * N, ep->counts_dev, N, ncclInt32,
+                                ep->comm, st));
+    EP_CUDA(h, cudaMemcpyAsync(ep->counts_host, ep->counts_dev, sizeof(int) * N * N,
+                               cudaMemcpyDeviceToHost, st));
+    EP_CUDA(h, cudaStreamSynchronize(st));
+    for (int p2 = 0; p2 < N; p2++) {
+      const int s = ep->counts_host[ep->rank * N + p2];
+      const int r = ep->counts_host[p2 * N + ep->rank];
+      if (s < 0 || r < 0 || s > h->max_tokens || r > h->max_tokens)
+        return ep_fail(h, GPTOSS_E_COMM, "row counts exchanged between ranks are out of range");
+      soff[p2 + 1] = soff[p2] + s;
+      roff[p2 + 1] = roff[p2] + r;
+    }
+    if (soff[N] > ep->send_cap || roff[N] > h->rows_cap)
+      return ep_fail(h, GPTOSS_E_CAPACITY, "more rows routed than the engine was created for");
+    // 3. dispatch
+    EP_NCCL(h, g_nccl.GroupStart());
+    for (int p2 = 0; p2 < N; p2++) {
+      const size_t s = soff[p2 + 1] - soff[p2], r = roff[p2 + 1] - roff[p2];
+      if (s) {
+        EP_NCCL(h, g_nccl.Send(ep->send_rows + (size_t)soff[p2] * H, s * H, ncclBfloat16, p2,
+                               ep->comm, st));
+        EP_NCCL(h, g_nccl.Send(ep->send_e + (size_t)soff[p2] * K, s * K, ncclInt32, p2, ep->comm,
+                               st));
+        EP_NCCL(h, g_nccl.Send(ep->send_w + (size_t)soff[p2] * K, s * K, ncclFloat32, p2,
+                               ep->comm, st));
+      }
+      if (r) {
+        EP_NCCL(h, g_nccl.Recv(ep->recv_rows + (size_t)roff[p2] * H, r * H, ncclBfloat16, p2,
+                               ep->comm, st));
+        EP_NCCL(h, g_nccl.Recv(ep->recv_e + (size_t)roff[p2] * K, r * K, ncclInt32, p2, ep->comm,
+                               st));
+        EP_NCCL(h, g_nccl.Recv(ep->recv_w + (size_t)roff[p2] * K, r * K, ncclFloat32, p2,
+                               ep->comm, st));
+      }
+    }
+    EP_NCCL(h, g_nccl.GroupEnd());
+  }
+  // 4. owner: this rank's experts on everything received
+  const int R = roff[N];
+  h->stage_rows = ep->recv_rows;
+  h->stage_expert = ep->recv_e;
+  h->stage_weight = ep->recv_w;
+  h->stage_R = R;
+  {
+    EpStageScope sc(h, 1, st);
+    EP_CUDA(h, launch_permute(h, st));
+  }
+  {
+    EpStageScope sc(h, 2, st);
+    EP_CUDA(h, launch_gate_up(h, layer, st));
+  }
+  {
+    EpStageScope sc(h, 3, st);
+    EP_CUDA(h, launch_down(h, layer, st));
+  }
+  {
+    EpStageScope sc(h, 6, st);
+    EP_CUDA(h, launch_reduce_rows(h, ep->out_rows, R, st));
+    // 5. return the per-row sums to the homes
+    EP_NCCL(h, g_nccl.GroupStart());
+    for (int p2 = 0; p2 < N; p2++) {
+      const size_t s = soff[p2 + 1] - soff[p2], r = roff[p2 + 1] - roff[p2];
+      if (r)
+        EP_NCCL(h, g_nccl.Send(ep->out_rows + (size_t)roff[p2] * H, r * H, ncclBfloat16, p2,
+                               ep->comm, st));
+      if (s)
+        EP_NCCL(h, g_nccl.Recv(ep->ret_rows + (size_t)soff[p2] * H, s * H, ncclBfloat16, p2,
+                               ep->comm, st));
+    }
+    EP_NCCL(h, g_nccl.GroupEnd());
+  }
+  {
+    // 6. home: one returned row per (token, owner)
+    EpStageScope sc(h, 4, st);
+    EP_CUDA(h, launch_combine_rows(true, static_cast<bf16 *>(x_io), ep->ret_rows, ep->s_row_of, T,
+                                   N, H, ep->send_cap, h->status, st, &h->launches));
+  }
+  return GPTOSS_OK;
+}
+
+void ep_destroy(gptoss_moe *h) {
+  EpState *ep = static_cast<EpState *>(h->ep);
+  if (!ep) return;
+  if (ep->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(ep->comm);
+  cudaFree(ep->own_key); cudaFree(ep->own_w); cudaFree(ep->s_block_counts);
+  cudaFree(ep->s_offsets); cudaFree(ep->s_sorted_row); cudaFree(ep->s_sorted_w);
+  cudaFree(ep->s_row_of); cudaFree(ep->s_mtile); cudaFree(ep->send_rows); cudaFree(ep->send_e);
+  cudaFree(ep->send_w); cudaFree(ep->ret_rows); cudaFree(ep->recv_rows); cudaFree(ep->recv_e);
+  cudaFree(ep->recv_w); cudaFree(ep->out_rows); cudaFree(ep->counts_dev);
+  if (ep->counts_host) cudaFreeHost(ep->counts_host);
+  delete ep;
+  h->ep = nullptr;
+}
+
 }  // namespace gptoss
-extern "C" {
-int gptoss_moe_ep_unique_id(void *) { return GPTOSS_E_STATE; }
-int gptoss_moe_ep_init(gptoss_moe_t *, const void *) { return GPTOSS_E_STATE; }
+
+using namespace gptoss;
+
+extern "C" int gptoss_moe_ep_unique_id(void *id128) {
+  if (!id128) return GPTOSS_E_INVALID;
+  std::string err;
+  if (!load_nccl(&err)) return set_global_error(GPTOSS_E_COMM, err.c_str());
+  static_assert(sizeof(ncclUniqueId) == 128, "id buffer size");
+  ncclUniqueId id;
+  ncclResult_t r = g_nccl.GetUniqueId(&id);
+  if (r != ncclSuccess) return set_global_error(GPTOSS_E_COMM, g_nccl.GetErrorString(r));
+  memcpy(id128, &id, sizeof(id));
+  return GPTOSS_OK;
+}
+
+extern "C" int gptoss_moe_ep_init(gptoss_moe_t *h, const void *id128) {
+  if (!h || !id128) return GPTOSS_E_INVALID;
+  if (h->ep_size <= 1) return ep_fail(h, GPTOSS_E_STATE, "engine was created with ep_size <= 1");
+  if (h->ep) return ep_fail(h, GPTOSS_E_STATE, "expert parallelism already set up");
+  if (h->ep_size > GPTOSS_MAX_TOPK)
+    return ep_fail(h, GPTOSS_E_INVALID, "at most 8 ranks (one combine slot per owner)");
+  std::string err;
+  if (!load_nccl(&err)) return ep_fail(h, GPTOSS_E_COMM, err);
+  EP_CUDA(h, cudaSetDevice(h->cfg.device));
+  EpState *ep = new EpState();
+  h->ep = ep;
+  ep->N = h->ep_size;
+  ep->rank = h->ep_rank;
+  const int N = ep->N, K = h->K, H = h->H;
+  const size_t T = h->max_tokens;
+  ep->send_cap = static_cast<int>(T) * (N < K ? N : K);
+  ep->s_blocks_cap = (static_cast<int>(T) + kPermTokens - 1) / kPermTokens;
+  ep->s_mtiles_cap = ep->send_cap / kTileM + N + 1;
+  EP_CUDA(h, ep_alloc(&ep->own_key, T * N));
+  EP_CUDA(h, ep_alloc(&ep->own_w, T * N));
+  EP_CUDA(h, ep_alloc(&ep->s_block_counts, (size_t)ep->s_blocks_cap * N));
+  EP_CUDA(h, ep_alloc(&ep->s_offsets, (size_t)N + 1));
+  EP_CUDA(h, ep_alloc(&ep->s_sorted_row, (size_t)ep->send_cap));
+  EP_CUDA(h, ep_alloc(&ep->s_sorted_w, (size_t)ep->send_cap));
+  EP_CUDA(h, ep_alloc(&ep->s_row_of, T * N));
+  EP_CUDA(h, ep_alloc(&ep->s_mtile, (size_t)3 * ep->s_mtiles_cap + 1));
+  EP_CUDA(h, ep_alloc(&ep->send_rows, (size_t)ep->send_cap * H));
+  EP_CUDA(h, ep_alloc(&ep->send_e, (size_t)ep->send_cap * K));
+  EP_CUDA(h, ep_alloc(&ep->send_w, (size_t)ep->send_cap * K));
+  EP_CUDA(h, ep_alloc(&ep->ret_rows, (size_t)ep->send_cap * H));
+  EP_CUDA(h, ep_alloc(&ep->recv_rows, (size_t)h->rows_cap * H));
+  EP_CUDA(h, ep_alloc(&ep->recv_e, (size_t)h->rows_cap * K));
+  EP_CUDA(h, ep_alloc(&ep->recv_w, (size_t)h->rows_cap * K));
+  EP_CUDA(h, ep_alloc(&ep->out_rows, (size_t)h->rows_cap * H));
+  EP_CUDA(h, ep_alloc(&ep->counts_dev, (size_t)N * N));
+  EP_CUDA(h, cudaMemset(ep->counts_dev, 0, sizeof(int) * N * N));
+  EP_CUDA(h, cudaMemset(ep->s_offsets, 0, sizeof(int) * (N + 1)));
+  EP_CUDA(h, cudaMallocHost(reinterpret_cast<void **>(&ep->counts_host), sizeof(int) * N * N));
+  ncclUniqueId id;
+  memcpy(&id, id128, sizeof(id));
+  EP_NCCL(h, g_nccl.CommInitRank(&ep->comm, N, id, ep->rank));
+  return GPTOSS_OK;
 }

@@ -312,6 +312,46 @@ cudaError_t launch_reduce_rows(gptoss_moe *h, bf16 *out_rows, int R, cudaStream_
   return cudaGetLastError();
 }
 
+// The same kernels on caller-named buffers: expert parallelism sorts a rank's
+// tokens by OWNER with them (one "expert" per peer rank) before dispatch.
+cudaError_t launch_perm_plan(const PermPlan &p, int *status, cudaStream_t stream,
+                             long long *launches) {
+  if (p.R <= 0) {
+    cudaError_t e = cudaMemsetAsync(p.expert_offsets, 0, sizeof(int) * (p.El + 1), stream);
+    if (e != cudaSuccess) return e;
+    return cudaMemsetAsync(p.num_mtiles, 0, sizeof(int), stream);
+  }
+  const int nblocks = (p.R + kPermTokens - 1) / kPermTokens;
+  if (nblocks > p.blocks_cap) return cudaErrorInvalidValue;
+  perm_count_kernel<<<nblocks, 256, p.El * sizeof(int), stream>>>(p.slot_expert, p.R, p.K, p.El,
+                                                                   p.block_counts, status);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  const size_t smem = (static_cast<size_t>(3 + kScanThreads / 32) * p.El + 1) * sizeof(int);
+  perm_scan_scatter_kernel<<<nblocks, kScanThreads, smem, stream>>>(
+      p.slot_expert, p.slot_weight, p.R, p.K, p.El, p.block_counts, nblocks, p.expert_offsets,
+      p.sorted_row, p.sorted_weight, p.row_of, p.mtile_expert, p.mtile_row0, p.mtile_rows,
+      p.num_mtiles, p.mtiles_cap, p.assign_cap, status);
+  if (launches) *launches += 2;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_combine_rows(bool residual, bf16 *out, const bf16 *ys, const int *row_of, int R,
+                                int K, int H, int assign_cap, int *status, cudaStream_t stream,
+                                long long *launches) {
+  if (R <= 0) return cudaSuccess;
+  const int warps = 8;
+  const int grid = (R + warps - 1) / warps;
+  if (residual)
+    combine_rows_kernel<true><<<grid, warps * 32, 0, stream>>>(out, ys, row_of, R, K, H,
+                                                               assign_cap, status);
+  else
+    combine_rows_kernel<false><<<grid, warps * 32, 0, stream>>>(out, ys, row_of, R, K, H,
+                                                                assign_cap, status);
+  if (launches) ++*launches;
+  return cudaGetLastError();
+}
+
 }  // namespace gptoss
 
 // ---------------------------------------------------------------------------
