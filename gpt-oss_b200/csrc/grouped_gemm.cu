@@ -10,13 +10,15 @@
 // mlp2_120b_kernel of the reference (getp-csrc/matmul/matmul.cpp:1023-1465,
 // :1470-1914) including their fused epilogues (:1384-1430, :1842-1873).
 //
-// One persistent CTA per SM, 6 warps:
+// One persistent CTA per SM, 10 warps (the epilogue needs 8 of them: with 4 it,
+// not the main loop, set the time per tile):
 //   warp 0      TMA producer: A tile [128 rows, 64 k] and B tile [BN rows, 64 k]
 //               per stage, 128-byte swizzle, 4-stage mbarrier ring
 //   warp 1      allocates TMEM and issues tcgen05.mma (M=128, N=BN, K=16, bf16 ->
 //               fp32) from one thread; two accumulators of 256 TMEM columns so the
 //               epilogue of a tile overlaps the main loop of the next one
-//   warps 2-5   epilogue: tcgen05.ld of the warp's 32 TMEM lanes (= 32 rows),
+//   warps 2-9   epilogue, two warps per TMEM lane quarter, each taking half of the
+//               tile's columns: tcgen05.ld of the warp's 32 TMEM lanes (= 32 rows),
 //               bias + SwiGLU (gate and up are adjacent accumulator columns, held
 //               by one thread) or bias * routing weight, bf16, 16-byte stores
 // Tile order: tile id = m_tile * n_tiles + n_tile, so the CTAs of one wave share
@@ -29,10 +31,11 @@
 
 #include "common.cuh"
 #include "engine.h"
+#include "gemm_epilogue.cuh"
 
 namespace gptoss {
 
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;  // producer warp, MMA warp, 8 epilogue warps
 constexpr int kStages = 4;
 constexpr int kAccCols = 256;         // TMEM columns reserved per accumulator
 constexpr int kTmemCols = 512;
@@ -44,98 +47,6 @@ constexpr int kABytes = kTileM * kTileK * 2;  // 16 KB
 constexpr int kBN = 240;
 
 int gemm_tile_n(int) { return kBN; }
-
-enum { kEpiSwiglu = 0, kEpiDown = 1 };
-
-// gate * sigmoid(alpha * gate) * (up + 1) with the reference CPU path's clamps
-// (run.cpp:711-724): gate from above only, up on both sides.
-__device__ __forceinline__ float swiglu_act(float g, float u, float limit) {
-  g = fminf(g, limit);
-  u = fminf(fmaxf(u, -limit), limit);
-  const float s = __fdividef(1.0f, 1.0f + __expf(-1.702f * g));
-  return g * s * (u + 1.0f);
-}
-
-struct GemmArgs {
-  const float *bias;        // [El, n_cols]
-  bf16 *out;                // hact [*, out_ld] or ys [*, out_ld]
-  const float *row_weight;  // down only: routing weight per sorted row
-  const int *mtile_expert, *mtile_row0, *mtile_rows, *num_mtiles;
-  int k_dim;    // contraction length
-  int n_cols;   // weight rows per expert
-  int out_ld;   // leading dimension of out
-  float limit;
-  int *status;
-  int skip_epilogue;  // measurement aid: release the accumulator without reading it
-};
-
-// bias add for 8 accumulator columns n .. n+7 of expert row `bias`
-__device__ __forceinline__ void add_bias8(const uint32_t *r, const float *bias, int n, float *v) {
-  const float4 b0 = __ldg(reinterpret_cast<const float4 *>(bias + n));
-  const float4 b1 = __ldg(reinterpret_cast<const float4 *>(bias + n + 4));
-  v[0] = __uint_as_float(r[0]) + b0.x;
-  v[1] = __uint_as_float(r[1]) + b0.y;
-  v[2] = __uint_as_float(r[2]) + b0.z;
-  v[3] = __uint_as_float(r[3]) + b0.w;
-  v[4] = __uint_as_float(r[4]) + b1.x;
-  v[5] = __uint_as_float(r[5]) + b1.y;
-  v[6] = __uint_as_float(r[6]) + b1.z;
-  v[7] = __uint_as_float(r[7]) + b1.w;
-}
-
-// One row's NC (16 or 32) fp32 accumulators, columns n0 .. n0+NC-1 of expert e:
-// bias, activation or routing weight, bf16, 16-byte stores.
-template <int EPI, int NC>
-__device__ __forceinline__ void epilogue_chunk(const uint32_t *r, int n0, int e, int grow,
-                                               bool row_ok, float wrow, const GemmArgs &g) {
-  const float *bias = g.bias + static_cast<size_t>(e) * g.n_cols;
-#pragma unroll
-  for (int q = 0; q < NC / 16; q++) {  // 16 accumulator columns per step
-    const int n = n0 + q * 16;
-    const int valid = g.n_cols - n;  // columns of this step that exist (multiple of 8)
-    if (valid <= 0) break;
-    float v[16];
-    add_bias8(r + q * 16, bias, n, v);
-    if (valid >= 16) {
-      add_bias8(r + q * 16 + 8, bias, n + 8, v + 8);
-    } else {
-#pragma unroll
-      for (int i = 8; i < 16; i++) v[i] = 0.f;
-    }
-    if (EPI == kEpiSwiglu) {
-      // 16 columns = 8 (gate, up) pairs -> 8 activations -> one 16-byte store
-      uint4 o;
-      o.x = pack_bf16(swiglu_act(v[0], v[1], g.limit), swiglu_act(v[2], v[3], g.limit));
-      o.y = pack_bf16(swiglu_act(v[4], v[5], g.limit), swiglu_act(v[6], v[7], g.limit));
-      o.z = pack_bf16(swiglu_act(v[8], v[9], g.limit), swiglu_act(v[10], v[11], g.limit));
-      o.w = pack_bf16(swiglu_act(v[12], v[13], g.limit), swiglu_act(v[14], v[15], g.limit));
-      if (row_ok) {
-        bf16 *dst = g.out + static_cast<size_t>(grow) * g.out_ld + (n >> 1);
-        if (valid >= 16)
-          *reinterpret_cast<uint4 *>(dst) = o;
-        else
-          *reinterpret_cast<uint2 *>(dst) = make_uint2(o.x, o.y);
-      }
-    } else {
-      if (row_ok) {
-        bf16 *dst = g.out + static_cast<size_t>(grow) * g.out_ld + n;
-        uint4 o;
-        o.x = pack_bf16(v[0] * wrow, v[1] * wrow);
-        o.y = pack_bf16(v[2] * wrow, v[3] * wrow);
-        o.z = pack_bf16(v[4] * wrow, v[5] * wrow);
-        o.w = pack_bf16(v[6] * wrow, v[7] * wrow);
-        *reinterpret_cast<uint4 *>(dst) = o;
-        if (valid >= 16) {
-          o.x = pack_bf16(v[8] * wrow, v[9] * wrow);
-          o.y = pack_bf16(v[10] * wrow, v[11] * wrow);
-          o.z = pack_bf16(v[12] * wrow, v[13] * wrow);
-          o.w = pack_bf16(v[14] * wrow, v[15] * wrow);
-          *reinterpret_cast<uint4 *>(dst + 8) = o;
-        }
-      }
-    }
-  }
-}
 
 template <int BN, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -155,6 +66,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint64_t *tempty_bar = tfull_bar + 2;        // [2]
   uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(tempty_bar + 2);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
+  // per-epilogue-warp staging tiles behind the barriers (256 bytes reserved)
+  unsigned char *epi_stage = smem + kStages * kStageBytes + 256;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -165,7 +78,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int a = 0; a < 2; a++) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 4);
+      mbar_init(&tempty_bar[a], kGemmThreads / 32 - 2);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -190,10 +103,23 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      // the schedule entry of the next tile is fetched while this tile's loads are
+      // issued, so the ring does not drain at a tile boundary
+      int e_next = 0, row0_next = 0;
+      if (static_cast<int>(blockIdx.x) < total_tiles) {
+        e_next = g.mtile_expert[blockIdx.x / n_tiles];
+        row0_next = g.mtile_row0[blockIdx.x / n_tiles];
+      }
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
         const int mt = tile / n_tiles, nt = tile - mt * n_tiles;
-        const int e = g.mtile_expert[mt];
-        const int row0 = g.mtile_row0[mt];
+        const int e = e_next;
+        const int row0 = row0_next;
+        const int tile2 = tile + gridDim.x;
+        if (tile2 < total_tiles) {
+          e_next = g.mtile_expert[tile2 / n_tiles];
+          row0_next = g.mtile_row0[tile2 / n_tiles];
+        }
+        (void)mt;
         const int brow = e * g.n_cols + nt * BN;
         for (int kb = 0; kb < kb_count; kb++) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
@@ -260,6 +186,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else {
     const int q = warp & 3;  // TMEM lanes [32q, 32q+32) are the ones this warp may read
+    const int half = (warp - 2) >> 2;  // which half of the tile's columns
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
@@ -268,10 +195,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int row0 = g.mtile_row0[mt];
       const int rows = g.mtile_rows[mt];
       const int row = q * 32 + lane;
-      const bool row_ok = row < rows;
-      const int grow = row0 + row;
       float wrow = 0.f;
-      if (EPI == kEpiDown && row_ok) wrow = g.row_weight[grow];
+      if (EPI == kEpiDown && row < rows) wrow = g.row_weight[row0 + row];
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) {
         set_status(g.status, kStatusWaitTimeoutEpilogue);
         *abort_flag = 1;
@@ -279,36 +204,16 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kAccCols;
-      if (!g.skip_epilogue) {
-        // TMEM -> registers through two register buffers: the load of the next 32
-        // columns is in flight while the current 32 are processed
-        constexpr int kFull = BN / 32;
-        constexpr bool kTail = (BN % 32) != 0;  // 16 more columns
-        uint32_t ra[32], rb[32];
-        tmem_ld32(taddr, ra);
-        tmem_ld_wait32(ra);
-#pragma unroll
-        for (int c = 0; c < kFull; c += 2) {
-          if (c + 1 < kFull) {
-            tmem_ld32(taddr + (c + 1) * 32, rb);
-          } else if (kTail) {
-            tmem_ld16(taddr + kFull * 32, *reinterpret_cast<uint32_t(*)[16]>(rb));
-          }
-          epilogue_chunk<EPI, 32>(ra, nt * BN + c * 32, e, grow, row_ok, wrow, g);
-          if (c + 1 < kFull || kTail) tmem_ld_wait32(rb);
-          if (c + 1 < kFull) {
-            if (c + 2 < kFull) {
-              tmem_ld32(taddr + (c + 2) * 32, ra);
-            } else if (kTail) {
-              tmem_ld16(taddr + kFull * 32, *reinterpret_cast<uint32_t(*)[16]>(ra));
-            }
-            epilogue_chunk<EPI, 32>(rb, nt * BN + (c + 1) * 32, e, grow, row_ok, wrow, g);
-            if (c + 2 < kFull || kTail) tmem_ld_wait32(ra);
-          }
-        }
-        if (kTail)
-          epilogue_chunk<EPI, 16>((kFull & 1) ? rb : ra, nt * BN + kFull * 32, e, grow, row_ok,
-                                  wrow, g);
+      if (!(g.skip_epilogue & 1)) {
+        // two warps share a lane quarter and split the tile's columns
+        constexpr int kSplit = ((BN / 16 + 1) / 2) * 16;
+        unsigned char *stage = epi_stage + (warp - 2) * kEpiStageBytes;
+        if (half == 0)
+          epilogue_cols<EPI, kSplit>(taddr, nt * BN, e, row0 + q * 32, rows - q * 32, lane, wrow,
+                                     g, stage);
+        else
+          epilogue_cols<EPI, BN - kSplit>(taddr + kSplit, nt * BN + kSplit, e, row0 + q * 32,
+                                          rows - q * 32, lane, wrow, g, stage);
       }
       tc_fence_before();
       __syncwarp();
@@ -458,7 +363,9 @@ template <int EPI>
 static cudaError_t launch_tc(gptoss_moe *h, const CUtensorMap &ta, const CUtensorMap &tb,
                              const GemmArgs &g, cudaStream_t stream) {
   constexpr int kStageBytes = kABytes + kBN * kTileK * 2;
-  const size_t smem = 1024 + kStages * kStageBytes + 256;
+  // alignment slack + operand ring + barriers + one staging tile per epilogue warp
+  const size_t smem =
+      1024 + kStages * kStageBytes + 256 + (kGemmThreads / 32 - 2) * kEpiStageBytes;
   // per device, cheap: set on every launch so every GPU a process drives has it
   cudaError_t e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<kBN, EPI>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -492,7 +492,7 @@ int gptoss_moe_set_option(gptoss_moe_t *h, const char *name, int value) {
   } else if (!strcmp(name, "exact_ties")) {
     h->opt_exact_ties = value != 0;
   } else if (!strcmp(name, "skip_epilogue")) {
-    h->opt_skip_epilogue = value != 0;
+    h->opt_skip_epilogue = value;
   } else if (!strcmp(name, "time_stages")) {
     // value 1 starts a fresh series of measurements (event pairs are reused)
     h->opt_time_stages = value != 0;

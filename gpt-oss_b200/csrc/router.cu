@@ -8,7 +8,7 @@
 //
 // Layout: a CTA owns 32 consecutive tokens.  8 warps = 2 token groups of 16 x 4
 // expert slices; bf16 tensor-core MMAs (m16n8k16, fp32 accumulate) over K chunks
-// of 64 that are staged in shared memory with a 3-deep cp.async pipeline.  The
+// of 64 that are staged in shared memory with a 3- to 6-deep cp.async pipeline.  The
 // fp32 logits of the 32 tokens then sit in shared memory and one warp per token
 // does the selection in registers.
 //
@@ -24,7 +24,9 @@ namespace gptoss {
 
 constexpr int kRtTokens = 32;      // tokens per CTA
 constexpr int kRtKC = 64;          // K elements per pipeline stage
-constexpr int kRtStages = 3;
+// cp.async ring depth per expert-tile count: enough bytes in flight per SM to
+// cover HBM latency while two CTAs still fit one SM where possible
+template <int NT> struct RtStages { static constexpr int value = NT <= 2 ? 6 : (NT == 4 ? 4 : 3); };
 constexpr int kRtRowBytes = 144;   // 128 B of data + 16 B pad: conflict-free ldmatrix
 constexpr int kRtThreads = 256;
 constexpr float kTieGuard = 1e-3f;
@@ -91,6 +93,7 @@ router_topk_kernel(const bf16 *__restrict__ t, const bf16 *__restrict__ w_router
                    int E, int K, int *__restrict__ topk_i, float *__restrict__ topk_v,
                    float *__restrict__ logits_out, int exact_ties) {
   constexpr int EPAD = 32 * NT;
+  constexpr int kRtStages = RtStages<NT>::value;
   constexpr int kStageBytes = (kRtTokens + EPAD) * kRtRowBytes;
   extern __shared__ __align__(128) unsigned char smem[];
   float *lg = reinterpret_cast<float *>(smem + kRtStages * kStageBytes);  // [32][EPAD]
@@ -299,6 +302,7 @@ static cudaError_t launch_router_nt(const bf16 *t, const bf16 *w_router, const f
                                     float *topk_v, float *logits_opt, int exact_ties,
                                     cudaStream_t stream) {
   constexpr int EPAD = 32 * NT;
+  constexpr int kRtStages = RtStages<NT>::value;
   const size_t smem =
       static_cast<size_t>(kRtStages) * (kRtTokens + EPAD) * kRtRowBytes + kRtTokens * EPAD * 4;
   cudaError_t e = cudaFuncSetAttribute(router_topk_kernel<NT>,
