@@ -188,6 +188,71 @@ def run_reference_arm(args, shape):
     print(json.dumps(line), flush=True)
 
 
+def measure_c3_layer(args, pkg, dev, rank, world, local_rank, barrier):
+    """The 120b-shape layer (T=6144 tokens per GPU, 128 experts) beside the headline
+    workload: all experts local at N=1, expert parallel (owner = e % N, NCCL dispatch
+    and return) at N>1.  Weak scaling: every rank brings its own 6144 tokens."""
+    import torch
+    import torch.distributed as dist
+
+    shape = workload_shape("c3")
+    T, H, IM, E, K = (shape.n_tokens, shape.hidden_dim, shape.intermediate_dim, shape.n_experts,
+                      shape.experts_per_token)
+    eng = pkg.MoeEngine(H, IM, E, K, n_layers=1, max_tokens=T, swiglu_limit=shape.swiglu_limit,
+                        ep_rank=rank, ep_size=world, device=local_rank)
+    w = device_weights(shape, dev)  # same seed on every rank: one set of weights, sharded
+    eng.load_layer_bf16(0, w["w_router"], w["b_router"], w["w_mlp1"], w["b_mlp1"], w["w_mlp2"],
+                        w["b_mlp2"], on_device=True)
+    del w
+    torch.cuda.empty_cache()
+    if os.environ.get("GPTOSS_GEMM_IMPL"):
+        eng.set_option("gemm_impl", int(os.environ["GPTOSS_GEMM_IMPL"]))
+    if world > 1:
+        uid = torch.zeros(128, dtype=torch.uint8, device=dev)
+        if rank == 0:
+            uid.copy_(torch.frombuffer(bytearray(pkg.MoeEngine.ep_unique_id()), dtype=torch.uint8))
+        dist.broadcast(uid, 0)
+        eng.ep_init(bytes(uid.cpu().numpy().tobytes()))
+    g = torch.Generator(device=dev)
+    g.manual_seed(shape.seed + 2000 + rank)
+    t = torch.randn((T, H), generator=g, device=dev).bfloat16()
+    x = torch.randn((T, H), generator=g, device=dev).bfloat16()
+    stream = torch.cuda.current_stream().cuda_stream
+    steps = max(3, min(args.steps, 30))
+    for _ in range(3):
+        eng.forward(0, t, x, None, T, stream)
+    barrier()
+    if eng.device_status() != 0:
+        raise SystemExit("device status non-zero in the 120b-shape layer")
+    eng.set_option("time_stages", 1)
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(steps):
+        eng.forward(0, t, x, None, T, stream)
+    ev1.record()
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        tt = torch.tensor([ms], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms = float(tt.item())
+    names = ["route", "permute", "gate_up", "down", "combine"]
+    if world > 1:
+        names += ["dispatch", "return"]
+    stage_ms = {s: eng.stage_ms(s) for s in names}
+    eng.close()
+    return {
+        "workload": shape.name, "tokens_per_gpu": T, "experts": E,
+        "parallelism": "all experts local" if world == 1 else f"expert parallel x{world} (NCCL)",
+        "value": world * T * steps / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms / steps,
+        "steps": steps, "stage_ms": stage_ms,
+        # rank 0's own gate_up launch; under expert parallelism its row count varies a
+        # little around T*K per rank
+        "gate_up_tflops": 2.0 * T * K * 2 * IM * H / (stage_ms["gate_up"] * 1e-3) / 1e12,
+    }
+
+
 def run_ours(args, shape):
     import torch
     import torch.distributed as dist
@@ -210,6 +275,10 @@ def run_ours(args, shape):
     w = device_weights(shape, dev)
     eng.load_layer_bf16(0, w["w_router"], w["b_router"], w["w_mlp1"], w["b_mlp1"], w["w_mlp2"],
                         w["b_mlp2"], on_device=True)
+    if os.environ.get("GPTOSS_GEMM_IMPL"):  # 0 = single-CTA tcgen05, 2 = CTA pairs
+        eng.set_option("gemm_impl", int(os.environ["GPTOSS_GEMM_IMPL"]))
+    if os.environ.get("GPTOSS_PAIR_STAGES"):  # tuning aid
+        eng.set_option("pair_stages", int(os.environ["GPTOSS_PAIR_STAGES"]))
     if os.environ.get("GPTOSS_SKIP_EPILOGUE"):  # measurement aid: main loop only
         eng.set_option("skip_epilogue", int(os.environ["GPTOSS_SKIP_EPILOGUE"]))
     g = torch.Generator(device=dev)
@@ -271,6 +340,10 @@ def run_ours(args, shape):
         e2e_s = float(tt.item())
     e2e_value = world * T * e2e_steps / e2e_s
 
+    extra = None
+    if not args.no_extra and args.workload == "c2":
+        extra = measure_c3_layer(args, pkg, dev, rank, world, local_rank, barrier)
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -283,7 +356,10 @@ def run_ours(args, shape):
     peak_kind = "bf16_tflops" if timed_s < 1.0 else "bf16_tflops_sustained"
     achieved = flops_gate_up / (stage_ms["gate_up"] * 1e-3) / 1e12
     roofline = {
-        "kernel": "grouped_gemm_tc_kernel<240, swiglu> (gate_up)", "bound": "tensor",
+        "kernel": ("grouped_gemm_tc_kernel<240, swiglu> (gate_up, single CTA)"
+                   if os.environ.get("GPTOSS_GEMM_IMPL") == "0"
+                   else "grouped_gemm_pair_kernel<swiglu, 6> (gate_up, CTA pairs)"),
+        "bound": "tensor",
         "achieved": achieved, "peak": peaks[peak_kind], "unit": "TFLOP/s",
         "frac": achieved / peaks[peak_kind], "peak_source": f"{peaks['source']} {peak_kind}",
         "traffic": None, "kernel_ms": stage_ms["gate_up"],
@@ -323,6 +399,9 @@ def run_ours(args, shape):
                 "d2h_bytes_per_step": T * H * 2, "steps": e2e_steps},
         "gpu_launches": launches, "clocks": clocks,
     }
+    if extra is not None:
+        extra["gate_up_frac_of_peak"] = extra["gate_up_tflops"] / peaks["bf16_tflops"]
+        line["layer_120b"] = extra
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -338,6 +417,8 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=None,
                     help="tokens in the CPU sample (default 256 for ours, 64 for reference)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="skip the 120b-shape layer measured beside the headline workload")
     args = ap.parse_args()
     entry.load_package()
     shape = workload_shape(args.workload)

@@ -30,6 +30,7 @@ WEIGHTS_BF16 = 0
 WEIGHTS_MXFP4 = 1
 GEMM_TCGEN05 = 0
 GEMM_SIMT = 1
+GEMM_PAIR = 2
 
 STAGES = ("route", "permute", "gate_up", "down", "combine", "dispatch", "return")
 

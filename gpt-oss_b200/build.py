@@ -14,8 +14,9 @@ PKG_DIR = pathlib.Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB = PKG_DIR / "libgptoss_moe_b200.so"
 
-CU_SOURCES = ["moe_api.cu", "router.cu", "permute.cu", "grouped_gemm.cu", "weights.cu", "ep.cu"]
-HEADERS = ["common.cuh", "engine.h", "ep.h", "gemm_epilogue.cuh"]
+CU_SOURCES = ["moe_api.cu", "router.cu", "permute.cu", "grouped_gemm.cu", "grouped_gemm_pair.cu",
+              "weights.cu", "ep.cu"]
+HEADERS = ["common.cuh", "engine.h", "ep.h", "gemm_epilogue.cuh", "umma_2sm.cuh"]
 
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",

@@ -31,7 +31,8 @@ struct LayerWeights {
   float *b2 = nullptr;        // [E_local, H]
   uint8_t *w1_blocks = nullptr, *w1_scales = nullptr;  // MXFP4 storage
   uint8_t *w2_blocks = nullptr, *w2_scales = nullptr;
-  CUtensorMap tmap_w1, tmap_w2;
+  CUtensorMap tmap_w1, tmap_w2;            // boxes of 240 weight rows (N operand)
+  CUtensorMap tmap_w1_rows, tmap_w2_rows;  // boxes of 128 weight rows (M operand, CTA pairs)
   bool loaded = false;
 };
 
@@ -90,11 +91,12 @@ struct gptoss_moe {
   int *pos_dev = nullptr;
 
   int *status = nullptr;  // device status word
-  int opt_gemm_impl = GPTOSS_GEMM_TCGEN05;
+  int opt_gemm_impl = GPTOSS_GEMM_PAIR;
   int opt_keep_logits = 0;
   int opt_exact_ties = 1;
   int opt_time_stages = 0;
   int opt_skip_epilogue = 0;
+  int opt_pair_stages = 6;  // operand ring depth of the CTA-pair GEMM (4, 5 or 6)
   gptoss::StageTimer timers[8];
   long long launches = 0;
   mutable std::string err;
@@ -145,6 +147,9 @@ cudaError_t launch_down(gptoss_moe *h, int layer, cudaStream_t stream);
 int make_tmap_2d_bf16(CUtensorMap *map, const void *base, uint64_t inner, uint64_t outer,
                       uint32_t box_inner, uint32_t box_outer, std::string *err);
 int gemm_tile_n(int which);  // N extent of one tile: 0 = gate_up, 1 = down
+// grouped_gemm_pair.cu
+cudaError_t launch_gate_up_pair(gptoss_moe *h, int layer, cudaStream_t stream);
+cudaError_t launch_down_pair(gptoss_moe *h, int layer, cudaStream_t stream);
 
 // moe_api.cu: error text for entry points that take no handle (read back with
 // gptoss_moe_last_error(NULL)); returns `code`

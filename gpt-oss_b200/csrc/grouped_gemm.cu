@@ -376,6 +376,7 @@ static cudaError_t launch_tc(gptoss_moe *h, const CUtensorMap &ta, const CUtenso
 }
 
 cudaError_t launch_gate_up(gptoss_moe *h, int layer, cudaStream_t stream) {
+  if (h->opt_gemm_impl == GPTOSS_GEMM_PAIR) return launch_gate_up_pair(h, layer, stream);
   LayerWeights &lw = h->layers[layer];
   GemmArgs g;
   g.bias = lw.b1;
@@ -401,6 +402,7 @@ cudaError_t launch_gate_up(gptoss_moe *h, int layer, cudaStream_t stream) {
 }
 
 cudaError_t launch_down(gptoss_moe *h, int layer, cudaStream_t stream) {
+  if (h->opt_gemm_impl == GPTOSS_GEMM_PAIR) return launch_down_pair(h, layer, stream);
   LayerWeights &lw = h->layers[layer];
   GemmArgs g;
   g.bias = lw.b2;

@@ -1,0 +1,382 @@
+// Grouped expert GEMMs on CTA pairs (tcgen05 cta_group::2), weights as the M
+// operand.
+//
+// Same math and same outputs as grouped_gemm.cu, computed transposed:
+//   D^T[n, j] = sum_k W[e][n, k] * X[tok0 + j, k]
+// A pair of CTAs (one cluster of 2, the two SMs of a TPC) owns 256 weight rows of
+// one expert (128 per CTA, the MMA's M) and a tile of up to 256 of that expert's
+// tokens (the MMA's N, any multiple of 16).  Each CTA loads its own 128 weight
+// rows and its own half of the token tile - 32 KB per 64-deep K block instead of
+// the 46 KB of the single-CTA kernel - and the even CTA issues one
+// tcgen05.mma.cta_group::2 (M=256, N=tokens) that reads both CTAs' shared memory
+// and writes 128 accumulator rows into each CTA's TMEM.  What this buys:
+//   * a third less L2->SM and shared-memory traffic per flop (the single-CTA
+//     kernel is bound by it, not by the tensor pipe);
+//   * no ragged-M waste: the last token tile of an expert is as narrow as the
+//     expert's rows need (rounded up to 16), so 192 rows per expert (120b shape)
+//     or a handful (decode shapes) cost their own N, not a 128-row tile;
+//   * each expert's weights are the streamed operand, read once per token tile.
+// No TMA load uses multicast: the halves of the shared operand are loaded by the
+// CTA that holds them.
+//
+// Warp roles per CTA (320 threads): warp 0 lane 0 = TMA producer (both CTAs; the
+// odd CTA's loads complete on the even CTA's full barrier), warp 1 lane 0 of the
+// even CTA = MMA issuer, warp 1 = paired TMEM allocation, warps 2-9 = epilogue.
+// tcgen05.commit with a 2-CTA mask releases the stage / publishes the accumulator
+// in both CTAs; the odd CTA's epilogue warps release the accumulator with a
+// remote mbarrier arrive.
+//
+// Epilogue (transposed): a TMEM lane is an output feature, a column a token.  A
+// warp reads 32 lanes x 32 tokens, adds the lane's bias, pairs gate/up rows
+// (adjacent lanes) by shuffle or applies the token's routing weight, and writes
+// bf16 into a [32 tokens][row] shared tile shared by the 4 warps that cover the
+// CTA's 128 rows; the tile is then written to global memory row-wise (whole
+// 128- / 256-byte segments per token) with streaming stores.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "engine.h"
+#include "gemm_epilogue.cuh"
+#include "umma_2sm.cuh"
+
+namespace gptoss {
+
+constexpr int kPairThreads = 320;
+constexpr int kPairOperandBytes = 128 * kTileK * 2;          // 16 KB: 128 rows x 64 k
+constexpr int kPairStageBytes = 2 * kPairOperandBytes;       // weights + token half
+constexpr int kPairEpiWarps = kPairThreads / 32 - 2;
+constexpr int kAccColsPair = 256;  // TMEM columns per accumulator (up to 256 tokens), two of them
+
+template <int EPI>
+struct PairStage {
+  static constexpr int kRowBytes = (EPI == kEpiSwiglu) ? 128 : 256;  // per token, per CTA
+  // 16 bytes of padding keep the 2-byte writes of the SwiGLU epilogue off each
+  // other's banks; the 256-byte rows of the down epilogue go unpadded so that six
+  // operand stages still fit
+  static constexpr int kPitch = (EPI == kEpiSwiglu) ? kRowBytes + 16 : kRowBytes;
+  static constexpr int kTileBytes = 32 * kPitch;
+  static constexpr int kTotalBytes = 2 /*halves*/ * 2 /*buffers*/ * kTileBytes;
+};
+
+template <int EPI, int kPairStages>
+__global__ void __launch_bounds__(kPairThreads, 1)
+grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
+                         const __grid_constant__ CUtensorMap tmap_x, const GemmArgs g) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  unsigned char *smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
+  uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + kPairStages * kPairStageBytes);
+  uint64_t *empty_bar = full_bar + kPairStages;
+  uint64_t *tfull_bar = empty_bar + kPairStages;  // [2]
+  uint64_t *tempty_bar = tfull_bar + 2;           // [2], used in the even CTA
+  uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(tempty_bar + 2);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
+  unsigned char *epi_stage = smem + kPairStages * kPairStageBytes + 256;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; s++) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; a++) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 2 * kPairEpiWarps);  // epilogue warps of both CTAs
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_x);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_holder, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_barrier_all();  // the peer's barriers exist before anything targets them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  const int w_pairs = (g.n_cols + 255) / 256;
+  const int total_tiles = *g.num_mtiles * w_pairs;
+  const int kb_count = (g.k_dim + kTileK - 1) / kTileK;
+  const int cl = blockIdx.x >> 1, ncl = gridDim.x >> 1;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int e_next = 0, tok0_next = 0, ntok_next = 0;
+      if (cl < total_tiles) {
+        const int tt = cl / w_pairs;
+        e_next = g.mtile_expert[tt];
+        tok0_next = g.mtile_row0[tt];
+        ntok_next = g.mtile_rows[tt];
+      }
+      for (int tile = cl; ok && tile < total_tiles; tile += ncl) {
+        const int tt = tile / w_pairs, wp = tile - tt * w_pairs;
+        const int e = e_next, tok0 = tok0_next, ntok = ntok_next;
+        const int tile2 = tile + ncl;
+        if (tile2 < total_tiles) {
+          const int tt2 = tile2 / w_pairs;
+          e_next = g.mtile_expert[tt2];
+          tok0_next = g.mtile_row0[tt2];
+          ntok_next = g.mtile_rows[tt2];
+        }
+        const int half_n = ((ntok + 15) & ~15) >> 1;  // token rows each CTA contributes
+        const int wrow = e * g.n_cols + wp * 256 + static_cast<int>(rank) * 128;
+        const int trow = tok0 + static_cast<int>(rank) * half_n;
+        for (int kb = 0; kb < kb_count; kb++) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+            set_status(g.status, kStatusWaitTimeoutProducer);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          unsigned char *sa = smem + stage * kPairStageBytes;
+          if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * kPairStageBytes);
+          tma_load_2d_pair(sa, &tmap_w, &full_bar[stage], kb * kTileK, wrow);
+          tma_load_2d_pair(sa + kPairOperandBytes, &tmap_x, &full_bar[stage], kb * kTileK, trow);
+          if (++stage == kPairStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = cl; ok && tile < total_tiles; tile += ncl) {
+        const int ntok = g.mtile_rows[tile / w_pairs];
+        const uint32_t idesc = umma_idesc_bf16(256, (ntok + 15) & ~15);
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_flag)) {
+          set_status(g.status, kStatusWaitTimeoutMma);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kAccColsPair;
+        for (int kb = 0; kb < kb_count; kb++) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+            set_status(g.status, kStatusWaitTimeoutMma);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * kPairStageBytes);
+          const uint64_t da = umma_smem_desc_sw128(sa);
+          const uint64_t db = umma_smem_desc_sw128(sa + kPairOperandBytes);
+#pragma unroll
+          for (int k = 0; k < kTileK / 16; k++)
+            umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit_pair(&empty_bar[stage], 3);  // frees the stage in both CTAs
+          if (++stage == kPairStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit_pair(&tfull_bar[acc], 3);  // accumulator ready in both CTAs
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    using ST = PairStage<EPI>;
+    const int q = warp & 3;            // TMEM lanes [32q, 32q+32)
+    const int half = (warp - 2) >> 2;  // token chunks c with (c & 1) == half
+    const int tg = ((warp - 2) & 3) * 32 + lane;  // thread index among the half's 4 warps
+    const bool odd = (lane & 1) != 0;
+    int acc = 0, buf = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = cl; tile < total_tiles; tile += ncl) {
+      const int tt = tile / w_pairs, wp = tile - tt * w_pairs;
+      const int e = g.mtile_expert[tt];
+      const int tok0 = g.mtile_row0[tt];
+      const int ntok = g.mtile_rows[tt];
+      const int n_cta = wp * 256 + static_cast<int>(rank) * 128;  // first weight row of this CTA
+      const int n_lane = n_cta + q * 32 + lane;
+      const float bias_v =
+          n_lane < g.n_cols ? __ldg(g.bias + static_cast<size_t>(e) * g.n_cols + n_lane) : 0.f;
+      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) {
+        set_status(g.status, kStatusWaitTimeoutEpilogue);
+        *abort_flag = 1;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t taddr =
+          tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kAccColsPair;
+      const int n_chunks = (ntok + 31) >> 5;
+      if (!(g.skip_epilogue & 1)) {
+        for (int c = half; c < n_chunks; c += 2) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c * 32, r);
+          tmem_ld_wait32(r);
+          unsigned char *tile_s = epi_stage + (half * 2 + buf) * ST::kTileBytes;
+          if (EPI == kEpiSwiglu) {
+            // lanes (2i, 2i+1) hold gate and up of feature i; each of the two takes
+            // every other token
+#pragma unroll
+            for (int m = 0; m < 16; m++) {
+              const float lo = __uint_as_float(r[2 * m]) + bias_v;
+              const float hi = __uint_as_float(r[2 * m + 1]) + bias_v;
+              const float own = odd ? hi : lo;
+              const float send = odd ? lo : hi;
+              const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+              const float a = swiglu_act(odd ? recv : own, odd ? own : recv, g.limit);
+              const int j = 2 * m + (odd ? 1 : 0);
+              *reinterpret_cast<bf16 *>(tile_s + j * ST::kPitch + q * 32 + (lane >> 1) * 2) =
+                  __float2bfloat16_rn(a);
+            }
+          } else {
+            const int jt = c * 32 + lane;
+            const float w_lane = jt < ntok ? g.row_weight[tok0 + jt] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+              r[j] = __float_as_uint((__uint_as_float(r[j]) + bias_v) *
+                                     __shfl_sync(0xffffffffu, w_lane, j));
+            // lanes (2i, 2i+1) hold columns (2i, 2i+1); each takes every other token
+            // and stores both columns as one 32-bit word
+#pragma unroll
+            for (int m = 0; m < 16; m++) {
+              const float own = __uint_as_float(odd ? r[2 * m + 1] : r[2 * m]);
+              const float send = __uint_as_float(odd ? r[2 * m] : r[2 * m + 1]);
+              const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+              const int j = 2 * m + (odd ? 1 : 0);
+              *reinterpret_cast<uint32_t *>(tile_s + j * ST::kPitch + q * 64 + (lane >> 1) * 4) =
+                  pack_bf16(odd ? recv : own, odd ? own : recv);
+            }
+          }
+          // make the tile visible to the bulk-copy engine; the first warp of the half
+          // also makes sure the copy that last read the other buffer is done before
+          // anyone passes the barrier and starts to refill it
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          if (tg < 32) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          named_barrier_sync(1 + half, 128);
+          // write out: one bulk copy per token row (a whole 128- / 256-byte segment)
+          const int col0 = (EPI == kEpiSwiglu) ? (n_cta >> 1) : n_cta;
+          if (tg < 32 && !(g.skip_epilogue & 2)) {
+            const int jt = c * 32 + tg;
+            int bytes = (g.out_ld - col0) * 2;
+            bytes = bytes < ST::kRowBytes ? bytes : ST::kRowBytes;
+            if (jt < ntok && bytes > 0) {
+              bf16 *dst = g.out + static_cast<size_t>(tok0 + jt) * g.out_ld + col0;
+              asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
+                           "r"(smem_u32(tile_s + tg * ST::kPitch)), "r"(bytes)
+                           : "memory");
+            }
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+          buf ^= 1;
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (rank == 0)
+          mbar_arrive(&tempty_bar[acc]);
+        else
+          mbar_arrive_cluster(&tempty_bar[acc], 0);
+      }
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+    // the staging tiles must outlive the bulk copies that read them
+    if (tg < 32) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  }
+
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 2000000ull) {
+    }
+  }
+  cluster_barrier_all();  // neither CTA frees TMEM while the pair may still use it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
+template <int EPI, int STAGES>
+static cudaError_t launch_pair_stages(gptoss_moe *h, const CUtensorMap &tw, const CUtensorMap &tx,
+                                      const GemmArgs &g, cudaStream_t stream) {
+  const size_t smem = 1024 + STAGES * kPairStageBytes + 256 + PairStage<EPI>::kTotalBytes;
+  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_pair_kernel<EPI, STAGES>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(h->num_sms & ~1));
+  cfg.blockDim = dim3(kPairThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  h->launches++;
+  return cudaLaunchKernelEx(&cfg, grouped_gemm_pair_kernel<EPI, STAGES>, tw, tx, g);
+}
+
+template <int EPI>
+static cudaError_t launch_pair(gptoss_moe *h, const CUtensorMap &tw, const CUtensorMap &tx,
+                               const GemmArgs &g, cudaStream_t stream) {
+  switch (h->opt_pair_stages) {
+    case 4: return launch_pair_stages<EPI, 4>(h, tw, tx, g, stream);
+    case 5: return launch_pair_stages<EPI, 5>(h, tw, tx, g, stream);
+    default: return launch_pair_stages<EPI, 6>(h, tw, tx, g, stream);
+  }
+}
+
+cudaError_t launch_gate_up_pair(gptoss_moe *h, int layer, cudaStream_t stream) {
+  LayerWeights &lw = h->layers[layer];
+  GemmArgs g;
+  g.bias = lw.b1;
+  g.out = h->hact;
+  g.row_weight = nullptr;
+  g.mtile_expert = h->mtile_expert;
+  g.mtile_row0 = h->mtile_row0;
+  g.mtile_rows = h->mtile_rows;
+  g.num_mtiles = h->num_mtiles;
+  g.k_dim = h->H;
+  g.n_cols = 2 * h->IM;
+  g.out_ld = h->IM;
+  g.limit = h->cfg.swiglu_limit;
+  g.status = h->status;
+  g.skip_epilogue = h->opt_skip_epilogue;
+  return launch_pair<kEpiSwiglu>(h, lw.tmap_w1_rows, h->tmap_xs, g, stream);
+}
+
+cudaError_t launch_down_pair(gptoss_moe *h, int layer, cudaStream_t stream) {
+  LayerWeights &lw = h->layers[layer];
+  GemmArgs g;
+  g.bias = lw.b2;
+  g.out = h->ys;
+  g.row_weight = h->sorted_weight;
+  g.mtile_expert = h->mtile_expert;
+  g.mtile_row0 = h->mtile_row0;
+  g.mtile_rows = h->mtile_rows;
+  g.num_mtiles = h->num_mtiles;
+  g.k_dim = h->IM;
+  g.n_cols = h->H;
+  g.out_ld = h->H;
+  g.limit = h->cfg.swiglu_limit;
+  g.status = h->status;
+  g.skip_epilogue = h->opt_skip_epilogue;
+  return launch_pair<kEpiDown>(h, lw.tmap_w2_rows, h->tmap_h, g, stream);
+}
+
+}  // namespace gptoss

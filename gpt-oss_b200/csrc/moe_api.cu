@@ -191,7 +191,11 @@ static int finish_layer(gptoss_moe *h, LayerWeights &lw) {
   const int bn = gemm_tile_n(0);
   if (make_tmap_2d_bf16(&lw.tmap_w1, lw.w1, h->H, (uint64_t)h->El * 2 * h->IM, kTileK, bn,
                         &terr) ||
-      make_tmap_2d_bf16(&lw.tmap_w2, lw.w2, h->IM, (uint64_t)h->El * h->H, kTileK, bn, &terr))
+      make_tmap_2d_bf16(&lw.tmap_w2, lw.w2, h->IM, (uint64_t)h->El * h->H, kTileK, bn, &terr) ||
+      make_tmap_2d_bf16(&lw.tmap_w1_rows, lw.w1, h->H, (uint64_t)h->El * 2 * h->IM, kTileK, 128,
+                        &terr) ||
+      make_tmap_2d_bf16(&lw.tmap_w2_rows, lw.w2, h->IM, (uint64_t)h->El * h->H, kTileK, 128,
+                        &terr))
     return fail(h, GPTOSS_E_CUDA, "%s", terr.c_str());
   lw.loaded = true;
   return GPTOSS_OK;
@@ -484,13 +488,16 @@ int gptoss_moe_get_activations(gptoss_moe_t *h, void *act_host, size_t bytes) {
 int gptoss_moe_set_option(gptoss_moe_t *h, const char *name, int value) {
   if (!h || !name) return GPTOSS_E_INVALID;
   if (!strcmp(name, "gemm_impl")) {
-    if (value != GPTOSS_GEMM_TCGEN05 && value != GPTOSS_GEMM_SIMT)
+    if (value != GPTOSS_GEMM_TCGEN05 && value != GPTOSS_GEMM_SIMT && value != GPTOSS_GEMM_PAIR)
       return fail(h, GPTOSS_E_INVALID, "unknown gemm_impl %d", value);
     h->opt_gemm_impl = value;
   } else if (!strcmp(name, "keep_logits")) {
     h->opt_keep_logits = value != 0;
   } else if (!strcmp(name, "exact_ties")) {
     h->opt_exact_ties = value != 0;
+  } else if (!strcmp(name, "pair_stages")) {
+    if (value < 4 || value > 6) return fail(h, GPTOSS_E_INVALID, "pair_stages must be 4, 5 or 6");
+    h->opt_pair_stages = value;
   } else if (!strcmp(name, "skip_epilogue")) {
     h->opt_skip_epilogue = value;
   } else if (!strcmp(name, "time_stages")) {

@@ -55,7 +55,7 @@ perm_scan_scatter_kernel(const int *__restrict__ slot_expert,
                          float *__restrict__ sorted_weight, int *__restrict__ row_of,
                          int *__restrict__ mtile_expert, int *__restrict__ mtile_row0,
                          int *__restrict__ mtile_rows, int *__restrict__ num_mtiles,
-                         int mtiles_cap, int assign_cap, int *status) {
+                         int mtiles_cap, int assign_cap, int *status, int tile_rows) {
   extern __shared__ int sm[];
   int *s_tot = sm;                 // [El] rows of each expert over all CTAs
   int *s_base = sm + El;           // [El] next free position for this CTA
@@ -110,7 +110,7 @@ perm_scan_scatter_kernel(const int *__restrict__ slot_expert,
       int local = 0;
       for (int j = 0; j < per; j++) {
         const int e = lane * per + j;
-        if (e < El) local += (s_tot[e] + kTileM - 1) / kTileM;
+        if (e < El) local += (s_tot[e] + tile_rows - 1) / tile_rows;
       }
       int incl = local;
 #pragma unroll
@@ -123,11 +123,16 @@ perm_scan_scatter_kernel(const int *__restrict__ slot_expert,
         const int e = lane * per + j;
         if (e < El) {
           const int rows = s_tot[e];
-          for (int i = 0; i * kTileM < rows; i++, mt++) {
+          // tiles of 128 rows are the MMA's fixed M; wider tiles are its N, which may be
+          // any multiple of 16: spread the expert's rows evenly over its tiles
+          const int cnt = (rows + tile_rows - 1) / tile_rows;
+          const int step =
+              (tile_rows == kTileM || cnt == 0) ? tile_rows : (((rows + cnt - 1) / cnt + 15) & ~15);
+          for (int i = 0; i * step < rows; i++, mt++) {
             if (mt < mtiles_cap) {
               mtile_expert[mt] = e;
-              mtile_row0[mt] = s_off[e] + i * kTileM;
-              mtile_rows[mt] = min(kTileM, rows - i * kTileM);
+              mtile_row0[mt] = s_off[e] + i * step;
+              mtile_rows[mt] = min(step, rows - i * step);
             } else {
               set_status(status, kStatusBadIndex);
             }
@@ -283,7 +288,8 @@ cudaError_t launch_permute(gptoss_moe *h, cudaStream_t stream) {
   perm_scan_scatter_kernel<<<nblocks, kScanThreads, smem, stream>>>(
       h->stage_expert, h->stage_weight, R, K, El, h->block_counts, nblocks, h->expert_offsets,
       h->sorted_row, h->sorted_weight, h->row_of, h->mtile_expert, h->mtile_row0, h->mtile_rows,
-      h->num_mtiles, h->mtiles_cap, h->assign_cap, h->status);
+      h->num_mtiles, h->mtiles_cap, h->assign_cap, h->status,
+      h->opt_gemm_impl == GPTOSS_GEMM_PAIR ? 256 : kTileM);
   h->launches++;
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
@@ -331,7 +337,7 @@ cudaError_t launch_perm_plan(const PermPlan &p, int *status, cudaStream_t stream
   perm_scan_scatter_kernel<<<nblocks, kScanThreads, smem, stream>>>(
       p.slot_expert, p.slot_weight, p.R, p.K, p.El, p.block_counts, nblocks, p.expert_offsets,
       p.sorted_row, p.sorted_weight, p.row_of, p.mtile_expert, p.mtile_row0, p.mtile_rows,
-      p.num_mtiles, p.mtiles_cap, p.assign_cap, status);
+      p.num_mtiles, p.mtiles_cap, p.assign_cap, status, kTileM);
   if (launches) *launches += 2;
   return cudaGetLastError();
 }
@@ -436,7 +442,7 @@ extern "C" int gptoss_moe_permute_static(const int *slot_expert, const float *sl
   perm_scan_scatter_kernel<<<nblocks, kScanThreads, smem, st>>>(
       slot_expert, slot_weight, n_rows, top_k, n_experts, block_counts, nblocks, expert_offsets,
       sorted_row, sorted_weight, row_of, mtile_expert, mtile_row0, mtile_rows, num_mtiles,
-      kStaticMtilesPad, n_rows * top_k, status);
+      kStaticMtilesPad, n_rows * top_k, status, kTileM);
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_global_error(GPTOSS_E_CUDA, cudaGetErrorString(e));
   return GPTOSS_OK;

@@ -41,7 +41,9 @@ enum { GPTOSS_WEIGHTS_BF16 = 0, GPTOSS_WEIGHTS_MXFP4 = 1 };
  * CUDA-core kernel kept only so tests can cross-check the tensor-core path on
  * the GPU at sizes the CPU oracle cannot reach.  It is never selected
  * automatically. */
-enum { GPTOSS_GEMM_TCGEN05 = 0, GPTOSS_GEMM_SIMT = 1 };
+enum { GPTOSS_GEMM_TCGEN05 = 0, GPTOSS_GEMM_SIMT = 1, GPTOSS_GEMM_PAIR = 2 };
+/* GPTOSS_GEMM_PAIR: the tcgen05 kernel on CTA pairs (cta_group::2) with the
+ * weights as the M operand and token tiles of up to 256 as N. */
 
 /*
  * Shape of one engine.  Field meanings follow the reference's Config

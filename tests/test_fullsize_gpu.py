@@ -61,6 +61,11 @@ def test_full_size_layer(pkg, oracle, workload):
     x_tc2 = run(pkg.GEMM_TCGEN05)
     assert torch.equal(x_tc, x_tc2), "two runs on the same input must agree bit for bit"
     x_simt = run(pkg.GEMM_SIMT)
+    x_pair = run(pkg.GEMM_PAIR)
+    x_pair2 = run(pkg.GEMM_PAIR)
+    assert torch.equal(x_pair, x_pair2)
+    helpers.check_activations(x_pair.float().cpu().numpy(), x_simt.float().cpu().numpy(),
+                              "cta-pair kernel vs simt", max_abs=4e-2, mean_rel=1e-3)
 
     pos_h = pos.cpu().numpy()
     active = pos_h >= 0

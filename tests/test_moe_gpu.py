@@ -69,6 +69,26 @@ def test_layer_against_oracle(pkg, oracle, T, H, IM, E, K, inactive):
     _compare(pkg, oracle, shape, d)
 
 
+@pytest.mark.parametrize("T,H,IM,E,K,inactive", EDGE_CASES)
+def test_layer_against_oracle_single_cta_kernel(pkg, oracle, T, H, IM, E, K, inactive):
+    """The default grouped GEMM runs on CTA pairs; the single-CTA tcgen05 kernel stays
+    selectable and is held to the same bar."""
+    shape = synth.MoeShape("edge", T, H, IM, E, K, 7.0, 1000 + T + E + K)
+    d = synth.make_layer(shape, inactive_every=inactive)
+    _compare(pkg, oracle, shape, d, gemm_impl=pkg.GEMM_TCGEN05)
+
+
+@pytest.mark.parametrize("rows", [1, 15, 16, 17, 255, 256, 257, 600])
+def test_cta_pair_kernel_token_tile_edges(pkg, oracle, rows):
+    """One expert gets exactly `rows` rows: token tiles of 1..256 and the step to a second tile."""
+    shape = synth.MoeShape("tile", rows, 128, 64, 4, 1, 7.0, 77)
+    d = synth.make_layer(shape)
+    d["w_router"][:] = 0.0
+    d["b_router"][:] = synth.bf16_round(np.array([0.0, 1.0, 0.0, 0.0], np.float32))  # all to expert 1
+    got, want = _compare(pkg, oracle, shape, d, gemm_impl=pkg.GEMM_PAIR)
+    assert (want["topk_i"] == 1).all()
+
+
 def test_empty_batch_and_all_inactive(pkg, oracle):
     shape = synth.MoeShape("empty", 8, 64, 64, 8, 4, 7.0, 3)
     d = synth.make_layer(shape)
