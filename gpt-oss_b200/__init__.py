@@ -202,6 +202,13 @@ class MoeEngine:
         self._check(self.lib.gptoss_moe_load_layer_bf16(self.handle, layer, *args,
                                                         1 if on_device else 0))
 
+    def load_layer_mxfp4(self, layer, w_router_bf16, b_router, w1_blocks, w1_scales, b_mlp1,
+                         w2_blocks, w2_scales, b_mlp2, on_device):
+        args = [_ptr(a) for a in (w_router_bf16, b_router, w1_blocks, w1_scales, b_mlp1,
+                                  w2_blocks, w2_scales, b_mlp2)]
+        self._check(self.lib.gptoss_moe_load_layer_mxfp4(self.handle, layer, *args,
+                                                         1 if on_device else 0))
+
     # -- compute
     def forward(self, layer, t, x, pos, n_tokens, stream=0):
         self._check(self.lib.gptoss_moe_forward(self.handle, layer, _ptr(t), _ptr(x), _ptr(pos),

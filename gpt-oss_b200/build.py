@@ -15,7 +15,7 @@ CSRC = PKG_DIR / "csrc"
 LIB = PKG_DIR / "libgptoss_moe_b200.so"
 
 CU_SOURCES = ["moe_api.cu", "router.cu", "permute.cu", "grouped_gemm.cu", "grouped_gemm_pair.cu",
-              "weights.cu", "ep.cu"]
+              "weights.cu", "mxfp4.cu", "ep.cu"]
 HEADERS = ["common.cuh", "engine.h", "ep.h", "gemm_epilogue.cuh", "umma_2sm.cuh"]
 
 NVCC_FLAGS = [

@@ -30,6 +30,8 @@ struct GemmArgs {
   int *status;
   int skip_epilogue;  // measurement aid: bit 0 = do not read the accumulator,
                       // bit 1 = compute but do not store
+  const uint8_t *wq = nullptr;  // MXFP4: tiled packed codes of the weight operand
+  const uint8_t *ws = nullptr;  // MXFP4: tiled scales
 };
 
 // gate * sigmoid(alpha * gate) * (up + 1) with the reference CPU path's clamps

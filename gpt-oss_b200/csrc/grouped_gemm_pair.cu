@@ -58,8 +58,30 @@ struct PairStage {
   static constexpr int kTotalBytes = 2 /*halves*/ * 2 /*buffers*/ * kTileBytes;
 };
 
-template <int EPI, int kPairStages>
-__global__ void __launch_bounds__(kPairThreads, 1)
+// MXFP4 weights (MX = true): the producer bulk-copies the packed codes (4 KB) and
+// scales (256 B) of the CTA's 128 rows x 64 k into a small raw ring; four extra
+// warps (one thread per weight row) expand them to bf16 straight into the
+// operand ring, in the 128-byte-swizzled layout TMA would have written, and
+// count as arrivals on the even CTA's full barrier beside the token tiles' bytes.
+constexpr int kRawStages = 4;
+constexpr int kRawCodeBytes = 128 * 32;
+constexpr int kRawStageBytes = kRawCodeBytes + 128 * 2;
+constexpr int kDequantWarps = 4;
+
+// two e2m1 codes (one byte, low nibble = even element) -> two bf16 whose value is
+// code * 2^-126: sign to bit 15, the three magnitude bits to exponent bit 0-1 and
+// mantissa bit 6 (for magnitude 1 this is the bf16 subnormal 2^-127)
+__device__ __forceinline__ uint32_t e2m1x2_to_bf16x2_raw(uint32_t x) {
+  return ((x & 0x08u) << 12) | ((x & 0x07u) << 6) | ((x & 0x80u) << 24) | ((x & 0x70u) << 18);
+}
+__device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
+  __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162 *>(&a),
+                             *reinterpret_cast<__nv_bfloat162 *>(&b));
+  return *reinterpret_cast<uint32_t *>(&r);
+}
+
+template <int EPI, int kPairStages, bool MX>
+__global__ void __launch_bounds__(kPairThreads + (MX ? kDequantWarps * 32 : 0), 1)
 grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
                          const __grid_constant__ CUtensorMap tmap_x, const GemmArgs g) {
   extern __shared__ unsigned char smem_raw[];
@@ -69,17 +91,25 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
   uint64_t *empty_bar = full_bar + kPairStages;
   uint64_t *tfull_bar = empty_bar + kPairStages;  // [2]
   uint64_t *tempty_bar = tfull_bar + 2;           // [2], used in the even CTA
-  uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(tempty_bar + 2);
+  uint64_t *raw_full = tempty_bar + 2;            // [kRawStages] (MX)
+  uint64_t *raw_empty = raw_full + kRawStages;    // [kRawStages] (MX)
+  uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(raw_empty + kRawStages);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
   unsigned char *epi_stage = smem + kPairStages * kPairStageBytes + 256;
+  unsigned char *raw_ring = epi_stage + PairStage<EPI>::kTotalBytes;  // (MX)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_cta_rank();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPairStages; s++) {
-      mbar_init(&full_bar[s], 1);
+      // MX: the leader's producer plus the dequantising warps of both CTAs
+      mbar_init(&full_bar[s], MX ? 1 + 2 * kDequantWarps : 1);
       mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < kRawStages; s++) {
+      mbar_init(&raw_full[s], 1);
+      mbar_init(&raw_empty[s], kDequantWarps);
     }
     for (int a = 0; a < 2; a++) {
       mbar_init(&tfull_bar[a], 1);
@@ -107,8 +137,8 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
 
   if (warp == 0) {
     if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
+      int stage = 0, rs = 0;
+      uint32_t phase = 0, rphase = 0;
       bool ok = true;
       int e_next = 0, tok0_next = 0, ntok_next = 0;
       if (cl < total_tiles) {
@@ -138,9 +168,31 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
             break;
           }
           unsigned char *sa = smem + stage * kPairStageBytes;
-          if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * kPairStageBytes);
-          tma_load_2d_pair(sa, &tmap_w, &full_bar[stage], kb * kTileK, wrow);
-          tma_load_2d_pair(sa + kPairOperandBytes, &tmap_x, &full_bar[stage], kb * kTileK, trow);
+          if (!MX) {
+            if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * kPairStageBytes);
+            tma_load_2d_pair(sa, &tmap_w, &full_bar[stage], kb * kTileK, wrow);
+            tma_load_2d_pair(sa + kPairOperandBytes, &tmap_x, &full_bar[stage], kb * kTileK, trow);
+          } else {
+            // token halves by TMA (both CTAs' bytes go to the even CTA's barrier); this
+            // CTA's packed weight block by two bulk copies into the raw ring
+            if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * kPairOperandBytes);
+            tma_load_2d_pair(sa + kPairOperandBytes, &tmap_x, &full_bar[stage], kb * kTileK, trow);
+            if (!mbar_wait(&raw_empty[rs], rphase ^ 1u, abort_flag)) {
+              set_status(g.status, kStatusWaitTimeoutProducer);
+              *abort_flag = 1;
+              ok = false;
+              break;
+            }
+            const size_t blk = (static_cast<size_t>(e) * (2 * w_pairs) + 2 * wp + rank) * kb_count + kb;
+            unsigned char *rdst = raw_ring + rs * kRawStageBytes;
+            mbar_arrive_expect_tx(&raw_full[rs], kRawStageBytes);
+            bulk_load(rdst, g.wq + blk * kRawCodeBytes, kRawCodeBytes, &raw_full[rs]);
+            bulk_load(rdst + kRawCodeBytes, g.ws + blk * 256, 256, &raw_full[rs]);
+            if (++rs == kRawStages) {
+              rs = 0;
+              rphase ^= 1u;
+            }
+          }
           if (++stage == kPairStages) {
             stage = 0;
             phase ^= 1u;
@@ -189,6 +241,65 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
         umma_commit_pair(&tfull_bar[acc], 3);  // accumulator ready in both CTAs
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else if (MX && warp >= kPairThreads / 32) {
+    // dequantising warps: thread dt expands weight row dt of the CTA's block
+    const int dt = threadIdx.x - kPairThreads;
+    int stage = 0, rs = 0;
+    uint32_t phase = 0, rphase = 0;
+    bool ok = true;
+    for (int tile = cl; ok && tile < total_tiles; tile += ncl) {
+      for (int kb = 0; kb < kb_count; kb++) {
+        if (!mbar_wait(&raw_full[rs], rphase, abort_flag) ||
+            !mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+          set_status(g.status, kStatusWaitTimeoutProducer);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        tc_fence_after();  // the MMAs that read this operand slot are done
+        const unsigned char *rq = raw_ring + rs * kRawStageBytes;
+        const uint4 q0 = *reinterpret_cast<const uint4 *>(rq + dt * 32);
+        const uint4 q1 = *reinterpret_cast<const uint4 *>(rq + dt * 32 + 16);
+        const uint32_t sc = *reinterpret_cast<const uint16_t *>(rq + kRawCodeBytes + dt * 2);
+        // value = raw * 2^126 * 2^(s-127): two exact multiplications by powers of two
+        const uint32_t k126 = 0x7E807E80u;  // bf16x2 (2^126, 2^126)
+        uint32_t s0 = sc & 0xffu, s1 = sc >> 8;
+        s0 = s0 ? (s0 << 7) : 0x0040u;  // e8m0 0 = 2^-127, a bf16 subnormal
+        s1 = s1 ? (s1 << 7) : 0x0040u;
+        const uint32_t m0 = s0 | (s0 << 16), m1 = s1 | (s1 << 16);
+        unsigned char *row = smem + stage * kPairStageBytes + dt * 128;
+        const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+        for (int c = 0; c < 8; c++) {  // 8 elements (one packed word) -> one 16-byte chunk
+          const uint32_t w = words[c];
+          const uint32_t mul = c < 4 ? m0 : m1;
+          uint4 o;
+          o.x = bf16x2_mul(bf16x2_mul(e2m1x2_to_bf16x2_raw(w & 0xffu), k126), mul);
+          o.y = bf16x2_mul(bf16x2_mul(e2m1x2_to_bf16x2_raw((w >> 8) & 0xffu), k126), mul);
+          o.z = bf16x2_mul(bf16x2_mul(e2m1x2_to_bf16x2_raw((w >> 16) & 0xffu), k126), mul);
+          o.w = bf16x2_mul(bf16x2_mul(e2m1x2_to_bf16x2_raw(w >> 24), k126), mul);
+          // 128-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ (r & 7)
+          *reinterpret_cast<uint4 *>(row + ((c ^ (dt & 7)) << 4)) = o;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&raw_empty[rs]);
+          if (rank == 0)
+            mbar_arrive(&full_bar[stage]);
+          else
+            mbar_arrive_cluster(&full_bar[stage], 0);
+        }
+        if (++rs == kRawStages) {
+          rs = 0;
+          rphase ^= 1u;
+        }
+        if (++stage == kPairStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
       }
     }
   } else {
@@ -308,16 +419,17 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
   }
 }
 
-template <int EPI, int STAGES>
+template <int EPI, int STAGES, bool MX>
 static cudaError_t launch_pair_stages(gptoss_moe *h, const CUtensorMap &tw, const CUtensorMap &tx,
                                       const GemmArgs &g, cudaStream_t stream) {
-  const size_t smem = 1024 + STAGES * kPairStageBytes + 256 + PairStage<EPI>::kTotalBytes;
-  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_pair_kernel<EPI, STAGES>,
+  const size_t smem = 1024 + STAGES * kPairStageBytes + 256 + PairStage<EPI>::kTotalBytes +
+                      (MX ? kRawStages * kRawStageBytes : 0);
+  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_pair_kernel<EPI, STAGES, MX>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(h->num_sms & ~1));
-  cfg.blockDim = dim3(kPairThreads);
+  cfg.blockDim = dim3(kPairThreads + (MX ? kDequantWarps * 32 : 0));
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -328,55 +440,50 @@ static cudaError_t launch_pair_stages(gptoss_moe *h, const CUtensorMap &tw, cons
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   h->launches++;
-  return cudaLaunchKernelEx(&cfg, grouped_gemm_pair_kernel<EPI, STAGES>, tw, tx, g);
+  return cudaLaunchKernelEx(&cfg, grouped_gemm_pair_kernel<EPI, STAGES, MX>, tw, tx, g);
 }
 
 template <int EPI>
 static cudaError_t launch_pair(gptoss_moe *h, const CUtensorMap &tw, const CUtensorMap &tx,
                                const GemmArgs &g, cudaStream_t stream) {
+  // MXFP4: the raw ring takes the room of one operand stage
+  if (h->cfg.weight_format == GPTOSS_WEIGHTS_MXFP4)
+    return launch_pair_stages<EPI, 5, true>(h, tx, tx, g, stream);
   switch (h->opt_pair_stages) {
-    case 4: return launch_pair_stages<EPI, 4>(h, tw, tx, g, stream);
-    case 5: return launch_pair_stages<EPI, 5>(h, tw, tx, g, stream);
-    default: return launch_pair_stages<EPI, 6>(h, tw, tx, g, stream);
+    case 4: return launch_pair_stages<EPI, 4, false>(h, tw, tx, g, stream);
+    case 5: return launch_pair_stages<EPI, 5, false>(h, tw, tx, g, stream);
+    default: return launch_pair_stages<EPI, 6, false>(h, tw, tx, g, stream);
   }
+}
+
+static GemmArgs pair_args(gptoss_moe *h, bool down, const LayerWeights &lw) {
+  GemmArgs g;
+  g.bias = down ? lw.b2 : lw.b1;
+  g.out = down ? h->ys : h->hact;
+  g.row_weight = down ? h->sorted_weight : nullptr;
+  g.mtile_expert = h->mtile_expert;
+  g.mtile_row0 = h->mtile_row0;
+  g.mtile_rows = h->mtile_rows;
+  g.num_mtiles = h->num_mtiles;
+  g.k_dim = down ? h->IM : h->H;
+  g.n_cols = down ? h->H : 2 * h->IM;
+  g.out_ld = down ? h->H : h->IM;
+  g.limit = h->cfg.swiglu_limit;
+  g.status = h->status;
+  g.skip_epilogue = h->opt_skip_epilogue;
+  g.wq = down ? lw.w2_blocks : lw.w1_blocks;
+  g.ws = down ? lw.w2_scales : lw.w1_scales;
+  return g;
 }
 
 cudaError_t launch_gate_up_pair(gptoss_moe *h, int layer, cudaStream_t stream) {
   LayerWeights &lw = h->layers[layer];
-  GemmArgs g;
-  g.bias = lw.b1;
-  g.out = h->hact;
-  g.row_weight = nullptr;
-  g.mtile_expert = h->mtile_expert;
-  g.mtile_row0 = h->mtile_row0;
-  g.mtile_rows = h->mtile_rows;
-  g.num_mtiles = h->num_mtiles;
-  g.k_dim = h->H;
-  g.n_cols = 2 * h->IM;
-  g.out_ld = h->IM;
-  g.limit = h->cfg.swiglu_limit;
-  g.status = h->status;
-  g.skip_epilogue = h->opt_skip_epilogue;
-  return launch_pair<kEpiSwiglu>(h, lw.tmap_w1_rows, h->tmap_xs, g, stream);
+  return launch_pair<kEpiSwiglu>(h, lw.tmap_w1_rows, h->tmap_xs, pair_args(h, false, lw), stream);
 }
 
 cudaError_t launch_down_pair(gptoss_moe *h, int layer, cudaStream_t stream) {
   LayerWeights &lw = h->layers[layer];
-  GemmArgs g;
-  g.bias = lw.b2;
-  g.out = h->ys;
-  g.row_weight = h->sorted_weight;
-  g.mtile_expert = h->mtile_expert;
-  g.mtile_row0 = h->mtile_row0;
-  g.mtile_rows = h->mtile_rows;
-  g.num_mtiles = h->num_mtiles;
-  g.k_dim = h->IM;
-  g.n_cols = h->H;
-  g.out_ld = h->H;
-  g.limit = h->cfg.swiglu_limit;
-  g.status = h->status;
-  g.skip_epilogue = h->opt_skip_epilogue;
-  return launch_pair<kEpiDown>(h, lw.tmap_w2_rows, h->tmap_h, g, stream);
+  return launch_pair<kEpiDown>(h, lw.tmap_w2_rows, h->tmap_h, pair_args(h, true, lw), stream);
 }
 
 }  // namespace gptoss

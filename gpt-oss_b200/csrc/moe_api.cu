@@ -287,12 +287,7 @@ int gptoss_moe_load_layer_bf16(gptoss_moe_t *h, int layer, const void *w_router,
   return finish_layer(h, lw);
 }
 
-int gptoss_moe_load_layer_mxfp4(gptoss_moe_t *h, int, const void *, const float *,
-                                const uint8_t *, const uint8_t *, const float *, const uint8_t *,
-                                const uint8_t *, const float *, int) {
-  if (!h) return GPTOSS_E_INVALID;
-  return fail(h, GPTOSS_E_INVALID, "MXFP4 expert weights are not implemented yet");
-}
+// gptoss_moe_load_layer_mxfp4 lives in mxfp4.cu
 
 // ------------------------------------------------------------------ stages
 static int check_layer(gptoss_moe *h, int layer, int n_tokens) {
@@ -490,6 +485,8 @@ int gptoss_moe_set_option(gptoss_moe_t *h, const char *name, int value) {
   if (!strcmp(name, "gemm_impl")) {
     if (value != GPTOSS_GEMM_TCGEN05 && value != GPTOSS_GEMM_SIMT && value != GPTOSS_GEMM_PAIR)
       return fail(h, GPTOSS_E_INVALID, "unknown gemm_impl %d", value);
+    if (h->cfg.weight_format == GPTOSS_WEIGHTS_MXFP4 && value != GPTOSS_GEMM_PAIR)
+      return fail(h, GPTOSS_E_INVALID, "MXFP4 weights are only read by the CTA-pair kernel");
     h->opt_gemm_impl = value;
   } else if (!strcmp(name, "keep_logits")) {
     h->opt_keep_logits = value != 0;

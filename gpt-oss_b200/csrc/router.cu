@@ -67,19 +67,35 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
 // (run.cpp:356-369): exact float products summed in double, rounded to float
 // once at the end.  Whole warp cooperates; every lane returns the result.
 __device__ __forceinline__ float warp_exact_dot(const bf16 *a, const bf16 *b, int H, int lane) {
-  double acc = 0.0;
+  // Loads of up to 4 pieces per lane are issued together (their latency overlaps)
+  // and four independent accumulators keep the fp64 add chains short.  The order
+  // of the fp64 additions differs from the reference's left-to-right sum by
+  // rounding errors ~1e-16 relative, which the final rounding to float hides.
+  double acc0 = 0.0, acc1 = 0.0, acc2 = 0.0, acc3 = 0.0;
   const uint4 *a4 = reinterpret_cast<const uint4 *>(a);
   const uint4 *b4 = reinterpret_cast<const uint4 *>(b);
-  for (int p = lane; p < (H >> 3); p += 32) {
-    uint4 av = __ldg(a4 + p), bv = __ldg(b4 + p);
-    const uint32_t aw[4] = {av.x, av.y, av.z, av.w};
-    const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+  const int n4 = H >> 3;
+  for (int p0 = lane; p0 < n4; p0 += 128) {
+    uint4 av[4], bv[4];
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-      acc += static_cast<double>(__fmul_rn(bf16_lo(aw[i]), bf16_lo(bw[i])));
-      acc += static_cast<double>(__fmul_rn(bf16_hi(aw[i]), bf16_hi(bw[i])));
+    for (int u = 0; u < 4; u++) {
+      const int p = p0 + u * 32;
+      av[u] = p < n4 ? __ldg(a4 + p) : make_uint4(0, 0, 0, 0);
+      bv[u] = p < n4 ? __ldg(b4 + p) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      acc0 += static_cast<double>(__fmul_rn(bf16_lo(av[u].x), bf16_lo(bv[u].x)));
+      acc1 += static_cast<double>(__fmul_rn(bf16_hi(av[u].x), bf16_hi(bv[u].x)));
+      acc2 += static_cast<double>(__fmul_rn(bf16_lo(av[u].y), bf16_lo(bv[u].y)));
+      acc3 += static_cast<double>(__fmul_rn(bf16_hi(av[u].y), bf16_hi(bv[u].y)));
+      acc0 += static_cast<double>(__fmul_rn(bf16_lo(av[u].z), bf16_lo(bv[u].z)));
+      acc1 += static_cast<double>(__fmul_rn(bf16_hi(av[u].z), bf16_hi(bv[u].z)));
+      acc2 += static_cast<double>(__fmul_rn(bf16_lo(av[u].w), bf16_lo(bv[u].w)));
+      acc3 += static_cast<double>(__fmul_rn(bf16_hi(av[u].w), bf16_hi(bv[u].w)));
     }
   }
+  double acc = (acc0 + acc1) + (acc2 + acc3);
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
   return __double2float_rn(acc);
@@ -102,26 +118,41 @@ router_topk_kernel(const bf16 *__restrict__ t, const bf16 *__restrict__ w_router
   const int tok0 = blockIdx.x * kRtTokens;
   const int nk = (H + kRtKC - 1) / kRtKC;
 
-  auto load_chunk = [&](int kc, int stage) {
-    unsigned char *base = smem + stage * kStageBytes;
-    const int k0 = kc * kRtKC;
-    for (int p = tid; p < (kRtTokens + EPAD) * 8; p += kRtThreads) {
-      const int row = p >> 3, c = p & 7;
-      const int k = k0 + c * 8;
-      const void *src;
-      bool ok = k < H;
+  // Every thread copies the same (row, 16-byte piece) slots of each chunk: their
+  // source rows and shared-memory offsets are worked out once, the loop only adds
+  // the chunk's K offset.
+  constexpr int kSlots = ((kRtTokens + EPAD) * 8 + kRtThreads - 1) / kRtThreads;
+  const bf16 *slot_src[kSlots];  // row start + piece offset, nullptr = row does not exist
+  uint32_t slot_dst[kSlots];     // byte offset inside a stage
+  int slot_k[kSlots];            // first K element of the piece inside a chunk
+#pragma unroll
+  for (int i = 0; i < kSlots; i++) {
+    const int p = tid + i * kRtThreads;
+    const int row = p >> 3, c = p & 7;
+    slot_dst[i] = row * kRtRowBytes + c * 16;
+    slot_k[i] = c * 8;
+    slot_src[i] = nullptr;
+    if (p < (kRtTokens + EPAD) * 8) {
       if (row < kRtTokens) {
-        const int tok = tok0 + row;
-        ok = ok && tok < T;
-        src = ok ? static_cast<const void *>(t + static_cast<size_t>(tok) * H + k)
-                 : static_cast<const void *>(t);
-      } else {
-        const int e = row - kRtTokens;
-        ok = ok && e < E;
-        src = ok ? static_cast<const void *>(w_router + static_cast<size_t>(e) * H + k)
-                 : static_cast<const void *>(w_router);
+        if (tok0 + row < T) slot_src[i] = t + static_cast<size_t>(tok0 + row) * H + c * 8;
+      } else if (row - kRtTokens < E) {
+        slot_src[i] = w_router + static_cast<size_t>(row - kRtTokens) * H + c * 8;
       }
-      cp_async16(smem_u32(base + row * kRtRowBytes + c * 16), src, ok ? 16u : 0u);
+    } else {
+      slot_dst[i] = 0xffffffffu;  // no such slot
+    }
+  }
+  const uint32_t smem_base = smem_u32(smem);
+  auto load_chunk = [&](int kc, int stage) {
+    const int k0 = kc * kRtKC;
+#pragma unroll
+    for (int i = 0; i < kSlots; i++) {
+      if (slot_dst[i] != 0xffffffffu) {
+        const bool ok = slot_src[i] != nullptr && k0 + slot_k[i] < H;
+        const void *src = ok ? static_cast<const void *>(slot_src[i] + k0)
+                             : static_cast<const void *>(t);
+        cp_async16(smem_base + stage * kStageBytes + slot_dst[i], src, ok ? 16u : 0u);
+      }
     }
   };
 

@@ -89,3 +89,27 @@ def make_layer(shape: MoeShape, n_tokens: int | None = None, inactive_every: int
         pos[::inactive_every] = -1
     d["pos"] = pos
     return d
+
+
+# ---------------------------------------------------------------- MXFP4
+E2M1_VALUES = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0,
+                        -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0], dtype=np.float32)
+
+
+def mxfp4_random(rng, rows_shape, k, scale_lo=119, scale_hi=123):
+    """Random MXFP4 tensor [..., k]: packed codes [..., k/2] (uniform over the 16 e2m1
+    codes, low nibble = even element) and e8m0 scales [..., k/32] (uniform in
+    [scale_lo, scale_hi], i.e. 2^-8 .. 2^-4 by default)."""
+    codes = rng.integers(0, 16, size=(*rows_shape, k), dtype=np.uint8)
+    blocks = (codes[..., 0::2] | (codes[..., 1::2] << 4)).astype(np.uint8)
+    scales = rng.integers(scale_lo, scale_hi + 1, size=(*rows_shape, k // 32), dtype=np.uint8)
+    return blocks, scales
+
+
+def mxfp4_dequant(blocks, scales):
+    """Packed codes + e8m0 scales -> float32 (exact; every value is a bf16 number)."""
+    lo = E2M1_VALUES[blocks & 0x0F]
+    hi = E2M1_VALUES[blocks >> 4]
+    vals = np.stack([lo, hi], axis=-1).reshape(*blocks.shape[:-1], blocks.shape[-1] * 2)
+    s = np.exp2(scales.astype(np.float32) - 127.0)
+    return (vals.reshape(*scales.shape, 32) * s[..., None]).reshape(vals.shape).astype(np.float32)
