@@ -29,7 +29,8 @@ struct LayerWeights {
   float *b1 = nullptr;        // [E_local, 2*IM]
   bf16 *w2 = nullptr;         // [E_local, H, IM]
   float *b2 = nullptr;        // [E_local, H]
-  uint8_t *w1_blocks = nullptr, *w1_scales = nullptr;  // MXFP4 storage
+  // MXFP4 storage, tiled: [expert][128-row block][64-k block][4096 B codes + 256 B scales]
+  uint8_t *w1_blocks = nullptr, *w1_scales = nullptr;  // (scales pointers unused: kept in the tile)
   uint8_t *w2_blocks = nullptr, *w2_scales = nullptr;
   CUtensorMap tmap_w1, tmap_w2;            // boxes of 240 weight rows (N operand)
   CUtensorMap tmap_w1_rows, tmap_w2_rows;  // boxes of 128 weight rows (M operand, CTA pairs)
@@ -69,6 +70,7 @@ struct gptoss_moe {
   const int *stage_expert = nullptr;         // [R, K] local expert id or -1
   const float *stage_weight = nullptr;       // [R, K]
   int stage_R = 0;
+  int cur_tile_rows = 128;  // row tile of the schedule the last permutation built
 
   // permutation outputs
   int *block_counts = nullptr;   // [perm_blocks_cap, El]
@@ -84,7 +86,9 @@ struct gptoss_moe {
   gptoss::bf16 *xs = nullptr;    // [assign_cap + pad, H]  gathered inputs
   gptoss::bf16 *hact = nullptr;  // [assign_cap + pad, IM] SwiGLU activations
   gptoss::bf16 *ys = nullptr;    // [assign_cap, H]        weighted expert outputs
-  CUtensorMap tmap_xs, tmap_h;
+  CUtensorMap tmap_xs, tmap_h;            // boxes of 128 rows
+  CUtensorMap tmap_xs32, tmap_h32;        // boxes of 32 rows (narrow token tiles)
+  CUtensorMap tmap_xs8, tmap_h8;          // boxes of 8 rows
 
   // host-call staging
   gptoss::bf16 *t_dev = nullptr, *x_dev = nullptr;

@@ -28,10 +28,10 @@ struct GemmArgs {
   int out_ld;   // leading dimension of out
   float limit;
   int *status;
-  int skip_epilogue;  // measurement aid: bit 0 = do not read the accumulator,
-                      // bit 1 = compute but do not store
-  const uint8_t *wq = nullptr;  // MXFP4: tiled packed codes of the weight operand
-  const uint8_t *ws = nullptr;  // MXFP4: tiled scales
+  int skip_epilogue;  // measurement aid, bit mask: 1 = do not read the accumulator,
+                      // 2 = compute but do not store, 4 = no proxy fence after the
+                      // MXFP4 conversion, 8 = no conversion, 16 = no MMA issue
+  const uint8_t *wq = nullptr;  // MXFP4: tiled packed codes + scales of the weight operand
 };
 
 // gate * sigmoid(alpha * gate) * (up + 1) with the reference CPU path's clamps

@@ -43,7 +43,6 @@ namespace gptoss {
 
 constexpr int kPairThreads = 320;
 constexpr int kPairOperandBytes = 128 * kTileK * 2;          // 16 KB: 128 rows x 64 k
-constexpr int kPairStageBytes = 2 * kPairOperandBytes;       // weights + token half
 constexpr int kPairEpiWarps = kPairThreads / 32 - 2;
 constexpr int kAccColsPair = 256;  // TMEM columns per accumulator (up to 256 tokens), two of them
 
@@ -63,10 +62,10 @@ struct PairStage {
 // warps (one thread per weight row) expand them to bf16 straight into the
 // operand ring, in the 128-byte-swizzled layout TMA would have written, and
 // count as arrivals on the even CTA's full barrier beside the token tiles' bytes.
-constexpr int kRawStages = 4;
+constexpr int kPairBarrierBytes = 1024;  // mbarriers, TMEM address holder, abort flag
 constexpr int kRawCodeBytes = 128 * 32;
 constexpr int kRawStageBytes = kRawCodeBytes + 128 * 2;
-constexpr int kDequantWarps = 4;
+constexpr int kDequantWarps = 8;  // two threads per weight row
 
 // two e2m1 codes (one byte, low nibble = even element) -> two bf16 whose value is
 // code * 2^-126: sign to bit 15, the three magnitude bits to exponent bit 0-1 and
@@ -80,10 +79,16 @@ __device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
   return *reinterpret_cast<uint32_t *>(&r);
 }
 
-template <int EPI, int kPairStages, bool MX>
-__global__ void __launch_bounds__(kPairThreads + (MX ? kDequantWarps * 32 : 0), 1)
+// TOKB = token rows a CTA's operand slot holds (128: token tiles of up to 256; 32:
+// tiles of up to 64 for decode-sized batches, which buys a deeper ring)
+// kRawStages = depth of the raw (packed) weight ring, 0 without MX
+template <int EPI, int kPairStages, bool MX, int TOKB, int kRawStages>
+__global__ void __launch_bounds__(kPairThreads + (MX ? (kDequantWarps + 1) * 32 : 0), 1)
 grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
-                         const __grid_constant__ CUtensorMap tmap_x, const GemmArgs g) {
+                         const __grid_constant__ CUtensorMap tmap_x,
+                         const __grid_constant__ CUtensorMap tmap_x32,
+                         const __grid_constant__ CUtensorMap tmap_x8, const GemmArgs g) {
+  constexpr int kPairStageBytes = kPairOperandBytes + TOKB * kTileK * 2;  // weights + token half
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   unsigned char *smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
@@ -95,8 +100,17 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
   uint64_t *raw_empty = raw_full + kRawStages;    // [kRawStages] (MX)
   uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(raw_empty + kRawStages);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
-  unsigned char *epi_stage = smem + kPairStages * kPairStageBytes + 256;
+  static_assert((2 * kPairStages + 4 + 2 * kRawStages) * 8 + 8 <= kPairBarrierBytes,
+                "barrier region too small");
+  unsigned char *epi_stage = smem + kPairStages * kPairStageBytes + kPairBarrierBytes;
   unsigned char *raw_ring = epi_stage + PairStage<EPI>::kTotalBytes;  // (MX)
+  // (MX) byte of two e2m1 codes -> the two values as bf16 (normal numbers; the
+  // subnormal detour of the bit trick is paid 256 times here, not per element)
+  uint32_t *lut = reinterpret_cast<uint32_t *>(raw_ring + kRawStages * kRawStageBytes);
+  if (MX) {
+    for (uint32_t x = threadIdx.x; x < 256; x += blockDim.x)
+      lut[x] = bf16x2_mul(e2m1x2_to_bf16x2_raw(x), 0x7E807E80u);  // * (2^126, 2^126)
+  }
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_cta_rank();
@@ -137,8 +151,8 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
 
   if (warp == 0) {
     if (lane == 0) {
-      int stage = 0, rs = 0;
-      uint32_t phase = 0, rphase = 0;
+      int stage = 0;
+      uint32_t phase = 0;
       bool ok = true;
       int e_next = 0, tok0_next = 0, ntok_next = 0;
       if (cl < total_tiles) {
@@ -160,6 +174,11 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
         const int half_n = ((ntok + 15) & ~15) >> 1;  // token rows each CTA contributes
         const int wrow = e * g.n_cols + wp * 256 + static_cast<int>(rank) * 128;
         const int trow = tok0 + static_cast<int>(rank) * half_n;
+        // narrow token tiles are loaded with a narrower box: 8, 32 or 128 rows per CTA
+        const CUtensorMap *tx =
+            half_n <= 8 ? &tmap_x8 : ((half_n <= 32 || TOKB == 32) ? &tmap_x32 : &tmap_x);
+        const uint32_t tok_bytes =
+            (half_n <= 8 ? 8 : ((half_n <= 32 || TOKB == 32) ? 32 : 128)) * kTileK * 2;
         for (int kb = 0; kb < kb_count; kb++) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
             set_status(g.status, kStatusWaitTimeoutProducer);
@@ -169,33 +188,46 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
           }
           unsigned char *sa = smem + stage * kPairStageBytes;
           if (!MX) {
-            if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * kPairStageBytes);
+            if (rank == 0)
+              mbar_arrive_expect_tx(&full_bar[stage], 2 * (kPairOperandBytes + tok_bytes));
             tma_load_2d_pair(sa, &tmap_w, &full_bar[stage], kb * kTileK, wrow);
-            tma_load_2d_pair(sa + kPairOperandBytes, &tmap_x, &full_bar[stage], kb * kTileK, trow);
-          } else {
-            // token halves by TMA (both CTAs' bytes go to the even CTA's barrier); this
-            // CTA's packed weight block by two bulk copies into the raw ring
-            if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * kPairOperandBytes);
-            tma_load_2d_pair(sa + kPairOperandBytes, &tmap_x, &full_bar[stage], kb * kTileK, trow);
-            if (!mbar_wait(&raw_empty[rs], rphase ^ 1u, abort_flag)) {
-              set_status(g.status, kStatusWaitTimeoutProducer);
-              *abort_flag = 1;
-              ok = false;
-              break;
-            }
-            const size_t blk = (static_cast<size_t>(e) * (2 * w_pairs) + 2 * wp + rank) * kb_count + kb;
-            unsigned char *rdst = raw_ring + rs * kRawStageBytes;
-            mbar_arrive_expect_tx(&raw_full[rs], kRawStageBytes);
-            bulk_load(rdst, g.wq + blk * kRawCodeBytes, kRawCodeBytes, &raw_full[rs]);
-            bulk_load(rdst + kRawCodeBytes, g.ws + blk * 256, 256, &raw_full[rs]);
-            if (++rs == kRawStages) {
-              rs = 0;
-              rphase ^= 1u;
-            }
+          } else if (rank == 0) {
+            // the weights arrive through the raw ring and the dequantising warps
+            mbar_arrive_expect_tx(&full_bar[stage], 2 * tok_bytes);
           }
+          tma_load_2d_pair(sa + kPairOperandBytes, tx, &full_bar[stage], kb * kTileK, trow);
           if (++stage == kPairStages) {
             stage = 0;
             phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (MX && warp == kPairThreads / 32 + kDequantWarps) {
+    // raw-weight producer: one bulk copy (packed codes + scales of 128 rows x 64 k) per
+    // K block into a ring deep enough to cover HBM latency at HBM bandwidth
+    if (lane == 0) {
+      int rs = 0;
+      uint32_t rphase = 0;
+      bool ok = true;
+      for (int tile = cl; ok && tile < total_tiles; tile += ncl) {
+        const int tt = tile / w_pairs, wp = tile - tt * w_pairs;
+        const int e = g.mtile_expert[tt];
+        const size_t blk0 =
+            (static_cast<size_t>(e) * (2 * w_pairs) + 2 * wp + rank) * kb_count;
+        for (int kb = 0; kb < kb_count; kb++) {
+          if (!mbar_wait(&raw_empty[rs], rphase ^ 1u, abort_flag)) {
+            set_status(g.status, kStatusWaitTimeoutProducer);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&raw_full[rs], kRawStageBytes);
+          bulk_load(raw_ring + rs * kRawStageBytes, g.wq + (blk0 + kb) * kRawStageBytes,
+                    kRawStageBytes, &raw_full[rs]);
+          if (++rs == kRawStages) {
+            rs = 0;
+            rphase ^= 1u;
           }
         }
       }
@@ -228,6 +260,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
           const uint32_t sa = smem_u32(smem + stage * kPairStageBytes);
           const uint64_t da = umma_smem_desc_sw128(sa);
           const uint64_t db = umma_smem_desc_sw128(sa + kPairOperandBytes);
+          if (!(g.skip_epilogue & 16))
 #pragma unroll
           for (int k = 0; k < kTileK / 16; k++)
             umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
@@ -243,9 +276,11 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
         if (acc == 0) acc_phase ^= 1u;
       }
     }
-  } else if (MX && warp >= kPairThreads / 32) {
-    // dequantising warps: thread dt expands weight row dt of the CTA's block
+  } else if (MX && warp >= kPairThreads / 32 && warp < kPairThreads / 32 + kDequantWarps) {
+    // dequantising warps: threads 2r and 2r+1 expand the two 32-element halves of
+    // weight row r of the CTA's block (one scale byte each)
     const int dt = threadIdx.x - kPairThreads;
+    const int wr = dt >> 1, hf = dt & 1;
     int stage = 0, rs = 0;
     uint32_t phase = 0, rphase = 0;
     bool ok = true;
@@ -260,30 +295,26 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
         }
         tc_fence_after();  // the MMAs that read this operand slot are done
         const unsigned char *rq = raw_ring + rs * kRawStageBytes;
-        const uint4 q0 = *reinterpret_cast<const uint4 *>(rq + dt * 32);
-        const uint4 q1 = *reinterpret_cast<const uint4 *>(rq + dt * 32 + 16);
-        const uint32_t sc = *reinterpret_cast<const uint16_t *>(rq + kRawCodeBytes + dt * 2);
-        // value = raw * 2^126 * 2^(s-127): two exact multiplications by powers of two
-        const uint32_t k126 = 0x7E807E80u;  // bf16x2 (2^126, 2^126)
-        uint32_t s0 = sc & 0xffu, s1 = sc >> 8;
-        s0 = s0 ? (s0 << 7) : 0x0040u;  // e8m0 0 = 2^-127, a bf16 subnormal
-        s1 = s1 ? (s1 << 7) : 0x0040u;
-        const uint32_t m0 = s0 | (s0 << 16), m1 = s1 | (s1 << 16);
-        unsigned char *row = smem + stage * kPairStageBytes + dt * 128;
-        const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        const uint4 q0 = *reinterpret_cast<const uint4 *>(rq + dt * 16);
+        uint32_t sc = rq[kRawCodeBytes + dt];
+        // codes come out of the table as bf16 values; times 2^(s-127), exact
+        sc = sc ? (sc << 7) : 0x0040u;  // e8m0 0 = 2^-127, a bf16 subnormal
+        const uint32_t mul = sc | (sc << 16);
+        unsigned char *row = smem + stage * kPairStageBytes + wr * 128;
+        const uint32_t words[4] = {q0.x, q0.y, q0.z, q0.w};
+        if (!(g.skip_epilogue & 8))
 #pragma unroll
-        for (int c = 0; c < 8; c++) {  // 8 elements (one packed word) -> one 16-byte chunk
+        for (int c = 0; c < 4; c++) {  // 8 elements (one packed word) -> one 16-byte chunk
           const uint32_t w = words[c];
-          const uint32_t mul = c < 4 ? m0 : m1;
           uint4 o;
-          o.x = bf16x2_mul(bf16x2_mul(e2m1x2_to_bf16x2_raw(w & 0xffu), k126), mul);
-          o.y = bf16x2_mul(bf16x2_mul(e2m1x2_to_bf16x2_raw((w >> 8) & 0xffu), k126), mul);
-          o.z = bf16x2_mul(bf16x2_mul(e2m1x2_to_bf16x2_raw((w >> 16) & 0xffu), k126), mul);
-          o.w = bf16x2_mul(bf16x2_mul(e2m1x2_to_bf16x2_raw(w >> 24), k126), mul);
-          // 128-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ (r & 7)
-          *reinterpret_cast<uint4 *>(row + ((c ^ (dt & 7)) << 4)) = o;
+          o.x = bf16x2_mul(lut[w & 0xffu], mul);
+          o.y = bf16x2_mul(lut[(w >> 8) & 0xffu], mul);
+          o.z = bf16x2_mul(lut[(w >> 16) & 0xffu], mul);
+          o.w = bf16x2_mul(lut[w >> 24], mul);
+          // 128-byte swizzle: 16-byte chunk j of row r sits at chunk j ^ (r & 7)
+          *reinterpret_cast<uint4 *>(row + (((hf * 4 + c) ^ (wr & 7)) << 4)) = o;
         }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (!(g.skip_epilogue & 4)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) {
           mbar_arrive(&raw_empty[rs]);
@@ -419,17 +450,18 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
   }
 }
 
-template <int EPI, int STAGES, bool MX>
-static cudaError_t launch_pair_stages(gptoss_moe *h, const CUtensorMap &tw, const CUtensorMap &tx,
+template <int EPI, int STAGES, bool MX, int TOKB, int RAWS>
+static cudaError_t launch_pair_stages(gptoss_moe *h, const CUtensorMap &tw, const CUtensorMap *tx,
                                       const GemmArgs &g, cudaStream_t stream) {
-  const size_t smem = 1024 + STAGES * kPairStageBytes + 256 + PairStage<EPI>::kTotalBytes +
-                      (MX ? kRawStages * kRawStageBytes : 0);
-  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_pair_kernel<EPI, STAGES, MX>,
+  const size_t smem = 1024 + STAGES * (kPairOperandBytes + TOKB * kTileK * 2) + kPairBarrierBytes +
+                      PairStage<EPI>::kTotalBytes +
+                      (MX ? RAWS * kRawStageBytes + 1024 : 0);
+  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_pair_kernel<EPI, STAGES, MX, TOKB, RAWS>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(h->num_sms & ~1));
-  cfg.blockDim = dim3(kPairThreads + (MX ? kDequantWarps * 32 : 0));
+  cfg.blockDim = dim3(kPairThreads + (MX ? (kDequantWarps + 1) * 32 : 0));
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -440,19 +472,30 @@ static cudaError_t launch_pair_stages(gptoss_moe *h, const CUtensorMap &tw, cons
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   h->launches++;
-  return cudaLaunchKernelEx(&cfg, grouped_gemm_pair_kernel<EPI, STAGES, MX>, tw, tx, g);
+  return cudaLaunchKernelEx(&cfg, grouped_gemm_pair_kernel<EPI, STAGES, MX, TOKB, RAWS>, tw, tx[0], tx[1], tx[2],
+                            g);
 }
 
 template <int EPI>
-static cudaError_t launch_pair(gptoss_moe *h, const CUtensorMap &tw, const CUtensorMap &tx,
+// tx: the token-side tensor maps with boxes of 128, 32 and 8 rows
+static cudaError_t launch_pair(gptoss_moe *h, const CUtensorMap &tw, const CUtensorMap *tx,
                                const GemmArgs &g, cudaStream_t stream) {
-  // MXFP4: the raw ring takes the room of one operand stage
-  if (h->cfg.weight_format == GPTOSS_WEIGHTS_MXFP4)
-    return launch_pair_stages<EPI, 5, true>(h, tx, tx, g, stream);
+  // MXFP4: the raw ring takes the room of two operand stages; decode-sized batches run
+  // with 64-token tiles, whose small token slots allow a 7-deep operand ring
+  if (h->cfg.weight_format == GPTOSS_WEIGHTS_MXFP4) {
+#ifndef GPTOSS_NARROW_STAGES
+#define GPTOSS_NARROW_STAGES 7
+#define GPTOSS_NARROW_RAW 12
+#endif
+    if (h->cur_tile_rows == 64)
+      return launch_pair_stages<EPI, GPTOSS_NARROW_STAGES, true, 32, GPTOSS_NARROW_RAW>(h, tx[0], tx, g,
+                                                                                      stream);
+    return launch_pair_stages<EPI, 4, true, 128, 12>(h, tx[0], tx, g, stream);
+  }
   switch (h->opt_pair_stages) {
-    case 4: return launch_pair_stages<EPI, 4, false>(h, tw, tx, g, stream);
-    case 5: return launch_pair_stages<EPI, 5, false>(h, tw, tx, g, stream);
-    default: return launch_pair_stages<EPI, 6, false>(h, tw, tx, g, stream);
+    case 4: return launch_pair_stages<EPI, 4, false, 128, 0>(h, tw, tx, g, stream);
+    case 5: return launch_pair_stages<EPI, 5, false, 128, 0>(h, tw, tx, g, stream);
+    default: return launch_pair_stages<EPI, 6, false, 128, 0>(h, tw, tx, g, stream);
   }
 }
 
@@ -472,18 +515,19 @@ static GemmArgs pair_args(gptoss_moe *h, bool down, const LayerWeights &lw) {
   g.status = h->status;
   g.skip_epilogue = h->opt_skip_epilogue;
   g.wq = down ? lw.w2_blocks : lw.w1_blocks;
-  g.ws = down ? lw.w2_scales : lw.w1_scales;
   return g;
 }
 
 cudaError_t launch_gate_up_pair(gptoss_moe *h, int layer, cudaStream_t stream) {
   LayerWeights &lw = h->layers[layer];
-  return launch_pair<kEpiSwiglu>(h, lw.tmap_w1_rows, h->tmap_xs, pair_args(h, false, lw), stream);
+  const CUtensorMap tx[3] = {h->tmap_xs, h->tmap_xs32, h->tmap_xs8};
+  return launch_pair<kEpiSwiglu>(h, lw.tmap_w1_rows, tx, pair_args(h, false, lw), stream);
 }
 
 cudaError_t launch_down_pair(gptoss_moe *h, int layer, cudaStream_t stream) {
   LayerWeights &lw = h->layers[layer];
-  return launch_pair<kEpiDown>(h, lw.tmap_w2_rows, h->tmap_h, pair_args(h, true, lw), stream);
+  const CUtensorMap tx[3] = {h->tmap_h, h->tmap_h32, h->tmap_h8};
+  return launch_pair<kEpiDown>(h, lw.tmap_w2_rows, tx, pair_args(h, true, lw), stream);
 }
 
 }  // namespace gptoss

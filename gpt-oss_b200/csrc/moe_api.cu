@@ -102,7 +102,7 @@ int gptoss_moe_create(const gptoss_moe_config_t *cfg, gptoss_moe_t **out) {
   h->max_tokens = cfg->max_tokens;
   h->rows_cap = cfg->max_tokens * ep_size;
   h->assign_cap = h->rows_cap * K;
-  h->mtiles_cap = h->assign_cap / kTileM + h->El + 1;
+  h->mtiles_cap = h->assign_cap / 64 + h->El + 1;  // the narrowest row tile is 64
   h->perm_blocks_cap = (h->rows_cap + kPermTokens - 1) / kPermTokens;
   h->num_sms = prop.multiProcessorCount;
   h->layers.resize(h->L);
@@ -141,7 +141,11 @@ int gptoss_moe_create(const gptoss_moe_config_t *cfg, gptoss_moe_t **out) {
 #undef CKH
   std::string terr;
   if (make_tmap_2d_bf16(&h->tmap_xs, h->xs, H, h->assign_cap, kTileK, kTileM, &terr) ||
-      make_tmap_2d_bf16(&h->tmap_h, h->hact, IM, h->assign_cap, kTileK, kTileM, &terr)) {
+      make_tmap_2d_bf16(&h->tmap_h, h->hact, IM, h->assign_cap, kTileK, kTileM, &terr) ||
+      make_tmap_2d_bf16(&h->tmap_xs32, h->xs, H, h->assign_cap, kTileK, 32, &terr) ||
+      make_tmap_2d_bf16(&h->tmap_h32, h->hact, IM, h->assign_cap, kTileK, 32, &terr) ||
+      make_tmap_2d_bf16(&h->tmap_xs8, h->xs, H, h->assign_cap, kTileK, 8, &terr) ||
+      make_tmap_2d_bf16(&h->tmap_h8, h->hact, IM, h->assign_cap, kTileK, 8, &terr)) {
     int rc = fail(nullptr, GPTOSS_E_CUDA, "%s", terr.c_str());
     gptoss_moe_destroy(h);
     return rc;

@@ -12,8 +12,8 @@
 // stage): weight rows are cut into blocks of 128 (one CTA's M tile; the last
 // block of an expert is zero padded, and the block count per expert is even so a
 // CTA pair always owns two), the contraction dimension into K blocks of 64:
-//   q[expert][block][kblock][128 rows][32 bytes]   packed codes
-//   s[expert][block][kblock][128 rows][2 bytes]    scales of the two 32-groups
+//   tile[expert][block][kblock] = { codes[128 rows][32 bytes], scales[128 rows][2 bytes] }
+// i.e. 4352 contiguous bytes per (block, K block): one bulk copy per stage.
 #include "common.cuh"
 #include "engine.h"
 
@@ -44,7 +44,11 @@ mxfp4_tile_codes_kernel(uint8_t *__restrict__ q, const uint8_t *__restrict__ blo
         memcpy(&v, tmp, 16);
       }
     }
-    reinterpret_cast<uint4 *>(q + static_cast<size_t>(e_local) * total * 16)[i] = v;
+    // 4352-byte tiles: 4096 bytes of codes, then 256 bytes of scales
+    const size_t tile = i >> 8, inside = i & 255;
+    const size_t tiles_per_expert = static_cast<size_t>(nb) * kb_count;
+    *reinterpret_cast<uint4 *>(q + (static_cast<size_t>(e_local) * tiles_per_expert + tile) * 4352 +
+                               inside * 16) = v;
   }
 }
 
@@ -64,7 +68,9 @@ mxfp4_tile_scales_kernel(uint8_t *__restrict__ s, const uint8_t *__restrict__ sc
     uint8_t v = 127;  // 2^0; the codes it scales are zero padding
     if (row < rows && grp < k_groups)
       v = scales[(static_cast<size_t>(e_global) * rows + row) * k_groups + grp];
-    s[static_cast<size_t>(e_local) * total + i] = v;
+    const size_t tile = i >> 8, inside = i & 255;
+    const size_t tiles_per_expert = static_cast<size_t>(nb) * kb_count;
+    s[(static_cast<size_t>(e_local) * tiles_per_expert + tile) * 4352 + 4096 + inside] = v;
   }
 }
 
@@ -77,8 +83,7 @@ static int tile_tensor(gptoss_moe *h, const uint8_t *blocks, const uint8_t *scal
   const int k_bytes = k / 2, k_groups = k / 32;
   const int kb_count = (k + kTileK - 1) / kTileK;
   const int nb = static_cast<int>(mxfp4_blocks_per_expert(rows));
-  const size_t per_q = static_cast<size_t>(nb) * kb_count * 128 * 32;
-  const size_t per_s = static_cast<size_t>(nb) * kb_count * 128 * 2;
+  const size_t per_q = static_cast<size_t>(nb) * kb_count * 4352;  // codes + scales
   const size_t src_q = static_cast<size_t>(h->E) * rows * k_bytes;
   const size_t src_s = static_cast<size_t>(h->E) * rows * k_groups;
   auto fail = [&](const char *what, cudaError_t e) {
@@ -88,8 +93,6 @@ static int tile_tensor(gptoss_moe *h, const uint8_t *blocks, const uint8_t *scal
   cudaError_t e;
   if (!*q_out && (e = cudaMalloc(reinterpret_cast<void **>(q_out), per_q * h->El)) != cudaSuccess)
     return fail("cudaMalloc(codes)", e);
-  if (!*s_out && (e = cudaMalloc(reinterpret_cast<void **>(s_out), per_s * h->El)) != cudaSuccess)
-    return fail("cudaMalloc(scales)", e);
   const uint8_t *dq = blocks, *ds = scales;
   uint8_t *tq = nullptr, *ts = nullptr;
   if (!on_device) {
@@ -107,7 +110,7 @@ static int tile_tensor(gptoss_moe *h, const uint8_t *blocks, const uint8_t *scal
   for (int j = 0; j < h->El; j++) {
     const int eg = j * h->ep_size + h->ep_rank;
     mxfp4_tile_codes_kernel<<<592, 256>>>(*q_out, dq, rows, k_bytes, nb, kb_count, j, eg);
-    mxfp4_tile_scales_kernel<<<592, 256>>>(*s_out, ds, rows, k_groups, nb, kb_count, j, eg);
+    mxfp4_tile_scales_kernel<<<592, 256>>>(*q_out, ds, rows, k_groups, nb, kb_count, j, eg);
     h->launches += 2;
   }
   e = cudaDeviceSynchronize();

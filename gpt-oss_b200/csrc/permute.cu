@@ -280,6 +280,15 @@ combine_rows_kernel(bf16 *__restrict__ out, const bf16 *__restrict__ ys,
 
 cudaError_t launch_permute(gptoss_moe *h, cudaStream_t stream) {
   const int R = h->stage_R, K = h->K, El = h->El;
+  // row tile of the GEMM schedule: 128 = the single-CTA kernel's fixed M; the
+  // CTA-pair kernel takes token tiles of up to 256, or up to 64 when MXFP4 weights
+  // meet a decode-sized batch (on average at most 128 rows per expert)
+  h->cur_tile_rows = kTileM;
+  if (h->opt_gemm_impl == GPTOSS_GEMM_PAIR) {
+    const bool decode = h->cfg.weight_format == GPTOSS_WEIGHTS_MXFP4 &&
+                        static_cast<long long>(R) * K <= 128ll * El;
+    h->cur_tile_rows = decode ? 64 : 256;
+  }
   const int nblocks = (R + kPermTokens - 1) / kPermTokens;
   if (R <= 0) {
     // nothing routed here: empty schedule
@@ -297,8 +306,7 @@ cudaError_t launch_permute(gptoss_moe *h, cudaStream_t stream) {
   perm_scan_scatter_kernel<<<nblocks, kScanThreads, smem, stream>>>(
       h->stage_expert, h->stage_weight, R, K, El, h->block_counts, nblocks, h->expert_offsets,
       h->sorted_row, h->sorted_weight, h->row_of, h->mtile_expert, h->mtile_row0, h->mtile_rows,
-      h->num_mtiles, h->mtiles_cap, h->assign_cap, h->status,
-      h->opt_gemm_impl == GPTOSS_GEMM_PAIR ? 256 : kTileM);
+      h->num_mtiles, h->mtiles_cap, h->assign_cap, h->status, h->cur_tile_rows);
   h->launches++;
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;

@@ -59,8 +59,10 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint64_t *bar, uint32_t targ
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
                : "=r"(remote)
                : "r"(smem_u32(bar)), "r"(target_cta));
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote)
-               : "memory");
+  // default semantics (release at CTA scope): what the arrival orders is this CTA's own
+  // shared memory and TMEM, read by the tensor core, not by the other CTA's threads; a
+  // cluster-scope release here costs about a microsecond per arrival
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
 }
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t *smem_result, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(

@@ -170,9 +170,12 @@ int gptoss_moe_get_activations(gptoss_moe_t *h, void *act_host, size_t bytes);
 
 /* Options: "gemm_impl" (GPTOSS_GEMM_*), "keep_logits" (0/1),
  * "exact_ties" (0/1, default 1: re-evaluate near-tied router logits in fp64),
- * "time_stages" (0/1, see gptoss_moe_stage_ms), "skip_epilogue" (0/1, a
- * measurement aid: the grouped GEMMs run their main loop but write nothing, so
- * results are garbage while it is on). */
+ * "time_stages" (0/1, see gptoss_moe_stage_ms), "pair_stages" (4..6, operand
+ * ring depth of the CTA-pair GEMM with bf16 weights), "skip_epilogue" (a bit
+ * mask, default 0, measurement aid only - results are garbage while any bit is
+ * set: 1 = the grouped GEMMs do not read their accumulators, 2 = compute but do
+ * not store, 4 = MXFP4 path without the proxy fence, 8 = MXFP4 path without the
+ * code -> bf16 conversion, 16 = no MMA issue). */
 int gptoss_moe_set_option(gptoss_moe_t *h, const char *name, int value);
 /* Kernels launched by this handle since creation. */
 long long gptoss_moe_launch_count(const gptoss_moe_t *h);
