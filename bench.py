@@ -192,8 +192,8 @@ def run_reference_arm(args, shape):
 
 def measure_c3_layer(args, pkg, dev, rank, world, local_rank, barrier):
     """The 120b-shape layer (T=6144 tokens per GPU, 128 experts) beside the headline
-    workload: all experts local at N=1, expert parallel (owner = e % N, NCCL dispatch
-    and return) at N>1.  Weak scaling: every rank brings its own 6144 tokens."""
+    workload: all experts local at N=1, expert parallel (owner = e % N) at N>1.  Weak
+    scaling: every rank brings its own 6144 tokens."""
     import torch
     import torch.distributed as dist
 
@@ -221,38 +221,53 @@ def measure_c3_layer(args, pkg, dev, rank, world, local_rank, barrier):
     x = torch.randn((T, H), generator=g, device=dev).bfloat16()
     stream = torch.cuda.current_stream().cuda_stream
     steps = max(3, min(args.steps, 30))
-    for _ in range(3):
-        eng.forward(0, t, x, None, T, stream)
-    barrier()
-    if eng.device_status() != 0:
-        raise SystemExit("device status non-zero in the 120b-shape layer")
-    eng.set_option("time_stages", 1)
-    barrier()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for _ in range(steps):
-        eng.forward(0, t, x, None, T, stream)
-    ev1.record()
-    barrier()
-    ms = ev0.elapsed_time(ev1)
-    if world > 1:
-        tt = torch.tensor([ms], device=dev)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        ms = float(tt.item())
     names = ["route", "permute", "gate_up", "down", "combine"]
     if world > 1:
         names += ["dispatch", "return"]
-    stage_ms = {s: eng.stage_ms(s) for s in names}
+
+    def timed():
+        for _ in range(3):
+            eng.forward(0, t, x, None, T, stream)
+        barrier()
+        if eng.device_status() != 0:
+            raise SystemExit("device status non-zero in the 120b-shape layer")
+        eng.set_option("time_stages", 1)
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(steps):
+            eng.forward(0, t, x, None, T, stream)
+        ev1.record()
+        barrier()
+        ms = ev0.elapsed_time(ev1)
+        if world > 1:
+            tt = torch.tensor([ms], device=dev)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            ms = float(tt.item())
+        stage_ms = {s: eng.stage_ms(s) for s in names}
+        eng.set_option("time_stages", 0)
+        return {"value": world * T * steps / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms / steps,
+                "steps": steps, "stage_ms": stage_ms}
+
+    # expert parallelism: rows read from the peers' memory where the ranks could map each
+    # other (the default then), and over NCCL send / recv for comparison
+    transport = eng.ep_transport if world > 1 else -1
+    res = timed()
+    other = None
+    if transport == 1:
+        eng.set_option("ep_transport", 0)
+        other = timed()
     eng.close()
-    return {
-        "workload": shape.name, "tokens_per_gpu": T, "experts": E,
-        "parallelism": "all experts local" if world == 1 else f"expert parallel x{world} (NCCL)",
-        "value": world * T * steps / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms / steps,
-        "steps": steps, "stage_ms": stage_ms,
-        # rank 0's own gate_up launch; under expert parallelism its row count varies a
-        # little around T*K per rank
-        "gate_up_tflops": 2.0 * T * K * 2 * IM * H / (stage_ms["gate_up"] * 1e-3) / 1e12,
-    }
+    how = {-1: "all experts local", 0: f"expert parallel x{world} (NCCL send/recv)",
+           1: f"expert parallel x{world} (rows read from peer memory over NVLink)"}[transport]
+    out = {"workload": shape.name, "tokens_per_gpu": T, "experts": E, "parallelism": how}
+    out.update(res)
+    # rank 0's own gate_up launch; under expert parallelism its row count varies a little
+    # around T*K per rank
+    out["gate_up_tflops"] = 2.0 * T * K * 2 * IM * H / (res["stage_ms"]["gate_up"] * 1e-3) / 1e12
+    if other is not None:
+        out["nccl_send_recv"] = other
+    return out
 
 
 def run_ours(args, shape):

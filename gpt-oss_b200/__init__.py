@@ -100,6 +100,7 @@ def load_library() -> ctypes.CDLL:
         "gptoss_moe_stage_ms": (c_int, [vp, c_int, fp]),
         "gptoss_moe_ep_unique_id": (c_int, [vp]),
         "gptoss_moe_ep_init": (c_int, [vp, vp]),
+        "gptoss_moe_ep_transport": (c_int, [vp]),
         "gptoss_moe_version": (c_char_p, []),
         "gptoss_moe_permute_static": (c_int, [vp, vp, c_int, c_int, c_int, vp, vp, vp, vp, vp]),
     }
@@ -288,3 +289,8 @@ class MoeEngine:
     def ep_init(self, unique_id: bytes):
         buf = (ctypes.c_ubyte * 128).from_buffer_copy(unique_id)
         self._check(self.lib.gptoss_moe_ep_init(self.handle, ctypes.cast(buf, ctypes.c_void_p)))
+
+    @property
+    def ep_transport(self) -> int:
+        """0 = NCCL send/recv, 1 = peer memory, -1 before ep_init."""
+        return int(self.lib.gptoss_moe_ep_transport(self.handle))

@@ -121,9 +121,11 @@ cudaError_t launch_rmsnorm(bf16 *out, const bf16 *x, const float *w, const int *
 
 // permute.cu
 cudaError_t launch_permute(gptoss_moe *h, cudaStream_t stream);
+cudaError_t launch_permute_plan_only(gptoss_moe *h, cudaStream_t stream);
 cudaError_t launch_combine(gptoss_moe *h, bf16 *x, const int *topk_i_rows, int T,
                            cudaStream_t stream);
-cudaError_t launch_reduce_rows(gptoss_moe *h, bf16 *out_rows, int R, cudaStream_t stream);
+cudaError_t launch_reduce_rows(gptoss_moe *h, bf16 *out_rows, int R, cudaStream_t stream,
+                               bool skip_empty = false);
 
 // A counting sort of (row, slot) pairs by key on caller-named buffers.
 struct PermPlan {

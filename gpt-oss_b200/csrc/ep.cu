@@ -25,6 +25,21 @@
 //      one slot per owner)
 // Ranks must call the layer in lock step (also with zero tokens).
 //
+// Second transport ("ep_transport" 1, ranks in separate processes on one node):
+// no row is packed, sent or received.  Every rank publishes its activations in a
+// buffer that its peers map through CUDA IPC and all-gathers the routing result
+// (expert ids and weights of its tokens, a few hundred KB).  Each owner then sorts
+// ALL tokens of all ranks by its local experts and its gather kernel pulls the
+// rows it needs straight out of the home ranks' memory over NVLink into expert
+// order - dispatch and gather are one kernel.  After the owner's experts and the
+// per-row pre-reduction, a one-integer all-gather tells every home that the sums
+// are complete, and the home's combine kernel pulls the (at most min(N, K)) sums
+// of each token from the owners' memory, adds them in owner order in fp32 and
+// adds the residual - return and combine are one kernel.  No host
+// synchronisation; the two small collectives are the only NCCL calls.  The two
+// transports add the same values in the same order, so their results are equal
+// bit for bit.
+//
 // NCCL is loaded with dlopen on first use, so single-GPU users of the library do
 // not need it; in a process that already loaded NCCL (PyTorch) the same copy is
 // picked up.
@@ -33,6 +48,7 @@
 #include <dlfcn.h>
 #include <nccl.h>
 #include <stdio.h>
+#include <unistd.h>
 
 #include <vector>
 
@@ -107,7 +123,127 @@ struct EpState {
   bf16 *out_rows = nullptr;     // [N*T, H] per-row sums over this rank's experts
   int *counts_dev = nullptr;    // [N, N] counts_dev[src][dst]
   int *counts_host = nullptr;   // pinned copy
+  // peer-memory transport
+  int transport = 0;            // 0 = NCCL send / recv, 1 = peer loads
+  bool peer_ok = false;
+  std::string peer_why;         // why the peer transport is not available
+  int max_t = 0;
+  bf16 *pub_t = nullptr;        // [max_t, H] this rank's activations, mapped by the peers
+  int *all_meta = nullptr;      // [N][2 * max_t * K]: expert ids, then weights (float bits)
+  int *sync_dev = nullptr;      // [N] completion round of every rank
+  int round = 0;
+  void *peer_t[GPTOSS_MAX_TOPK] = {};    // peers' pub_t (own entry: the local buffer)
+  void *peer_out[GPTOSS_MAX_TOPK] = {};  // peers' out_rows
 };
+
+struct PeerRows {
+  const bf16 *p[GPTOSS_MAX_TOPK];
+};
+
+// This rank's routing result in all-gather layout: ids of rows >= T are -1.
+__global__ void __launch_bounds__(256)
+ep_publish_meta_kernel(const int *__restrict__ topk_i, const float *__restrict__ topk_v, int T,
+                       int max_t, int K, int *__restrict__ slot) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= max_t * K) return;
+  const bool live = i < T * K;
+  slot[i] = live ? topk_i[i] : -1;
+  slot[max_t * K + i] = live ? __float_as_int(topk_v[i]) : 0;
+}
+
+// Owner view of every rank's tokens: global row g = src * max_t + t keeps the slots
+// whose expert lives here (local id e / N), the others become -1.
+__global__ void __launch_bounds__(256)
+ep_owner_slots_kernel(const int *__restrict__ all_meta, int N, int rank, int max_t, int K,
+                      int *__restrict__ stage_e, float *__restrict__ stage_w) {
+  const int per = max_t * K;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= N * per) return;
+  const int src = i / per, j = i - src * per;
+  const int e = all_meta[static_cast<size_t>(src) * 2 * per + j];
+  const bool mine = e >= 0 && e % N == rank;
+  stage_e[i] = mine ? e / N : -1;
+  stage_w[i] = mine ? __int_as_float(all_meta[static_cast<size_t>(src) * 2 * per + per + j]) : 0.f;
+}
+
+// xs[r, :] = activations of global row sorted_row[r], read from the home rank's
+// published buffer (a peer mapping for every rank but this one); one warp per row,
+// eight 16-byte loads in flight per lane to cover the NVLink round trip.
+__global__ void __launch_bounds__(256)
+gather_rows_peer_kernel(bf16 *__restrict__ xs, const PeerRows src, int max_t,
+                        const int *__restrict__ sorted_row,
+                        const int *__restrict__ expert_offsets, int El, int H, int R,
+                        int *status) {
+  const int total = expert_offsets[El];
+  const int lane = threadIdx.x & 31;
+  const int nwarps = gridDim.x * (blockDim.x >> 5);
+  const int n4 = H >> 3;
+  for (int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < total; r += nwarps) {
+    const int g = sorted_row[r];
+    if (g < 0 || g >= R) {
+      set_status(status, kStatusBadIndex);
+      continue;
+    }
+    const int home = g / max_t, tok = g - home * max_t;
+    const uint4 *s4 = reinterpret_cast<const uint4 *>(src.p[home] + static_cast<size_t>(tok) * H);
+    uint4 *d4 = reinterpret_cast<uint4 *>(xs + static_cast<size_t>(r) * H);
+    for (int p0 = lane; p0 < n4; p0 += 256) {
+      uint4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; u++)
+        if (p0 + u * 32 < n4) v[u] = __ldg(s4 + p0 + u * 32);
+#pragma unroll
+      for (int u = 0; u < 8; u++)
+        if (p0 + u * 32 < n4) d4[p0 + u * 32] = v[u];
+    }
+  }
+}
+
+// x[t] += sum over the owners o (ascending) of token t of the owner's pre-reduced row
+// (rank * max_t + t) in its out_rows, read from the owner's memory.  One warp per token.
+__global__ void __launch_bounds__(256)
+combine_peer_kernel(bf16 *__restrict__ x, const PeerRows outs, const int *__restrict__ topk_i,
+                    int T, int K, int N, int rank, int max_t, int H) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  uint32_t owners = 0;
+  for (int k = 0; k < K; k++) {
+    const int e = topk_i[t * K + k];
+    if (e >= 0) owners |= 1u << (e % N);
+  }
+  if (owners == 0) return;  // inactive row: x untouched
+  const size_t row = (static_cast<size_t>(rank) * max_t + t) * H;
+  uint4 *o4 = reinterpret_cast<uint4 *>(x + static_cast<size_t>(t) * H);
+  const int n4 = H >> 3;
+  for (int p = lane; p < n4; p += 32) {
+    uint4 v[GPTOSS_MAX_TOPK];
+#pragma unroll
+    for (int o = 0; o < GPTOSS_MAX_TOPK; o++)
+      if (o < N && ((owners >> o) & 1u))
+        v[o] = __ldg(reinterpret_cast<const uint4 *>(outs.p[o] + row) + p);
+    const uint4 xv = o4[p];
+    float s[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) s[i] = 0.f;
+#pragma unroll
+    for (int o = 0; o < GPTOSS_MAX_TOPK; o++) {
+      if (o < N && ((owners >> o) & 1u)) {
+        s[0] += bf16_lo(v[o].x); s[1] += bf16_hi(v[o].x); s[2] += bf16_lo(v[o].y);
+        s[3] += bf16_hi(v[o].y); s[4] += bf16_lo(v[o].z); s[5] += bf16_hi(v[o].z);
+        s[6] += bf16_lo(v[o].w); s[7] += bf16_hi(v[o].w);
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16(bf16_lo(xv.x) + s[0], bf16_hi(xv.x) + s[1]);
+    o.y = pack_bf16(bf16_lo(xv.y) + s[2], bf16_hi(xv.y) + s[3]);
+    o.z = pack_bf16(bf16_lo(xv.z) + s[4], bf16_hi(xv.z) + s[5]);
+    o.w = pack_bf16(bf16_lo(xv.w) + s[6], bf16_hi(xv.w) + s[7]);
+    o4[p] = o;
+  }
+}
+
+__global__ void ep_mark_round_kernel(int *slot, int round) { *slot = round; }
 
 // own_key[t, o] = o when token t has at least one selected expert on rank o.
 __global__ void __launch_bounds__(256)
@@ -206,12 +342,107 @@ struct EpStageScope {
   }
 };
 
+// The layer over peer memory (see the head of this file).
+static int ep_forward_peer(gptoss_moe *h, EpState *ep, int layer, const bf16 *t, void *x_io, int T,
+                           cudaStream_t st) {
+  const int N = ep->N, K = h->K, H = h->H, max_t = ep->max_t;
+  const int per = max_t * K;
+  int *my_meta = ep->all_meta + static_cast<size_t>(ep->rank) * 2 * per;
+  {
+    EpStageScope sc(h, 5, st);
+    // 1. publish: activations where the peers can read them, routing result to everyone.
+    //    The all-gather doubles as the barrier "every rank's activations are in place".
+    if (T > 0)
+      EP_CUDA(h, cudaMemcpyAsync(ep->pub_t, t, static_cast<size_t>(T) * H * sizeof(bf16),
+                                 cudaMemcpyDeviceToDevice, st));
+    ep_publish_meta_kernel<<<(per + 255) / 256, 256, 0, st>>>(h->topk_i, h->topk_v, T, max_t, K,
+                                                              my_meta);
+    h->launches++;
+    EP_CUDA(h, cudaGetLastError());
+    EP_NCCL(h, g_nccl.AllGather(my_meta, ep->all_meta, static_cast<size_t>(2) * per, ncclInt32,
+                                ep->comm, st));
+    // 2. owner view of all N * max_t rows
+    ep_owner_slots_kernel<<<(N * per + 255) / 256, 256, 0, st>>>(ep->all_meta, N, ep->rank, max_t,
+                                                                 K, ep->recv_e, ep->recv_w);
+    h->launches++;
+    EP_CUDA(h, cudaGetLastError());
+  }
+  const int R = N * max_t;
+  h->stage_rows = nullptr;  // rows are pulled from the homes, not staged here
+  h->stage_expert = ep->recv_e;
+  h->stage_weight = ep->recv_w;
+  h->stage_R = R;
+  PeerRows src, outs;
+  for (int p = 0; p < GPTOSS_MAX_TOPK; p++) {
+    src.p[p] = static_cast<const bf16 *>(p < N ? ep->peer_t[p] : nullptr);
+    outs.p[p] = static_cast<const bf16 *>(p < N ? ep->peer_out[p] : nullptr);
+  }
+  src.p[ep->rank] = t;  // own rows straight from the caller's buffer
+  {
+    // 3. sort by local expert; dispatch and gather in one kernel
+    EpStageScope sc(h, 1, st);
+    EP_CUDA(h, launch_permute_plan_only(h, st));
+    gather_rows_peer_kernel<<<h->num_sms * 4, 256, 0, st>>>(h->xs, src, max_t, h->sorted_row,
+                                                            h->expert_offsets, h->El, H, R,
+                                                            h->status);
+    h->launches++;
+    EP_CUDA(h, cudaGetLastError());
+  }
+  {
+    EpStageScope sc(h, 2, st);
+    EP_CUDA(h, launch_gate_up(h, layer, st));
+  }
+  {
+    EpStageScope sc(h, 3, st);
+    EP_CUDA(h, launch_down(h, layer, st));
+  }
+  {
+    // 4. per-row sums over this rank's experts, then "my sums are complete" to everyone
+    EpStageScope sc(h, 6, st);
+    EP_CUDA(h, launch_reduce_rows(h, ep->out_rows, R, st, /*skip_empty=*/true));
+    ep->round++;
+    ep_mark_round_kernel<<<1, 1, 0, st>>>(ep->sync_dev + ep->rank, ep->round);
+    h->launches++;
+    EP_NCCL(h, g_nccl.AllGather(ep->sync_dev + ep->rank, ep->sync_dev, 1, ncclInt32, ep->comm, st));
+  }
+  {
+    // 5. return and combine in one kernel
+    EpStageScope sc(h, 4, st);
+    if (T > 0) {
+      const int warps = 8;
+      combine_peer_kernel<<<(T + warps - 1) / warps, warps * 32, 0, st>>>(
+          static_cast<bf16 *>(x_io), outs, h->topk_i, T, K, N, ep->rank, max_t, H);
+      h->launches++;
+      EP_CUDA(h, cudaGetLastError());
+    }
+  }
+  return GPTOSS_OK;
+}
+
+int ep_set_transport(gptoss_moe *h, int transport) {
+  EpState *ep = static_cast<EpState *>(h->ep);
+  if (!ep) return ep_fail(h, GPTOSS_E_STATE, "expert parallelism is not set up");
+  if (transport != 0 && transport != 1)
+    return ep_fail(h, GPTOSS_E_INVALID, "ep_transport: 0 = NCCL send/recv, 1 = peer memory");
+  if (transport == 1 && !ep->peer_ok)
+    return ep_fail(h, GPTOSS_E_STATE, "peer-memory transport unavailable: " + ep->peer_why);
+  ep->transport = transport;
+  return GPTOSS_OK;
+}
+
+int ep_get_transport(const gptoss_moe *h) {
+  const EpState *ep = static_cast<const EpState *>(h->ep);
+  return ep ? ep->transport : -1;
+}
+
 int ep_forward(gptoss_moe *h, int layer, const void *t_in, void *x_io, int T, void *stream) {
   EpState *ep = static_cast<EpState *>(h->ep);
   if (!ep || !ep->comm)
     return ep_fail(h, GPTOSS_E_STATE,
                    "expert parallelism is not set up: call gptoss_moe_ep_init first");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (ep->transport == 1)
+    return ep_forward_peer(h, ep, layer, static_cast<const bf16 *>(t_in), x_io, T, st);
   const int N = ep->N, K = h->K, H = h->H;
   const bf16 *t = static_cast<const bf16 *>(t_in);
   std::vector<int> soff(N + 1, 0), roff(N + 1, 0);
@@ -329,9 +560,87 @@ int ep_forward(gptoss_moe *h, int layer, const void *t_in, void *x_io, int T, vo
   return GPTOSS_OK;
 }
 
+struct PeerBlob {  // what a rank tells the others at start-up
+  cudaIpcMemHandle_t t, out;
+  int ok, max_t, hidden, pid;
+};
+
+static int ep_map_peers(gptoss_moe *h, EpState *ep) {
+  const int N = ep->N;
+  PeerBlob mine = {};
+  mine.max_t = ep->max_t;
+  mine.hidden = h->H;
+  mine.pid = static_cast<int>(getpid());
+  mine.ok = cudaIpcGetMemHandle(&mine.t, ep->pub_t) == cudaSuccess &&
+            cudaIpcGetMemHandle(&mine.out, ep->out_rows) == cudaSuccess;
+  if (!mine.ok) {
+    ep->peer_why = std::string("cudaIpcGetMemHandle: ") + cudaGetErrorString(cudaGetLastError());
+  }
+  static_assert(sizeof(PeerBlob) % 4 == 0, "exchanged as 32-bit words");
+  PeerBlob *blobs_dev = nullptr;
+  std::vector<PeerBlob> blobs(N);
+  EP_CUDA(h, ep_alloc(&blobs_dev, (size_t)N));
+  EP_CUDA(h, cudaMemcpy(blobs_dev + ep->rank, &mine, sizeof(mine), cudaMemcpyHostToDevice));
+  EP_NCCL(h, g_nccl.AllGather(blobs_dev + ep->rank, blobs_dev, sizeof(PeerBlob) / 4, ncclInt32,
+                              ep->comm, nullptr));
+  EP_CUDA(h, cudaStreamSynchronize(nullptr));
+  EP_CUDA(h, cudaMemcpy(blobs.data(), blobs_dev, sizeof(PeerBlob) * N, cudaMemcpyDeviceToHost));
+  bool ok = true;
+  for (int p = 0; p < N && ok; p++) {
+    if (!blobs[p].ok) {
+      ok = false;
+      if (ep->peer_why.empty()) ep->peer_why = "a peer rank could not export its buffers";
+    } else if (blobs[p].max_t != ep->max_t || blobs[p].hidden != h->H) {
+      ok = false;
+      ep->peer_why = "ranks were created with different max_tokens or hidden sizes";
+    } else if (p != ep->rank && blobs[p].pid == mine.pid) {
+      ok = false;
+      ep->peer_why = "ranks share a process (IPC mappings need one process per rank)";
+    }
+  }
+  for (int p = 0; p < N && ok; p++) {
+    if (p == ep->rank) {
+      ep->peer_t[p] = ep->pub_t;
+      ep->peer_out[p] = ep->out_rows;
+      continue;
+    }
+    cudaError_t e = cudaIpcOpenMemHandle(&ep->peer_t[p], blobs[p].t, cudaIpcMemLazyEnablePeerAccess);
+    if (e == cudaSuccess)
+      e = cudaIpcOpenMemHandle(&ep->peer_out[p], blobs[p].out, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+      ok = false;
+      ep->peer_why = std::string("cudaIpcOpenMemHandle: ") + cudaGetErrorString(e);
+      cudaGetLastError();
+    }
+  }
+  // second round: the transport is usable only if every rank mapped every peer
+  int mapped = ok ? 1 : 0;
+  int *flags_dev = reinterpret_cast<int *>(blobs_dev);
+  std::vector<int> flags(N, 0);
+  EP_CUDA(h, cudaMemcpy(flags_dev + ep->rank, &mapped, sizeof(int), cudaMemcpyHostToDevice));
+  EP_NCCL(h, g_nccl.AllGather(flags_dev + ep->rank, flags_dev, 1, ncclInt32, ep->comm, nullptr));
+  EP_CUDA(h, cudaStreamSynchronize(nullptr));
+  EP_CUDA(h, cudaMemcpy(flags.data(), flags_dev, sizeof(int) * N, cudaMemcpyDeviceToHost));
+  cudaFree(blobs_dev);
+  for (int p = 0; p < N; p++)
+    if (!flags[p]) {
+      ok = false;
+      if (ep->peer_why.empty()) ep->peer_why = "a peer rank could not map this rank's buffers";
+    }
+  ep->peer_ok = ok;
+  ep->transport = ok ? 1 : 0;
+  return GPTOSS_OK;
+}
+
 void ep_destroy(gptoss_moe *h) {
   EpState *ep = static_cast<EpState *>(h->ep);
   if (!ep) return;
+  for (int p = 0; p < ep->N; p++) {
+    if (p == ep->rank) continue;
+    if (ep->peer_t[p]) cudaIpcCloseMemHandle(ep->peer_t[p]);
+    if (ep->peer_out[p]) cudaIpcCloseMemHandle(ep->peer_out[p]);
+  }
+  cudaFree(ep->pub_t); cudaFree(ep->all_meta); cudaFree(ep->sync_dev);
   if (ep->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(ep->comm);
   cudaFree(ep->own_key); cudaFree(ep->own_w); cudaFree(ep->s_block_counts);
   cudaFree(ep->s_offsets); cudaFree(ep->s_sorted_row); cudaFree(ep->s_sorted_w);
@@ -400,5 +709,19 @@ extern "C" int gptoss_moe_ep_init(gptoss_moe_t *h, const void *id128) {
   ncclUniqueId id;
   memcpy(&id, id128, sizeof(id));
   EP_NCCL(h, g_nccl.CommInitRank(&ep->comm, N, id, ep->rank));
-  return GPTOSS_OK;
+  // peer-memory transport: buffers the peers map, handles exchanged over the new
+  // communicator.  Every rank takes part in the exchange whatever happens locally, so a
+  // rank that cannot export or map memory does not leave the others waiting; the
+  // transport is offered only when every rank mapped every peer.
+  ep->max_t = static_cast<int>(T);
+  EP_CUDA(h, ep_alloc(&ep->pub_t, T * H));
+  EP_CUDA(h, ep_alloc(&ep->all_meta, (size_t)N * 2 * T * K));
+  EP_CUDA(h, ep_alloc(&ep->sync_dev, (size_t)N));
+  EP_CUDA(h, cudaMemset(ep->sync_dev, 0, sizeof(int) * N));
+  return ep_map_peers(h, ep);
+}
+
+extern "C" int gptoss_moe_ep_transport(const gptoss_moe_t *h) {
+  if (!h) return -1;
+  return ep_get_transport(h);
 }

@@ -9,4 +9,9 @@ namespace gptoss {
 // h->topk_i / h->topk_v.
 int ep_forward(gptoss_moe *h, int layer, const void *t, void *x, int n_tokens, void *stream);
 void ep_destroy(gptoss_moe *h);
+// 0 = rows travel with NCCL send / recv, 1 = owners and homes read each other's
+// memory (ranks in separate processes of one node); -1 from the getter before
+// gptoss_moe_ep_init.
+int ep_set_transport(gptoss_moe *h, int transport);
+int ep_get_transport(const gptoss_moe *h);
 }  // namespace gptoss

@@ -499,6 +499,8 @@ int gptoss_moe_set_option(gptoss_moe_t *h, const char *name, int value) {
   } else if (!strcmp(name, "pair_stages")) {
     if (value < 4 || value > 6) return fail(h, GPTOSS_E_INVALID, "pair_stages must be 4, 5 or 6");
     h->opt_pair_stages = value;
+  } else if (!strcmp(name, "ep_transport")) {
+    return ep_set_transport(h, value);
   } else if (!strcmp(name, "skip_epilogue")) {
     h->opt_skip_epilogue = value;
   } else if (!strcmp(name, "time_stages")) {

@@ -64,15 +64,29 @@ perm_scan_scatter_kernel(const int *__restrict__ slot_expert,
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   constexpr int kWarps = kScanThreads / 32;
 
+  // totals and this CTA's base per expert: the CTAs' counts are split over
+  // kScanThreads / El thread groups (adjacent threads = adjacent experts) and summed
+  // through shared atomics, so a long list of CTAs does not serialise on El threads
   for (int e = tid; e < El; e += kScanThreads) {
-    int tot = 0, before = 0;
-    for (int b = 0; b < nblocks; b++) {
-      const int c = block_counts[static_cast<size_t>(b) * El + e];
-      tot += c;
-      if (b < static_cast<int>(blockIdx.x)) before += c;
+    s_tot[e] = 0;
+    s_base[e] = 0;
+  }
+  __syncthreads();
+  {
+    const int groups = El < kScanThreads ? kScanThreads / El : 1;
+    const int grp = tid / El;  // 0 for every thread when El >= kScanThreads
+    if (grp < groups) {
+      for (int e = tid - grp * El; e < El; e += kScanThreads) {
+        int tot = 0, before = 0;
+        for (int b = grp; b < nblocks; b += groups) {
+          const int c = block_counts[static_cast<size_t>(b) * El + e];
+          tot += c;
+          if (b < static_cast<int>(blockIdx.x)) before += c;
+        }
+        if (tot) atomicAdd(&s_tot[e], tot);
+        if (before) atomicAdd(&s_base[e], before);
+      }
     }
-    s_tot[e] = tot;
-    s_base[e] = before;
   }
   __syncthreads();
   if (warp == 0) {
@@ -221,7 +235,8 @@ gather_rows_kernel(bf16 *__restrict__ xs, const bf16 *__restrict__ rows,
 // otherwise: out[row] = bf16(sum_k ys[row_of[row,k]]) for every row (zero when
 //           the row has no valid slot) - the owner-side pre-reduction under
 //           expert parallelism (getp-csrc/expert.cpp:394-410).
-template <bool RESIDUAL>
+// SKIP_EMPTY: rows without a valid slot are not written at all (nobody reads them).
+template <bool RESIDUAL, bool SKIP_EMPTY = false>
 __global__ void __launch_bounds__(256)
 combine_rows_kernel(bf16 *__restrict__ out, const bf16 *__restrict__ ys,
                     const int *__restrict__ row_of, int R, int K, int H, int assign_cap,
@@ -244,7 +259,7 @@ combine_rows_kernel(bf16 *__restrict__ out, const bf16 *__restrict__ ys,
       }
     }
   }
-  if (RESIDUAL && nvalid == 0) return;
+  if ((RESIDUAL || SKIP_EMPTY) && nvalid == 0) return;
   uint4 *o4 = reinterpret_cast<uint4 *>(out + static_cast<size_t>(row) * H);
   const int n4 = H >> 3;
   for (int p = lane; p < n4; p += 32) {
@@ -279,6 +294,17 @@ combine_rows_kernel(bf16 *__restrict__ out, const bf16 *__restrict__ ys,
 }
 
 cudaError_t launch_permute(gptoss_moe *h, cudaStream_t stream) {
+  cudaError_t e = launch_permute_plan_only(h, stream);
+  if (e != cudaSuccess || h->stage_R <= 0) return e;
+  gather_rows_kernel<<<h->num_sms * 4, 256, 0, stream>>>(h->xs, h->stage_rows, h->sorted_row,
+                                                         h->expert_offsets, h->El, h->H,
+                                                         h->stage_R, h->status);
+  h->launches++;
+  return cudaGetLastError();
+}
+
+// Sorted order and tile schedule only; the caller gathers the rows.
+cudaError_t launch_permute_plan_only(gptoss_moe *h, cudaStream_t stream) {
   const int R = h->stage_R, K = h->K, El = h->El;
   // row tile of the GEMM schedule: 128 = the single-CTA kernel's fixed M; the
   // CTA-pair kernel takes token tiles of up to 256, or up to 64 when MXFP4 weights
@@ -308,12 +334,6 @@ cudaError_t launch_permute(gptoss_moe *h, cudaStream_t stream) {
       h->sorted_row, h->sorted_weight, h->row_of, h->mtile_expert, h->mtile_row0, h->mtile_rows,
       h->num_mtiles, h->mtiles_cap, h->assign_cap, h->status, h->cur_tile_rows);
   h->launches++;
-  e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
-  gather_rows_kernel<<<h->num_sms * 4, 256, 0, stream>>>(h->xs, h->stage_rows, h->sorted_row,
-                                                         h->expert_offsets, El, h->H, R,
-                                                         h->status);
-  h->launches++;
   return cudaGetLastError();
 }
 
@@ -326,11 +346,16 @@ cudaError_t launch_combine(gptoss_moe *h, bf16 *x, const int *, int T, cudaStrea
   return cudaGetLastError();
 }
 
-cudaError_t launch_reduce_rows(gptoss_moe *h, bf16 *out_rows, int R, cudaStream_t stream) {
+cudaError_t launch_reduce_rows(gptoss_moe *h, bf16 *out_rows, int R, cudaStream_t stream,
+                               bool skip_empty) {
   if (R <= 0) return cudaSuccess;
   const int warps = 8;
-  combine_rows_kernel<false><<<(R + warps - 1) / warps, warps * 32, 0, stream>>>(
-      out_rows, h->ys, h->row_of, R, h->K, h->H, h->assign_cap, h->status);
+  if (skip_empty)
+    combine_rows_kernel<false, true><<<(R + warps - 1) / warps, warps * 32, 0, stream>>>(
+        out_rows, h->ys, h->row_of, R, h->K, h->H, h->assign_cap, h->status);
+  else
+    combine_rows_kernel<false><<<(R + warps - 1) / warps, warps * 32, 0, stream>>>(
+        out_rows, h->ys, h->row_of, R, h->K, h->H, h->assign_cap, h->status);
   h->launches++;
   return cudaGetLastError();
 }

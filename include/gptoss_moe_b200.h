@@ -170,6 +170,7 @@ int gptoss_moe_get_activations(gptoss_moe_t *h, void *act_host, size_t bytes);
 
 /* Options: "gemm_impl" (GPTOSS_GEMM_*), "keep_logits" (0/1),
  * "exact_ties" (0/1, default 1: re-evaluate near-tied router logits in fp64),
+ * "ep_transport" (0/1, see gptoss_moe_ep_transport),
  * "time_stages" (0/1, see gptoss_moe_stage_ms), "pair_stages" (4..6, operand
  * ring depth of the CTA-pair GEMM with bf16 weights), "skip_epilogue" (a bit
  * mask, default 0, measurement aid only - results are garbage while any bit is
@@ -197,6 +198,17 @@ int gptoss_moe_stage_ms(gptoss_moe_t *h, int stage, float *ms);
  */
 int gptoss_moe_ep_unique_id(void *id128);
 int gptoss_moe_ep_init(gptoss_moe_t *h, const void *id128);
+/* How rows travel between ranks: 0 = NCCL send / recv (dispatch, owner experts,
+ * return, combine as separate steps, one host synchronisation per layer for the
+ * row counts), 1 = peer memory (each owner's gather kernel reads the rows it
+ * needs out of the home ranks' HBM over NVLink and each home's combine kernel
+ * reads the owners' per-row sums the same way; two small all-gathers per layer,
+ * no host synchronisation; the reference's counterpart is the peer copies of
+ * expert.cpp:1520-1535 and :1577).  gptoss_moe_ep_init selects 1 when every rank could map
+ * every peer's buffers through CUDA IPC (one process per rank, one node), else 0;
+ * gptoss_moe_set_option(h, "ep_transport", v) changes it (all ranks alike).
+ * Both give the same bits.  Returns -1 before gptoss_moe_ep_init. */
+int gptoss_moe_ep_transport(const gptoss_moe_t *h);
 
 /*
  * The permutation stage for callers that cannot allocate device memory.  (No

@@ -1,4 +1,5 @@
-"""Expert parallelism on real GPUs: one process per GPU, NCCL dispatch and return.
+"""Expert parallelism on real GPUs: one process per GPU; rows travel by NCCL send/recv
+or are read from the peers' memory.
 
 Every rank has its own tokens and 1/N of the experts; each rank's result must
 equal the CPU oracle (all experts) on that rank's tokens.  Needs >= 2 GPUs, so it
@@ -58,12 +59,21 @@ def _worker(rank, world, uid, tmp):
             x = helpers.to_dev_bf16(d["x"], dev)
             pos = torch.from_numpy(d["pos"]).to(dev)
             stream = torch.cuda.current_stream().cuda_stream
-            for rep in range(2):  # twice: buffers are reused between layers
-                x.copy_(helpers.to_dev_bf16(d["x"], dev))
-                eng.forward(0, t, x, pos, T, stream)
-            torch.cuda.synchronize()
-            assert eng.device_status() == 0
-            got = x.float().cpu().numpy()
+            # both transports (NCCL send/recv; peer memory where the ranks could map each
+            # other's buffers) must give the same bits
+            transports = [0, 1] if eng.ep_transport == 1 else [0]
+            outs = []
+            for tr in transports:
+                eng.set_option("ep_transport", tr)
+                for rep in range(2):  # twice: buffers are reused between layers
+                    x.copy_(helpers.to_dev_bf16(d["x"], dev))
+                    eng.forward(0, t, x, pos, T, stream)
+                torch.cuda.synchronize()
+                assert eng.device_status() == 0
+                outs.append(x.float().cpu().numpy())
+            for o in outs[1:]:
+                np.testing.assert_array_equal(o, outs[0])
+            got = outs[-1]
             active = d["pos"] >= 0
             r = eng.get_routing(T)
             helpers.check_indices(r["topk_i"], want["topk_i"], want["logits"], active)
@@ -73,7 +83,7 @@ def _worker(rank, world, uid, tmp):
             # this rank's expert groups hold exactly the rows routed to its experts
             mine = ep_plan.local_expert_slice(E, rank, world)
             assert r["expert_offsets"].shape[0] == len(mine) + 1
-            report.append("ok")
+            report.append("ok transports=%s" % transports)
             eng.close()
     except Exception as exc:  # noqa: BLE001
         report.append(f"fail: {exc!r}")
@@ -91,4 +101,6 @@ def test_expert_parallel_two_or_more_gpus(pkg, tmp_path):
     mp.spawn(_worker, args=(world, uids, str(tmp_path)), nprocs=world, join=True)
     for r in range(world):
         lines = (tmp_path / f"rank{r}.txt").read_text().splitlines()
-        assert lines == ["ok"] * len(CASES), f"rank {r}: {lines}"
+        assert len(lines) == len(CASES) and all(l.startswith("ok") for l in lines), \
+            f"rank {r}: {lines}"
+        print(f"rank {r}: {lines}")
