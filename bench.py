@@ -225,7 +225,7 @@ def measure_c3_layer(args, pkg, dev, rank, world, local_rank, barrier):
     if world > 1:
         names += ["dispatch", "return"]
 
-    def timed():
+    def timed(T=T):
         for _ in range(3):
             eng.forward(0, t, x, None, T, stream)
         barrier()
@@ -253,7 +253,11 @@ def measure_c3_layer(args, pkg, dev, rank, world, local_rank, barrier):
     # other (the default then), and over NCCL send / recv for comparison
     transport = eng.ep_transport if world > 1 else -1
     res = timed()
-    other = None
+    other = strong = None
+    if world > 1:
+        # strong-scaling reading: the same 6144 tokens split over the ranks
+        strong = timed(T // world)
+        strong["tokens_per_gpu"] = T // world
     if transport == 1:
         eng.set_option("ep_transport", 0)
         other = timed()
@@ -265,6 +269,8 @@ def measure_c3_layer(args, pkg, dev, rank, world, local_rank, barrier):
     # rank 0's own gate_up launch; under expert parallelism its row count varies a little
     # around T*K per rank
     out["gate_up_tflops"] = 2.0 * T * K * 2 * IM * H / (res["stage_ms"]["gate_up"] * 1e-3) / 1e12
+    if strong is not None:
+        out["strong_scaling"] = strong
     if other is not None:
         out["nccl_send_recv"] = other
     return out
