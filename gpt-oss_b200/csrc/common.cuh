@@ -80,13 +80,19 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity,
                                           volatile int *abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
+  // the global timer is slow to read: first look at it after 1024 failed polls, so that
+  // the short waits of a running pipeline never pay for it
+  uint64_t t0 = 0;
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0x3ff) == 0) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0)
+        t0 = now;
+      else if (now - t0 > kWaitLimitNs)
+        return false;
     }
   }
 }

@@ -57,11 +57,11 @@ struct PairStage {
   static constexpr int kTotalBytes = 2 /*halves*/ * 2 /*buffers*/ * kTileBytes;
 };
 
-// MXFP4 weights (MX = true): the producer bulk-copies the packed codes (4 KB) and
-// scales (256 B) of the CTA's 128 rows x 64 k into a small raw ring; four extra
-// warps (one thread per weight row) expand them to bf16 straight into the
-// operand ring, in the 128-byte-swizzled layout TMA would have written, and
-// count as arrivals on the even CTA's full barrier beside the token tiles' bytes.
+// MXFP4 weights (MX = true): a producer warp bulk-copies the packed codes (4 KB) and
+// scales (256 B) of the CTA's 128 rows x 64 k into a raw ring; eight extra warps, each
+// taking every eighth K block whole, expand them to bf16 straight into the operand
+// ring, in the 128-byte-swizzled layout TMA would have written, and count as one
+// arrival per CTA on the even CTA's full barrier beside the token tiles' bytes.
 constexpr int kPairBarrierBytes = 1024;  // mbarriers, TMEM address holder, abort flag
 constexpr int kRawCodeBytes = 128 * 32;
 constexpr int kRawStageBytes = kRawCodeBytes + 128 * 2;
@@ -81,8 +81,10 @@ __device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
 
 // TOKB = token rows a CTA's operand slot holds (128: token tiles of up to 256; 32:
 // tiles of up to 64 for decode-sized batches, which buys a deeper ring)
-// kRawStages = depth of the raw (packed) weight ring, 0 without MX
-template <int EPI, int kPairStages, bool MX, int TOKB, int kRawStages>
+// kRawStages = depth of the raw (packed) weight ring, 0 without MX; LUTREP = copies of the
+// code table, a power of two (32: one per bank, every lane reads its own copy and no
+// lookup conflicts; 16: lanes l and l + 16 share one)
+template <int EPI, int kPairStages, bool MX, int TOKB, int kRawStages, int LUTREP>
 __global__ void __launch_bounds__(kPairThreads + (MX ? (kDequantWarps + 1) * 32 : 0), 1)
 grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
                          const __grid_constant__ CUtensorMap tmap_x,
@@ -108,22 +110,30 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
   // subnormal detour of the bit trick is paid 256 times here, not per element)
   uint32_t *lut = reinterpret_cast<uint32_t *>(raw_ring + kRawStages * kRawStageBytes);
   if (MX) {
-    for (uint32_t x = threadIdx.x; x < 256; x += blockDim.x)
-      lut[x] = bf16x2_mul(e2m1x2_to_bf16x2_raw(x), 0x7E807E80u);  // * (2^126, 2^126)
+    for (uint32_t x = threadIdx.x; x < 256 * LUTREP; x += blockDim.x)
+      lut[x] = bf16x2_mul(e2m1x2_to_bf16x2_raw(x / LUTREP), 0x7E807E80u);  // * (2^126, 2^126)
   }
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_cta_rank();
+  // (MX) operand stage s is always filled by the same kWarpsPerBlock dequantising warps,
+  // and a raw stage always drained by the same ones: every warp then meets the phases of
+  // its barriers one by one, in order, and a parity wait can never be a whole turn of
+  // the ring ahead of the barrier it polls
+  constexpr int kWarpsPerBlock = MX ? (kDequantWarps / kPairStages > 0 ? kDequantWarps / kPairStages : 1) : 1;
+  static_assert(!MX || (kRawStages % kPairStages == 0 && kWarpsPerBlock * kPairStages <= kDequantWarps &&
+                        8 % kWarpsPerBlock == 0),
+                "dequantising warps must map to fixed ring stages");
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPairStages; s++) {
-      // MX: the leader's producer plus the dequantising warps of both CTAs
-      mbar_init(&full_bar[s], MX ? 1 + 2 * kDequantWarps : 1);
+      // MX: the leader's producer plus the dequantising warps of the block in each CTA
+      mbar_init(&full_bar[s], MX ? 1 + 2 * kWarpsPerBlock : 1);
       mbar_init(&empty_bar[s], 1);
     }
     for (int s = 0; s < kRawStages; s++) {
       mbar_init(&raw_full[s], 1);
-      mbar_init(&raw_empty[s], kDequantWarps);
+      mbar_init(&raw_empty[s], kWarpsPerBlock);
     }
     for (int a = 0; a < 2; a++) {
       mbar_init(&tfull_bar[a], 1);
@@ -276,43 +286,57 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
         if (acc == 0) acc_phase ^= 1u;
       }
     }
-  } else if (MX && warp >= kPairThreads / 32 && warp < kPairThreads / 32 + kDequantWarps) {
-    // dequantising warps: threads 2r and 2r+1 expand the two 32-element halves of
-    // weight row r of the CTA's block (one scale byte each)
-    const int dt = threadIdx.x - kPairThreads;
-    const int wr = dt >> 1, hf = dt & 1;
-    int stage = 0, rs = 0;
-    uint32_t phase = 0, rphase = 0;
-    bool ok = true;
-    for (int tile = cl; ok && tile < total_tiles; tile += ncl) {
-      for (int kb = 0; kb < kb_count; kb++) {
+  } else if (MX && warp >= kPairThreads / 32) {
+    // dequantising warps: group j = dw / kWarpsPerBlock expands the K blocks n = j, j + S,
+    // j + 2S, ... of the CTA's sequence (S = operand stages) into operand stage j, each
+    // warp of the group a share of the block's 16-byte chunks, so that the waits, the
+    // fence and the arrivals of one block overlap the table lookups of the others.  Chunk
+    // c = half (c & 1) of weight row c >> 1: 32 codes under one scale byte.
+    const int dw = warp - kPairThreads / 32;
+    const int grp = dw / kWarpsPerBlock, sub = dw - grp * kWarpsPerBlock;
+    const int my_tiles = cl < total_tiles ? (total_tiles - cl + ncl - 1) / ncl : 0;
+    const int total_kb = my_tiles * kb_count;
+    const uint32_t *lutl = lut + (lane & (LUTREP - 1));
+    constexpr int kChunkIters = 8 / kWarpsPerBlock;
+    if (grp < kPairStages) {
+      const int stage = grp;
+      uint32_t phase = 0;
+      for (int n = grp; n < total_kb; n += kPairStages, phase ^= 1u) {
+        const int rs = n % kRawStages;
+        const uint32_t rphase = (n / kRawStages) & 1;
         if (!mbar_wait(&raw_full[rs], rphase, abort_flag) ||
             !mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
           set_status(g.status, kStatusWaitTimeoutProducer);
           *abort_flag = 1;
-          ok = false;
           break;
         }
         tc_fence_after();  // the MMAs that read this operand slot are done
         const unsigned char *rq = raw_ring + rs * kRawStageBytes;
-        const uint4 q0 = *reinterpret_cast<const uint4 *>(rq + dt * 16);
-        uint32_t sc = rq[kRawCodeBytes + dt];
-        // codes come out of the table as bf16 values; times 2^(s-127), exact
-        sc = sc ? (sc << 7) : 0x0040u;  // e8m0 0 = 2^-127, a bf16 subnormal
-        const uint32_t mul = sc | (sc << 16);
-        unsigned char *row = smem + stage * kPairStageBytes + wr * 128;
-        const uint32_t words[4] = {q0.x, q0.y, q0.z, q0.w};
-        if (!(g.skip_epilogue & 8))
+        unsigned char *slot = smem + stage * kPairStageBytes;
+        if (!(g.skip_epilogue & 8)) {
+#pragma unroll 2
+          for (int i = 0; i < kChunkIters; i++) {
+            const int c = (sub * kChunkIters + i) * 32 + lane;
+            const int wr = c >> 1, hf = c & 1;
+            const uint4 q0 = *reinterpret_cast<const uint4 *>(rq + c * 16);
+            uint32_t sc = rq[kRawCodeBytes + c];
+            // codes come out of the table as bf16 values; times 2^(s-127), exact
+            sc = sc ? (sc << 7) : 0x0040u;  // e8m0 0 = 2^-127, a bf16 subnormal
+            const uint32_t mul = sc | (sc << 16);
+            unsigned char *row = slot + wr * 128;
+            const uint32_t words[4] = {q0.x, q0.y, q0.z, q0.w};
 #pragma unroll
-        for (int c = 0; c < 4; c++) {  // 8 elements (one packed word) -> one 16-byte chunk
-          const uint32_t w = words[c];
-          uint4 o;
-          o.x = bf16x2_mul(lut[w & 0xffu], mul);
-          o.y = bf16x2_mul(lut[(w >> 8) & 0xffu], mul);
-          o.z = bf16x2_mul(lut[(w >> 16) & 0xffu], mul);
-          o.w = bf16x2_mul(lut[w >> 24], mul);
-          // 128-byte swizzle: 16-byte chunk j of row r sits at chunk j ^ (r & 7)
-          *reinterpret_cast<uint4 *>(row + (((hf * 4 + c) ^ (wr & 7)) << 4)) = o;
+            for (int j = 0; j < 4; j++) {  // 8 elements (one packed word) -> one 16-byte chunk
+              const uint32_t w = words[j];
+              uint4 o;
+              o.x = bf16x2_mul(lutl[(w & 0xffu) * LUTREP], mul);
+              o.y = bf16x2_mul(lutl[((w >> 8) & 0xffu) * LUTREP], mul);
+              o.z = bf16x2_mul(lutl[((w >> 16) & 0xffu) * LUTREP], mul);
+              o.w = bf16x2_mul(lutl[(w >> 24) * LUTREP], mul);
+              // 128-byte swizzle: 16-byte chunk j of row r sits at chunk j ^ (r & 7)
+              *reinterpret_cast<uint4 *>(row + (((hf * 4 + j) ^ (wr & 7)) << 4)) = o;
+            }
+          }
         }
         if (!(g.skip_epilogue & 4)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
@@ -322,14 +346,6 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
             mbar_arrive(&full_bar[stage]);
           else
             mbar_arrive_cluster(&full_bar[stage], 0);
-        }
-        if (++rs == kRawStages) {
-          rs = 0;
-          rphase ^= 1u;
-        }
-        if (++stage == kPairStages) {
-          stage = 0;
-          phase ^= 1u;
         }
       }
     }
@@ -450,13 +466,13 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
   }
 }
 
-template <int EPI, int STAGES, bool MX, int TOKB, int RAWS>
+template <int EPI, int STAGES, bool MX, int TOKB, int RAWS, int LUTREP>
 static cudaError_t launch_pair_stages(gptoss_moe *h, const CUtensorMap &tw, const CUtensorMap *tx,
                                       const GemmArgs &g, cudaStream_t stream) {
   const size_t smem = 1024 + STAGES * (kPairOperandBytes + TOKB * kTileK * 2) + kPairBarrierBytes +
                       PairStage<EPI>::kTotalBytes +
-                      (MX ? RAWS * kRawStageBytes + 1024 : 0);
-  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_pair_kernel<EPI, STAGES, MX, TOKB, RAWS>,
+                      (MX ? RAWS * kRawStageBytes + 1024 * LUTREP : 0);
+  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_pair_kernel<EPI, STAGES, MX, TOKB, RAWS, LUTREP>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg = {};
@@ -472,7 +488,7 @@ static cudaError_t launch_pair_stages(gptoss_moe *h, const CUtensorMap &tw, cons
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   h->launches++;
-  return cudaLaunchKernelEx(&cfg, grouped_gemm_pair_kernel<EPI, STAGES, MX, TOKB, RAWS>, tw, tx[0], tx[1], tx[2],
+  return cudaLaunchKernelEx(&cfg, grouped_gemm_pair_kernel<EPI, STAGES, MX, TOKB, RAWS, LUTREP>, tw, tx[0], tx[1], tx[2],
                             g);
 }
 
@@ -481,21 +497,22 @@ template <int EPI>
 static cudaError_t launch_pair(gptoss_moe *h, const CUtensorMap &tw, const CUtensorMap *tx,
                                const GemmArgs &g, cudaStream_t stream) {
   // MXFP4: the raw ring takes the room of two operand stages; decode-sized batches run
-  // with 64-token tiles, whose small token slots allow a 7-deep operand ring
+  // with 64-token tiles, whose small token slots leave room for one code table per bank
   if (h->cfg.weight_format == GPTOSS_WEIGHTS_MXFP4) {
 #ifndef GPTOSS_NARROW_STAGES
-#define GPTOSS_NARROW_STAGES 7
+#define GPTOSS_NARROW_STAGES 6
 #define GPTOSS_NARROW_RAW 12
+#define GPTOSS_NARROW_LUTREP 16
 #endif
     if (h->cur_tile_rows == 64)
-      return launch_pair_stages<EPI, GPTOSS_NARROW_STAGES, true, 32, GPTOSS_NARROW_RAW>(h, tx[0], tx, g,
-                                                                                      stream);
-    return launch_pair_stages<EPI, 4, true, 128, 12>(h, tx[0], tx, g, stream);
+      return launch_pair_stages<EPI, GPTOSS_NARROW_STAGES, true, 32, GPTOSS_NARROW_RAW,
+                                GPTOSS_NARROW_LUTREP>(h, tx[0], tx, g, stream);
+    return launch_pair_stages<EPI, 4, true, 128, 12, 1>(h, tx[0], tx, g, stream);
   }
   switch (h->opt_pair_stages) {
-    case 4: return launch_pair_stages<EPI, 4, false, 128, 0>(h, tw, tx, g, stream);
-    case 5: return launch_pair_stages<EPI, 5, false, 128, 0>(h, tw, tx, g, stream);
-    default: return launch_pair_stages<EPI, 6, false, 128, 0>(h, tw, tx, g, stream);
+    case 4: return launch_pair_stages<EPI, 4, false, 128, 0, 1>(h, tw, tx, g, stream);
+    case 5: return launch_pair_stages<EPI, 5, false, 128, 0, 1>(h, tw, tx, g, stream);
+    default: return launch_pair_stages<EPI, 6, false, 128, 0, 1>(h, tw, tx, g, stream);
   }
 }
 
