@@ -59,6 +59,18 @@ class MoeError(RuntimeError):
         self.code = code
 
 
+class ModelConfig(ctypes.Structure):
+    """gptoss_model_config_t: the reference's Config / .bin header (run.cpp:26-46)."""
+    _fields_ = [("vocab_size", ctypes.c_int), ("hidden_dim", ctypes.c_int),
+                ("n_experts", ctypes.c_int), ("experts_per_token", ctypes.c_int),
+                ("intermediate_dim", ctypes.c_int), ("n_layers", ctypes.c_int),
+                ("head_dim", ctypes.c_int), ("n_attn_heads", ctypes.c_int),
+                ("n_kv_heads", ctypes.c_int), ("seq_len", ctypes.c_int),
+                ("initial_context_length", ctypes.c_int), ("rope_theta", ctypes.c_float),
+                ("rope_scaling_factor", ctypes.c_float), ("sliding_window", ctypes.c_int),
+                ("swiglu_limit", ctypes.c_float)]
+
+
 _lib = None
 
 
@@ -103,6 +115,15 @@ def load_library() -> ctypes.CDLL:
         "gptoss_moe_ep_transport": (c_int, [vp]),
         "gptoss_moe_version": (c_char_p, []),
         "gptoss_moe_permute_static": (c_int, [vp, vp, c_int, c_int, c_int, vp, vp, vp, vp, vp]),
+        "gptoss_decode_create": (c_int, [ctypes.POINTER(ModelConfig), c_int, c_int,
+                                         ctypes.POINTER(vp)]),
+        "gptoss_decode_destroy": (c_int, [vp]),
+        "gptoss_decode_last_error": (c_char_p, [vp]),
+        "gptoss_decode_load_bin": (c_int, [vp, vp]),
+        "gptoss_decode_load_weights": (c_int, [vp, vp]),
+        "gptoss_decode_step": (c_int, [vp, vp, vp, c_int, vp, vp]),
+        "gptoss_decode_get_logits": (c_int, [vp, c_int, vp]),
+        "gptoss_decode_moe": (vp, [vp]),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(lib, name)
@@ -294,3 +315,56 @@ class MoeEngine:
     def ep_transport(self) -> int:
         """0 = NCCL send/recv, 1 = peer memory, -1 before ep_init."""
         return int(self.lib.gptoss_moe_ep_transport(self.handle))
+
+
+class DecodeEngine:
+    """Mirror of include/gptoss_decode_b200.h: one greedy decode step for a batch of
+    sequences (row i owns KV-cache slot i)."""
+
+    def __init__(self, cfg: dict, max_batch: int, device: int = 0):
+        self.lib = load_library()
+        self.cfg = dict(cfg)
+        self.max_batch = max_batch
+        c = ModelConfig(**cfg)
+        h = ctypes.c_void_p()
+        rc = self.lib.gptoss_decode_create(ctypes.byref(c), max_batch, device, ctypes.byref(h))
+        if rc != 0:
+            raise MoeError(rc, (self.lib.gptoss_decode_last_error(None) or b"").decode())
+        self.handle = h
+
+    def _check(self, rc):
+        if rc != 0:
+            raise MoeError(rc, (self.lib.gptoss_decode_last_error(self.handle) or b"").decode())
+
+    def load_bin(self, image: np.ndarray):
+        """image: the whole .bin file as a uint8/float32 array (e.g. np.memmap); tensors
+        start 60 bytes in."""
+        raw = image.view(np.uint8).reshape(-1)
+        first = raw[60:]
+        self._check(self.lib.gptoss_decode_load_bin(self.handle,
+                                                    ctypes.c_void_p(first.ctypes.data)))
+
+    def step(self, tokens, pos, stream: int = 0):
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+        pos = np.ascontiguousarray(pos, dtype=np.int32)
+        nxt = np.empty(tokens.shape[0], dtype=np.int32)
+        self._check(self.lib.gptoss_decode_step(self.handle, _ptr(tokens), _ptr(pos),
+                                                tokens.shape[0], _ptr(nxt),
+                                                ctypes.c_void_p(stream)))
+        return nxt
+
+    def logits(self, row: int) -> np.ndarray:
+        out = np.empty(self.cfg["vocab_size"], dtype=np.float32)
+        self._check(self.lib.gptoss_decode_get_logits(self.handle, row, _ptr(out)))
+        return out
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.lib.gptoss_decode_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001
+            pass

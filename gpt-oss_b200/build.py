@@ -15,7 +15,7 @@ CSRC = PKG_DIR / "csrc"
 LIB = PKG_DIR / "libgptoss_moe_b200.so"
 
 CU_SOURCES = ["moe_api.cu", "router.cu", "permute.cu", "grouped_gemm.cu", "grouped_gemm_pair.cu",
-              "weights.cu", "mxfp4.cu", "ep.cu"]
+              "weights.cu", "mxfp4.cu", "ep.cu", "decode.cu"]
 HEADERS = ["common.cuh", "engine.h", "ep.h", "gemm_epilogue.cuh", "umma_2sm.cuh"]
 
 NVCC_FLAGS = [
@@ -41,7 +41,8 @@ def _stale(target: pathlib.Path, deps) -> bool:
 def build_library(force: bool = False, verbose: bool = False) -> pathlib.Path:
     """Compile every CUDA source for sm_100a into libgptoss_moe_b200.so."""
     srcs = [CSRC / s for s in CU_SOURCES]
-    deps = srcs + [CSRC / h for h in HEADERS] + [PKG_DIR.parent / "include" / "gptoss_moe_b200.h"]
+    deps = (srcs + [CSRC / h for h in HEADERS] +
+            [PKG_DIR.parent / "include" / n for n in ("gptoss_moe_b200.h", "gptoss_decode_b200.h")])
     if not force and not _stale(LIB, deps):
         return LIB
     cmd = [_nvcc(), *NVCC_FLAGS, "-o", str(LIB), *map(str, srcs), "-ldl"]

@@ -1,0 +1,580 @@
+// Batched greedy decode step around the MoE block: see include/gptoss_decode_b200.h.
+//
+// What runs per step for a batch of B rows (row i = one sequence with its own
+// KV-cache slot), following forward() of the reference (run.cpp:536-766) row by
+// row:
+//   embed_rows_kernel                    x = E[token]                      (run.cpp:550-552)
+//   per layer:
+//     rmsnorm_rows_kernel                t = rmsnorm(x) * w                (run.cpp:556)
+//     cuBLAS GEMM                        qkv = t Wqkv^T                    (run.cpp:568)
+//     qkv_rope_cache_kernel              + bias, rotate q and k, append k,v (run.cpp:571-596)
+//     attn_decode_kernel                 softmax(qK/sqrt(D) | sink) V      (run.cpp:601-647)
+//     cuBLAS GEMM + bias_residual_kernel x += o Wo^T + b_o                 (run.cpp:649-661)
+//     rmsnorm_rows_kernel, gptoss_moe_forward                              (run.cpp:664-750)
+//   rmsnorm_rows_kernel, cuBLAS GEMM     logits = rmsnorm(x) Wout^T        (run.cpp:752-757)
+//   argmax_rows_kernel                   next = argmax (lowest index on ties)
+// Rows with pos < 0 are skipped by every kernel (the GEMMs compute them and the
+// results are ignored).
+#include <cublas_v2.h>
+#include <dlfcn.h>
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/gptoss_decode_b200.h"
+#include "common.cuh"
+#include "engine.h"
+
+namespace gptoss {
+
+struct CublasApi {
+  void *lib = nullptr;
+  cublasStatus_t (*Create)(cublasHandle_t *) = nullptr;
+  cublasStatus_t (*Destroy)(cublasHandle_t) = nullptr;
+  cublasStatus_t (*SetStream)(cublasHandle_t, cudaStream_t) = nullptr;
+  cublasStatus_t (*GemmEx)(cublasHandle_t, cublasOperation_t, cublasOperation_t, int, int, int,
+                           const void *, const void *, cudaDataType, int, const void *,
+                           cudaDataType, int, const void *, void *, cudaDataType, int,
+                           cublasComputeType_t, cublasGemmAlgo_t) = nullptr;
+};
+static CublasApi g_blas;
+
+static bool load_cublas(std::string *err) {
+  if (g_blas.lib) return true;
+  void *lib = dlopen("libcublas.so.12", RTLD_NOW | RTLD_GLOBAL);
+  if (!lib) lib = dlopen("libcublas.so", RTLD_NOW | RTLD_GLOBAL);
+  if (!lib) lib = dlopen("/usr/local/cuda/lib64/libcublas.so.12", RTLD_NOW | RTLD_GLOBAL);
+  if (!lib) {
+    *err = std::string("cannot load cuBLAS: ") + dlerror();
+    return false;
+  }
+#define SYM(field, name)                                                \
+  *reinterpret_cast<void **>(&g_blas.field) = dlsym(lib, name);         \
+  if (!g_blas.field) {                                                  \
+    *err = std::string("cuBLAS symbol missing: ") + name;               \
+    return false;                                                       \
+  }
+  SYM(Create, "cublasCreate_v2")
+  SYM(Destroy, "cublasDestroy_v2")
+  SYM(SetStream, "cublasSetStream_v2")
+  SYM(GemmEx, "cublasGemmEx")
+#undef SYM
+  g_blas.lib = lib;
+  return true;
+}
+
+// x[i, :] = table[token[i], :]
+__global__ void __launch_bounds__(256)
+embed_rows_kernel(bf16 *__restrict__ x, const bf16 *__restrict__ table,
+                  const int *__restrict__ tokens, const int *__restrict__ pos, int B, int H,
+                  int V, int *status) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= B || pos[row] < 0) return;
+  const int tok = tokens[row];
+  if (tok < 0 || tok >= V) {
+    set_status(status, kStatusBadIndex);
+    return;
+  }
+  const uint4 *s4 = reinterpret_cast<const uint4 *>(table + static_cast<size_t>(tok) * H);
+  uint4 *d4 = reinterpret_cast<uint4 *>(x + static_cast<size_t>(row) * H);
+  for (int p = lane; p < (H >> 3); p += 32) d4[p] = __ldg(s4 + p);
+}
+
+// qkv [B, (Hq + 2 Hkv) D] fp32 (rows q | k | v) + bias; q and k rotated
+// (apply_rotary_emb, run.cpp:511-533: pairs (i, i + D/2), cos/sin of pos * inv_freq[i]
+// times the YaRN concentration); q stays fp32, k and v go to the row's cache slot at
+// position pos as bf16.  One CTA per row.
+__global__ void __launch_bounds__(256)
+qkv_rope_cache_kernel(const float *__restrict__ qkv, const float *__restrict__ bias,
+                      const int *__restrict__ pos, const float *__restrict__ inv_freq,
+                      float concentration, float *__restrict__ q_out, bf16 *__restrict__ k_cache,
+                      bf16 *__restrict__ v_cache, int B, int Hq, int Hkv, int D, int S) {
+  const int row = blockIdx.x;
+  const int p = pos[row];
+  if (p < 0) return;
+  const int half = D >> 1;
+  const int dq = Hq * D, dkv = Hkv * D, ld = dq + 2 * dkv;
+  const float *src = qkv + static_cast<size_t>(row) * ld;
+  // rotated pairs of q and k
+  for (int i = threadIdx.x; i < (Hq + Hkv) * half; i += blockDim.x) {
+    const int head = i / half, j = i - head * half;
+    const int base = head * D;  // q heads first, then k heads: contiguous in qkv
+    const float x1 = src[base + j] + bias[base + j];
+    const float x2 = src[base + half + j] + bias[base + half + j];
+    const float ang = static_cast<float>(p) * inv_freq[j];
+    const float c = cosf(ang) * concentration, s = sinf(ang) * concentration;
+    const float o1 = x1 * c - x2 * s, o2 = x2 * c + x1 * s;
+    if (head < Hq) {
+      q_out[static_cast<size_t>(row) * dq + base + j] = o1;
+      q_out[static_cast<size_t>(row) * dq + base + half + j] = o2;
+    } else {
+      const int kb = base - dq;
+      bf16 *dst = k_cache + (static_cast<size_t>(row) * S + p) * dkv;
+      dst[kb + j] = __float2bfloat16_rn(o1);
+      dst[kb + half + j] = __float2bfloat16_rn(o2);
+    }
+  }
+  for (int i = threadIdx.x; i < dkv; i += blockDim.x) {
+    bf16 *dst = v_cache + (static_cast<size_t>(row) * S + p) * dkv;
+    dst[i] = __float2bfloat16_rn(src[dq + dkv + i] + bias[dq + dkv + i]);
+  }
+}
+
+// One warp per (row, query head): online softmax over the cache positions t0..pos plus
+// the head's sink logit, which takes probability mass but has no value row
+// (run.cpp:601-647; the sliding-window mask of even layers, run.cpp:176-183, 619-621,
+// becomes the lower bound t0 = pos - window + 1).  Each lane walks every 32nd position
+// with its own running maximum, sum and D-wide accumulator; the lanes are merged at the
+// end.  Output bf16 [B, Hq D].
+template <int D>
+__global__ void __launch_bounds__(128)
+attn_decode_kernel(const float *__restrict__ q, const bf16 *__restrict__ k_cache,
+                   const bf16 *__restrict__ v_cache, const float *__restrict__ sinks,
+                   const int *__restrict__ pos, bf16 *__restrict__ out, int B, int Hq, int Hkv,
+                   int S, int window) {
+  const int lane = threadIdx.x & 31;
+  const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= B * Hq) return;
+  const int row = w / Hq, h = w - row * Hq;
+  const int p = pos[row];
+  if (p < 0) return;
+  const int kvh = h / (Hq / Hkv);
+  const int dkv = Hkv * D;
+  const int t0 = window > 0 ? max(0, p - window + 1) : 0;
+  float qr[D];
+#pragma unroll
+  for (int i = 0; i < D; i++) qr[i] = q[(static_cast<size_t>(row) * Hq + h) * D + i];
+  const float scale = 1.0f / sqrtf(static_cast<float>(D));
+  float m = -INFINITY, l = 0.f;
+  float acc[D];
+#pragma unroll
+  for (int i = 0; i < D; i++) acc[i] = 0.f;
+  for (int t = t0 + lane; t <= p; t += 32) {
+    const size_t off = (static_cast<size_t>(row) * S + t) * dkv + kvh * D;
+    const uint4 *k4 = reinterpret_cast<const uint4 *>(k_cache + off);
+    float s = 0.f;
+#pragma unroll
+    for (int c = 0; c < D / 8; c++) {
+      const uint4 v = __ldg(k4 + c);
+      s += qr[8 * c + 0] * bf16_lo(v.x) + qr[8 * c + 1] * bf16_hi(v.x) +
+           qr[8 * c + 2] * bf16_lo(v.y) + qr[8 * c + 3] * bf16_hi(v.y) +
+           qr[8 * c + 4] * bf16_lo(v.z) + qr[8 * c + 5] * bf16_hi(v.z) +
+           qr[8 * c + 6] * bf16_lo(v.w) + qr[8 * c + 7] * bf16_hi(v.w);
+    }
+    s *= scale;
+    const float m_new = fmaxf(m, s);
+    const float corr = __expf(m - m_new), pr = __expf(s - m_new);
+    l = l * corr + pr;
+    const uint4 *v4 = reinterpret_cast<const uint4 *>(v_cache + off);
+#pragma unroll
+    for (int c = 0; c < D / 8; c++) {
+      const uint4 v = __ldg(v4 + c);
+      acc[8 * c + 0] = acc[8 * c + 0] * corr + pr * bf16_lo(v.x);
+      acc[8 * c + 1] = acc[8 * c + 1] * corr + pr * bf16_hi(v.x);
+      acc[8 * c + 2] = acc[8 * c + 2] * corr + pr * bf16_lo(v.y);
+      acc[8 * c + 3] = acc[8 * c + 3] * corr + pr * bf16_hi(v.y);
+      acc[8 * c + 4] = acc[8 * c + 4] * corr + pr * bf16_lo(v.z);
+      acc[8 * c + 5] = acc[8 * c + 5] * corr + pr * bf16_hi(v.z);
+      acc[8 * c + 6] = acc[8 * c + 6] * corr + pr * bf16_lo(v.w);
+      acc[8 * c + 7] = acc[8 * c + 7] * corr + pr * bf16_hi(v.w);
+    }
+    m = m_new;
+  }
+  // merge the lanes: common maximum (the sink logit included), rescaled sums
+  float m_all = m;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) m_all = fmaxf(m_all, __shfl_xor_sync(0xffffffffu, m_all, off));
+  const float sink = sinks[h];
+  m_all = fmaxf(m_all, sink);
+  const float mine = (m == -INFINITY) ? 0.f : __expf(m - m_all);
+  l *= mine;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+  l += __expf(sink - m_all);
+  const float inv = 1.0f / l;
+  bf16 *dst = out + (static_cast<size_t>(row) * Hq + h) * D;
+#pragma unroll
+  for (int i = 0; i < D; i++) {
+    float a = acc[i] * mine;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
+    if (lane == (i & 31)) dst[i] = __float2bfloat16_rn(a * inv);
+  }
+}
+
+// x[row] = bf16(x[row] + proj[row] + bias) for active rows.
+__global__ void __launch_bounds__(256)
+bias_residual_kernel(bf16 *__restrict__ x, const float *__restrict__ proj,
+                     const float *__restrict__ bias, const int *__restrict__ pos, int B, int H) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= static_cast<size_t>(B) * H) return;
+  const int row = static_cast<int>(i / H), c = static_cast<int>(i - static_cast<size_t>(row) * H);
+  if (pos[row] < 0) return;
+  x[i] = __float2bfloat16_rn(__bfloat162float(x[i]) + proj[i] + bias[c]);
+}
+
+// next[row] = index of the largest logit, lowest index among equals; -1 on inactive rows.
+__global__ void __launch_bounds__(256)
+argmax_rows_kernel(const float *__restrict__ logits, const int *__restrict__ pos,
+                   int *__restrict__ next, int V) {
+  const int row = blockIdx.x;
+  if (pos[row] < 0) {
+    if (threadIdx.x == 0) next[row] = -1;
+    return;
+  }
+  const float *l = logits + static_cast<size_t>(row) * V;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = l[i];
+    if (v > best || (v == best && i < bi)) {
+      best = v;
+      bi = i;
+    }
+  }
+  __shared__ float sv[256];
+  __shared__ int si[256];
+  sv[threadIdx.x] = best;
+  si[threadIdx.x] = bi;
+  __syncthreads();
+  for (int s = 128; s > 0; s >>= 1) {
+    if (threadIdx.x < s) {
+      const float v = sv[threadIdx.x + s];
+      const int i = si[threadIdx.x + s];
+      if (v > sv[threadIdx.x] || (v == sv[threadIdx.x] && i < si[threadIdx.x])) {
+        sv[threadIdx.x] = v;
+        si[threadIdx.x] = i;
+      }
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) next[row] = si[0] == 0x7fffffff ? 0 : si[0];
+}
+
+}  // namespace gptoss
+
+using namespace gptoss;
+
+struct gptoss_decode {
+  gptoss_model_config_t cfg;
+  int max_batch = 0, device = 0;
+  gptoss_moe *moe = nullptr;
+  cublasHandle_t blas = nullptr;
+  bool loaded = false;
+  // weights
+  bf16 *emb = nullptr, *unemb = nullptr, *w_qkv = nullptr, *w_o = nullptr;
+  float *rms_attn = nullptr, *rms_ffn = nullptr, *rms_out = nullptr;
+  float *b_qkv = nullptr, *b_o = nullptr, *sinks = nullptr, *inv_freq = nullptr;
+  float concentration = 1.f;
+  // state
+  bf16 *x = nullptr, *t = nullptr, *attn = nullptr, *k_cache = nullptr, *v_cache = nullptr;
+  float *qkv = nullptr, *q = nullptr, *proj = nullptr, *logits = nullptr;
+  int *d_tokens = nullptr, *d_pos = nullptr, *d_next = nullptr, *status = nullptr;
+  int *h_pinned = nullptr;  // tokens | pos | next, max_batch each
+  std::string err;
+};
+
+static thread_local std::string g_decode_create_err;
+
+static int dfail(gptoss_decode *h, int code, const char *fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  if (h)
+    h->err = buf;
+  else
+    g_decode_create_err = buf;
+  return code;
+}
+
+#define DCK(h, call)                                                                  \
+  do {                                                                                \
+    cudaError_t e__ = (call);                                                         \
+    if (e__ != cudaSuccess)                                                           \
+      return dfail((h), GPTOSS_E_CUDA, "%s: %s", #call, cudaGetErrorString(e__));     \
+  } while (0)
+
+template <typename T>
+static cudaError_t dalloc(T **p, size_t n) {
+  return cudaMalloc(reinterpret_cast<void **>(p), (n ? n : 1) * sizeof(T));
+}
+
+// inv_freq and concentration exactly as the reference computes them on the host
+// (compute_concentration_and_inv_freq, run.cpp:423-474; ntk_beta 32, ntk_alpha 1,
+// run.cpp:583-584), in float.
+static void rope_tables(const gptoss_model_config_t &c, std::vector<float> *inv_freq,
+                        float *concentration) {
+  const int d_half = c.head_dim / 2;
+  const float base = c.rope_theta, sf = c.rope_scaling_factor;
+  const float ctx = static_cast<float>(c.initial_context_length);
+  const float ntk_beta = 32.0f, ntk_alpha = 1.0f;
+  inv_freq->resize(d_half);
+  std::vector<float> freq(d_half);
+  for (int i = 0; i < d_half; i++)
+    freq[i] = powf(base, static_cast<float>(2 * i) / static_cast<float>(c.head_dim));
+  if (sf > 1.0f) {
+    *concentration = 0.1f * logf(sf) + 1.0f;
+    const float low = d_half * logf(ctx / (ntk_beta * 2.0f * M_PI)) / logf(base);
+    const float high = d_half * logf(ctx / (ntk_alpha * 2.0f * M_PI)) / logf(base);
+    for (int i = 0; i < d_half; i++) {
+      const float interpolation = 1.0f / (sf * freq[i]);
+      const float extrapolation = 1.0f / freq[i];
+      float ramp = (static_cast<float>(i) - low) / (high - low);
+      ramp = ramp < 0 ? 0 : (ramp > 1 ? 1 : ramp);
+      const float mask = 1.0f - ramp;
+      (*inv_freq)[i] = interpolation * (1.0f - mask) + extrapolation * mask;
+    }
+  } else {
+    *concentration = 1.0f;
+    for (int i = 0; i < d_half; i++) (*inv_freq)[i] = 1.0f / freq[i];
+  }
+}
+
+extern "C" {
+
+const char *gptoss_decode_last_error(const gptoss_decode_t *h) {
+  return h ? h->err.c_str() : g_decode_create_err.c_str();
+}
+
+gptoss_moe_t *gptoss_decode_moe(gptoss_decode_t *h) { return h ? h->moe : nullptr; }
+
+int gptoss_decode_destroy(gptoss_decode_t *h) {
+  if (!h) return GPTOSS_OK;
+  cudaSetDevice(h->device);
+  if (h->moe) gptoss_moe_destroy(h->moe);
+  if (h->blas) g_blas.Destroy(h->blas);
+  cudaFree(h->emb); cudaFree(h->unemb); cudaFree(h->w_qkv); cudaFree(h->w_o);
+  cudaFree(h->rms_attn); cudaFree(h->rms_ffn); cudaFree(h->rms_out); cudaFree(h->b_qkv);
+  cudaFree(h->b_o); cudaFree(h->sinks); cudaFree(h->inv_freq); cudaFree(h->x); cudaFree(h->t);
+  cudaFree(h->attn); cudaFree(h->k_cache); cudaFree(h->v_cache); cudaFree(h->qkv); cudaFree(h->q);
+  cudaFree(h->proj); cudaFree(h->logits); cudaFree(h->d_tokens); cudaFree(h->d_pos);
+  cudaFree(h->d_next); cudaFree(h->status);
+  if (h->h_pinned) cudaFreeHost(h->h_pinned);
+  delete h;
+  return GPTOSS_OK;
+}
+
+int gptoss_decode_create(const gptoss_model_config_t *cfg, int max_batch, int device,
+                         gptoss_decode_t **out) {
+  if (!cfg || !out) return dfail(nullptr, GPTOSS_E_INVALID, "null argument");
+  *out = nullptr;
+  const gptoss_model_config_t &c = *cfg;
+  if (c.vocab_size <= 0 || c.hidden_dim <= 0 || c.n_layers <= 0 || c.head_dim <= 0 ||
+      c.n_attn_heads <= 0 || c.n_kv_heads <= 0 || c.seq_len <= 0 || max_batch <= 0)
+    return dfail(nullptr, GPTOSS_E_INVALID, "non-positive dimension");
+  if (c.head_dim != 32 && c.head_dim != 64 && c.head_dim != 128)
+    return dfail(nullptr, GPTOSS_E_INVALID, "head_dim must be 32, 64 or 128");
+  if (c.n_attn_heads % c.n_kv_heads)
+    return dfail(nullptr, GPTOSS_E_INVALID, "n_attn_heads must be a multiple of n_kv_heads");
+  if (c.hidden_dim % 8)
+    return dfail(nullptr, GPTOSS_E_INVALID, "hidden_dim must be a multiple of 8");
+  gptoss_moe_config_t mc = {};
+  mc.hidden_dim = c.hidden_dim;
+  mc.intermediate_dim = c.intermediate_dim;
+  mc.n_experts = c.n_experts;
+  mc.experts_per_token = c.experts_per_token;
+  mc.n_layers = c.n_layers;
+  mc.max_tokens = max_batch;
+  mc.swiglu_limit = c.swiglu_limit;
+  mc.ep_rank = 0;
+  mc.ep_size = 1;
+  mc.weight_format = GPTOSS_WEIGHTS_BF16;
+  mc.device = device;
+  gptoss_moe *moe = nullptr;
+  int rc = gptoss_moe_create(&mc, &moe);
+  if (rc != GPTOSS_OK) return dfail(nullptr, rc, "MoE engine: %s", gptoss_moe_last_error(nullptr));
+  gptoss_decode *h = new gptoss_decode();
+  h->cfg = c;
+  h->max_batch = max_batch;
+  h->device = device;
+  h->moe = moe;
+  auto bail = [&](int code, const std::string &msg) {
+    g_decode_create_err = msg;
+    gptoss_decode_destroy(h);
+    return code;
+  };
+  std::string err;
+  if (!load_cublas(&err)) return bail(GPTOSS_E_STATE, err);
+  if (g_blas.Create(&h->blas) != CUBLAS_STATUS_SUCCESS) return bail(GPTOSS_E_CUDA, "cublasCreate failed");
+  const size_t V = c.vocab_size, H = c.hidden_dim, L = c.n_layers, D = c.head_dim;
+  const size_t dq = c.n_attn_heads * D, dkv = c.n_kv_heads * D, B = max_batch, S = c.seq_len;
+  cudaError_t e = cudaSuccess;
+  auto A = [&](cudaError_t r) { if (e == cudaSuccess) e = r; };
+  A(dalloc(&h->emb, V * H)); A(dalloc(&h->unemb, V * H));
+  A(dalloc(&h->w_qkv, L * (dq + 2 * dkv) * H)); A(dalloc(&h->w_o, L * H * dq));
+  A(dalloc(&h->rms_attn, L * H)); A(dalloc(&h->rms_ffn, L * H)); A(dalloc(&h->rms_out, H));
+  A(dalloc(&h->b_qkv, L * (dq + 2 * dkv))); A(dalloc(&h->b_o, L * H));
+  A(dalloc(&h->sinks, L * c.n_attn_heads)); A(dalloc(&h->inv_freq, D / 2));
+  A(dalloc(&h->x, B * H)); A(dalloc(&h->t, B * H)); A(dalloc(&h->attn, B * dq));
+  A(dalloc(&h->k_cache, L * B * S * dkv)); A(dalloc(&h->v_cache, L * B * S * dkv));
+  A(dalloc(&h->qkv, B * (dq + 2 * dkv))); A(dalloc(&h->q, B * dq)); A(dalloc(&h->proj, B * H));
+  A(dalloc(&h->logits, B * V));
+  A(dalloc(&h->d_tokens, B)); A(dalloc(&h->d_pos, B)); A(dalloc(&h->d_next, B));
+  A(dalloc(&h->status, 1));
+  A(cudaMallocHost(reinterpret_cast<void **>(&h->h_pinned), 3 * B * sizeof(int)));
+  if (e == cudaSuccess) e = cudaMemset(h->status, 0, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(h->x, 0, B * H * sizeof(bf16));
+  if (e != cudaSuccess) return bail(GPTOSS_E_CUDA, std::string("allocation: ") + cudaGetErrorString(e));
+  std::vector<float> inv;
+  rope_tables(c, &inv, &h->concentration);
+  e = cudaMemcpy(h->inv_freq, inv.data(), inv.size() * 4, cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) return bail(GPTOSS_E_CUDA, cudaGetErrorString(e));
+  *out = h;
+  return GPTOSS_OK;
+}
+
+int gptoss_decode_load_weights(gptoss_decode_t *h, const gptoss_model_weights_t *w) {
+  if (!h || !w) return GPTOSS_E_INVALID;
+  const gptoss_model_config_t &c = h->cfg;
+  const size_t V = c.vocab_size, H = c.hidden_dim, L = c.n_layers, D = c.head_dim;
+  const size_t dq = c.n_attn_heads * D, dkv = c.n_kv_heads * D;
+  const size_t E = c.n_experts, IM = c.intermediate_dim;
+  DCK(h, cudaSetDevice(h->device));
+  int rc;
+  if ((rc = upload_f32_as_bf16(h->moe, h->emb, w->token_embedding_table, V * H)) ||
+      (rc = upload_f32_as_bf16(h->moe, h->unemb, w->out, V * H)) ||
+      (rc = upload_f32_as_bf16(h->moe, h->w_qkv, w->w_qkv, L * (dq + 2 * dkv) * H)) ||
+      (rc = upload_f32_as_bf16(h->moe, h->w_o, w->w_o, L * H * dq)))
+    return dfail(h, rc, "weight upload: %s", gptoss_moe_last_error(h->moe));
+  DCK(h, cudaMemcpy(h->rms_attn, w->rms_attn_w, L * H * 4, cudaMemcpyHostToDevice));
+  DCK(h, cudaMemcpy(h->rms_ffn, w->rms_ffn_w, L * H * 4, cudaMemcpyHostToDevice));
+  DCK(h, cudaMemcpy(h->rms_out, w->rms_out_w, H * 4, cudaMemcpyHostToDevice));
+  DCK(h, cudaMemcpy(h->b_qkv, w->b_qkv, L * (dq + 2 * dkv) * 4, cudaMemcpyHostToDevice));
+  DCK(h, cudaMemcpy(h->b_o, w->b_o, L * H * 4, cudaMemcpyHostToDevice));
+  DCK(h, cudaMemcpy(h->sinks, w->attn_sinks, L * c.n_attn_heads * 4, cudaMemcpyHostToDevice));
+  for (size_t l = 0; l < L; l++) {
+    rc = gptoss_moe_load_layer_f32(h->moe, static_cast<int>(l), w->w_router + l * E * H,
+                                   w->b_router + l * E, w->w_mlp1 + l * E * 2 * IM * H,
+                                   w->b_mlp1 + l * E * 2 * IM, w->w_mlp2 + l * E * H * IM,
+                                   w->b_mlp2 + l * E * H);
+    if (rc) return dfail(h, rc, "MoE layer %d: %s", static_cast<int>(l), gptoss_moe_last_error(h->moe));
+  }
+  h->loaded = true;
+  return GPTOSS_OK;
+}
+
+int gptoss_decode_load_bin(gptoss_decode_t *h, const float *p) {
+  if (!h || !p) return GPTOSS_E_INVALID;
+  const gptoss_model_config_t &c = h->cfg;
+  const size_t V = c.vocab_size, H = c.hidden_dim, L = c.n_layers, D = c.head_dim;
+  const size_t dqkv = (c.n_attn_heads + 2 * c.n_kv_heads) * D, dq = c.n_attn_heads * D;
+  const size_t E = c.n_experts, IM = c.intermediate_dim;
+  gptoss_model_weights_t w;
+  // the file's order (memory_map_weights, run.cpp:207-248)
+  w.token_embedding_table = p; p += V * H;
+  w.out = p;                   p += V * H;
+  w.rms_attn_w = p;            p += L * H;
+  w.rms_ffn_w = p;             p += L * H;
+  w.rms_out_w = p;             p += H;
+  w.w_qkv = p;                 p += L * H * dqkv;
+  w.b_qkv = p;                 p += L * dqkv;
+  w.w_o = p;                   p += L * dq * H;
+  w.b_o = p;                   p += L * H;
+  w.attn_sinks = p;            p += L * c.n_attn_heads;
+  w.w_router = p;              p += L * H * E;
+  w.b_router = p;              p += L * E;
+  w.w_mlp1 = p;                p += L * E * 2 * IM * H;
+  w.b_mlp1 = p;                p += L * E * 2 * IM;
+  w.w_mlp2 = p;                p += L * E * H * IM;
+  w.b_mlp2 = p;
+  return gptoss_decode_load_weights(h, &w);
+}
+
+// C[B, N] (fp32) = X[B, K] (bf16) . W[N, K]^T (bf16)
+static int gemm_xwt(gptoss_decode *h, const bf16 *x, const bf16 *w, float *c, int B, int N, int K) {
+  const float one = 1.f, zero = 0.f;
+  cublasStatus_t s = g_blas.GemmEx(h->blas, CUBLAS_OP_T, CUBLAS_OP_N, N, B, K, &one, w,
+                                   CUDA_R_16BF, K, x, CUDA_R_16BF, K, &zero, c, CUDA_R_32F, N,
+                                   CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
+  if (s != CUBLAS_STATUS_SUCCESS) return dfail(h, GPTOSS_E_CUDA, "cublasGemmEx failed (%d)", (int)s);
+  return GPTOSS_OK;
+}
+
+int gptoss_decode_step(gptoss_decode_t *h, const int *tokens, const int *pos, int B, int *next,
+                       void *stream) {
+  if (!h || !tokens || !pos || !next) return GPTOSS_E_INVALID;
+  if (!h->loaded) return dfail(h, GPTOSS_E_STATE, "weights not loaded");
+  if (B < 0 || B > h->max_batch) return dfail(h, GPTOSS_E_CAPACITY, "batch %d > max_batch %d", B, h->max_batch);
+  if (B == 0) return GPTOSS_OK;
+  const gptoss_model_config_t &c = h->cfg;
+  for (int i = 0; i < B; i++)
+    if (pos[i] >= c.seq_len) return dfail(h, GPTOSS_E_CAPACITY, "row %d: position %d >= seq_len %d", i, pos[i], c.seq_len);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  DCK(h, cudaSetDevice(h->device));
+  if (g_blas.SetStream(h->blas, st) != CUBLAS_STATUS_SUCCESS) return dfail(h, GPTOSS_E_CUDA, "cublasSetStream failed");
+  const int H = c.hidden_dim, D = c.head_dim, Hq = c.n_attn_heads, Hkv = c.n_kv_heads;
+  const int dq = Hq * D, dkv = Hkv * D, S = c.seq_len, V = c.vocab_size;
+  int *hp = h->h_pinned;
+  memcpy(hp, tokens, B * sizeof(int));
+  memcpy(hp + h->max_batch, pos, B * sizeof(int));
+  DCK(h, cudaMemcpyAsync(h->d_tokens, hp, B * sizeof(int), cudaMemcpyHostToDevice, st));
+  DCK(h, cudaMemcpyAsync(h->d_pos, hp + h->max_batch, B * sizeof(int), cudaMemcpyHostToDevice, st));
+  const int warps = 8;
+  embed_rows_kernel<<<(B + warps - 1) / warps, warps * 32, 0, st>>>(h->x, h->emb, h->d_tokens,
+                                                                   h->d_pos, B, H, V, h->status);
+  DCK(h, cudaGetLastError());
+  int rc;
+  for (int l = 0; l < c.n_layers; l++) {
+    DCK(h, launch_rmsnorm(h->t, h->x, h->rms_attn + static_cast<size_t>(l) * H, h->d_pos, B, H, st, nullptr));
+    if ((rc = gemm_xwt(h, h->t, h->w_qkv + static_cast<size_t>(l) * (dq + 2 * dkv) * H, h->qkv, B,
+                       dq + 2 * dkv, H)))
+      return rc;
+    bf16 *kc = h->k_cache + static_cast<size_t>(l) * h->max_batch * S * dkv;
+    bf16 *vc = h->v_cache + static_cast<size_t>(l) * h->max_batch * S * dkv;
+    qkv_rope_cache_kernel<<<B, 256, 0, st>>>(h->qkv, h->b_qkv + static_cast<size_t>(l) * (dq + 2 * dkv),
+                                             h->d_pos, h->inv_freq, h->concentration, h->q, kc, vc,
+                                             B, Hq, Hkv, D, S);
+    DCK(h, cudaGetLastError());
+    // sliding window on even layers (run.cpp:619)
+    const int window = (c.sliding_window > 0 && (l % 2 == 0)) ? c.sliding_window : 0;
+    const int nw = B * Hq, grid = (nw + 3) / 4;
+    const float *sinks = h->sinks + static_cast<size_t>(l) * Hq;
+    if (D == 32)
+      attn_decode_kernel<32><<<grid, 128, 0, st>>>(h->q, kc, vc, sinks, h->d_pos, h->attn, B, Hq, Hkv, S, window);
+    else if (D == 64)
+      attn_decode_kernel<64><<<grid, 128, 0, st>>>(h->q, kc, vc, sinks, h->d_pos, h->attn, B, Hq, Hkv, S, window);
+    else
+      attn_decode_kernel<128><<<grid, 128, 0, st>>>(h->q, kc, vc, sinks, h->d_pos, h->attn, B, Hq, Hkv, S, window);
+    DCK(h, cudaGetLastError());
+    if ((rc = gemm_xwt(h, h->attn, h->w_o + static_cast<size_t>(l) * H * dq, h->proj, B, H, dq))) return rc;
+    const size_t n = static_cast<size_t>(B) * H;
+    bias_residual_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(
+        h->x, h->proj, h->b_o + static_cast<size_t>(l) * H, h->d_pos, B, H);
+    DCK(h, cudaGetLastError());
+    DCK(h, launch_rmsnorm(h->t, h->x, h->rms_ffn + static_cast<size_t>(l) * H, h->d_pos, B, H, st, nullptr));
+    rc = gptoss_moe_forward(h->moe, l, h->t, h->x, h->d_pos, B, st);
+    if (rc) return dfail(h, rc, "MoE layer %d: %s", l, gptoss_moe_last_error(h->moe));
+  }
+  DCK(h, launch_rmsnorm(h->t, h->x, h->rms_out, h->d_pos, B, H, st, nullptr));
+  if ((rc = gemm_xwt(h, h->t, h->unemb, h->logits, B, V, H))) return rc;
+  argmax_rows_kernel<<<B, 256, 0, st>>>(h->logits, h->d_pos, h->d_next, V);
+  DCK(h, cudaGetLastError());
+  DCK(h, cudaMemcpyAsync(hp + 2 * h->max_batch, h->d_next, B * sizeof(int), cudaMemcpyDeviceToHost, st));
+  DCK(h, cudaStreamSynchronize(st));
+  memcpy(next, hp + 2 * h->max_batch, B * sizeof(int));
+  int dev_status = 0;
+  DCK(h, cudaMemcpy(&dev_status, h->status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (dev_status) {
+    cudaMemset(h->status, 0, sizeof(int));
+    return dfail(h, GPTOSS_E_DEVICE, "a decode kernel reported status %d (token id out of range?)", dev_status);
+  }
+  return GPTOSS_OK;
+}
+
+int gptoss_decode_get_logits(gptoss_decode_t *h, int row, float *logits_host) {
+  if (!h || !logits_host) return GPTOSS_E_INVALID;
+  if (row < 0 || row >= h->max_batch) return dfail(h, GPTOSS_E_INVALID, "row out of range");
+  DCK(h, cudaSetDevice(h->device));
+  DCK(h, cudaMemcpy(logits_host, h->logits + static_cast<size_t>(row) * h->cfg.vocab_size,
+                    sizeof(float) * h->cfg.vocab_size, cudaMemcpyDeviceToHost));
+  return GPTOSS_OK;
+}
+
+}  // extern "C"

@@ -166,3 +166,7 @@ cudaError_t launch_f32_to_bf16(bf16 *dst, const float *src, size_t n, cudaStream
                                long long *launches);
 
 }  // namespace gptoss
+
+// moe_api.cu: fp32 host tensor -> bf16 device tensor (round to nearest even) through a
+// pinned double buffer; errors go to the handle's error text
+extern "C" int upload_f32_as_bf16(gptoss_moe *h, gptoss::bf16 *dst, const float *src, size_t n);

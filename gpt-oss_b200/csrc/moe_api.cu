@@ -205,8 +205,9 @@ static int finish_layer(gptoss_moe *h, LayerWeights &lw) {
   return GPTOSS_OK;
 }
 
-// fp32 host -> bf16 device through a pinned double buffer.
-static int upload_f32_as_bf16(gptoss_moe *h, bf16 *dst, const float *src, size_t n) {
+// fp32 host -> bf16 device through a pinned double buffer (not part of the public
+// header; the decode engine's loader uses it too).
+int upload_f32_as_bf16(gptoss_moe *h, bf16 *dst, const float *src, size_t n) {
   const size_t chunk = (size_t)8 << 20;  // elements per chunk (32 MB of fp32)
   float *pinned[2] = {nullptr, nullptr}, *dtmp[2] = {nullptr, nullptr};
   cudaStream_t st;

@@ -113,3 +113,68 @@ def mxfp4_dequant(blocks, scales):
     vals = np.stack([lo, hi], axis=-1).reshape(*blocks.shape[:-1], blocks.shape[-1] * 2)
     s = np.exp2(scales.astype(np.float32) - 127.0)
     return (vals.reshape(*scales.shape, 32) * s[..., None]).reshape(vals.shape).astype(np.float32)
+
+
+# ---------------------------------------------------------------- whole models (.bin)
+# Field order of the reference's Config = header of the .bin file (run.cpp:26-46).
+MODEL_CONFIG_FIELDS = (
+    ("vocab_size", "i"), ("hidden_dim", "i"), ("n_experts", "i"), ("experts_per_token", "i"),
+    ("intermediate_dim", "i"), ("n_layers", "i"), ("head_dim", "i"), ("n_attn_heads", "i"),
+    ("n_kv_heads", "i"), ("seq_len", "i"), ("initial_context_length", "i"), ("rope_theta", "f"),
+    ("rope_scaling_factor", "f"), ("sliding_window", "i"), ("swiglu_limit", "f"),
+)
+
+# The tiny GPT-OSS-architecture model of the benchmark description (2 layers, hidden 128,
+# 4 query / 2 KV heads of 32, 8 experts top-4, vocabulary 201088); rope constants of the
+# reference's 7m export.
+TINY_MODEL = dict(vocab_size=201088, hidden_dim=128, n_experts=8, experts_per_token=4,
+                  intermediate_dim=128, n_layers=2, head_dim=32, n_attn_heads=4, n_kv_heads=2,
+                  seq_len=64, initial_context_length=4096, rope_theta=150000.0,
+                  rope_scaling_factor=32.0, sliding_window=128, swiglu_limit=7.0)
+# Same architecture with a small vocabulary, wider heads and a window short enough to bite.
+MINI_MODEL = dict(vocab_size=1000, hidden_dim=128, n_experts=8, experts_per_token=4,
+                  intermediate_dim=64, n_layers=3, head_dim=64, n_attn_heads=4, n_kv_heads=2,
+                  seq_len=64, initial_context_length=4096, rope_theta=150000.0,
+                  rope_scaling_factor=32.0, sliding_window=8, swiglu_limit=7.0)
+
+
+def model_tensors(cfg: dict, seed: int = 0):
+    """Random-init tensors of a whole model in the order of the .bin file
+    (memory_map_weights, run.cpp:207-248): weights bf16-exact N(0, 0.02), biases
+    N(0, 0.01), norm scales 1, sinks N(0, 0.02).  List of (name, float32 array)."""
+    rng = np.random.Generator(np.random.PCG64(seed))
+    V, H, L = cfg["vocab_size"], cfg["hidden_dim"], cfg["n_layers"]
+    D, Hq, Hkv = cfg["head_dim"], cfg["n_attn_heads"], cfg["n_kv_heads"]
+    E, IM = cfg["n_experts"], cfg["intermediate_dim"]
+    dqkv = (Hq + 2 * Hkv) * D
+
+    def w(*shape):
+        return bf16_round(rng.standard_normal(shape, dtype=np.float32) * np.float32(0.02))
+
+    def b(*shape):
+        return bf16_round(rng.standard_normal(shape, dtype=np.float32) * np.float32(0.01))
+
+    return [
+        ("token_embedding_table", w(V, H)), ("out", w(V, H)),
+        ("rms_attn_w", np.ones((L, H), np.float32)), ("rms_ffn_w", np.ones((L, H), np.float32)),
+        ("rms_out_w", np.ones((H,), np.float32)),
+        ("w_qkv", w(L, dqkv, H)), ("b_qkv", b(L, dqkv)),
+        ("w_o", w(L, H, Hq * D)), ("b_o", b(L, H)), ("attn_sinks", w(L, Hq)),
+        ("w_router", w(L, E, H)), ("b_router", b(L, E)),
+        ("w_mlp1", w(L, E, 2 * IM, H)), ("b_mlp1", b(L, E, 2 * IM)),
+        ("w_mlp2", w(L, E, H, IM)), ("b_mlp2", b(L, E, H)),
+    ]
+
+
+def write_model_bin(path, cfg: dict, seed: int = 0):
+    """Writes a checkpoint in the reference's .bin layout: the 60-byte Config header, then
+    little-endian fp32 tensors.  Returns the tensors as a dict."""
+    import struct
+
+    tensors = model_tensors(cfg, seed)
+    with open(path, "wb") as f:
+        for name, kind in MODEL_CONFIG_FIELDS:
+            f.write(struct.pack("<" + kind, cfg[name]))
+        for _, a in tensors:
+            f.write(np.ascontiguousarray(a, dtype="<f4").tobytes())
+    return dict(tensors)

@@ -1,0 +1,105 @@
+/*
+ * gptoss_decode_b200.h - C ABI of the batched greedy decode step around the MoE block.
+ *
+ * One call = one token for each of up to max_batch sequences: embedding gather,
+ * and per layer RMSNorm, QKV projection + bias, YaRN rotary embedding, KV-cache
+ * append, attention over the cache with a per-head sink logit (128-token sliding
+ * window on even layers), output projection + bias + residual, RMSNorm, the MoE
+ * block (gptoss_moe_b200.h), then the final RMSNorm, the logits and their argmax.
+ * It replaces gpu_forward_device_batch of the reference's getp engine
+ * (getp-csrc/getp_run.cpp:501-894) and computes what forward() computes for one
+ * sequence (run.cpp:536-766), for every row of the batch.
+ *
+ * The dense projections (QKV, attention output, logits) are plain GEMMs and go
+ * through cuBLAS (bf16 operands, fp32 accumulate and output), loaded with dlopen
+ * at gptoss_decode_create.  Everything else is this library's own kernels.
+ * Activations between kernels: the residual stream and the normalised rows are
+ * bf16 (the MoE block's interface), q, the attention logits and the projection
+ * outputs fp32, the KV cache bf16.
+ */
+#ifndef GPTOSS_DECODE_B200_H
+#define GPTOSS_DECODE_B200_H
+
+#include "gptoss_moe_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* The reference's Config, which is also the header of the .bin checkpoint
+ * (run.cpp:26-46): 15 four-byte fields in this order. */
+typedef struct {
+  int vocab_size;
+  int hidden_dim;
+  int n_experts;
+  int experts_per_token;
+  int intermediate_dim;
+  int n_layers;
+  int head_dim;
+  int n_attn_heads;
+  int n_kv_heads;
+  int seq_len;
+  int initial_context_length;
+  float rope_theta;
+  float rope_scaling_factor;
+  int sliding_window;
+  float swiglu_limit;
+} gptoss_model_config_t;
+
+/* The reference's TransformerWeights (run.cpp:48-84): fp32 tensors on the host,
+ * normally pointers into the mmap of the .bin file.  Shapes as in run.cpp:207-248. */
+typedef struct {
+  const float *token_embedding_table; /* [V, H] */
+  const float *rms_attn_w;            /* [L, H] */
+  const float *rms_ffn_w;             /* [L, H] */
+  const float *w_qkv;                 /* [L, (Hq + 2 Hkv) D, H], rows q | k | v */
+  const float *w_o;                   /* [L, H, Hq D] */
+  const float *b_qkv;                 /* [L, (Hq + 2 Hkv) D] */
+  const float *b_o;                   /* [L, H] */
+  const float *attn_sinks;            /* [L, Hq] */
+  const float *w_router;              /* [L, E, H] */
+  const float *b_router;              /* [L, E] */
+  const float *w_mlp1;                /* [L, E, 2 IM, H], gate rows even, up rows odd */
+  const float *w_mlp2;                /* [L, E, H, IM] */
+  const float *b_mlp1;                /* [L, E, 2 IM] */
+  const float *b_mlp2;                /* [L, E, H] */
+  const float *rms_out_w;             /* [H] */
+  const float *out;                   /* [V, H] unembedding */
+} gptoss_model_weights_t;
+
+typedef struct gptoss_decode gptoss_decode_t;
+
+/* Allocates everything for max_batch sequences of up to cfg->seq_len positions on
+ * `device` (KV cache: L * max_batch * seq_len * Hkv * D * 2 bf16).  No CPU
+ * fallback: fails unless the device is sm_100 and cuBLAS can be loaded. */
+int gptoss_decode_create(const gptoss_model_config_t *cfg, int max_batch, int device,
+                         gptoss_decode_t **out);
+int gptoss_decode_destroy(gptoss_decode_t *h);
+/* Error text of the last failed call on this handle (or of the last failed create
+ * when h is NULL). */
+const char *gptoss_decode_last_error(const gptoss_decode_t *h);
+
+/* Converts and uploads every tensor (fp32 host -> bf16 device, biases and norm
+ * scales stay fp32); replaces init_device_context (getp_run.cpp:150-302). */
+int gptoss_decode_load_weights(gptoss_decode_t *h, const gptoss_model_weights_t *w);
+/* The same from the address of the first tensor of a .bin image (file base + 60
+ * bytes), tensors in the file's order (memory_map_weights, run.cpp:207-248). */
+int gptoss_decode_load_bin(gptoss_decode_t *h, const float *first_tensor);
+
+/* One step.  tokens[i] / pos[i]: the token to feed to batch row i and its position
+ * (host arrays); pos[i] < 0 marks a row that does no work (its cache is untouched
+ * and next[i] = -1), the reference's inactive-row rule.  Row i owns KV-cache slot
+ * i; a sequence starts over simply by feeding pos 0 again.  next[i] receives the
+ * argmax of the row's logits (lowest index among equals, sample_argmax,
+ * run.cpp:780-791).  Synchronises the stream before returning. */
+int gptoss_decode_step(gptoss_decode_t *h, const int *tokens, const int *pos, int batch,
+                       int *next, void *stream);
+/* fp32 logits [vocab_size] of batch row `row` from the last step. */
+int gptoss_decode_get_logits(gptoss_decode_t *h, int row, float *logits_host);
+/* The MoE engine inside (for its options, taps and stage timers). */
+gptoss_moe_t *gptoss_decode_moe(gptoss_decode_t *h);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GPTOSS_DECODE_B200_H */

@@ -106,5 +106,19 @@ def rmsnorm_rows(x, w, which: str = "oracle"):
     return out
 
 
+def model_logits(bin_path, tokens, vocab_size: int):
+    """Teacher-forced fp32 logits [len(tokens), vocab_size] of the whole model from the
+    reference's own forward() (only with the compiled reference, ``_ref``)."""
+    lib = _load(REF_LIB)
+    toks = np.ascontiguousarray(tokens, dtype=np.int32)
+    out = np.empty((toks.shape[0], vocab_size), dtype=np.float32)
+    lib.ref_model_logits.argtypes = [ctypes.c_char_p, _i, ctypes.c_int, _f]
+    lib.ref_model_logits.restype = ctypes.c_int
+    rc = lib.ref_model_logits(str(bin_path).encode(), _ip(toks), toks.shape[0], _fp(out))
+    if rc != 0:
+        raise RuntimeError(f"ref_model_logits returned {rc}")
+    return out
+
+
 def set_threads(n: int) -> None:
     os.environ["OMP_NUM_THREADS"] = str(n)

@@ -122,6 +122,22 @@ ref_model_decode(const char *bin_path, const int *tokens, int n_prompt, int n_st
   return 0;
 }
 
+// Teacher-forced logits of the whole model: forward() (run.cpp:536-766) on
+// tokens[pos] at pos = 0..n-1, the fp32 logits of every call copied to
+// logits_out [n, vocab_size].
+__attribute__((visibility("default"))) int
+ref_model_logits(const char *bin_path, const int *tokens, int n, float *logits_out) {
+  Transformer tr;
+  build_transformer(&tr, const_cast<char *>(bin_path));
+  const size_t V = tr.config.vocab_size;
+  for (int pos = 0; pos < n; pos++) {
+    float *logits = forward(&tr, tokens[pos], pos);
+    memcpy(logits_out + (size_t)pos * V, logits, sizeof(float) * V);
+  }
+  free_transformer(&tr);
+  return 0;
+}
+
 __attribute__((visibility("default"))) int ref_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

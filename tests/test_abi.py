@@ -19,6 +19,21 @@ def test_header_symbols_are_exported(pkg):
     assert not missing, f"declared in the header but not exported: {missing}"
 
 
+def test_decode_header_symbols_are_exported(pkg):
+    lib = pkg.load_library()
+    text = (pkg.HEADER_PATH.parent / "gptoss_decode_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    names = sorted(set(re.findall(r"\b(gptoss_decode_[a-z0-9_]+)\s*\(", text)))
+    assert len(names) >= 8
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, f"declared in the header but not exported: {missing}"
+    # the model config mirrors the 15 four-byte fields of the checkpoint header
+    assert ctypes.sizeof(pkg.ModelConfig) == 60
+    body = text[text.index("typedef struct {"):text.index("} gptoss_model_config_t;")]
+    order = re.findall(r"\b(?:int|float)\s+([a-z_]+);", body)
+    assert order == [f[0] for f in pkg.ModelConfig._fields_]
+
+
 def test_version_string(pkg):
     assert b"sm_100a" in pkg.load_library().gptoss_moe_version()
 

@@ -1,0 +1,134 @@
+"""Whole-model decode step on the GPU against the reference's forward().
+
+Teacher forcing: the golden record (tests/golden/make_golden_model.py) holds the token
+fed at every position and the reference's logits there; the GPU is fed the same tokens
+and must reproduce the logits within tolerance and pick the same next token unless the
+reference's own top logits are closer than the tolerance band (greedy ids of a
+random-init model sit on near-flat logits).
+"""
+import pathlib
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = pathlib.Path(__file__).resolve().parents[1]
+
+# logits have std 0.23; activations pass through bf16 between kernels
+LOGIT_MAX_ABS = 2e-2
+LOGIT_MEAN_ABS = 2e-3
+
+
+def _golden(name):
+    return np.load(ROOT / "tests" / "golden" / f"model_{name}.npz")
+
+
+def _run_teacher_forced(pkg, cfg, seed, tokens, tmp_path, rows=(0,), max_batch=4,
+                        stagger=0):
+    """Feeds `tokens` position by position to every row in `rows` (row r starts
+    r * stagger steps late, idle rows and late rows are inactive) and returns the logits
+    of rows[0] at every position plus the next-token ids of every row."""
+    from gpt_oss_b200 import synth
+
+    path = tmp_path / "model.bin"
+    synth.write_model_bin(path, cfg, seed)
+    image = np.memmap(path, dtype=np.uint8, mode="r")
+    eng = pkg.DecodeEngine(cfg, max_batch)
+    eng.load_bin(np.asarray(image))
+    n = len(tokens)
+    probe_logits, nexts = [], {r: [] for r in rows}
+    for step in range(n + stagger * (len(rows) - 1)):
+        tok = np.full(max_batch, -1, np.int32)
+        pos = np.full(max_batch, -1, np.int32)
+        for j, r in enumerate(rows):
+            p = step - j * stagger
+            if 0 <= p < n:
+                tok[r], pos[r] = tokens[p], p
+        nxt = eng.step(tok, pos)
+        for j, r in enumerate(rows):
+            p = step - j * stagger
+            if 0 <= p < n:
+                nexts[r].append(int(nxt[r]))
+                if j == 0:
+                    probe_logits.append(eng.logits(r))
+            else:
+                assert nxt[r] == -1
+    eng.close()
+    return np.stack(probe_logits), nexts
+
+
+def _check_against_golden(g, logits, nexts):
+    probes = g["probes"]
+    err = np.abs(logits[:, probes].astype(np.float64) - g["probe_logits"])
+    assert err.max() <= LOGIT_MAX_ABS, f"logits max-abs {err.max():.3e}"
+    assert err.mean() <= LOGIT_MEAN_ABS, f"logits mean-abs {err.mean():.3e}"
+    top_ids, top_logits = g["top_ids"], g["top_logits"]
+    # the reference's best logits are reproduced at their ids
+    got_top = np.take_along_axis(logits, top_ids.astype(np.int64), axis=1)
+    assert np.abs(got_top - top_logits).max() <= LOGIT_MAX_ABS
+    mismatches = 0
+    for p, nx in enumerate(nexts):
+        if nx == top_ids[p, 0]:
+            continue
+        mismatches += 1
+        where = np.nonzero(top_ids[p] == nx)[0]
+        assert where.size, f"position {p}: token {nx} is not among the reference's top 8"
+        gap = top_logits[p, 0] - top_logits[p, where[0]]
+        assert gap <= 2 * LOGIT_MAX_ABS, f"position {p}: picked a logit {gap:.4f} below the best"
+    assert mismatches <= len(nexts) // 8
+
+
+@pytest.mark.parametrize("name", ["tiny", "mini"])
+def test_decode_matches_reference_logits(pkg, tmp_path, name):
+    from gpt_oss_b200 import synth
+
+    g = _golden(name)
+    cfg = synth.TINY_MODEL if name == "tiny" else synth.MINI_MODEL
+    logits, nexts = _run_teacher_forced(pkg, cfg, int(g["seed"]), g["tokens"], tmp_path)
+    _check_against_golden(g, logits, nexts[0])
+
+
+def test_rows_are_independent_and_inactive_rows_idle(pkg, tmp_path):
+    """Three sequences in one batch, started 5 steps apart in rows 0, 2, 3 (row 1 never
+    used): every row reproduces the single-sequence result bit for bit."""
+    from gpt_oss_b200 import synth
+
+    g = _golden("mini")
+    tokens = g["tokens"][:24]
+    cfg = synth.MINI_MODEL
+    _, solo = _run_teacher_forced(pkg, cfg, int(g["seed"]), tokens, tmp_path)
+    _, multi = _run_teacher_forced(pkg, cfg, int(g["seed"]), tokens, tmp_path, rows=(0, 2, 3),
+                                   stagger=5)
+    for r in (0, 2, 3):
+        assert multi[r] == solo[0], f"row {r}"
+
+
+def test_live_reference_when_present(pkg, oracle, tmp_path):
+    """Fresh seed, full logits against the compiled reference where it travelled along."""
+    from gpt_oss_b200 import synth
+
+    if not oracle.have_ref():
+        pytest.skip("compiled reference not present")
+    # one layer and few positions: little room for a near-tie in the router, where a bf16
+    # pipeline and the fp32 reference would part ways
+    cfg = dict(synth.MINI_MODEL, vocab_size=777, sliding_window=5, n_layers=1)
+    rng = np.random.default_rng(77)
+    tokens = rng.integers(0, cfg["vocab_size"], size=12, dtype=np.int32)
+    logits, _ = _run_teacher_forced(pkg, cfg, 9, tokens, tmp_path)
+    want = oracle.model_logits(tmp_path / "model.bin", tokens, cfg["vocab_size"])
+    err = np.abs(logits - want)
+    assert err.max() <= LOGIT_MAX_ABS and err.mean() <= LOGIT_MEAN_ABS, (err.max(), err.mean())
+
+
+def test_decode_argument_errors(pkg):
+    from gpt_oss_b200 import synth
+
+    bad = dict(synth.MINI_MODEL, head_dim=48)
+    with pytest.raises(pkg.MoeError) as ei:
+        pkg.DecodeEngine(bad, 2)
+    assert ei.value.code == pkg.GPTOSS_E_INVALID
+    eng = pkg.DecodeEngine(synth.MINI_MODEL, 2)
+    with pytest.raises(pkg.MoeError) as ei:  # weights not loaded
+        eng.step(np.zeros(2, np.int32), np.zeros(2, np.int32))
+    assert ei.value.code == pkg.GPTOSS_E_STATE
+    eng.close()
