@@ -124,6 +124,7 @@ def load_library() -> ctypes.CDLL:
         "gptoss_decode_step": (c_int, [vp, vp, vp, c_int, vp, vp]),
         "gptoss_decode_get_logits": (c_int, [vp, c_int, vp]),
         "gptoss_decode_moe": (vp, [vp]),
+        "gptoss_decode_device_count": (c_int, []),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(lib, name)

@@ -58,3 +58,33 @@ def build_library(force: bool = False, verbose: bool = False) -> pathlib.Path:
     if verbose:
         print(res.stdout + res.stderr)
     return LIB
+
+
+HOST_LIB = PKG_DIR / "libgptoss_getp_b200.so"
+HARNESS = PKG_DIR.parent / "tests" / "host" / "_build" / "getp_harness"
+
+
+def build_host(force: bool = False) -> pathlib.Path:
+    """Compile the C++17 getp entry points (host/getp_run_b200.cpp, no CUDA in it) into
+    libgptoss_getp_b200.so next to the CUDA library, and the test host program that calls
+    them (tests/host/getp_harness.cpp).  `encode` stays undefined in the library: the
+    host program supplies its tokenizer."""
+    gxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else (shutil.which("g++") or "g++")
+    src = PKG_DIR / "host" / "getp_run_b200.cpp"
+    deps = [src, PKG_DIR / "host" / "getp_abi.h", PKG_DIR.parent / "include" / "gptoss_decode_b200.h"]
+    if force or _stale(HOST_LIB, deps):
+        cmd = [gxx, "-std=c++17", "-O2", "-fPIC", "-shared", "-pthread", "-Wall", "-o", str(HOST_LIB),
+               str(src), "-L", str(PKG_DIR), "-lgptoss_moe_b200", "-Wl,-rpath,$ORIGIN"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError("g++ failed:\n" + res.stdout + res.stderr)
+    hsrc = PKG_DIR.parent / "tests" / "host" / "getp_harness.cpp"
+    if hsrc.exists() and (force or _stale(HARNESS, deps + [hsrc, HOST_LIB])):
+        HARNESS.parent.mkdir(parents=True, exist_ok=True)
+        cmd = [gxx, "-std=c++17", "-O2", "-pthread", "-Wall", "-o", str(HARNESS), str(hsrc),
+               "-L", str(PKG_DIR), "-lgptoss_getp_b200", "-lgptoss_moe_b200",
+               "-Wl,-rpath," + str(PKG_DIR), "-Wl,-rpath,$ORIGIN/../../../gpt-oss_b200"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError("g++ failed:\n" + res.stdout + res.stderr)
+    return HOST_LIB

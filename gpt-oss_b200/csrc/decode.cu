@@ -345,6 +345,21 @@ const char *gptoss_decode_last_error(const gptoss_decode_t *h) {
 
 gptoss_moe_t *gptoss_decode_moe(gptoss_decode_t *h) { return h ? h->moe : nullptr; }
 
+int gptoss_decode_device_count(void) {
+  int n = 0, good = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  for (int d = 0; d < n; d++) {
+    int major = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, d) == cudaSuccess &&
+        major == 10)
+      good++;
+  }
+  return good;
+}
+
 int gptoss_decode_destroy(gptoss_decode_t *h) {
   if (!h) return GPTOSS_OK;
   cudaSetDevice(h->device);

@@ -1,0 +1,192 @@
+// warm_up / inference / finish of the getp mode on B200: the host side of the engine,
+// C++17, no CUDA in this file - it drives the extern "C" layer of
+// include/gptoss_decode_b200.h.
+//
+// Takes the place of getp-csrc/getp_run.cpp of the reference, with its behaviour at the
+// boundary:
+//   warm_up    one engine per GPU, every weight converted and uploaded once, all device
+//              memory allocated for the largest batch (getp_run.cpp:413-446)
+//   inference  prompts encoded with the host program's tokenizer; requests split evenly
+//              over the GPUs, one host thread per GPU; each GPU works through its
+//              requests in static batches, one decode step per iteration for every
+//              unfinished sequence of the batch, finished sequences staying in place as
+//              inactive rows; greedy (argmax) decoding; tok_gens row i = generated ids
+//              terminated by -1; returns the number of generated tokens
+//              (getp_run.cpp:457-499, :896-1009, :1011-1074)
+//   finish     frees everything (getp_run.cpp:448-455)
+// Errors end the process with a message on stderr, as the reference does
+// (getp-csrc/common/defines.h:94-102).
+//
+// Environment: GPTOSS_GETP_GPUS (default: all sm_100 devices), GPTOSS_GETP_BATCH
+// (sequences per GPU batch; default 896, or 768 with 128 experts, the reference's
+// MAX_BATCH_SIZE / MAX_BATCH_SIZE_120B, defines.h:30-31).
+#include "getp_abi.h"
+
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "../../include/gptoss_decode_b200.h"
+
+namespace {
+
+// Ids that end a sequence (getp_run.cpp:977) and the step limit per request
+// (getp_run.cpp:463).
+constexpr int kEosA = 199999, kEosB = 200002;
+constexpr int kMaxSteps = 1024;
+
+struct Sequence {
+  std::vector<int> prompt;
+  int *out = nullptr;  // the request's row of tok_gens
+  int out_cap = 0;     // ids that fit before the terminator
+  int pos = 0, token = 0, generated = 0;
+  bool finished = false;
+};
+
+struct Device {
+  gptoss_decode_t *engine = nullptr;
+  int batch = 0;
+};
+
+std::vector<Device> g_devices;
+
+[[noreturn]] void die(const char *what, const char *detail) {
+  std::fprintf(stderr, "getp (B200): %s: %s\n", what, detail ? detail : "");
+  std::exit(EXIT_FAILURE);
+}
+
+int env_int(const char *name, int fallback) {
+  const char *v = std::getenv(name);
+  return (v && *v) ? std::atoi(v) : fallback;
+}
+
+// One GPU's share of the requests, batch after batch.
+long long run_on_device(Device &dev, const Config &cfg, Sequence *seqs, int count) {
+  long long total = 0;
+  std::vector<int> tokens(dev.batch), pos(dev.batch), next(dev.batch);
+  for (int first = 0; first < count; first += dev.batch) {
+    const int B = std::min(dev.batch, count - first);
+    Sequence *batch = seqs + first;
+    int unfinished = B;
+    while (unfinished > 0) {
+      for (int i = 0; i < B; i++) {
+        tokens[i] = batch[i].finished ? -1 : batch[i].token;
+        pos[i] = batch[i].finished ? -1 : batch[i].pos;
+      }
+      if (gptoss_decode_step(dev.engine, tokens.data(), pos.data(), B, next.data(), nullptr) !=
+          GPTOSS_OK)
+        die("decode step", gptoss_decode_last_error(dev.engine));
+      for (int i = 0; i < B; i++) {
+        Sequence &s = batch[i];
+        if (s.finished) continue;
+        s.pos++;
+        int tok;
+        if (s.pos < static_cast<int>(s.prompt.size())) {
+          tok = s.prompt[s.pos];  // still feeding the prompt
+        } else {
+          tok = next[i];
+          if (s.generated < s.out_cap) s.out[s.generated] = tok;
+          s.generated++;
+        }
+        s.token = tok;
+        const bool eos = tok == kEosA || tok == kEosB;
+        // also stop where the caller's output row or the KV cache would overflow
+        // (the reference checks neither)
+        if (eos || s.pos + 1 >= kMaxSteps || s.pos + 1 >= cfg.seq_len ||
+            s.generated >= s.out_cap) {
+          s.finished = true;
+          unfinished--;
+        }
+      }
+    }
+    for (int i = 0; i < B; i++) {
+      Sequence &s = batch[i];
+      const int n = std::min(s.generated, s.out_cap);
+      s.out[n] = -1;
+      total += n;
+    }
+  }
+  return total;
+}
+
+}  // namespace
+
+void warm_up(Transformer *transformer, Tokenizer *) {
+  const Config &cfg = transformer->config;
+  int n_gpus = gptoss_decode_device_count();
+  if (n_gpus <= 0) die("warm_up", "no sm_100 GPU visible (there is no CPU fallback)");
+  n_gpus = std::min(n_gpus, std::max(1, env_int("GPTOSS_GETP_GPUS", n_gpus)));
+  const int batch = std::max(1, env_int("GPTOSS_GETP_BATCH", cfg.n_experts >= 128 ? 768 : 896));
+  static_assert(sizeof(Config) == sizeof(gptoss_model_config_t), "checkpoint header layout");
+  static_assert(sizeof(TransformerWeights) == sizeof(gptoss_model_weights_t), "weight table layout");
+  gptoss_model_config_t mc;
+  std::memcpy(&mc, &cfg, sizeof(mc));
+  gptoss_model_weights_t mw;
+  std::memcpy(&mw, &transformer->weights, sizeof(mw));
+  g_devices.assign(n_gpus, Device());
+  std::vector<std::thread> workers;
+  std::vector<std::string> errors(n_gpus);
+  for (int d = 0; d < n_gpus; d++) {
+    workers.emplace_back([&, d]() {
+      Device &dev = g_devices[d];
+      dev.batch = batch;
+      if (gptoss_decode_create(&mc, batch, d, &dev.engine) != GPTOSS_OK) {
+        errors[d] = std::string("create: ") + gptoss_decode_last_error(nullptr);
+        return;
+      }
+      if (gptoss_decode_load_weights(dev.engine, &mw) != GPTOSS_OK)
+        errors[d] = std::string("weights: ") + gptoss_decode_last_error(dev.engine);
+    });
+  }
+  for (auto &w : workers) w.join();
+  for (int d = 0; d < n_gpus; d++)
+    if (!errors[d].empty()) die("warm_up", errors[d].c_str());
+  std::printf("getp (B200): %d GPU(s), batch %d per GPU\n", n_gpus, batch);
+}
+
+long long inference(Transformer *transformer, Tokenizer *tokenizer, Sampler *, Requests *requests) {
+  if (g_devices.empty()) die("inference", "warm_up has not run");
+  const Config &cfg = transformer->config;
+  const int n = requests->num_reqs;
+  if (n <= 0) return 0;
+  std::vector<Sequence> seqs(n);
+  const size_t text_stride = static_cast<size_t>(requests->max_token_len) * (requests->max_seq_len + 1);
+  for (int i = 0; i < n; i++) {
+    Sequence &s = seqs[i];
+    const char *text = requests->str_reqs + i * text_stride;
+    s.out = requests->tok_gens + static_cast<size_t>(i) * (requests->max_seq_len + 1);
+    s.out_cap = requests->max_seq_len;
+    s.prompt.resize(std::strlen(text) + 3);
+    int count = 0;
+    encode(tokenizer, text, -1, -1, s.prompt.data(), &count, cfg.initial_context_length);
+    if (count < 1) die("inference", "a request encoded to no tokens");
+    s.prompt.resize(count);
+    s.token = s.prompt[0];
+  }
+  // contiguous, near-equal shares, the first (n % gpus) one request longer
+  const int gpus = static_cast<int>(g_devices.size());
+  std::vector<long long> totals(gpus, 0);
+  std::vector<std::thread> workers;
+  int start = 0;
+  for (int d = 0; d < gpus; d++) {
+    const int share = n / gpus + (d < n % gpus ? 1 : 0);
+    if (share > 0)
+      workers.emplace_back([&, d, start, share]() {
+        totals[d] = run_on_device(g_devices[d], cfg, seqs.data() + start, share);
+      });
+    start += share;
+  }
+  for (auto &w : workers) w.join();
+  long long total = 0;
+  for (long long t : totals) total += t;
+  return total;
+}
+
+void finish(Transformer *, Tokenizer *) {
+  for (Device &d : g_devices) gptoss_decode_destroy(d.engine);
+  g_devices.clear();
+}

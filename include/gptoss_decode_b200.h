@@ -69,6 +69,10 @@ typedef struct {
 
 typedef struct gptoss_decode gptoss_decode_t;
 
+/* Number of visible CUDA devices of compute capability 10.x (0 when there is none or
+ * no driver). */
+int gptoss_decode_device_count(void);
+
 /* Allocates everything for max_batch sequences of up to cfg->seq_len positions on
  * `device` (KV cache: L * max_batch * seq_len * Hkv * D * 2 bf16).  No CPU
  * fallback: fails unless the device is sm_100 and cuBLAS can be loaded. */

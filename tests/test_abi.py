@@ -75,3 +75,27 @@ def test_missing_library_fails_loudly(pkg, monkeypatch, tmp_path):
     monkeypatch.setattr(pkg, "LIB_PATH", tmp_path / "nope.so")
     with pytest.raises(RuntimeError, match="no fallback"):
         pkg.load_library()
+
+
+def test_getp_host_program_fails_loudly_without_gpu(pkg, tmp_path):
+    """The C++ entry points build, link against the C ABI and refuse to run on a box
+    without an sm_100 GPU (no fallback)."""
+    import subprocess
+
+    import torch
+
+    from gpt_oss_b200 import build as native_build
+    from gpt_oss_b200 import synth
+
+    native_build.build_host()
+    assert native_build.HOST_LIB.exists() and native_build.HARNESS.exists()
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    cfg = dict(synth.MINI_MODEL, vocab_size=64, n_layers=1)
+    synth.write_model_bin(tmp_path / "m.bin", cfg, 1)
+    (tmp_path / "req.txt").write_text("1\n1 2 3\n")
+    res = subprocess.run([str(native_build.HARNESS), str(tmp_path / "m.bin"),
+                          str(tmp_path / "req.txt"), str(tmp_path / "out.txt")],
+                         capture_output=True, text=True, timeout=120)
+    assert res.returncode != 0
+    assert "no sm_100 GPU" in res.stderr

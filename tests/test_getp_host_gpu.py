@@ -1,0 +1,66 @@
+"""The C++ getp entry points (warm_up / inference / finish) driven by a host program the
+way the reference's getp() drives them, on the tiny model of the benchmark description.
+
+Prompts are lines of token ids (the test host's encode() parses them).  The first request
+is the golden prompt: its greedy continuation must follow the reference's until the first
+position where the reference's own two best logits are closer than the tolerance band.
+"""
+import os
+import pathlib
+import subprocess
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = pathlib.Path(__file__).resolve().parents[1]
+BAND = 4e-2  # twice the logit tolerance of the teacher-forced test
+
+
+def test_getp_entry_points_on_tiny_model(pkg, tmp_path):
+    from gpt_oss_b200 import build as native_build
+    from gpt_oss_b200 import synth
+
+    if not native_build.HARNESS.exists():
+        native_build.build_host()
+    g = np.load(ROOT / "tests" / "golden" / "model_tiny.npz")
+    cfg = synth.TINY_MODEL
+    n_prompt = int(g["n_prompt"])
+    bin_path = tmp_path / "tiny.bin"
+    synth.write_model_bin(bin_path, cfg, int(g["seed"]))
+    rng = np.random.default_rng(5)
+    prompts = [list(g["tokens"][:n_prompt]),
+               list(rng.integers(0, cfg["vocab_size"], size=9)),
+               list(rng.integers(0, cfg["vocab_size"], size=1)),
+               [17, 199999, 5]]  # an end-of-sequence id inside the prompt stops the request
+    req = tmp_path / "requests.txt"
+    req.write_text(f"{len(prompts)}\n" + "\n".join(" ".join(str(int(t)) for t in p) for p in prompts) + "\n")
+    out = tmp_path / "out.txt"
+    env = dict(os.environ, GPTOSS_GETP_GPUS="1", GPTOSS_GETP_BATCH="3")  # two batches: 3 + 1
+    res = subprocess.run([str(native_build.HARNESS), str(bin_path), str(req), str(out)],
+                         capture_output=True, text=True, env=env, timeout=600)
+    assert res.returncode == 0, res.stdout + res.stderr
+    rows = [[int(t) for t in line.split()] for line in out.read_text().splitlines()]
+    assert len(rows) == len(prompts)
+    # every request runs to the end of the KV cache unless it meets an end-of-sequence id
+    for p, r in zip(prompts[:3], rows[:3]):
+        assert all(0 <= t < cfg["vocab_size"] for t in r)
+        if not any(t in (199999, 200002) for t in r):
+            assert len(p) + len(r) == cfg["seq_len"]
+    assert rows[3] == []
+    total = int(res.stdout.split("generated ")[1].split()[0])
+    assert total == sum(len(r) for r in rows)
+    # the golden request against the reference's greedy continuation
+    want = g["tokens"][n_prompt:]
+    got = rows[0][:len(want)]
+    for i, (a, b) in enumerate(zip(got, want)):
+        if a == b:
+            continue
+        p = n_prompt - 1 + i  # position whose logits chose this token
+        ids, vals = g["top_ids"][p], g["top_logits"][p]
+        where = np.nonzero(ids == a)[0]
+        assert where.size and vals[0] - vals[where[0]] <= BAND, (
+            f"generated token {i}: {a} instead of {b}, outside the tie band")
+        break  # the sequences differ from here on by construction
+    else:
+        assert len(got) == len(want)
