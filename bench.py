@@ -1,7 +1,7 @@
 """Benchmark of the MoE block: tokens/s of one layer pass.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload c2|c3]
+                    [--workload c2|c3|c2s|c4|c5|tiny] [--no-extra] [--no-cpu-baseline]
 
 A step is one pass of the block (router -> top-4 -> permutation -> grouped
 gate_up + SwiGLU -> grouped down -> combine + residual) over one batch of
@@ -11,7 +11,20 @@ N=1 runs the gpt-oss-20b-shape layer at T=7168 ("c2"), the configuration the
 single-GPU metric is quoted on.  N>1 runs one such replica per GPU (the
 reference serves the 20b shape as data-parallel replicas, getp_run.cpp:1035-1060),
 so per-GPU work is fixed ("weak") and no data-path collective is involved.
---workload c3 runs the 120b-shape layer (T=6144, 128 experts) instead.
+The same line carries "layer_120b": the 120b-shape layer (T=6144 per GPU, 128
+experts) measured in the same run, with the experts sharded over the ranks when
+N>1 (rows read from peer memory over NVLink, or NCCL send/recv; both timed), a
+strong-scaling reading (the 6144 tokens split over the ranks) beside the weak one.
+
+Other workloads (each prints its own line):
+  c3    the 120b-shape layer as the headline workload
+  c2s   a quarter-size 20b-shape layer (8 experts, T=1792) for profiler captures
+  c4    the 120b-shape layer with MXFP4 expert weights at decode batch sizes
+        T = 64 / 256 / 1024 under a Zipf-skewed router
+  c5    one decode step of the full 120b-architecture model (36 layers, 6144
+        sequences with 512 positions of KV context), experts sharded over N >= 2 GPUs,
+        with the MoE share of the step time
+  tiny  a 16-token layer (smoke runs)
 
 --impl reference times the reference's own CPU code (oracle/_ref when it was
 built from the reference tree, else the C port in oracle/) on the host cores, on
@@ -530,13 +543,164 @@ def run_decode_mxfp4(args):
     eng.close()
 
 
+def run_decode_120b(args):
+    """--workload c5: one decode step of a 120b-architecture model (36 layers, hidden 2880,
+    64 query / 8 KV heads of 64, sinks, 128-token window on even layers, 128 experts top-4,
+    vocabulary 201088), random-init weights generated on the device, 6144 sequences split
+    over the GPUs, each with 512 positions of synthetic KV context; experts sharded over
+    the ranks (16 per GPU at 8).  Needs at least 2 GPUs: the bf16 experts alone are 229 GB.
+    GPTOSS_C5_LAYERS cuts the layer count for development runs (reported in the line)."""
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun")
+    layers = int(os.environ.get("GPTOSS_C5_LAYERS", "36"))
+    if world < 2 and layers > 24:
+        raise SystemExit("workload c5 needs at least 2 GPUs (229 GB of bf16 expert weights)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    pkg = entry.load_package()
+    ctx, total_seqs = 512, 6144
+    B = total_seqs // world
+    steps, warmup = args.steps, args.warmup
+    cfg = dict(vocab_size=201088, hidden_dim=2880, n_experts=128, experts_per_token=4,
+               intermediate_dim=2880, n_layers=layers, head_dim=64, n_attn_heads=64, n_kv_heads=8,
+               seq_len=ctx + warmup + steps + 8, initial_context_length=4096, rope_theta=150000.0,
+               rope_scaling_factor=32.0, sliding_window=128, swiglu_limit=7.0)
+    V, H, IM, E, D = cfg["vocab_size"], cfg["hidden_dim"], cfg["intermediate_dim"], cfg["n_experts"], 64
+    dq, dkv = cfg["n_attn_heads"] * D, cfg["n_kv_heads"] * D
+    eng = pkg.DecodeEngine(cfg, B, device=local_rank, ep_rank=rank, ep_size=world)
+    moe = eng.moe(ep_rank=rank, ep_size=world, device=local_rank)
+
+    def normal(gen, size, std, dtype=torch.bfloat16):
+        return (torch.randn(size, generator=gen, device=dev, dtype=torch.float32) * std).to(dtype)
+
+    g = torch.Generator(device=dev)
+    g.manual_seed(3)  # the same weights on every rank
+    for name in ("token_embedding_table", "out"):
+        eng.set_tensor(name, 0, normal(g, (V, H), 0.02))
+    eng.set_tensor("rms_out_w", 0, torch.ones(H, device=dev))
+    layer_shape = synth_shape_120b()
+    for l in range(layers):
+        eng.set_tensor("w_qkv", l, normal(g, (dq + 2 * dkv, H), 0.02))
+        eng.set_tensor("b_qkv", l, normal(g, (dq + 2 * dkv,), 0.01, torch.float32))
+        eng.set_tensor("w_o", l, normal(g, (H, dq), 0.02))
+        eng.set_tensor("b_o", l, normal(g, (H,), 0.01, torch.float32))
+        eng.set_tensor("attn_sinks", l, normal(g, (cfg["n_attn_heads"],), 0.02, torch.float32))
+        eng.set_tensor("rms_attn_w", l, torch.ones(H, device=dev))
+        eng.set_tensor("rms_ffn_w", l, torch.ones(H, device=dev))
+        layer_shape.seed = 3000 + l
+        w = device_weights(layer_shape, dev)  # all 128 experts; the engine keeps this rank's
+        moe.load_layer_bf16(l, w["w_router"], w["b_router"], w["w_mlp1"], w["b_mlp1"], w["w_mlp2"],
+                            w["b_mlp2"], on_device=True)
+        del w
+    torch.cuda.empty_cache()
+    if world > 1:
+        uid = torch.zeros(128, dtype=torch.uint8, device=dev)
+        if rank == 0:
+            uid.copy_(torch.frombuffer(bytearray(pkg.MoeEngine.ep_unique_id()), dtype=torch.uint8))
+        dist.broadcast(uid, 0)
+        moe.ep_init(bytes(uid.cpu().numpy().tobytes()))
+    # synthetic context: 512 cached positions per sequence and layer
+    gk = torch.Generator(device=dev)
+    gk.manual_seed(7000 + rank)
+    rows = 128
+    for l in range(layers):
+        for r0 in range(0, B, rows):
+            n = min(rows, B - r0)
+            k = torch.randn((n, ctx, dkv), generator=gk, device=dev, dtype=torch.bfloat16)
+            v = torch.randn((n, ctx, dkv), generator=gk, device=dev, dtype=torch.bfloat16)
+            eng.set_kv(l, r0, 0, k, v)
+    rng = np.random.default_rng(11 + rank)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    def run(n, first_pos):
+        for i in range(n):
+            tokens = rng.integers(0, V, size=B, dtype=np.int32)
+            eng.step(tokens, np.full(B, first_pos + i, np.int32))
+
+    run(warmup, ctx)
+    barrier()
+    moe.set_option("time_stages", 1)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    t0 = time.perf_counter()
+    run(steps, ctx + warmup)
+    ev1.record()
+    barrier()
+    wall = time.perf_counter() - t0
+    clocks = sampler.result()
+    ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        tt = torch.tensor([ms], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms = float(tt.item())
+    names = ["route", "permute", "gate_up", "down", "combine"] + (["dispatch", "return"] if world > 1 else [])
+    stage_ms = {s: moe.stage_ms(s) for s in names}
+    moe_ms_per_step = sum(stage_ms.values()) * layers
+    launches = moe.launch_count()
+    transport = moe.ep_transport if world > 1 else -1
+    eng.close()
+    if rank == 0:
+        peaks = read_peaks()
+        step_ms = ms / steps
+        gate_up_flops = 2.0 * B * 4 * 2 * IM * H  # this rank's share of the assignments, on average
+        line = {
+            "metric": "decode_tokens_per_s", "value": world * B * steps / (ms * 1e-3), "unit": UNIT,
+            "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": step_ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": f"gpt-oss-120b-decode-step-{layers}L-B{total_seqs}-ctx{ctx}",
+                       "sequences_per_gpu": B, "layers": layers, "kv_context": ctx,
+                       "parallelism": f"data parallel x{world} outside the experts, expert parallel x{world} "
+                                      + ("(peer memory)" if transport == 1 else "(NCCL send/recv)"),
+                       "l2": "weights and KV cache far larger than L2"},
+            "moe_share": moe_ms_per_step / step_ms, "moe_ms_per_step": moe_ms_per_step,
+            "moe_stage_ms_per_layer": stage_ms,
+            "roofline": {"kernel": "grouped_gemm_pair_kernel<swiglu, 6> (gate_up, per layer)",
+                         "bound": "tensor", "achieved": gate_up_flops / (stage_ms["gate_up"] * 1e-3) / 1e12,
+                         "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                         "frac": gate_up_flops / (stage_ms["gate_up"] * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"],
+                         "peak_source": f"{peaks['source']} bf16_tflops_sustained", "traffic": None},
+            "cpu_baseline": None,
+            # every step already goes through the public call with host token / position
+            # arrays in and host next-token ids out
+            "e2e": {"value": world * B * steps / wall, "unit": UNIT,
+                    "h2d_bytes_per_step": 8 * B, "d2h_bytes_per_step": 4 * B},
+            "gpu_launches": launches, "clocks": clocks,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def synth_shape_120b():
+    entry.load_package()
+    from gpt_oss_b200 import synth
+
+    return synth.MoeShape("gpt-oss-120b-layer", 0, 2880, 2880, 128, 4, 7.0, 0)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c2s", "c4", "tiny"])
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c2s", "c4", "c5", "tiny"])
     ap.add_argument("--cpu-tokens", type=int, default=None,
                     help="tokens in the CPU sample (default 256 for ours, 64 for reference)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -549,7 +713,12 @@ def main():
         args.warmup = max(3, args.warmup if args.warmup is not None else 5)
         run_decode_mxfp4(args)
         return
-    shape = workload_shape("c3" if args.workload == "c4" else args.workload)
+    if args.workload == "c5" and args.impl == "ours":
+        args.steps = args.steps if args.steps is not None else 8
+        args.warmup = max(3, args.warmup if args.warmup is not None else 3)
+        run_decode_120b(args)
+        return
+    shape = workload_shape("c3" if args.workload in ("c4", "c5") else args.workload)
     if args.impl == "reference":
         args.steps = args.steps if args.steps is not None else 5
         args.warmup = args.warmup if args.warmup is not None else 1

@@ -125,6 +125,10 @@ def load_library() -> ctypes.CDLL:
         "gptoss_decode_get_logits": (c_int, [vp, c_int, vp]),
         "gptoss_decode_moe": (vp, [vp]),
         "gptoss_decode_device_count": (c_int, []),
+        "gptoss_decode_create_ep": (c_int, [ctypes.POINTER(ModelConfig), c_int, c_int, c_int, c_int,
+                                            ctypes.POINTER(vp)]),
+        "gptoss_decode_set_tensor": (c_int, [vp, c_char_p, c_int, vp, c_int, c_int]),
+        "gptoss_decode_set_kv": (c_int, [vp, c_int, c_int, c_int, c_int, c_int, vp, vp]),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(lib, name)
@@ -193,6 +197,16 @@ class MoeEngine:
             self.handle = None
             raise MoeError(rc, text)
 
+    @classmethod
+    def borrowed(cls, handle, cfg: "MoeConfig"):
+        """The engine inside another object (a decode engine): same methods, not owned."""
+        self = cls.__new__(cls)
+        self.lib = load_library()
+        self.cfg = cfg
+        self.handle = handle
+        self._borrowed = True
+        return self
+
     # -- plumbing
     def _check(self, rc):
         if rc != GPTOSS_OK:
@@ -200,7 +214,8 @@ class MoeEngine:
 
     def close(self):
         if getattr(self, "handle", None):
-            self.lib.gptoss_moe_destroy(self.handle)
+            if not getattr(self, "_borrowed", False):
+                self.lib.gptoss_moe_destroy(self.handle)
             self.handle = None
 
     def __del__(self):
@@ -322,13 +337,15 @@ class DecodeEngine:
     """Mirror of include/gptoss_decode_b200.h: one greedy decode step for a batch of
     sequences (row i owns KV-cache slot i)."""
 
-    def __init__(self, cfg: dict, max_batch: int, device: int = 0):
+    def __init__(self, cfg: dict, max_batch: int, device: int = 0, ep_rank: int = 0,
+                 ep_size: int = 1):
         self.lib = load_library()
         self.cfg = dict(cfg)
         self.max_batch = max_batch
         c = ModelConfig(**cfg)
         h = ctypes.c_void_p()
-        rc = self.lib.gptoss_decode_create(ctypes.byref(c), max_batch, device, ctypes.byref(h))
+        rc = self.lib.gptoss_decode_create_ep(ctypes.byref(c), max_batch, device, ep_rank, ep_size,
+                                              ctypes.byref(h))
         if rc != 0:
             raise MoeError(rc, (self.lib.gptoss_decode_last_error(None) or b"").decode())
         self.handle = h
@@ -344,6 +361,26 @@ class DecodeEngine:
         first = raw[60:]
         self._check(self.lib.gptoss_decode_load_bin(self.handle,
                                                     ctypes.c_void_p(first.ctypes.data)))
+
+    def set_tensor(self, name: str, layer: int, src):
+        """src: float32 numpy array (host) or a CUDA torch tensor (bf16 weights, fp32 others)."""
+        on_device = hasattr(src, "data_ptr")
+        is_bf16 = on_device and str(src.dtype) == "torch.bfloat16"
+        self._check(self.lib.gptoss_decode_set_tensor(self.handle, name.encode(), layer, _ptr(src),
+                                                      int(on_device), int(is_bf16)))
+
+    def set_kv(self, layer: int, row0: int, pos0: int, k, v):
+        """k, v: CUDA bf16 tensors [rows, positions, n_kv_heads * head_dim]."""
+        self._check(self.lib.gptoss_decode_set_kv(self.handle, layer, row0, k.shape[0], pos0,
+                                                  k.shape[1], _ptr(k), _ptr(v)))
+
+    def moe(self, ep_rank: int = 0, ep_size: int = 1, device: int = 0) -> "MoeEngine":
+        """The MoE engine inside, with MoeEngine's methods (weights, options, timers, EP)."""
+        c = self.cfg
+        cfg = MoeConfig(c["hidden_dim"], c["intermediate_dim"], c["n_experts"],
+                        c["experts_per_token"], c["n_layers"], self.max_batch, c["swiglu_limit"],
+                        ep_rank, ep_size, WEIGHTS_BF16, device)
+        return MoeEngine.borrowed(ctypes.c_void_p(self.lib.gptoss_decode_moe(self.handle)), cfg)
 
     def step(self, tokens, pos, stream: int = 0):
         tokens = np.ascontiguousarray(tokens, dtype=np.int32)

@@ -132,7 +132,7 @@ qkv_rope_cache_kernel(const float *__restrict__ qkv, const float *__restrict__ b
 // with its own running maximum, sum and D-wide accumulator; the lanes are merged at the
 // end.  Output bf16 [B, Hq D].
 template <int D>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 attn_decode_kernel(const float *__restrict__ q, const bf16 *__restrict__ k_cache,
                    const bf16 *__restrict__ v_cache, const float *__restrict__ sinks,
                    const int *__restrict__ pos, bf16 *__restrict__ out, int B, int Hq, int Hkv,
@@ -266,6 +266,7 @@ struct gptoss_decode {
   gptoss_moe *moe = nullptr;
   cublasHandle_t blas = nullptr;
   bool loaded = false;
+  std::vector<unsigned> have;  // per layer (+1 for the model-wide tensors): bits of tensors set
   // weights
   bf16 *emb = nullptr, *unemb = nullptr, *w_qkv = nullptr, *w_o = nullptr;
   float *rms_attn = nullptr, *rms_ffn = nullptr, *rms_out = nullptr;
@@ -378,6 +379,11 @@ int gptoss_decode_destroy(gptoss_decode_t *h) {
 
 int gptoss_decode_create(const gptoss_model_config_t *cfg, int max_batch, int device,
                          gptoss_decode_t **out) {
+  return gptoss_decode_create_ep(cfg, max_batch, device, 0, 1, out);
+}
+
+int gptoss_decode_create_ep(const gptoss_model_config_t *cfg, int max_batch, int device,
+                            int ep_rank, int ep_size, gptoss_decode_t **out) {
   if (!cfg || !out) return dfail(nullptr, GPTOSS_E_INVALID, "null argument");
   *out = nullptr;
   const gptoss_model_config_t &c = *cfg;
@@ -398,8 +404,8 @@ int gptoss_decode_create(const gptoss_model_config_t *cfg, int max_batch, int de
   mc.n_layers = c.n_layers;
   mc.max_tokens = max_batch;
   mc.swiglu_limit = c.swiglu_limit;
-  mc.ep_rank = 0;
-  mc.ep_size = 1;
+  mc.ep_rank = ep_rank;
+  mc.ep_size = ep_size < 1 ? 1 : ep_size;
   mc.weight_format = GPTOSS_WEIGHTS_BF16;
   mc.device = device;
   gptoss_moe *moe = nullptr;
@@ -410,6 +416,7 @@ int gptoss_decode_create(const gptoss_model_config_t *cfg, int max_batch, int de
   h->max_batch = max_batch;
   h->device = device;
   h->moe = moe;
+  h->have.assign(c.n_layers + 1, 0u);
   auto bail = [&](int code, const std::string &msg) {
     g_decode_create_err = msg;
     gptoss_decode_destroy(h);
@@ -472,6 +479,74 @@ int gptoss_decode_load_weights(gptoss_decode_t *h, const gptoss_model_weights_t 
     if (rc) return dfail(h, rc, "MoE layer %d: %s", static_cast<int>(l), gptoss_moe_last_error(h->moe));
   }
   h->loaded = true;
+  return GPTOSS_OK;
+}
+
+int gptoss_decode_set_tensor(gptoss_decode_t *h, const char *name, int layer, const void *src,
+                             int on_device, int is_bf16) {
+  if (!h || !name || !src) return GPTOSS_E_INVALID;
+  const gptoss_model_config_t &c = h->cfg;
+  const size_t V = c.vocab_size, H = c.hidden_dim, D = c.head_dim;
+  const size_t dq = c.n_attn_heads * D, dqkv = dq + 2 * c.n_kv_heads * D;
+  struct Slot { const char *name; bool per_layer; bool bf; void *base; size_t n; int bit; };
+  const Slot slots[] = {
+      {"token_embedding_table", false, true, h->emb, V * H, 0},
+      {"out", false, true, h->unemb, V * H, 1},
+      {"rms_out_w", false, false, h->rms_out, H, 2},
+      {"w_qkv", true, true, h->w_qkv, dqkv * H, 0},
+      {"b_qkv", true, false, h->b_qkv, dqkv, 1},
+      {"w_o", true, true, h->w_o, H * dq, 2},
+      {"b_o", true, false, h->b_o, H, 3},
+      {"attn_sinks", true, false, h->sinks, static_cast<size_t>(c.n_attn_heads), 4},
+      {"rms_attn_w", true, false, h->rms_attn, H, 5},
+      {"rms_ffn_w", true, false, h->rms_ffn, H, 6},
+  };
+  DCK(h, cudaSetDevice(h->device));
+  for (const Slot &sl : slots) {
+    if (strcmp(sl.name, name)) continue;
+    if (sl.per_layer && (layer < 0 || layer >= c.n_layers)) return dfail(h, GPTOSS_E_INVALID, "layer out of range");
+    const size_t l = sl.per_layer ? layer : 0;
+    if (sl.bf) {
+      bf16 *dst = static_cast<bf16 *>(sl.base) + l * sl.n;
+      if (on_device && is_bf16) {
+        DCK(h, cudaMemcpy(dst, src, sl.n * sizeof(bf16), cudaMemcpyDeviceToDevice));
+      } else if (!on_device && !is_bf16) {
+        int rc = upload_f32_as_bf16(h->moe, dst, static_cast<const float *>(src), sl.n);
+        if (rc) return dfail(h, rc, "upload: %s", gptoss_moe_last_error(h->moe));
+      } else {
+        return dfail(h, GPTOSS_E_INVALID, "%s takes fp32 host data or bf16 device data", name);
+      }
+    } else {
+      if (is_bf16) return dfail(h, GPTOSS_E_INVALID, "%s is an fp32 tensor", name);
+      float *dst = static_cast<float *>(sl.base) + l * sl.n;
+      DCK(h, cudaMemcpy(dst, src, sl.n * sizeof(float),
+                        on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice));
+    }
+    h->have[sl.per_layer ? layer + 1 : 0] |= 1u << sl.bit;
+    bool all = h->have[0] == 0x7u;
+    for (int i = 1; i <= c.n_layers; i++) all = all && h->have[i] == 0x7fu;
+    h->loaded = all;  // the MoE engine checks its own layers
+    return GPTOSS_OK;
+  }
+  return dfail(h, GPTOSS_E_INVALID, "unknown tensor '%s'", name);
+}
+
+int gptoss_decode_set_kv(gptoss_decode_t *h, int layer, int row0, int n_rows, int pos0, int n_pos,
+                         const void *k_dev, const void *v_dev) {
+  if (!h || !k_dev || !v_dev) return GPTOSS_E_INVALID;
+  const gptoss_model_config_t &c = h->cfg;
+  if (layer < 0 || layer >= c.n_layers || row0 < 0 || n_rows < 0 || row0 + n_rows > h->max_batch ||
+      pos0 < 0 || n_pos < 0 || pos0 + n_pos > c.seq_len)
+    return dfail(h, GPTOSS_E_INVALID, "cache region out of range");
+  if (n_rows == 0 || n_pos == 0) return GPTOSS_OK;
+  DCK(h, cudaSetDevice(h->device));
+  const size_t dkv = static_cast<size_t>(c.n_kv_heads) * c.head_dim, S = c.seq_len;
+  const size_t off = ((static_cast<size_t>(layer) * h->max_batch + row0) * S + pos0) * dkv;
+  // per row: n_pos * dkv contiguous elements, rows S * dkv apart in the cache
+  DCK(h, cudaMemcpy2D(h->k_cache + off, S * dkv * sizeof(bf16), k_dev, n_pos * dkv * sizeof(bf16),
+                      n_pos * dkv * sizeof(bf16), n_rows, cudaMemcpyDeviceToDevice));
+  DCK(h, cudaMemcpy2D(h->v_cache + off, S * dkv * sizeof(bf16), v_dev, n_pos * dkv * sizeof(bf16),
+                      n_pos * dkv * sizeof(bf16), n_rows, cudaMemcpyDeviceToDevice));
   return GPTOSS_OK;
 }
 
@@ -549,14 +624,15 @@ int gptoss_decode_step(gptoss_decode_t *h, const int *tokens, const int *pos, in
     DCK(h, cudaGetLastError());
     // sliding window on even layers (run.cpp:619)
     const int window = (c.sliding_window > 0 && (l % 2 == 0)) ? c.sliding_window : 0;
-    const int nw = B * Hq, grid = (nw + 3) / 4;
+    // 8 warps per CTA: with 8 query heads per KV head they read the same cache rows
+    const int nw = B * Hq, grid = (nw + 7) / 8;
     const float *sinks = h->sinks + static_cast<size_t>(l) * Hq;
     if (D == 32)
-      attn_decode_kernel<32><<<grid, 128, 0, st>>>(h->q, kc, vc, sinks, h->d_pos, h->attn, B, Hq, Hkv, S, window);
+      attn_decode_kernel<32><<<grid, 256, 0, st>>>(h->q, kc, vc, sinks, h->d_pos, h->attn, B, Hq, Hkv, S, window);
     else if (D == 64)
-      attn_decode_kernel<64><<<grid, 128, 0, st>>>(h->q, kc, vc, sinks, h->d_pos, h->attn, B, Hq, Hkv, S, window);
+      attn_decode_kernel<64><<<grid, 256, 0, st>>>(h->q, kc, vc, sinks, h->d_pos, h->attn, B, Hq, Hkv, S, window);
     else
-      attn_decode_kernel<128><<<grid, 128, 0, st>>>(h->q, kc, vc, sinks, h->d_pos, h->attn, B, Hq, Hkv, S, window);
+      attn_decode_kernel<128><<<grid, 256, 0, st>>>(h->q, kc, vc, sinks, h->d_pos, h->attn, B, Hq, Hkv, S, window);
     DCK(h, cudaGetLastError());
     if ((rc = gemm_xwt(h, h->attn, h->w_o + static_cast<size_t>(l) * H * dq, h->proj, B, H, dq))) return rc;
     const size_t n = static_cast<size_t>(B) * H;

@@ -78,6 +78,12 @@ int gptoss_decode_device_count(void);
  * fallback: fails unless the device is sm_100 and cuBLAS can be loaded. */
 int gptoss_decode_create(const gptoss_model_config_t *cfg, int max_batch, int device,
                          gptoss_decode_t **out);
+/* The same with the experts sharded over ep_size ranks (expert e on rank e % ep_size,
+ * everything else replicated; getp-csrc/expert.cpp:709-1018).  After creation every
+ * rank calls gptoss_moe_ep_init(gptoss_decode_moe(h), id); the ranks then step in lock
+ * step, each on its own batch. */
+int gptoss_decode_create_ep(const gptoss_model_config_t *cfg, int max_batch, int device,
+                            int ep_rank, int ep_size, gptoss_decode_t **out);
 int gptoss_decode_destroy(gptoss_decode_t *h);
 /* Error text of the last failed call on this handle (or of the last failed create
  * when h is NULL). */
@@ -89,6 +95,20 @@ int gptoss_decode_load_weights(gptoss_decode_t *h, const gptoss_model_weights_t 
 /* The same from the address of the first tensor of a .bin image (file base + 60
  * bytes), tensors in the file's order (memory_map_weights, run.cpp:207-248). */
 int gptoss_decode_load_bin(gptoss_decode_t *h, const float *first_tensor);
+
+/* One tensor at a time, for models too large for a host image: name = a field of
+ * gptoss_model_weights_t outside the MoE block ("token_embedding_table", "out",
+ * "rms_out_w"; per layer "w_qkv", "b_qkv", "w_o", "b_o", "attn_sinks", "rms_attn_w",
+ * "rms_ffn_w"), src = that tensor (one layer of it) as fp32 on the host, or on the
+ * device as bf16 (weights) / fp32 (biases, scales, sinks).  The MoE tensors go through
+ * gptoss_moe_load_layer_* on gptoss_decode_moe(h). */
+int gptoss_decode_set_tensor(gptoss_decode_t *h, const char *name, int layer, const void *src,
+                             int on_device, int is_bf16);
+/* Writes K and V (bf16 device arrays [n_rows, n_pos, Hkv * D], K already rotated) into
+ * the cache of `layer` for rows row0.. and positions pos0..: a context without running
+ * the prompt (benchmarks with synthetic contexts). */
+int gptoss_decode_set_kv(gptoss_decode_t *h, int layer, int row0, int n_rows, int pos0, int n_pos,
+                         const void *k_dev, const void *v_dev);
 
 /* One step.  tokens[i] / pos[i]: the token to feed to batch row i and its position
  * (host arrays); pos[i] < 0 marks a row that does no work (its cache is untouched
