@@ -128,82 +128,98 @@ qkv_rope_cache_kernel(const float *__restrict__ qkv, const float *__restrict__ b
 // One warp per (row, query head): online softmax over the cache positions t0..pos plus
 // the head's sink logit, which takes probability mass but has no value row
 // (run.cpp:601-647; the sliding-window mask of even layers, run.cpp:176-183, 619-621,
-// becomes the lower bound t0 = pos - window + 1).  Each lane walks every 32nd position
-// with its own running maximum, sum and D-wide accumulator; the lanes are merged at the
-// end.  Output bf16 [B, Hq D].
+// becomes the lower bound t0 = pos - window + 1).  A cache row of D elements is read by
+// D/8 adjacent lanes, 16 bytes each, so a warp covers 256/D positions per iteration with
+// fully used 128-byte segments; the partial dot products meet by shuffle, every lane group
+// keeps its own running maximum, sum and 8-wide slice of the accumulator, and the groups
+// are merged at the end.  Few registers per thread, so many warps per SM hide the cache
+// latency.  Output bf16 [B, Hq D].
 template <int D>
 __global__ void __launch_bounds__(256)
 attn_decode_kernel(const float *__restrict__ q, const bf16 *__restrict__ k_cache,
                    const bf16 *__restrict__ v_cache, const float *__restrict__ sinks,
                    const int *__restrict__ pos, bf16 *__restrict__ out, int B, int Hq, int Hkv,
                    int S, int window) {
+  constexpr int LP = D / 8;    // lanes per position
+  constexpr int PP = 32 / LP;  // positions per warp iteration
   const int lane = threadIdx.x & 31;
   const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (w >= B * Hq) return;
   const int row = w / Hq, h = w - row * Hq;
   const int p = pos[row];
   if (p < 0) return;
+  const int sub = lane % LP, grp = lane / LP;
   const int kvh = h / (Hq / Hkv);
   const int dkv = Hkv * D;
   const int t0 = window > 0 ? max(0, p - window + 1) : 0;
-  float qr[D];
-#pragma unroll
-  for (int i = 0; i < D; i++) qr[i] = q[(static_cast<size_t>(row) * Hq + h) * D + i];
-  const float scale = 1.0f / sqrtf(static_cast<float>(D));
-  float m = -INFINITY, l = 0.f;
-  float acc[D];
-#pragma unroll
-  for (int i = 0; i < D; i++) acc[i] = 0.f;
-  for (int t = t0 + lane; t <= p; t += 32) {
-    const size_t off = (static_cast<size_t>(row) * S + t) * dkv + kvh * D;
-    const uint4 *k4 = reinterpret_cast<const uint4 *>(k_cache + off);
-    float s = 0.f;
-#pragma unroll
-    for (int c = 0; c < D / 8; c++) {
-      const uint4 v = __ldg(k4 + c);
-      s += qr[8 * c + 0] * bf16_lo(v.x) + qr[8 * c + 1] * bf16_hi(v.x) +
-           qr[8 * c + 2] * bf16_lo(v.y) + qr[8 * c + 3] * bf16_hi(v.y) +
-           qr[8 * c + 4] * bf16_lo(v.z) + qr[8 * c + 5] * bf16_hi(v.z) +
-           qr[8 * c + 6] * bf16_lo(v.w) + qr[8 * c + 7] * bf16_hi(v.w);
-    }
-    s *= scale;
-    const float m_new = fmaxf(m, s);
-    const float corr = __expf(m - m_new), pr = __expf(s - m_new);
-    l = l * corr + pr;
-    const uint4 *v4 = reinterpret_cast<const uint4 *>(v_cache + off);
-#pragma unroll
-    for (int c = 0; c < D / 8; c++) {
-      const uint4 v = __ldg(v4 + c);
-      acc[8 * c + 0] = acc[8 * c + 0] * corr + pr * bf16_lo(v.x);
-      acc[8 * c + 1] = acc[8 * c + 1] * corr + pr * bf16_hi(v.x);
-      acc[8 * c + 2] = acc[8 * c + 2] * corr + pr * bf16_lo(v.y);
-      acc[8 * c + 3] = acc[8 * c + 3] * corr + pr * bf16_hi(v.y);
-      acc[8 * c + 4] = acc[8 * c + 4] * corr + pr * bf16_lo(v.z);
-      acc[8 * c + 5] = acc[8 * c + 5] * corr + pr * bf16_hi(v.z);
-      acc[8 * c + 6] = acc[8 * c + 6] * corr + pr * bf16_lo(v.w);
-      acc[8 * c + 7] = acc[8 * c + 7] * corr + pr * bf16_hi(v.w);
-    }
-    m = m_new;
+  float qr[8];
+  {
+    const float4 *q4 =
+        reinterpret_cast<const float4 *>(q + (static_cast<size_t>(row) * Hq + h) * D + 8 * sub);
+    const float4 a = q4[0], b = q4[1];
+    const float scale = 1.0f / sqrtf(static_cast<float>(D));
+    qr[0] = a.x * scale; qr[1] = a.y * scale; qr[2] = a.z * scale; qr[3] = a.w * scale;
+    qr[4] = b.x * scale; qr[5] = b.y * scale; qr[6] = b.z * scale; qr[7] = b.w * scale;
   }
-  // merge the lanes: common maximum (the sink logit included), rescaled sums
+  float m = -INFINITY, l = 0.f;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) acc[i] = 0.f;
+  const size_t base = static_cast<size_t>(row) * S * dkv + kvh * D + 8 * sub;
+  // all lanes run the same number of iterations (shuffles inside); lanes past pos idle
+  for (int tb = t0; tb <= p; tb += PP) {
+    const int t = tb + grp;
+    const bool live = t <= p;
+    uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
+    if (live) {
+      kv = __ldg(reinterpret_cast<const uint4 *>(k_cache + base + static_cast<size_t>(t) * dkv));
+      vv = __ldg(reinterpret_cast<const uint4 *>(v_cache + base + static_cast<size_t>(t) * dkv));
+    }
+    float s = qr[0] * bf16_lo(kv.x) + qr[1] * bf16_hi(kv.x) + qr[2] * bf16_lo(kv.y) +
+              qr[3] * bf16_hi(kv.y) + qr[4] * bf16_lo(kv.z) + qr[5] * bf16_hi(kv.z) +
+              qr[6] * bf16_lo(kv.w) + qr[7] * bf16_hi(kv.w);
+#pragma unroll
+    for (int off = 1; off < LP; off <<= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    if (live) {
+      const float m_new = fmaxf(m, s);
+      const float corr = __expf(m - m_new), pr = __expf(s - m_new);
+      l = l * corr + pr;
+      acc[0] = acc[0] * corr + pr * bf16_lo(vv.x);
+      acc[1] = acc[1] * corr + pr * bf16_hi(vv.x);
+      acc[2] = acc[2] * corr + pr * bf16_lo(vv.y);
+      acc[3] = acc[3] * corr + pr * bf16_hi(vv.y);
+      acc[4] = acc[4] * corr + pr * bf16_lo(vv.z);
+      acc[5] = acc[5] * corr + pr * bf16_hi(vv.z);
+      acc[6] = acc[6] * corr + pr * bf16_lo(vv.w);
+      acc[7] = acc[7] * corr + pr * bf16_hi(vv.w);
+      m = m_new;
+    }
+  }
+  // merge the position groups: common maximum (the sink logit included), rescaled sums
   float m_all = m;
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) m_all = fmaxf(m_all, __shfl_xor_sync(0xffffffffu, m_all, off));
+  for (int off = LP; off < 32; off <<= 1) m_all = fmaxf(m_all, __shfl_xor_sync(0xffffffffu, m_all, off));
   const float sink = sinks[h];
   m_all = fmaxf(m_all, sink);
   const float mine = (m == -INFINITY) ? 0.f : __expf(m - m_all);
   l *= mine;
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+  for (int i = 0; i < 8; i++) acc[i] *= mine;
+#pragma unroll
+  for (int off = LP; off < 32; off <<= 1) {
+    l += __shfl_xor_sync(0xffffffffu, l, off);
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], off);
+  }
   l += __expf(sink - m_all);
-  const float inv = 1.0f / l;
-  bf16 *dst = out + (static_cast<size_t>(row) * Hq + h) * D;
-#pragma unroll
-  for (int i = 0; i < D; i++) {
-    float a = acc[i] * mine;
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
-    if (lane == (i & 31)) dst[i] = __float2bfloat16_rn(a * inv);
+  if (grp == 0) {
+    const float inv = 1.0f / l;
+    uint4 o;
+    o.x = pack_bf16(acc[0] * inv, acc[1] * inv);
+    o.y = pack_bf16(acc[2] * inv, acc[3] * inv);
+    o.z = pack_bf16(acc[4] * inv, acc[5] * inv);
+    o.w = pack_bf16(acc[6] * inv, acc[7] * inv);
+    *reinterpret_cast<uint4 *>(out + (static_cast<size_t>(row) * Hq + h) * D + 8 * sub) = o;
   }
 }
 

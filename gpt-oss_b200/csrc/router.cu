@@ -29,7 +29,7 @@ constexpr int kRtKC = 64;          // K elements per pipeline stage
 template <int NT> struct RtStages { static constexpr int value = NT <= 2 ? 6 : (NT == 4 ? 4 : 3); };
 constexpr int kRtRowBytes = 144;   // 128 B of data + 16 B pad: conflict-free ldmatrix
 constexpr int kRtThreads = 256;
-constexpr float kTieGuard = 1e-3f;
+constexpr float kTieGuard = 2.5e-4f;
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src),
