@@ -125,31 +125,36 @@ qkv_rope_cache_kernel(const float *__restrict__ qkv, const float *__restrict__ b
   }
 }
 
-// One warp per (row, query head): online softmax over the cache positions t0..pos plus
-// the head's sink logit, which takes probability mass but has no value row
-// (run.cpp:601-647; the sliding-window mask of even layers, run.cpp:176-183, 619-621,
-// becomes the lower bound t0 = pos - window + 1).  A cache row of D elements is read by
-// D/8 adjacent lanes, 16 bytes each, so a warp covers 256/D positions per iteration with
-// fully used 128-byte segments; the partial dot products meet by shuffle, every lane group
-// keeps its own running maximum, sum and 8-wide slice of the accumulator, and the groups
-// are merged at the end.  Few registers per thread, so many warps per SM hide the cache
-// latency.  Output bf16 [B, Hq D].
+// One CTA per (row, KV head), one warp per query head of the group: online softmax over
+// the cache positions t0..pos plus the head's sink logit, which takes probability mass
+// but has no value row (run.cpp:601-647; the sliding-window mask of even layers,
+// run.cpp:176-183, 619-621, becomes the lower bound t0 = pos - window + 1).  The CTA
+// stages tiles of 32 cache positions (K and V rows of the KV head) in shared memory
+// once for all its query heads, double buffered through registers.  Inside a warp a
+// cache row of D elements is read by D/8 adjacent lanes, 16 bytes each, so a warp
+// covers 256/D positions per step; the partial dot products meet by shuffle, every lane
+// group keeps its own running maximum, sum and 8-wide slice of the accumulator, and the
+// groups are merged at the end.  Output bf16 [B, Hq D].
+constexpr int kAttnTile = 32;
+
 template <int D>
 __global__ void __launch_bounds__(256)
 attn_decode_kernel(const float *__restrict__ q, const bf16 *__restrict__ k_cache,
                    const bf16 *__restrict__ v_cache, const float *__restrict__ sinks,
                    const int *__restrict__ pos, bf16 *__restrict__ out, int B, int Hq, int Hkv,
                    int S, int window) {
-  constexpr int LP = D / 8;    // lanes per position
-  constexpr int PP = 32 / LP;  // positions per warp iteration
-  const int lane = threadIdx.x & 31;
-  const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (w >= B * Hq) return;
-  const int row = w / Hq, h = w - row * Hq;
+  constexpr int LP = D / 8;                // lanes per position
+  constexpr int PP = 32 / LP;              // positions per warp step
+  constexpr int kChunks = kAttnTile * LP;  // 16-byte chunks of one K (or V) tile
+  __shared__ uint4 tile_k[2][kChunks];
+  __shared__ uint4 tile_v[2][kChunks];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int row = blockIdx.x / Hkv, kvh = blockIdx.x - row * Hkv;
   const int p = pos[row];
-  if (p < 0) return;
+  if (p < 0) return;  // the whole CTA leaves
+  const int group = Hq / Hkv;  // query heads per KV head = warps of this CTA
+  const int h = kvh * group + warp;
   const int sub = lane % LP, grp = lane / LP;
-  const int kvh = h / (Hq / Hkv);
   const int dkv = Hkv * D;
   const int t0 = window > 0 ? max(0, p - window + 1) : 0;
   float qr[8];
@@ -165,36 +170,97 @@ attn_decode_kernel(const float *__restrict__ q, const bf16 *__restrict__ k_cache
   float acc[8];
 #pragma unroll
   for (int i = 0; i < 8; i++) acc[i] = 0.f;
-  const size_t base = static_cast<size_t>(row) * S * dkv + kvh * D + 8 * sub;
-  // all lanes run the same number of iterations (shuffles inside); lanes past pos idle
-  for (int tb = t0; tb <= p; tb += PP) {
-    const int t = tb + grp;
-    const bool live = t <= p;
-    uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
-    if (live) {
-      kv = __ldg(reinterpret_cast<const uint4 *>(k_cache + base + static_cast<size_t>(t) * dkv));
-      vv = __ldg(reinterpret_cast<const uint4 *>(v_cache + base + static_cast<size_t>(t) * dkv));
-    }
-    float s = qr[0] * bf16_lo(kv.x) + qr[1] * bf16_hi(kv.x) + qr[2] * bf16_lo(kv.y) +
-              qr[3] * bf16_hi(kv.y) + qr[4] * bf16_lo(kv.z) + qr[5] * bf16_hi(kv.z) +
-              qr[6] * bf16_lo(kv.w) + qr[7] * bf16_hi(kv.w);
+  const size_t base = static_cast<size_t>(row) * S * dkv + kvh * D;
+  constexpr int kPerThread = (kChunks + 255) / 256;  // chunks a thread stages (block <= 256)
+  uint4 rk[kPerThread], rv[kPerThread];
+  auto fetch = [&](int tile0) {
 #pragma unroll
-    for (int off = 1; off < LP; off <<= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-    if (live) {
-      const float m_new = fmaxf(m, s);
-      const float corr = __expf(m - m_new), pr = __expf(s - m_new);
-      l = l * corr + pr;
-      acc[0] = acc[0] * corr + pr * bf16_lo(vv.x);
-      acc[1] = acc[1] * corr + pr * bf16_hi(vv.x);
-      acc[2] = acc[2] * corr + pr * bf16_lo(vv.y);
-      acc[3] = acc[3] * corr + pr * bf16_hi(vv.y);
-      acc[4] = acc[4] * corr + pr * bf16_lo(vv.z);
-      acc[5] = acc[5] * corr + pr * bf16_hi(vv.z);
-      acc[6] = acc[6] * corr + pr * bf16_lo(vv.w);
-      acc[7] = acc[7] * corr + pr * bf16_hi(vv.w);
-      m = m_new;
+    for (int u = 0; u < kPerThread; u++) {
+      const int c = tid + u * blockDim.x;
+      rk[u] = rv[u] = make_uint4(0, 0, 0, 0);
+      const int t = tile0 + c / LP;
+      if (c < kChunks && t <= p) {
+        const size_t off = base + static_cast<size_t>(t) * dkv + 8 * (c % LP);
+        rk[u] = __ldg(reinterpret_cast<const uint4 *>(k_cache + off));
+        rv[u] = __ldg(reinterpret_cast<const uint4 *>(v_cache + off));
+      }
     }
+  };
+  auto stash = [&](int buf) {
+#pragma unroll
+    for (int u = 0; u < kPerThread; u++) {
+      const int c = tid + u * blockDim.x;
+      if (c < kChunks) {
+        tile_k[buf][c] = rk[u];
+        tile_v[buf][c] = rv[u];
+      }
+    }
+  };
+  // blockDim may be smaller than 256 (few query heads per KV head): stage in several rounds
+  const int rounds = (kChunks + kPerThread * blockDim.x - 1) / (kPerThread * blockDim.x);
+  auto fetch_stash_all = [&](int tile0, int buf) {
+    for (int r = 0; r < rounds; r++) {
+#pragma unroll
+      for (int u = 0; u < kPerThread; u++) {
+        const int c = tid + (r * kPerThread + u) * blockDim.x;
+        if (c < kChunks) {
+          const int t = tile0 + c / LP;
+          uint4 a = make_uint4(0, 0, 0, 0), b = a;
+          if (t <= p) {
+            const size_t off = base + static_cast<size_t>(t) * dkv + 8 * (c % LP);
+            a = __ldg(reinterpret_cast<const uint4 *>(k_cache + off));
+            b = __ldg(reinterpret_cast<const uint4 *>(v_cache + off));
+          }
+          tile_k[buf][c] = a;
+          tile_v[buf][c] = b;
+        }
+      }
+    }
+  };
+  const bool wide = rounds == 1;  // every chunk of a tile has its own thread slot
+  int buf = 0;
+  fetch_stash_all(t0, 0);
+  __syncthreads();
+  for (int tile0 = t0; tile0 <= p; tile0 += kAttnTile) {
+    const bool more = tile0 + kAttnTile <= p;
+    if (more && wide) fetch(tile0 + kAttnTile);  // next tile in flight during the math
+    if (warp < group) {
+#pragma unroll
+      for (int j = 0; j < kAttnTile / PP; j++) {
+        const int c = (j * PP + grp) * LP + sub;
+        const int t = tile0 + j * PP + grp;
+        const uint4 kv = tile_k[buf][c], vv = tile_v[buf][c];
+        float s = qr[0] * bf16_lo(kv.x) + qr[1] * bf16_hi(kv.x) + qr[2] * bf16_lo(kv.y) +
+                  qr[3] * bf16_hi(kv.y) + qr[4] * bf16_lo(kv.z) + qr[5] * bf16_hi(kv.z) +
+                  qr[6] * bf16_lo(kv.w) + qr[7] * bf16_hi(kv.w);
+#pragma unroll
+        for (int off = 1; off < LP; off <<= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+        if (t <= p) {
+          const float m_new = fmaxf(m, s);
+          const float corr = __expf(m - m_new), pr = __expf(s - m_new);
+          l = l * corr + pr;
+          acc[0] = acc[0] * corr + pr * bf16_lo(vv.x);
+          acc[1] = acc[1] * corr + pr * bf16_hi(vv.x);
+          acc[2] = acc[2] * corr + pr * bf16_lo(vv.y);
+          acc[3] = acc[3] * corr + pr * bf16_hi(vv.y);
+          acc[4] = acc[4] * corr + pr * bf16_lo(vv.z);
+          acc[5] = acc[5] * corr + pr * bf16_hi(vv.z);
+          acc[6] = acc[6] * corr + pr * bf16_lo(vv.w);
+          acc[7] = acc[7] * corr + pr * bf16_hi(vv.w);
+          m = m_new;
+        }
+      }
+    }
+    if (more) {
+      if (wide)
+        stash(buf ^ 1);
+      else
+        fetch_stash_all(tile0 + kAttnTile, buf ^ 1);
+    }
+    __syncthreads();
+    buf ^= 1;
   }
+  if (warp >= group) return;
   // merge the position groups: common maximum (the sink logit included), rescaled sums
   float m_all = m;
 #pragma unroll
@@ -246,11 +312,31 @@ argmax_rows_kernel(const float *__restrict__ logits, const int *__restrict__ pos
   const float *l = logits + static_cast<size_t>(row) * V;
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = l[i];
-    if (v > best || (v == best && i < bi)) {
-      best = v;
-      bi = i;
+  if ((V & 3) == 0) {  // rows are 16-byte aligned: four logits per load, two loads in flight
+    const float4 *l4 = reinterpret_cast<const float4 *>(l);
+    const int n4 = V >> 2;
+    for (int i = threadIdx.x; i < n4; i += 2 * blockDim.x) {
+      const int i2 = i + blockDim.x;
+      const float4 a = __ldcs(l4 + i);
+      const float4 b = i2 < n4 ? __ldcs(l4 + i2) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+      const float va[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        const int idx = (u < 4 ? 4 * i : 4 * i2) + (u & 3);
+        // indices only grow inside a thread, so a strict comparison keeps the lowest one
+        if (va[u] > best) {
+          best = va[u];
+          bi = idx;
+        }
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float v = l[i];
+      if (v > best) {
+        best = v;
+        bi = i;
+      }
     }
   }
   __shared__ float sv[256];
@@ -408,8 +494,9 @@ int gptoss_decode_create_ep(const gptoss_model_config_t *cfg, int max_batch, int
     return dfail(nullptr, GPTOSS_E_INVALID, "non-positive dimension");
   if (c.head_dim != 32 && c.head_dim != 64 && c.head_dim != 128)
     return dfail(nullptr, GPTOSS_E_INVALID, "head_dim must be 32, 64 or 128");
-  if (c.n_attn_heads % c.n_kv_heads)
-    return dfail(nullptr, GPTOSS_E_INVALID, "n_attn_heads must be a multiple of n_kv_heads");
+  if (c.n_attn_heads % c.n_kv_heads || c.n_attn_heads / c.n_kv_heads > 8)
+    return dfail(nullptr, GPTOSS_E_INVALID,
+                 "n_attn_heads must be a multiple of n_kv_heads, at most 8 times it");
   if (c.hidden_dim % 8)
     return dfail(nullptr, GPTOSS_E_INVALID, "hidden_dim must be a multiple of 8");
   gptoss_moe_config_t mc = {};
@@ -640,15 +727,15 @@ int gptoss_decode_step(gptoss_decode_t *h, const int *tokens, const int *pos, in
     DCK(h, cudaGetLastError());
     // sliding window on even layers (run.cpp:619)
     const int window = (c.sliding_window > 0 && (l % 2 == 0)) ? c.sliding_window : 0;
-    // 8 warps per CTA: with 8 query heads per KV head they read the same cache rows
-    const int nw = B * Hq, grid = (nw + 7) / 8;
+    // one CTA per (row, KV head), one warp per query head of the group
+    const int grid = B * Hkv, threads = 32 * (Hq / Hkv);
     const float *sinks = h->sinks + static_cast<size_t>(l) * Hq;
     if (D == 32)
-      attn_decode_kernel<32><<<grid, 256, 0, st>>>(h->q, kc, vc, sinks, h->d_pos, h->attn, B, Hq, Hkv, S, window);
+      attn_decode_kernel<32><<<grid, threads, 0, st>>>(h->q, kc, vc, sinks, h->d_pos, h->attn, B, Hq, Hkv, S, window);
     else if (D == 64)
-      attn_decode_kernel<64><<<grid, 256, 0, st>>>(h->q, kc, vc, sinks, h->d_pos, h->attn, B, Hq, Hkv, S, window);
+      attn_decode_kernel<64><<<grid, threads, 0, st>>>(h->q, kc, vc, sinks, h->d_pos, h->attn, B, Hq, Hkv, S, window);
     else
-      attn_decode_kernel<128><<<grid, 256, 0, st>>>(h->q, kc, vc, sinks, h->d_pos, h->attn, B, Hq, Hkv, S, window);
+      attn_decode_kernel<128><<<grid, threads, 0, st>>>(h->q, kc, vc, sinks, h->d_pos, h->attn, B, Hq, Hkv, S, window);
     DCK(h, cudaGetLastError());
     if ((rc = gemm_xwt(h, h->attn, h->w_o + static_cast<size_t>(l) * H * dq, h->proj, B, H, dq))) return rc;
     const size_t n = static_cast<size_t>(B) * H;
