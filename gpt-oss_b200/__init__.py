@@ -99,6 +99,8 @@ def load_library() -> ctypes.CDLL:
         ),
         "gptoss_moe_forward": (c_int, [vp, c_int, vp, vp, vp, c_int, vp]),
         "gptoss_moe_forward_host": (c_int, [vp, c_int, vp, vp, vp, c_int]),
+        "gptoss_moe_forward_host_submit": (c_int, [vp, c_int, vp, vp, vp, c_int, ip]),
+        "gptoss_moe_forward_host_wait": (c_int, [vp, c_int]),
         "gptoss_moe_route": (c_int, [vp, c_int, vp, vp, c_int, vp]),
         "gptoss_moe_permute": (c_int, [vp, vp, c_int, vp]),
         "gptoss_moe_experts": (c_int, [vp, c_int, vp]),
@@ -255,6 +257,16 @@ class MoeEngine:
     def forward_host(self, layer, t_host, x_host, pos_host, n_tokens):
         self._check(self.lib.gptoss_moe_forward_host(self.handle, layer, _ptr(t_host),
                                                      _ptr(x_host), _ptr(pos_host), n_tokens))
+
+    def forward_host_submit(self, layer, t_host, x_host, pos_host, n_tokens) -> int:
+        ticket = ctypes.c_int()
+        self._check(self.lib.gptoss_moe_forward_host_submit(
+            self.handle, layer, _ptr(t_host), _ptr(x_host), _ptr(pos_host), n_tokens,
+            ctypes.byref(ticket)))
+        return int(ticket.value)
+
+    def forward_host_wait(self, ticket: int):
+        self._check(self.lib.gptoss_moe_forward_host_wait(self.handle, ticket))
 
     def route(self, layer, t, pos, n_tokens, stream=0):
         self._check(self.lib.gptoss_moe_route(self.handle, layer, _ptr(t), _ptr(pos), n_tokens,

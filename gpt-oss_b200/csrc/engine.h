@@ -93,6 +93,18 @@ struct gptoss_moe {
   // host-call staging
   gptoss::bf16 *t_dev = nullptr, *x_dev = nullptr;
   int *pos_dev = nullptr;
+  // pipelined host-buffer path: staging slots, one stream per direction and one for the
+  // kernels, events that order them
+  struct HostSlot {
+    gptoss::bf16 *t = nullptr, *x = nullptr;
+    int *pos = nullptr;
+    cudaEvent_t h2d = nullptr, done = nullptr, d2h = nullptr;
+    bool busy = false;
+  };
+  static constexpr int kHostSlots = 3;
+  HostSlot host_slots[kHostSlots];
+  cudaStream_t s_h2d = nullptr, s_comp = nullptr, s_d2h = nullptr;
+  long long host_submitted = 0;
 
   int *status = nullptr;  // device status word
   int opt_gemm_impl = GPTOSS_GEMM_PAIR;

@@ -170,6 +170,16 @@ int gptoss_moe_destroy(gptoss_moe_t *h) {
   cudaFree(h->mtile_rows); cudaFree(h->num_mtiles); cudaFree(h->status); cudaFree(h->xs);
   cudaFree(h->hact); cudaFree(h->ys); cudaFree(h->t_dev); cudaFree(h->x_dev);
   cudaFree(h->pos_dev);
+  for (auto &sl : h->host_slots) {
+    if (sl.busy) cudaEventSynchronize(sl.d2h);
+    cudaFree(sl.t); cudaFree(sl.x); cudaFree(sl.pos);
+    if (sl.h2d) cudaEventDestroy(sl.h2d);
+    if (sl.done) cudaEventDestroy(sl.done);
+    if (sl.d2h) cudaEventDestroy(sl.d2h);
+  }
+  if (h->s_h2d) cudaStreamDestroy(h->s_h2d);
+  if (h->s_comp) cudaStreamDestroy(h->s_comp);
+  if (h->s_d2h) cudaStreamDestroy(h->s_d2h);
   for (auto &t : h->timers) {
     for (auto e : t.beg) cudaEventDestroy(e);
     for (auto e : t.end) cudaEventDestroy(e);
@@ -437,6 +447,75 @@ int gptoss_moe_forward_host(gptoss_moe_t *h, int layer, const void *t_host, void
   if (rc) return rc;
   CK(h, cudaMemcpyAsync(x_host, h->x_dev, bytes, cudaMemcpyDeviceToHost, st));
   CK(h, cudaStreamSynchronize(st));
+  return GPTOSS_OK;
+}
+
+int gptoss_moe_forward_host_submit(gptoss_moe_t *h, int layer, const void *t_host, void *x_host,
+                                   const int *pos_host, int n_tokens, int *ticket) {
+  if (!h || !ticket) return GPTOSS_E_INVALID;
+  if ((!t_host || !x_host) && n_tokens > 0)
+    return fail(h, GPTOSS_E_INVALID, "null activation pointer");
+  int rc = check_layer(h, layer, n_tokens);
+  if (rc) return rc;
+  if (h->ep_size > 1)
+    return fail(h, GPTOSS_E_STATE, "the pipelined host path is for engines with all experts local");
+  CK(h, cudaSetDevice(h->cfg.device));
+  if (!h->s_comp) {
+    CK(h, cudaStreamCreateWithFlags(&h->s_h2d, cudaStreamNonBlocking));
+    CK(h, cudaStreamCreateWithFlags(&h->s_comp, cudaStreamNonBlocking));
+    CK(h, cudaStreamCreateWithFlags(&h->s_d2h, cudaStreamNonBlocking));
+  }
+  const int si = static_cast<int>(h->host_submitted % gptoss_moe::kHostSlots);
+  gptoss_moe::HostSlot &sl = h->host_slots[si];
+  if (!sl.t) {
+    const size_t cap = (size_t)h->max_tokens * h->H;
+    CK(h, dev_alloc(&sl.t, cap));
+    CK(h, dev_alloc(&sl.x, cap));
+    CK(h, dev_alloc(&sl.pos, (size_t)h->max_tokens));
+    CK(h, cudaEventCreateWithFlags(&sl.h2d, cudaEventDisableTiming));
+    CK(h, cudaEventCreateWithFlags(&sl.done, cudaEventDisableTiming));
+    CK(h, cudaEventCreateWithFlags(&sl.d2h, cudaEventDisableTiming));
+  }
+  if (sl.busy) {  // the submission that used this slot three calls ago
+    CK(h, cudaEventSynchronize(sl.d2h));
+    sl.busy = false;
+  }
+  const size_t bytes = (size_t)n_tokens * h->H * sizeof(bf16);
+  if (n_tokens > 0) {
+    CK(h, cudaMemcpyAsync(sl.t, t_host, bytes, cudaMemcpyHostToDevice, h->s_h2d));
+    CK(h, cudaMemcpyAsync(sl.x, x_host, bytes, cudaMemcpyHostToDevice, h->s_h2d));
+    if (pos_host)
+      CK(h, cudaMemcpyAsync(sl.pos, pos_host, (size_t)n_tokens * 4, cudaMemcpyHostToDevice, h->s_h2d));
+  }
+  CK(h, cudaEventRecord(sl.h2d, h->s_h2d));
+  CK(h, cudaStreamWaitEvent(h->s_comp, sl.h2d, 0));
+  if (n_tokens > 0) {
+    rc = gptoss_moe_forward(h, layer, sl.t, sl.x, pos_host ? sl.pos : nullptr, n_tokens, h->s_comp);
+    if (rc) return rc;
+  }
+  CK(h, cudaEventRecord(sl.done, h->s_comp));
+  CK(h, cudaStreamWaitEvent(h->s_d2h, sl.done, 0));
+  if (n_tokens > 0)
+    CK(h, cudaMemcpyAsync(x_host, sl.x, bytes, cudaMemcpyDeviceToHost, h->s_d2h));
+  CK(h, cudaEventRecord(sl.d2h, h->s_d2h));
+  sl.busy = true;
+  *ticket = static_cast<int>(h->host_submitted & 0x7fffffff);
+  h->host_submitted++;
+  return GPTOSS_OK;
+}
+
+int gptoss_moe_forward_host_wait(gptoss_moe_t *h, int ticket) {
+  if (!h) return GPTOSS_E_INVALID;
+  const long long newest = h->host_submitted - 1;
+  const long long t = (newest & ~0x7fffffffll) | ticket;
+  if (ticket < 0 || t > newest) return fail(h, GPTOSS_E_INVALID, "unknown ticket");
+  if (newest - t >= gptoss_moe::kHostSlots) return GPTOSS_OK;  // its slot was reused: long done
+  gptoss_moe::HostSlot &sl = h->host_slots[t % gptoss_moe::kHostSlots];
+  if (sl.busy) {
+    CK(h, cudaSetDevice(h->cfg.device));
+    CK(h, cudaEventSynchronize(sl.d2h));
+    sl.busy = false;
+  }
   return GPTOSS_OK;
 }
 

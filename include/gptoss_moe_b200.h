@@ -137,6 +137,21 @@ int gptoss_moe_forward(gptoss_moe_t *h, int layer, const void *t, void *x, const
 int gptoss_moe_forward_host(gptoss_moe_t *h, int layer, const void *t_host, void *x_host,
                             const int *pos_host, int n_tokens);
 
+/*
+ * The same for callers that stream batch after batch: submit returns once the
+ * copies and kernels are queued; up to three submissions are in flight, each in
+ * its own staging buffers, so the host->device copy of one batch, the kernels of
+ * the previous one and the device->host copy of the one before run at the same
+ * time (one stream per direction and one for the kernels).  x_host is valid
+ * after gptoss_moe_forward_host_wait(h, ticket); t_host, x_host and pos_host must
+ * stay untouched until then.  A fourth submit waits for the oldest.  All experts
+ * local only.  No counterpart in the reference, whose host loop copies, computes
+ * and copies back in turn (getp_run.cpp:956-961).
+ */
+int gptoss_moe_forward_host_submit(gptoss_moe_t *h, int layer, const void *t_host, void *x_host,
+                                   const int *pos_host, int n_tokens, int *ticket);
+int gptoss_moe_forward_host_wait(gptoss_moe_t *h, int ticket);
+
 /* The stages of gptoss_moe_forward, individually (same order). */
 /* router linear + bias + top-k + softmax (matmul.cpp:945, utility.cpp:274). */
 int gptoss_moe_route(gptoss_moe_t *h, int layer, const void *t, const int *pos, int n_tokens,

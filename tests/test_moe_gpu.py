@@ -179,3 +179,41 @@ def test_rmsnorm_against_oracle(pkg, oracle):
     torch.cuda.synchronize()
     helpers.check_activations(out.float().cpu().numpy(), want, "rmsnorm")
     eng.close()
+
+
+def test_streamed_host_path_matches_one_call_path(pkg):
+    """Seven batches of different sizes through submit / wait (three in flight) give the
+    same bits as one forward_host call each."""
+    from gpt_oss_b200 import synth
+
+    shape = synth.MoeShape("stream", 300, 256, 192, 8, 4, 7.0, 21)
+    d = synth.make_layer(shape)
+    eng = pkg.MoeEngine(shape.hidden_dim, shape.intermediate_dim, shape.n_experts,
+                        shape.experts_per_token, n_layers=1, max_tokens=300)
+    eng.load_layer_f32(0, d["w_router"], d["b_router"], d["w_mlp1"], d["b_mlp1"], d["w_mlp2"],
+                       d["b_mlp2"])
+    rng = np.random.default_rng(4)
+    sizes = [300, 17, 0, 128, 255, 1, 64]
+    batches = []
+    for n in sizes:
+        t = synth.bf16_bits(synth.bf16_round(rng.standard_normal((n, 256)).astype(np.float32)))
+        x = synth.bf16_bits(synth.bf16_round(rng.standard_normal((n, 256)).astype(np.float32)))
+        pos = np.arange(n, dtype=np.int32)
+        pos[2::9] = -1
+        batches.append((t, x, pos))
+    want = []
+    for t, x, pos in batches:
+        xo = x.copy()
+        eng.forward_host(0, t, xo, pos, t.shape[0])
+        want.append(xo)
+    got = [x.copy() for _, x, _ in batches]
+    tickets = [eng.forward_host_submit(0, t, g, pos, t.shape[0])
+               for (t, _, pos), g in zip(batches, got)]
+    for tk in reversed(tickets):  # any order; old tickets are long complete
+        eng.forward_host_wait(tk)
+    assert eng.device_status() == 0
+    for a, b in zip(got, want):
+        np.testing.assert_array_equal(a, b)
+    with pytest.raises(pkg.MoeError):
+        eng.forward_host_wait(10_000)
+    eng.close()
