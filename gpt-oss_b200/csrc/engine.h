@@ -126,7 +126,7 @@ namespace gptoss {
 // router.cu
 cudaError_t launch_router_topk(const bf16 *t, const bf16 *w_router, const float *b_router,
                                const int *pos, int T, int H, int E, int K, int *topk_i,
-                               float *topk_v, float *logits_opt, int exact_ties,
+                               float *topk_v, float *logits_opt, int exact_ties, int *status,
                                cudaStream_t stream, long long *launches);
 cudaError_t launch_rmsnorm(bf16 *out, const bf16 *x, const float *w, const int *pos, int T, int H,
                            cudaStream_t stream, long long *launches);

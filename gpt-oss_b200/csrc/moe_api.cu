@@ -354,7 +354,7 @@ int gptoss_moe_route(gptoss_moe_t *h, int layer, const void *t, const int *pos, 
   StageScope sc(h, 0, st);
   CK(h, launch_router_topk(static_cast<const bf16 *>(t), lw.w_router, lw.b_router, pos, n_tokens,
                            h->H, h->E, h->K, h->topk_i, h->topk_v,
-                           h->opt_keep_logits ? h->logits : nullptr, h->opt_exact_ties, st,
+                           h->opt_keep_logits ? h->logits : nullptr, h->opt_exact_ties, h->status, st,
                            &h->launches));
   return GPTOSS_OK;
 }

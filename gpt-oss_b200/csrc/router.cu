@@ -8,9 +8,12 @@
 //
 // Layout: a CTA owns 32 consecutive tokens.  8 warps = 2 token groups of 16 x 4
 // expert slices; bf16 tensor-core MMAs (m16n8k16, fp32 accumulate) over K chunks
-// of 64 that are staged in shared memory with a 3- to 6-deep cp.async pipeline.  The
-// fp32 logits of the 32 tokens then sit in shared memory and one warp per token
-// does the selection in registers.
+// of 64.  A ninth warp is the producer: one thread issues two TMA tile loads per
+// chunk (32 token rows, all expert rows; 128-byte swizzle, rows past T or E read
+// as zeros) into a ring of 3 to 8 stages guarded by full / empty mbarriers, so the
+// compute warps spend their instructions on ldmatrix and MMAs only.  The fp32 logits
+// of the 32 tokens then sit in shared memory and one warp per token does the
+// selection in registers.
 //
 // Exact selection: fp32 tensor-core accumulation differs from the reference's
 // double-precision dot product by up to ~1e-5, enough to flip two near-tied
@@ -24,24 +27,17 @@ namespace gptoss {
 
 constexpr int kRtTokens = 32;      // tokens per CTA
 constexpr int kRtKC = 64;          // K elements per pipeline stage
-// cp.async ring depth per expert-tile count: enough bytes in flight per SM to
-// cover HBM latency while two CTAs still fit one SM where possible
-template <int NT> struct RtStages { static constexpr int value = NT <= 2 ? 6 : (NT == 4 ? 4 : 3); };
-constexpr int kRtRowBytes = 144;   // 128 B of data + 16 B pad: conflict-free ldmatrix
-constexpr int kRtThreads = 256;
+// ring depth per expert-tile count: enough bytes in flight per SM to cover HBM
+// latency while two CTAs still fit one SM where possible
+template <int NT> struct RtStages { static constexpr int value = NT == 1 ? 8 : (NT == 2 ? 6 : (NT == 4 ? 4 : 3)); };
+constexpr int kRtRowBytes = 128;   // one 64-element K chunk of a row; 128-byte swizzle
+constexpr int kRtComputeWarps = 8;
+constexpr int kRtThreads = (kRtComputeWarps + 1) * 32;
 constexpr float kTieGuard = 2.5e-4f;
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src),
-               "r"(src_bytes)
-               : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() {
-  asm volatile("cp.async.commit_group;" ::: "memory");
-}
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+// byte offset of 16-byte chunk c of row r inside a 128-byte-swizzled tile
+__device__ __forceinline__ uint32_t sw128(int r, int c) {
+  return static_cast<uint32_t>(r) * kRtRowBytes + (static_cast<uint32_t>(c ^ (r & 7)) << 4);
 }
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t &r0, uint32_t &r1,
                                             uint32_t &r2, uint32_t &r3) {
@@ -104,57 +100,39 @@ __device__ __forceinline__ float warp_exact_dot(const bf16 *a, const bf16 *b, in
 // NT = 8-expert MMA tiles per warp; the CTA covers EPAD = 32*NT experts.
 template <int NT>
 __global__ void __launch_bounds__(kRtThreads)
-router_topk_kernel(const bf16 *__restrict__ t, const bf16 *__restrict__ w_router,
-                   const float *__restrict__ b_router, const int *__restrict__ pos, int T, int H,
-                   int E, int K, int *__restrict__ topk_i, float *__restrict__ topk_v,
-                   float *__restrict__ logits_out, int exact_ties) {
+router_topk_kernel(const __grid_constant__ CUtensorMap tmap_t,
+                   const __grid_constant__ CUtensorMap tmap_w, const bf16 *__restrict__ t,
+                   const bf16 *__restrict__ w_router, const float *__restrict__ b_router,
+                   const int *__restrict__ pos, int T, int H, int E, int K,
+                   int *__restrict__ topk_i, float *__restrict__ topk_v,
+                   float *__restrict__ logits_out, int exact_ties, int *status) {
   constexpr int EPAD = 32 * NT;
   constexpr int kRtStages = RtStages<NT>::value;
-  constexpr int kStageBytes = (kRtTokens + EPAD) * kRtRowBytes;
-  extern __shared__ __align__(128) unsigned char smem[];
-  float *lg = reinterpret_cast<float *>(smem + kRtStages * kStageBytes);  // [32][EPAD]
+  constexpr int kTokBytes = kRtTokens * kRtRowBytes;           // 4 KB
+  constexpr int kStageBytes = kTokBytes + EPAD * kRtRowBytes;  // both tiles 1024-byte aligned
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  unsigned char *smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
+  uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + kRtStages * kStageBytes);
+  uint64_t *empty_bar = full_bar + kRtStages;
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(empty_bar + kRtStages);
+  float *lg = reinterpret_cast<float *>(smem + kRtStages * kStageBytes + 256);  // [32][EPAD]
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int tok0 = blockIdx.x * kRtTokens;
   const int nk = (H + kRtKC - 1) / kRtKC;
 
-  // Every thread copies the same (row, 16-byte piece) slots of each chunk: their
-  // source rows and shared-memory offsets are worked out once, the loop only adds
-  // the chunk's K offset.
-  constexpr int kSlots = ((kRtTokens + EPAD) * 8 + kRtThreads - 1) / kRtThreads;
-  const bf16 *slot_src[kSlots];  // row start + piece offset, nullptr = row does not exist
-  uint32_t slot_dst[kSlots];     // byte offset inside a stage
-  int slot_k[kSlots];            // first K element of the piece inside a chunk
-#pragma unroll
-  for (int i = 0; i < kSlots; i++) {
-    const int p = tid + i * kRtThreads;
-    const int row = p >> 3, c = p & 7;
-    slot_dst[i] = row * kRtRowBytes + c * 16;
-    slot_k[i] = c * 8;
-    slot_src[i] = nullptr;
-    if (p < (kRtTokens + EPAD) * 8) {
-      if (row < kRtTokens) {
-        if (tok0 + row < T) slot_src[i] = t + static_cast<size_t>(tok0 + row) * H + c * 8;
-      } else if (row - kRtTokens < E) {
-        slot_src[i] = w_router + static_cast<size_t>(row - kRtTokens) * H + c * 8;
-      }
-    } else {
-      slot_dst[i] = 0xffffffffu;  // no such slot
+  if (tid == 0) {
+    for (int s = 0; s < kRtStages; s++) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], kRtComputeWarps);
     }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_t);
+    tma_prefetch_desc(&tmap_w);
   }
-  const uint32_t smem_base = smem_u32(smem);
-  auto load_chunk = [&](int kc, int stage) {
-    const int k0 = kc * kRtKC;
-#pragma unroll
-    for (int i = 0; i < kSlots; i++) {
-      if (slot_dst[i] != 0xffffffffu) {
-        const bool ok = slot_src[i] != nullptr && k0 + slot_k[i] < H;
-        const void *src = ok ? static_cast<const void *>(slot_src[i] + k0)
-                             : static_cast<const void *>(t);
-        cp_async16(smem_base + stage * kStageBytes + slot_dst[i], src, ok ? 16u : 0u);
-      }
-    }
-  };
+  __syncthreads();
 
   float acc[NT][4];
 #pragma unroll
@@ -165,45 +143,69 @@ router_topk_kernel(const bf16 *__restrict__ t, const bf16 *__restrict__ w_router
   const int tg = warp & 1;   // token group: rows tg*16 .. +15
   const int sl = warp >> 1;  // expert slice: experts sl*NT*8 .. +NT*8-1
 
-#pragma unroll
-  for (int s = 0; s < kRtStages - 1; s++) {
-    if (s < nk) load_chunk(s, s);
-    cp_async_commit();
-  }
-  for (int kc = 0; kc < nk; kc++) {
-    cp_async_wait<kRtStages - 2>();
-    __syncthreads();
-    {
-      const int nxt = kc + kRtStages - 1;
-      if (nxt < nk) load_chunk(nxt, nxt % kRtStages);
-      cp_async_commit();
-    }
-    const uint32_t sbase = smem_u32(smem + (kc % kRtStages) * kStageBytes);
-    const uint32_t a_base = sbase + (tg * 16 + (lane & 15)) * kRtRowBytes + (lane >> 4) * 16;
-    const uint32_t w_base = sbase + kRtTokens * kRtRowBytes;
-#pragma unroll
-    for (int kk = 0; kk < kRtKC / 16; kk++) {
-      uint32_t a[4];
-      ldmatrix_x4(a_base + kk * 32, a[0], a[1], a[2], a[3]);
-      if constexpr (NT == 1) {
-        uint32_t b0, b1;
-        const int row = sl * 8 + (lane & 7);
-        ldmatrix_x2(w_base + row * kRtRowBytes + kk * 32 + ((lane >> 3) & 1) * 16, b0, b1);
-        mma_bf16_16816(acc[0], a, b0, b1);
-      } else {
-#pragma unroll
-        for (int nt = 0; nt < NT; nt += 2) {
-          uint32_t b0, b1, b2, b3;
-          const int mat = lane >> 3;
-          const int row = (sl * NT + nt + (mat >> 1)) * 8 + (lane & 7);
-          ldmatrix_x4(w_base + row * kRtRowBytes + kk * 32 + (mat & 1) * 16, b0, b1, b2, b3);
-          mma_bf16_16816(acc[nt], a, b0, b1);
-          mma_bf16_16816(acc[nt + 1], a, b2, b3);
+  if (warp == kRtComputeWarps) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kc = 0; kc < nk; kc++) {
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+          set_status(status, kStatusWaitTimeoutProducer);
+          *abort_flag = 1;
+          break;
+        }
+        unsigned char *dst = smem + stage * kStageBytes;
+        mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
+        tma_load_2d(dst, &tmap_t, &full_bar[stage], kc * kRtKC, tok0);
+        tma_load_2d(dst + kTokBytes, &tmap_w, &full_bar[stage], kc * kRtKC, 0);
+        if (++stage == kRtStages) {
+          stage = 0;
+          phase ^= 1u;
         }
       }
     }
+  } else {
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int kc = 0; kc < nk; kc++) {
+      if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+        set_status(status, kStatusWaitTimeoutMma);
+        *abort_flag = 1;
+        break;
+      }
+      const uint32_t sbase = smem_u32(smem + stage * kStageBytes);
+      const uint32_t w_base = sbase + kTokBytes;
+      const int a_row = tg * 16 + (lane & 15);
+#pragma unroll
+      for (int kk = 0; kk < kRtKC / 16; kk++) {
+        uint32_t a[4];
+        ldmatrix_x4(sbase + sw128(a_row, kk * 2 + (lane >> 4)), a[0], a[1], a[2], a[3]);
+        if constexpr (NT == 1) {
+          uint32_t b0, b1;
+          const int row = sl * 8 + (lane & 7);
+          ldmatrix_x2(w_base + sw128(row, kk * 2 + ((lane >> 3) & 1)), b0, b1);
+          mma_bf16_16816(acc[0], a, b0, b1);
+        } else {
+#pragma unroll
+          for (int nt = 0; nt < NT; nt += 2) {
+            uint32_t b0, b1, b2, b3;
+            const int mat = lane >> 3;
+            const int row = (sl * NT + nt + (mat >> 1)) * 8 + (lane & 7);
+            ldmatrix_x4(w_base + sw128(row, kk * 2 + (mat & 1)), b0, b1, b2, b3);
+            mma_bf16_16816(acc[nt], a, b0, b1);
+            mma_bf16_16816(acc[nt + 1], a, b2, b3);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[stage]);
+      if (++stage == kRtStages) {
+        stage = 0;
+        phase ^= 1u;
+      }
+    }
   }
-  cp_async_wait<0>();
+  __syncthreads();
+  if (warp == kRtComputeWarps) return;  // the producer warp takes no part in the selection
 
   // accumulators -> shared logits [32][EPAD]
 #pragma unroll
@@ -215,7 +217,7 @@ router_topk_kernel(const bf16 *__restrict__ t, const bf16 *__restrict__ w_router
     lg[(r0 + 8) * EPAD + col] = acc[nt][2];
     lg[(r0 + 8) * EPAD + col + 1] = acc[nt][3];
   }
-  __syncthreads();
+  asm volatile("bar.sync 1, %0;" ::"n"(kRtComputeWarps * 32) : "memory");
 
   // selection: warp w owns tokens w*4 .. w*4+3 of the CTA
   const int rounds_sel = K;
@@ -330,39 +332,49 @@ router_topk_kernel(const bf16 *__restrict__ t, const bf16 *__restrict__ w_router
 template <int NT>
 static cudaError_t launch_router_nt(const bf16 *t, const bf16 *w_router, const float *b_router,
                                     const int *pos, int T, int H, int E, int K, int *topk_i,
-                                    float *topk_v, float *logits_opt, int exact_ties,
+                                    float *topk_v, float *logits_opt, int exact_ties, int *status,
                                     cudaStream_t stream) {
   constexpr int EPAD = 32 * NT;
   constexpr int kRtStages = RtStages<NT>::value;
-  const size_t smem =
-      static_cast<size_t>(kRtStages) * (kRtTokens + EPAD) * kRtRowBytes + kRtTokens * EPAD * 4;
+  // alignment slack + ring + barriers + logits
+  const size_t smem = 1024 + static_cast<size_t>(kRtStages) * (kRtTokens + EPAD) * kRtRowBytes +
+                      256 + kRtTokens * EPAD * 4;
+  static_assert(2 * RtStages<NT>::value * 8 + 4 <= 256, "barrier area");
+  // tiles of one 64-element K chunk: 32 token rows, EPAD expert rows (rows that do not
+  // exist read as zeros)
+  CUtensorMap tmap_t, tmap_w;
+  std::string err;
+  if (make_tmap_2d_bf16(&tmap_t, t, H, T, kRtKC, kRtTokens, &err) ||
+      make_tmap_2d_bf16(&tmap_w, w_router, H, E, kRtKC, EPAD, &err))
+    return cudaErrorInvalidValue;
   cudaError_t e = cudaFuncSetAttribute(router_topk_kernel<NT>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   const int grid = (T + kRtTokens - 1) / kRtTokens;
-  router_topk_kernel<NT><<<grid, kRtThreads, smem, stream>>>(
-      t, w_router, b_router, pos, T, H, E, K, topk_i, topk_v, logits_opt, exact_ties);
+  router_topk_kernel<NT><<<grid, kRtThreads, smem, stream>>>(tmap_t, tmap_w, t, w_router, b_router,
+                                                             pos, T, H, E, K, topk_i, topk_v,
+                                                             logits_opt, exact_ties, status);
   return cudaGetLastError();
 }
 
 cudaError_t launch_router_topk(const bf16 *t, const bf16 *w_router, const float *b_router,
                                const int *pos, int T, int H, int E, int K, int *topk_i,
-                               float *topk_v, float *logits_opt, int exact_ties,
+                               float *topk_v, float *logits_opt, int exact_ties, int *status,
                                cudaStream_t stream, long long *launches) {
   if (T <= 0) return cudaSuccess;
   if (launches) ++*launches;
   if (E <= 32)
     return launch_router_nt<1>(t, w_router, b_router, pos, T, H, E, K, topk_i, topk_v, logits_opt,
-                               exact_ties, stream);
+                               exact_ties, status, stream);
   if (E <= 64)
     return launch_router_nt<2>(t, w_router, b_router, pos, T, H, E, K, topk_i, topk_v, logits_opt,
-                               exact_ties, stream);
+                               exact_ties, status, stream);
   if (E <= 128)
     return launch_router_nt<4>(t, w_router, b_router, pos, T, H, E, K, topk_i, topk_v, logits_opt,
-                               exact_ties, stream);
+                               exact_ties, status, stream);
   if (E <= 256)
     return launch_router_nt<8>(t, w_router, b_router, pos, T, H, E, K, topk_i, topk_v, logits_opt,
-                               exact_ties, stream);
+                               exact_ties, status, stream);
   return cudaErrorInvalidValue;
 }
 
