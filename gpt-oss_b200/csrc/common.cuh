@@ -17,6 +17,7 @@ enum DeviceStatus : int {
   kStatusWaitTimeoutEpilogue = 103,
   kStatusBadIndex = 104,
   kStatusTmemAlloc = 105,
+  kStatusWaitTimeoutPeer = 106,  // another rank's flag did not arrive in time
 };
 
 __device__ __forceinline__ void set_status(int *status, int code) {

@@ -26,19 +26,23 @@
 // Ranks must call the layer in lock step (also with zero tokens).
 //
 // Second transport ("ep_transport" 1, ranks in separate processes on one node):
-// no row is packed, sent or received.  Every rank publishes its activations in a
-// buffer that its peers map through CUDA IPC and all-gathers the routing result
-// (expert ids and weights of its tokens, a few hundred KB).  Each owner then sorts
-// ALL tokens of all ranks by its local experts and its gather kernel pulls the
-// rows it needs straight out of the home ranks' memory over NVLink into expert
-// order - dispatch and gather are one kernel.  After the owner's experts and the
-// per-row pre-reduction, a one-integer all-gather tells every home that the sums
-// are complete, and the home's combine kernel pulls the (at most min(N, K)) sums
-// of each token from the owners' memory, adds them in owner order in fp32 and
-// adds the residual - return and combine are one kernel.  No host
-// synchronisation; the two small collectives are the only NCCL calls.  The two
-// transports add the same values in the same order, so their results are equal
-// bit for bit.
+// no row is packed, sent or received, and the layer makes no NCCL call and no host
+// synchronisation.  Every rank keeps its activations in a buffer that its peers
+// map through CUDA IPC and writes its routing result (expert ids and weights of
+// its tokens, a few hundred KB) straight into every peer's memory, followed by a
+// flag (release store at system scope, after the kernel that wrote the data has
+// ended).  Each owner waits for the N flags (acquire polls with a time limit),
+// sorts ALL tokens of all ranks by its local experts, and its gather kernel pulls
+// the rows it needs out of the home ranks' memory over NVLink into expert order -
+// dispatch and gather are one kernel.  After the owner's experts and the per-row
+// pre-reduction a second round of flags says "sums complete", and the home's
+// combine kernel waits for them and pulls the (at most min(N, K)) sums of each
+// token from the owners' memory, adds them in owner order in fp32 and adds the
+// residual - return and combine are one kernel.  A rank reuses a buffer only after
+// the flags that prove its readers are done: activations and routing slots after
+// the second flags of the same layer (every peer has gathered), sums after the
+// first flags of the next layer (every peer has combined).  The two transports add
+// the same values in the same order, so their results are equal bit for bit.
 //
 // NCCL is loaded with dlopen on first use, so single-GPU users of the library do
 // not need it; in a process that already loaded NCCL (PyTorch) the same copy is
@@ -129,8 +133,9 @@ struct EpState {
   std::string peer_why;         // why the peer transport is not available
   int max_t = 0;
   bf16 *pub_t = nullptr;        // [max_t, H] this rank's activations, mapped by the peers
-  int *all_meta = nullptr;      // [N][2 * max_t * K]: expert ids, then weights (float bits)
-  int *sync_dev = nullptr;      // [N] completion round of every rank
+  int *ctl = nullptr;           // mapped by the peers: flags [2][N], then all_meta
+  int *all_meta = nullptr;      // ctl + kCtlHeader: [N][2 * max_t * K] expert ids, then weights
+  void *peer_ctl[GPTOSS_MAX_TOPK] = {};  // peers' ctl (own entry: the local buffer)
   int round = 0;
   void *peer_t[GPTOSS_MAX_TOPK] = {};    // peers' pub_t (own entry: the local buffer)
   void *peer_out[GPTOSS_MAX_TOPK] = {};  // peers' out_rows
@@ -139,23 +144,80 @@ struct EpState {
 struct PeerRows {
   const bf16 *p[GPTOSS_MAX_TOPK];
 };
+struct PeerCtl {
+  int *p[GPTOSS_MAX_TOPK];
+};
+constexpr int kCtlHeader = 64;  // ints in front of all_meta: flags[which][source rank]
 
-// This rank's routing result in all-gather layout: ids of rows >= T are -1.
+// flags[which][rank] = round in every peer's control block.  Launched after the kernel
+// that produced the data the flag announces: that kernel has ended, so its writes (to
+// this GPU's memory or to the peers') are done before these stores are issued.
+__global__ void ep_signal_kernel(const PeerCtl ctl, int N, int which, int rank, int round) {
+  const int p = threadIdx.x;
+  if (p >= N) return;
+  __threadfence_system();
+  asm volatile("st.release.sys.global.b32 [%0], %1;" ::"l"(ctl.p[p] + which * N + rank), "r"(round)
+               : "memory");
+}
+
+// Waits until every rank's flag of this round is here; false (and a status) after
+// kWaitLimitNs.  Called by the first warp of a CTA, followed by a CTA barrier.
+__device__ __forceinline__ bool ep_wait_flags(const int *flags, int N, int round, int *status) {
+  const int lane = threadIdx.x & 31;
+  bool ok = true;
+  if (lane < N) {
+    const int *f = flags + lane;
+    uint64_t t0 = 0;
+    uint32_t spins = 0;
+    while (true) {
+      int v;
+      asm volatile("ld.acquire.sys.global.b32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+      if (v - round >= 0) break;
+      if ((++spins & 0xff) == 0) {
+        const uint64_t now = global_timer_ns();
+        if (t0 == 0) {
+          t0 = now;
+        } else if (now - t0 > kWaitLimitNs) {
+          set_status(status, kStatusWaitTimeoutPeer);
+          ok = false;
+          break;
+        }
+      }
+    }
+  }
+  return __all_sync(0xffffffffu, ok);
+}
+
+// This rank's routing result, written into slot `rank` of all_meta in every rank's
+// control block (its own included): ids of rows >= T are -1.
 __global__ void __launch_bounds__(256)
 ep_publish_meta_kernel(const int *__restrict__ topk_i, const float *__restrict__ topk_v, int T,
-                       int max_t, int K, int *__restrict__ slot) {
+                       int max_t, int K, const PeerCtl ctl, int N, int rank) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= max_t * K) return;
+  const int per = max_t * K;
+  if (i >= per) return;
   const bool live = i < T * K;
-  slot[i] = live ? topk_i[i] : -1;
-  slot[max_t * K + i] = live ? __float_as_int(topk_v[i]) : 0;
+  const int id = live ? topk_i[i] : -1;
+  const int w = live ? __float_as_int(topk_v[i]) : 0;
+  const size_t off = kCtlHeader + static_cast<size_t>(rank) * 2 * per + i;
+#pragma unroll
+  for (int p = 0; p < GPTOSS_MAX_TOPK; p++) {
+    if (p < N) {
+      ctl.p[p][off] = id;
+      ctl.p[p][off + per] = w;
+    }
+  }
 }
 
 // Owner view of every rank's tokens: global row g = src * max_t + t keeps the slots
 // whose expert lives here (local id e / N), the others become -1.
 __global__ void __launch_bounds__(256)
-ep_owner_slots_kernel(const int *__restrict__ all_meta, int N, int rank, int max_t, int K,
-                      int *__restrict__ stage_e, float *__restrict__ stage_w) {
+ep_owner_slots_kernel(const int *all_meta, const int *flags, int round, int N, int rank,
+                      int max_t, int K, int *__restrict__ stage_e, float *__restrict__ stage_w,
+                      int *status) {
+  // every rank's routing result (and, by the order of its stream, its activations)
+  if (threadIdx.x < 32) ep_wait_flags(flags, N, round, status);
+  __syncthreads();
   const int per = max_t * K;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= N * per) return;
@@ -203,7 +265,11 @@ gather_rows_peer_kernel(bf16 *__restrict__ xs, const PeerRows src, int max_t,
 // (rank * max_t + t) in its out_rows, read from the owner's memory.  One warp per token.
 __global__ void __launch_bounds__(256)
 combine_peer_kernel(bf16 *__restrict__ x, const PeerRows outs, const int *__restrict__ topk_i,
-                    int T, int K, int N, int rank, int max_t, int H) {
+                    int T, int K, int N, int rank, int max_t, int H, const int *flags, int round,
+                    int *status) {
+  // every owner's sums are complete (and every peer is done with this rank's activations)
+  if (threadIdx.x < 32) ep_wait_flags(flags, N, round, status);
+  __syncthreads();
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= T) return;
@@ -243,7 +309,7 @@ combine_peer_kernel(bf16 *__restrict__ x, const PeerRows outs, const int *__rest
   }
 }
 
-__global__ void ep_mark_round_kernel(int *slot, int round) { *slot = round; }
+
 
 // own_key[t, o] = o when token t has at least one selected expert on rank o.
 __global__ void __launch_bounds__(256)
@@ -347,23 +413,24 @@ static int ep_forward_peer(gptoss_moe *h, EpState *ep, int layer, const bf16 *t,
                            cudaStream_t st) {
   const int N = ep->N, K = h->K, H = h->H, max_t = ep->max_t;
   const int per = max_t * K;
-  int *my_meta = ep->all_meta + static_cast<size_t>(ep->rank) * 2 * per;
+  PeerCtl ctl;
+  for (int p = 0; p < GPTOSS_MAX_TOPK; p++) ctl.p[p] = static_cast<int *>(p < N ? ep->peer_ctl[p] : nullptr);
+  const int round = ++ep->round;
   {
     EpStageScope sc(h, 5, st);
-    // 1. publish: activations where the peers can read them, routing result to everyone.
-    //    The all-gather doubles as the barrier "every rank's activations are in place".
+    // 1. publish: activations where the peers can read them, routing result into every
+    //    rank's memory, then the flag "rank r of this round is in place"
     if (T > 0)
       EP_CUDA(h, cudaMemcpyAsync(ep->pub_t, t, static_cast<size_t>(T) * H * sizeof(bf16),
                                  cudaMemcpyDeviceToDevice, st));
     ep_publish_meta_kernel<<<(per + 255) / 256, 256, 0, st>>>(h->topk_i, h->topk_v, T, max_t, K,
-                                                              my_meta);
-    h->launches++;
+                                                              ctl, N, ep->rank);
+    ep_signal_kernel<<<1, 32, 0, st>>>(ctl, N, 0, ep->rank, round);
+    h->launches += 2;
     EP_CUDA(h, cudaGetLastError());
-    EP_NCCL(h, g_nccl.AllGather(my_meta, ep->all_meta, static_cast<size_t>(2) * per, ncclInt32,
-                                ep->comm, st));
-    // 2. owner view of all N * max_t rows
-    ep_owner_slots_kernel<<<(N * per + 255) / 256, 256, 0, st>>>(ep->all_meta, N, ep->rank, max_t,
-                                                                 K, ep->recv_e, ep->recv_w);
+    // 2. owner view of all N * max_t rows, once every rank's flag is here
+    ep_owner_slots_kernel<<<(N * per + 255) / 256, 256, 0, st>>>(
+        ep->all_meta, ep->ctl, round, N, ep->rank, max_t, K, ep->recv_e, ep->recv_w, h->status);
     h->launches++;
     EP_CUDA(h, cudaGetLastError());
   }
@@ -400,10 +467,9 @@ static int ep_forward_peer(gptoss_moe *h, EpState *ep, int layer, const bf16 *t,
     // 4. per-row sums over this rank's experts, then "my sums are complete" to everyone
     EpStageScope sc(h, 6, st);
     EP_CUDA(h, launch_reduce_rows(h, ep->out_rows, R, st, /*skip_empty=*/true));
-    ep->round++;
-    ep_mark_round_kernel<<<1, 1, 0, st>>>(ep->sync_dev + ep->rank, ep->round);
+    ep_signal_kernel<<<1, 32, 0, st>>>(ctl, N, 1, ep->rank, round);
     h->launches++;
-    EP_NCCL(h, g_nccl.AllGather(ep->sync_dev + ep->rank, ep->sync_dev, 1, ncclInt32, ep->comm, st));
+    EP_CUDA(h, cudaGetLastError());
   }
   {
     // 5. return and combine in one kernel
@@ -411,7 +477,8 @@ static int ep_forward_peer(gptoss_moe *h, EpState *ep, int layer, const bf16 *t,
     if (T > 0) {
       const int warps = 8;
       combine_peer_kernel<<<(T + warps - 1) / warps, warps * 32, 0, st>>>(
-          static_cast<bf16 *>(x_io), outs, h->topk_i, T, K, N, ep->rank, max_t, H);
+          static_cast<bf16 *>(x_io), outs, h->topk_i, T, K, N, ep->rank, max_t, H, ep->ctl + N, round,
+          h->status);
       h->launches++;
       EP_CUDA(h, cudaGetLastError());
     }
@@ -561,7 +628,7 @@ int ep_forward(gptoss_moe *h, int layer, const void *t_in, void *x_io, int T, vo
 }
 
 struct PeerBlob {  // what a rank tells the others at start-up
-  cudaIpcMemHandle_t t, out;
+  cudaIpcMemHandle_t t, out, ctl;
   int ok, max_t, hidden, pid;
 };
 
@@ -572,7 +639,8 @@ static int ep_map_peers(gptoss_moe *h, EpState *ep) {
   mine.hidden = h->H;
   mine.pid = static_cast<int>(getpid());
   mine.ok = cudaIpcGetMemHandle(&mine.t, ep->pub_t) == cudaSuccess &&
-            cudaIpcGetMemHandle(&mine.out, ep->out_rows) == cudaSuccess;
+            cudaIpcGetMemHandle(&mine.out, ep->out_rows) == cudaSuccess &&
+            cudaIpcGetMemHandle(&mine.ctl, ep->ctl) == cudaSuccess;
   if (!mine.ok) {
     ep->peer_why = std::string("cudaIpcGetMemHandle: ") + cudaGetErrorString(cudaGetLastError());
   }
@@ -602,11 +670,14 @@ static int ep_map_peers(gptoss_moe *h, EpState *ep) {
     if (p == ep->rank) {
       ep->peer_t[p] = ep->pub_t;
       ep->peer_out[p] = ep->out_rows;
+      ep->peer_ctl[p] = ep->ctl;
       continue;
     }
     cudaError_t e = cudaIpcOpenMemHandle(&ep->peer_t[p], blobs[p].t, cudaIpcMemLazyEnablePeerAccess);
     if (e == cudaSuccess)
       e = cudaIpcOpenMemHandle(&ep->peer_out[p], blobs[p].out, cudaIpcMemLazyEnablePeerAccess);
+    if (e == cudaSuccess)
+      e = cudaIpcOpenMemHandle(&ep->peer_ctl[p], blobs[p].ctl, cudaIpcMemLazyEnablePeerAccess);
     if (e != cudaSuccess) {
       ok = false;
       ep->peer_why = std::string("cudaIpcOpenMemHandle: ") + cudaGetErrorString(e);
@@ -639,8 +710,9 @@ void ep_destroy(gptoss_moe *h) {
     if (p == ep->rank) continue;
     if (ep->peer_t[p]) cudaIpcCloseMemHandle(ep->peer_t[p]);
     if (ep->peer_out[p]) cudaIpcCloseMemHandle(ep->peer_out[p]);
+    if (ep->peer_ctl[p]) cudaIpcCloseMemHandle(ep->peer_ctl[p]);
   }
-  cudaFree(ep->pub_t); cudaFree(ep->all_meta); cudaFree(ep->sync_dev);
+  cudaFree(ep->pub_t); cudaFree(ep->ctl);
   if (ep->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(ep->comm);
   cudaFree(ep->own_key); cudaFree(ep->own_w); cudaFree(ep->s_block_counts);
   cudaFree(ep->s_offsets); cudaFree(ep->s_sorted_row); cudaFree(ep->s_sorted_w);
@@ -715,9 +787,9 @@ extern "C" int gptoss_moe_ep_init(gptoss_moe_t *h, const void *id128) {
   // transport is offered only when every rank mapped every peer.
   ep->max_t = static_cast<int>(T);
   EP_CUDA(h, ep_alloc(&ep->pub_t, T * H));
-  EP_CUDA(h, ep_alloc(&ep->all_meta, (size_t)N * 2 * T * K));
-  EP_CUDA(h, ep_alloc(&ep->sync_dev, (size_t)N));
-  EP_CUDA(h, cudaMemset(ep->sync_dev, 0, sizeof(int) * N));
+  EP_CUDA(h, ep_alloc(&ep->ctl, (size_t)kCtlHeader + (size_t)N * 2 * T * K));
+  EP_CUDA(h, cudaMemset(ep->ctl, 0, sizeof(int) * kCtlHeader));
+  ep->all_meta = ep->ctl + kCtlHeader;
   return ep_map_peers(h, ep);
 }
 
