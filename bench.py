@@ -273,7 +273,11 @@ def measure_c3_layer(args, pkg, dev, rank, world, local_rank, barrier):
         # strong-scaling reading: the same 6144 tokens split over the ranks
         strong = timed(T // world)
         strong["tokens_per_gpu"] = T // world
+    overlap = None
     if transport == 1:
+        eng.set_option("ep_overlap", 1)
+        overlap = timed()
+        eng.set_option("ep_overlap", 0)
         eng.set_option("ep_transport", 0)
         other = timed()
     eng.close()
@@ -286,6 +290,8 @@ def measure_c3_layer(args, pkg, dev, rank, world, local_rank, barrier):
     out["gate_up_tflops"] = 2.0 * T * K * 2 * IM * H / (res["stage_ms"]["gate_up"] * 1e-3) / 1e12
     if strong is not None:
         out["strong_scaling"] = strong
+    if overlap is not None:
+        out["peer_memory_with_gather_overlap"] = overlap
     if other is not None:
         out["nccl_send_recv"] = other
     return out

@@ -82,6 +82,7 @@ struct gptoss_moe {
   int *mtile_row0 = nullptr;     // [mtiles_cap] first sorted row of the tile
   int *mtile_rows = nullptr;     // [mtiles_cap] valid rows in the tile
   int *num_mtiles = nullptr;     // [1]
+  int *mtile_split = nullptr;    // [1] first token tile of expert >= the split expert
 
   gptoss::bf16 *xs = nullptr;    // [assign_cap + pad, H]  gathered inputs
   gptoss::bf16 *hact = nullptr;  // [assign_cap + pad, IM] SwiGLU activations
@@ -112,6 +113,7 @@ struct gptoss_moe {
   int opt_exact_ties = 1;
   int opt_time_stages = 0;
   int opt_skip_epilogue = 0;
+  int opt_ep_overlap = 0;  // peer transport: second half of the experts gathered under the first half's GEMM
   int opt_pair_stages = 6;  // operand ring depth of the CTA-pair GEMM (4, 5 or 6)
   gptoss::StageTimer timers[8];
   long long launches = 0;
@@ -134,6 +136,8 @@ cudaError_t launch_rmsnorm(bf16 *out, const bf16 *x, const float *w, const int *
 // permute.cu
 cudaError_t launch_permute(gptoss_moe *h, cudaStream_t stream);
 cudaError_t launch_permute_plan_only(gptoss_moe *h, cudaStream_t stream);
+// h->mtile_split = index of the first token tile whose expert is >= e_split
+cudaError_t launch_mtile_split(gptoss_moe *h, int e_split, cudaStream_t stream);
 cudaError_t launch_combine(gptoss_moe *h, bf16 *x, const int *topk_i_rows, int T,
                            cudaStream_t stream);
 cudaError_t launch_reduce_rows(gptoss_moe *h, bf16 *out_rows, int R, cudaStream_t stream,
@@ -160,13 +164,15 @@ cudaError_t launch_combine_rows(bool residual, bf16 *out, const bf16 *ys, const 
                                 long long *launches);
 
 // grouped_gemm.cu
-cudaError_t launch_gate_up(gptoss_moe *h, int layer, cudaStream_t stream);
+// part: 0 = all token tiles; 1 / 2 = the tiles of the experts before / from the split
+// written by launch_mtile_split (CTA-pair kernel; the others do everything in part 1)
+cudaError_t launch_gate_up(gptoss_moe *h, int layer, cudaStream_t stream, int part = 0);
 cudaError_t launch_down(gptoss_moe *h, int layer, cudaStream_t stream);
 int make_tmap_2d_bf16(CUtensorMap *map, const void *base, uint64_t inner, uint64_t outer,
                       uint32_t box_inner, uint32_t box_outer, std::string *err);
 int gemm_tile_n(int which);  // N extent of one tile: 0 = gate_up, 1 = down
 // grouped_gemm_pair.cu
-cudaError_t launch_gate_up_pair(gptoss_moe *h, int layer, cudaStream_t stream);
+cudaError_t launch_gate_up_pair(gptoss_moe *h, int layer, cudaStream_t stream, int part = 0);
 cudaError_t launch_down_pair(gptoss_moe *h, int layer, cudaStream_t stream);
 
 // moe_api.cu: error text for entry points that take no handle (read back with

@@ -136,6 +136,8 @@ struct EpState {
   int *ctl = nullptr;           // mapped by the peers: flags [2][N], then all_meta
   int *all_meta = nullptr;      // ctl + kCtlHeader: [N][2 * max_t * K] expert ids, then weights
   void *peer_ctl[GPTOSS_MAX_TOPK] = {};  // peers' ctl (own entry: the local buffer)
+  cudaStream_t s2 = nullptr;    // second stream: the gather of the second half of the experts
+  cudaEvent_t ev_plan = nullptr, ev_second = nullptr;
   int round = 0;
   void *peer_t[GPTOSS_MAX_TOPK] = {};    // peers' pub_t (own entry: the local buffer)
   void *peer_out[GPTOSS_MAX_TOPK] = {};  // peers' out_rows
@@ -234,13 +236,15 @@ ep_owner_slots_kernel(const int *all_meta, const int *flags, int round, int N, i
 __global__ void __launch_bounds__(256)
 gather_rows_peer_kernel(bf16 *__restrict__ xs, const PeerRows src, int max_t,
                         const int *__restrict__ sorted_row,
-                        const int *__restrict__ expert_offsets, int El, int H, int R,
+                        const int *__restrict__ expert_offsets, int e_lo, int e_hi, int H, int R,
                         int *status) {
-  const int total = expert_offsets[El];
+  // the rows of experts e_lo .. e_hi-1
+  const int first = expert_offsets[e_lo], total = expert_offsets[e_hi];
   const int lane = threadIdx.x & 31;
   const int nwarps = gridDim.x * (blockDim.x >> 5);
   const int n4 = H >> 3;
-  for (int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < total; r += nwarps) {
+  for (int r = first + blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < total;
+       r += nwarps) {
     const int g = sorted_row[r];
     if (g < 0 || g >= R) {
       set_status(status, kStatusBadIndex);
@@ -445,19 +449,39 @@ static int ep_forward_peer(gptoss_moe *h, EpState *ep, int layer, const bf16 *t,
     outs.p[p] = static_cast<const bf16 *>(p < N ? ep->peer_out[p] : nullptr);
   }
   src.p[ep->rank] = t;  // own rows straight from the caller's buffer
+  // 3. sort by local expert; dispatch and gather in one kernel.  With the CTA-pair GEMM
+  //    the experts are taken in two halves: the rows of the second half are pulled on a
+  //    second stream while the first half is already being multiplied (the gather kernel
+  //    uses no shared memory and few registers, so its CTAs share the SMs with the GEMM's).
+  const bool halves = h->opt_ep_overlap && h->opt_gemm_impl == GPTOSS_GEMM_PAIR && h->El >= 2 && ep->s2;
+  const int e_mid = halves ? h->El / 2 : h->El;
   {
-    // 3. sort by local expert; dispatch and gather in one kernel
     EpStageScope sc(h, 1, st);
     EP_CUDA(h, launch_permute_plan_only(h, st));
+    if (halves) EP_CUDA(h, launch_mtile_split(h, e_mid, st));
     gather_rows_peer_kernel<<<h->num_sms * 4, 256, 0, st>>>(h->xs, src, max_t, h->sorted_row,
-                                                            h->expert_offsets, h->El, H, R,
+                                                            h->expert_offsets, 0, e_mid, H, R,
                                                             h->status);
     h->launches++;
     EP_CUDA(h, cudaGetLastError());
+    if (halves) {
+      // the second half starts when the first has the links to itself no longer
+      EP_CUDA(h, cudaEventRecord(ep->ev_plan, st));
+      EP_CUDA(h, cudaStreamWaitEvent(ep->s2, ep->ev_plan, 0));
+      gather_rows_peer_kernel<<<h->num_sms * 2, 256, 0, ep->s2>>>(
+          h->xs, src, max_t, h->sorted_row, h->expert_offsets, e_mid, h->El, H, R, h->status);
+      EP_CUDA(h, cudaGetLastError());
+      EP_CUDA(h, cudaEventRecord(ep->ev_second, ep->s2));
+      h->launches++;
+    }
   }
   {
     EpStageScope sc(h, 2, st);
-    EP_CUDA(h, launch_gate_up(h, layer, st));
+    EP_CUDA(h, launch_gate_up(h, layer, st, halves ? 1 : 0));
+    if (halves) {
+      EP_CUDA(h, cudaStreamWaitEvent(st, ep->ev_second, 0));
+      EP_CUDA(h, launch_gate_up(h, layer, st, 2));
+    }
   }
   {
     EpStageScope sc(h, 3, st);
@@ -713,6 +737,9 @@ void ep_destroy(gptoss_moe *h) {
     if (ep->peer_ctl[p]) cudaIpcCloseMemHandle(ep->peer_ctl[p]);
   }
   cudaFree(ep->pub_t); cudaFree(ep->ctl);
+  if (ep->s2) cudaStreamDestroy(ep->s2);
+  if (ep->ev_plan) cudaEventDestroy(ep->ev_plan);
+  if (ep->ev_second) cudaEventDestroy(ep->ev_second);
   if (ep->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(ep->comm);
   cudaFree(ep->own_key); cudaFree(ep->own_w); cudaFree(ep->s_block_counts);
   cudaFree(ep->s_offsets); cudaFree(ep->s_sorted_row); cudaFree(ep->s_sorted_w);
@@ -790,6 +817,9 @@ extern "C" int gptoss_moe_ep_init(gptoss_moe_t *h, const void *id128) {
   EP_CUDA(h, ep_alloc(&ep->ctl, (size_t)kCtlHeader + (size_t)N * 2 * T * K));
   EP_CUDA(h, cudaMemset(ep->ctl, 0, sizeof(int) * kCtlHeader));
   ep->all_meta = ep->ctl + kCtlHeader;
+  EP_CUDA(h, cudaStreamCreateWithFlags(&ep->s2, cudaStreamNonBlocking));
+  EP_CUDA(h, cudaEventCreateWithFlags(&ep->ev_plan, cudaEventDisableTiming));
+  EP_CUDA(h, cudaEventCreateWithFlags(&ep->ev_second, cudaEventDisableTiming));
   return ep_map_peers(h, ep);
 }
 

@@ -32,6 +32,11 @@ struct GemmArgs {
                       // 2 = compute but do not store, 4 = no proxy fence after the
                       // MXFP4 conversion, 8 = no conversion, 16 = no MMA issue
   const uint8_t *wq = nullptr;  // MXFP4: tiled packed codes + scales of the weight operand
+  // (CTA-pair kernel) 0 = every token tile; 1 / 2 = only the tiles before / from
+  // *tile_split, so that a launch can start on the first experts while the rows of the
+  // others are still on their way
+  int tile_part = 0;
+  const int *tile_split = nullptr;
 };
 
 // gate * sigmoid(alpha * gate) * (up + 1) with the reference CPU path's clamps

@@ -375,8 +375,9 @@ static cudaError_t launch_tc(gptoss_moe *h, const CUtensorMap &ta, const CUtenso
   return cudaGetLastError();
 }
 
-cudaError_t launch_gate_up(gptoss_moe *h, int layer, cudaStream_t stream) {
-  if (h->opt_gemm_impl == GPTOSS_GEMM_PAIR) return launch_gate_up_pair(h, layer, stream);
+cudaError_t launch_gate_up(gptoss_moe *h, int layer, cudaStream_t stream, int part) {
+  if (h->opt_gemm_impl == GPTOSS_GEMM_PAIR) return launch_gate_up_pair(h, layer, stream, part);
+  if (part == 2) return cudaSuccess;  // the other kernels take the whole schedule in part 1
   LayerWeights &lw = h->layers[layer];
   GemmArgs g;
   g.bias = lw.b1;

@@ -155,7 +155,13 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
   const uint32_t tmem_base = *tmem_holder;
 
   const int w_pairs = (g.n_cols + 255) / 256;
-  const int total_tiles = *g.num_mtiles * w_pairs;
+  // token tiles of this launch: all of them, or one side of g.tile_split (the schedule is
+  // ordered by expert, so a side is a range of experts)
+  int tt_lo = 0, tt_hi = *g.num_mtiles;
+  if (g.tile_part == 1) tt_hi = *g.tile_split;
+  if (g.tile_part == 2) tt_lo = *g.tile_split;
+  const int first_tile = tt_lo * w_pairs + (blockIdx.x >> 1);
+  const int total_tiles = tt_hi * w_pairs;
   const int kb_count = (g.k_dim + kTileK - 1) / kTileK;
   const int cl = blockIdx.x >> 1, ncl = gridDim.x >> 1;
 
@@ -165,13 +171,13 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
       uint32_t phase = 0;
       bool ok = true;
       int e_next = 0, tok0_next = 0, ntok_next = 0;
-      if (cl < total_tiles) {
-        const int tt = cl / w_pairs;
+      if (first_tile < total_tiles) {
+        const int tt = first_tile / w_pairs;
         e_next = g.mtile_expert[tt];
         tok0_next = g.mtile_row0[tt];
         ntok_next = g.mtile_rows[tt];
       }
-      for (int tile = cl; ok && tile < total_tiles; tile += ncl) {
+      for (int tile = first_tile; ok && tile < total_tiles; tile += ncl) {
         const int tt = tile / w_pairs, wp = tile - tt * w_pairs;
         const int e = e_next, tok0 = tok0_next, ntok = ntok_next;
         const int tile2 = tile + ncl;
@@ -220,7 +226,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
       int rs = 0;
       uint32_t rphase = 0;
       bool ok = true;
-      for (int tile = cl; ok && tile < total_tiles; tile += ncl) {
+      for (int tile = first_tile; ok && tile < total_tiles; tile += ncl) {
         const int tt = tile / w_pairs, wp = tile - tt * w_pairs;
         const int e = g.mtile_expert[tt];
         const size_t blk0 =
@@ -249,7 +255,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = cl; ok && tile < total_tiles; tile += ncl) {
+      for (int tile = first_tile; ok && tile < total_tiles; tile += ncl) {
         const int ntok = g.mtile_rows[tile / w_pairs];
         const uint32_t idesc = umma_idesc_bf16(256, (ntok + 15) & ~15);
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_flag)) {
@@ -294,7 +300,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
     // c = half (c & 1) of weight row c >> 1: 32 codes under one scale byte.
     const int dw = warp - kPairThreads / 32;
     const int grp = dw / kWarpsPerBlock, sub = dw - grp * kWarpsPerBlock;
-    const int my_tiles = cl < total_tiles ? (total_tiles - cl + ncl - 1) / ncl : 0;
+    const int my_tiles = first_tile < total_tiles ? (total_tiles - first_tile + ncl - 1) / ncl : 0;
     const int total_kb = my_tiles * kb_count;
     const uint32_t *lutl = lut + (lane & (LUTREP - 1));
     constexpr int kChunkIters = 8 / kWarpsPerBlock;
@@ -357,7 +363,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
     const bool odd = (lane & 1) != 0;
     int acc = 0, buf = 0;
     uint32_t acc_phase = 0;
-    for (int tile = cl; tile < total_tiles; tile += ncl) {
+    for (int tile = first_tile; tile < total_tiles; tile += ncl) {
       const int tt = tile / w_pairs, wp = tile - tt * w_pairs;
       const int e = g.mtile_expert[tt];
       const int tok0 = g.mtile_row0[tt];
@@ -535,10 +541,13 @@ static GemmArgs pair_args(gptoss_moe *h, bool down, const LayerWeights &lw) {
   return g;
 }
 
-cudaError_t launch_gate_up_pair(gptoss_moe *h, int layer, cudaStream_t stream) {
+cudaError_t launch_gate_up_pair(gptoss_moe *h, int layer, cudaStream_t stream, int part) {
   LayerWeights &lw = h->layers[layer];
   const CUtensorMap tx[3] = {h->tmap_xs, h->tmap_xs32, h->tmap_xs8};
-  return launch_pair<kEpiSwiglu>(h, lw.tmap_w1_rows, tx, pair_args(h, false, lw), stream);
+  GemmArgs g = pair_args(h, false, lw);
+  g.tile_part = part;
+  g.tile_split = h->mtile_split;
+  return launch_pair<kEpiSwiglu>(h, lw.tmap_w1_rows, tx, g, stream);
 }
 
 cudaError_t launch_down_pair(gptoss_moe *h, int layer, cudaStream_t stream) {

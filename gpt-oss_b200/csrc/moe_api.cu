@@ -129,6 +129,7 @@ int gptoss_moe_create(const gptoss_moe_config_t *cfg, gptoss_moe_t **out) {
   CKH(dev_alloc(&h->mtile_row0, (size_t)h->mtiles_cap));
   CKH(dev_alloc(&h->mtile_rows, (size_t)h->mtiles_cap));
   CKH(dev_alloc(&h->num_mtiles, 1));
+  CKH(dev_alloc(&h->mtile_split, 1));
   CKH(dev_alloc(&h->status, 1));
   CKH(dev_alloc(&h->xs, (size_t)h->assign_cap * H));
   CKH(dev_alloc(&h->hact, (size_t)h->assign_cap * IM));
@@ -137,6 +138,7 @@ int gptoss_moe_create(const gptoss_moe_config_t *cfg, gptoss_moe_t **out) {
   CKH(cudaMemset(h->hact, 0, (size_t)h->assign_cap * IM * sizeof(bf16)));
   CKH(cudaMemset(h->status, 0, sizeof(int)));
   CKH(cudaMemset(h->num_mtiles, 0, sizeof(int)));
+  CKH(cudaMemset(h->mtile_split, 0, sizeof(int)));
   CKH(cudaMemset(h->expert_offsets, 0, sizeof(int) * (h->El + 1)));
 #undef CKH
   std::string terr;
@@ -167,7 +169,7 @@ int gptoss_moe_destroy(gptoss_moe_t *h) {
   cudaFree(h->topk_i); cudaFree(h->topk_v); cudaFree(h->logits); cudaFree(h->block_counts);
   cudaFree(h->expert_offsets); cudaFree(h->sorted_row); cudaFree(h->sorted_weight);
   cudaFree(h->row_of); cudaFree(h->mtile_expert); cudaFree(h->mtile_row0);
-  cudaFree(h->mtile_rows); cudaFree(h->num_mtiles); cudaFree(h->status); cudaFree(h->xs);
+  cudaFree(h->mtile_rows); cudaFree(h->num_mtiles); cudaFree(h->mtile_split); cudaFree(h->status); cudaFree(h->xs);
   cudaFree(h->hact); cudaFree(h->ys); cudaFree(h->t_dev); cudaFree(h->x_dev);
   cudaFree(h->pos_dev);
   for (auto &sl : h->host_slots) {
@@ -579,6 +581,8 @@ int gptoss_moe_set_option(gptoss_moe_t *h, const char *name, int value) {
   } else if (!strcmp(name, "pair_stages")) {
     if (value < 4 || value > 6) return fail(h, GPTOSS_E_INVALID, "pair_stages must be 4, 5 or 6");
     h->opt_pair_stages = value;
+  } else if (!strcmp(name, "ep_overlap")) {
+    h->opt_ep_overlap = value != 0;
   } else if (!strcmp(name, "ep_transport")) {
     return ep_set_transport(h, value);
   } else if (!strcmp(name, "skip_epilogue")) {

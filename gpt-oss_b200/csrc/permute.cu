@@ -303,6 +303,31 @@ cudaError_t launch_permute(gptoss_moe *h, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
+// The tile schedule is ordered by expert: first tile of an expert >= e_split (the tile
+// count when there is none).
+__global__ void mtile_split_kernel(const int *__restrict__ mtile_expert,
+                                   const int *__restrict__ num_mtiles, int e_split,
+                                   int *__restrict__ out) {
+  __shared__ int best;
+  const int n = *num_mtiles;
+  if (threadIdx.x == 0) best = n;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x)
+    if (mtile_expert[i] >= e_split) {
+      atomicMin(&best, i);
+      break;  // later tiles of this thread are larger
+    }
+  __syncthreads();
+  if (threadIdx.x == 0) *out = best;
+}
+
+cudaError_t launch_mtile_split(gptoss_moe *h, int e_split, cudaStream_t stream) {
+  mtile_split_kernel<<<1, 256, 0, stream>>>(h->mtile_expert, h->num_mtiles, e_split,
+                                            h->mtile_split);
+  h->launches++;
+  return cudaGetLastError();
+}
+
 // Sorted order and tile schedule only; the caller gathers the rows.
 cudaError_t launch_permute_plan_only(gptoss_moe *h, cudaStream_t stream) {
   const int R = h->stage_R, K = h->K, El = h->El;

@@ -185,7 +185,9 @@ int gptoss_moe_get_activations(gptoss_moe_t *h, void *act_host, size_t bytes);
 
 /* Options: "gemm_impl" (GPTOSS_GEMM_*), "keep_logits" (0/1),
  * "exact_ties" (0/1, default 1: re-evaluate near-tied router logits in fp64),
- * "ep_transport" (0/1, see gptoss_moe_ep_transport),
+ * "ep_transport" (0/1, see gptoss_moe_ep_transport), "ep_overlap" (0/1, default 0;
+ * peer-memory transport only: the owner pulls the rows of the second half of its
+ * experts on a second stream while the gate_up GEMM of the first half runs),
  * "time_stages" (0/1, see gptoss_moe_stage_ms), "pair_stages" (4..6, operand
  * ring depth of the CTA-pair GEMM with bf16 weights), "skip_epilogue" (a bit
  * mask, default 0, measurement aid only - results are garbage while any bit is

@@ -61,10 +61,12 @@ def _worker(rank, world, uid, tmp):
             stream = torch.cuda.current_stream().cuda_stream
             # both transports (NCCL send/recv; peer memory where the ranks could map each
             # other's buffers) must give the same bits
-            transports = [0, 1] if eng.ep_transport == 1 else [0]
+            # (transport, overlap of the second half's gather with the first half's GEMM)
+            transports = [(0, 0), (1, 0), (1, 1)] if eng.ep_transport == 1 else [(0, 0)]
             outs = []
-            for tr in transports:
+            for tr, ov in transports:
                 eng.set_option("ep_transport", tr)
+                eng.set_option("ep_overlap", ov)
                 for rep in range(2):  # twice: buffers are reused between layers
                     x.copy_(helpers.to_dev_bf16(d["x"], dev))
                     eng.forward(0, t, x, pos, T, stream)
