@@ -219,8 +219,11 @@ int gptoss_moe_ep_init(gptoss_moe_t *h, const void *id128);
  * return, combine as separate steps, one host synchronisation per layer for the
  * row counts), 1 = peer memory (each owner's gather kernel reads the rows it
  * needs out of the home ranks' HBM over NVLink and each home's combine kernel
- * reads the owners' per-row sums the same way; two small all-gathers per layer,
- * no host synchronisation; the reference's counterpart is the peer copies of
+ * reads the owners' per-row sums the same way; routing results are written into
+ * the peers' memory and the two rendezvous of a layer are flags in peer memory
+ * with bounded polls - no NCCL call and no host synchronisation in the layer; a
+ * flag that does not arrive within 2 s leaves GPTOSS_E_DEVICE in
+ * gptoss_moe_device_status; the reference's counterpart is the peer copies of
  * expert.cpp:1520-1535 and :1577).  gptoss_moe_ep_init selects 1 when every rank could map
  * every peer's buffers through CUDA IPC (one process per rank, one node), else 0;
  * gptoss_moe_set_option(h, "ep_transport", v) changes it (all ranks alike).
