@@ -262,34 +262,46 @@ combine_rows_kernel(bf16 *__restrict__ out, const bf16 *__restrict__ ys,
   if ((RESIDUAL || SKIP_EMPTY) && nvalid == 0) return;
   uint4 *o4 = reinterpret_cast<uint4 *>(out + static_cast<size_t>(row) * H);
   const int n4 = H >> 3;
-  for (int p = lane; p < n4; p += 32) {
-    float a[8];
+  // two 16-byte columns per lane and trip: up to 2 * (K + 1) loads in flight per lane
+  for (int p0 = lane; p0 < n4; p0 += 64) {
+    const int p1 = p0 + 32;
+    const bool two = p1 < n4;
+    uint4 xv[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+    uint4 yv[2][GPTOSS_MAX_TOPK];
     if (RESIDUAL) {
-      const uint4 v = o4[p];
-      a[0] = bf16_lo(v.x); a[1] = bf16_hi(v.x); a[2] = bf16_lo(v.y); a[3] = bf16_hi(v.y);
-      a[4] = bf16_lo(v.z); a[5] = bf16_hi(v.z); a[6] = bf16_lo(v.w); a[7] = bf16_hi(v.w);
-    } else {
-#pragma unroll
-      for (int i = 0; i < 8; i++) a[i] = 0.f;
+      xv[0] = o4[p0];
+      if (two) xv[1] = o4[p1];
     }
-    float s[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) s[i] = 0.f;
 #pragma unroll
     for (int k = 0; k < GPTOSS_MAX_TOPK; k++) {
       if (k < K && src[k] >= 0) {
-        const uint4 v =
-            __ldg(reinterpret_cast<const uint4 *>(ys + static_cast<size_t>(src[k]) * H) + p);
-        s[0] += bf16_lo(v.x); s[1] += bf16_hi(v.x); s[2] += bf16_lo(v.y); s[3] += bf16_hi(v.y);
-        s[4] += bf16_lo(v.z); s[5] += bf16_hi(v.z); s[6] += bf16_lo(v.w); s[7] += bf16_hi(v.w);
+        const uint4 *y4 = reinterpret_cast<const uint4 *>(ys + static_cast<size_t>(src[k]) * H);
+        yv[0][k] = __ldcs(y4 + p0);
+        if (two) yv[1][k] = __ldcs(y4 + p1);
       }
     }
-    uint4 o;
-    o.x = pack_bf16(a[0] + s[0], a[1] + s[1]);
-    o.y = pack_bf16(a[2] + s[2], a[3] + s[3]);
-    o.z = pack_bf16(a[4] + s[4], a[5] + s[5]);
-    o.w = pack_bf16(a[6] + s[6], a[7] + s[7]);
-    o4[p] = o;
+#pragma unroll
+    for (int u = 0; u < 2; u++) {
+      if (u == 1 && !two) break;
+      float s[8];
+#pragma unroll
+      for (int i = 0; i < 8; i++) s[i] = 0.f;
+#pragma unroll
+      for (int k = 0; k < GPTOSS_MAX_TOPK; k++) {
+        if (k < K && src[k] >= 0) {
+          const uint4 v = yv[u][k];
+          s[0] += bf16_lo(v.x); s[1] += bf16_hi(v.x); s[2] += bf16_lo(v.y); s[3] += bf16_hi(v.y);
+          s[4] += bf16_lo(v.z); s[5] += bf16_hi(v.z); s[6] += bf16_lo(v.w); s[7] += bf16_hi(v.w);
+        }
+      }
+      const uint4 v = xv[u];  // zeros without a residual
+      uint4 o;
+      o.x = pack_bf16(bf16_lo(v.x) + s[0], bf16_hi(v.x) + s[1]);
+      o.y = pack_bf16(bf16_lo(v.y) + s[2], bf16_hi(v.y) + s[3]);
+      o.z = pack_bf16(bf16_lo(v.z) + s[4], bf16_hi(v.z) + s[5]);
+      o.w = pack_bf16(bf16_lo(v.w) + s[6], bf16_hi(v.w) + s[7]);
+      o4[u == 0 ? p0 : p1] = o;
+    }
   }
 }
 
