@@ -125,167 +125,194 @@ qkv_rope_cache_kernel(const float *__restrict__ qkv, const float *__restrict__ b
   }
 }
 
-// One CTA per (row, KV head), one warp per query head of the group: online softmax over
-// the cache positions t0..pos plus the head's sink logit, which takes probability mass
-// but has no value row (run.cpp:601-647; the sliding-window mask of even layers,
-// run.cpp:176-183, 619-621, becomes the lower bound t0 = pos - window + 1).  The CTA
-// stages tiles of 32 cache positions (K and V rows of the KV head) in shared memory
-// once for all its query heads, double buffered through registers.  Inside a warp a
-// cache row of D elements is read by D/8 adjacent lanes, 16 bytes each, so a warp
-// covers 256/D positions per step; the partial dot products meet by shuffle, every lane
-// group keeps its own running maximum, sum and 8-wide slice of the accumulator, and the
-// groups are merged at the end.  Output bf16 [B, Hq D].
-constexpr int kAttnTile = 32;
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                          uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, "
+      "{%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Attention of one decode step over the KV cache, on tensor cores.
+//
+// One CTA per (row, KV head): the up to 8 query heads that share the KV head are the rows
+// of an m16n8k16 tile (rows 8-15 stay zero), so K and V are read once for all of them.
+// The CTA's 4 warps take every fourth block of 16 cache positions; per block a warp
+// computes S = Q K^T (positions as the MMA's N), keeps a running maximum and sum per head
+// (online softmax, fp32), and accumulates O += P V with P rounded to bf16 (as V is); the
+// four partial results and the head's sink logit - which takes probability mass but has
+// no value row - are merged through shared memory (run.cpp:601-647; the sliding-window
+// mask of even layers, run.cpp:176-183, 619-621, is the lower bound t0 = pos - window + 1).
+// Cache rows past pos are read as zeros.  Output bf16 [B, Hq D].
+constexpr int kAttnWarps = 4;
 
 template <int D>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kAttnWarps * 32)
 attn_decode_kernel(const float *__restrict__ q, const bf16 *__restrict__ k_cache,
                    const bf16 *__restrict__ v_cache, const float *__restrict__ sinks,
                    const int *__restrict__ pos, bf16 *__restrict__ out, int B, int Hq, int Hkv,
                    int S, int window) {
-  constexpr int LP = D / 8;                // lanes per position
-  constexpr int PP = 32 / LP;              // positions per warp step
-  constexpr int kChunks = kAttnTile * LP;  // 16-byte chunks of one K (or V) tile
-  __shared__ uint4 tile_k[2][kChunks];
-  __shared__ uint4 tile_v[2][kChunks];
+  constexpr int RS = D * 2 + 16;        // padded row pitch of a staged tile (bytes)
+  constexpr int kChunks = 16 * (D / 8);  // 16-byte chunks of one 16-position tile
+  constexpr int kPerLane = kChunks / 32;
+  __shared__ __align__(16) unsigned char tiles[kAttnWarps][2][16 * RS];  // [warp][K | V]
+  __shared__ float sm_m[kAttnWarps][8], sm_l[kAttnWarps][8];
+  static_assert(8 * D * 4 <= 2 * 16 * RS, "a warp's partial output reuses its own tiles");
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int row = blockIdx.x / Hkv, kvh = blockIdx.x - row * Hkv;
   const int p = pos[row];
   if (p < 0) return;  // the whole CTA leaves
-  const int group = Hq / Hkv;  // query heads per KV head = warps of this CTA
-  const int h = kvh * group + warp;
-  const int sub = lane % LP, grp = lane / LP;
+  const int group = Hq / Hkv;
   const int dkv = Hkv * D;
   const int t0 = window > 0 ? max(0, p - window + 1) : 0;
-  float qr[8];
+  const int n_blocks = (p - t0 + 16) / 16;
+  const int hr = lane >> 2, qd = lane & 3;  // head row of this thread's fragment, quad lane
+
+  // Q fragments (A operand): rows = heads of the group, pre-scaled by 1/sqrt(D)
+  uint32_t qa[D / 16][4];
   {
-    const float4 *q4 =
-        reinterpret_cast<const float4 *>(q + (static_cast<size_t>(row) * Hq + h) * D + 8 * sub);
-    const float4 a = q4[0], b = q4[1];
     const float scale = 1.0f / sqrtf(static_cast<float>(D));
-    qr[0] = a.x * scale; qr[1] = a.y * scale; qr[2] = a.z * scale; qr[3] = a.w * scale;
-    qr[4] = b.x * scale; qr[5] = b.y * scale; qr[6] = b.z * scale; qr[7] = b.w * scale;
+    const float *qrow = q + (static_cast<size_t>(row) * Hq + kvh * group + hr) * D;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; kk++) {
+      float2 lo = make_float2(0.f, 0.f), hi = make_float2(0.f, 0.f);
+      if (hr < group) {
+        lo = *reinterpret_cast<const float2 *>(qrow + kk * 16 + 2 * qd);
+        hi = *reinterpret_cast<const float2 *>(qrow + kk * 16 + 8 + 2 * qd);
+      }
+      qa[kk][0] = pack_bf16(lo.x * scale, lo.y * scale);
+      qa[kk][1] = 0u;  // rows 8-15
+      qa[kk][2] = pack_bf16(hi.x * scale, hi.y * scale);
+      qa[kk][3] = 0u;
+    }
   }
   float m = -INFINITY, l = 0.f;
-  float acc[8];
+  float o[D / 8][2];
 #pragma unroll
-  for (int i = 0; i < 8; i++) acc[i] = 0.f;
+  for (int n = 0; n < D / 8; n++) o[n][0] = o[n][1] = 0.f;
+
   const size_t base = static_cast<size_t>(row) * S * dkv + kvh * D;
-  constexpr int kPerThread = (kChunks + 255) / 256;  // chunks a thread stages (block <= 256)
-  uint4 rk[kPerThread], rv[kPerThread];
-  auto fetch = [&](int tile0) {
+  unsigned char *tk = tiles[warp][0], *tv = tiles[warp][1];
+  const uint32_t tk_s = smem_u32(tk), tv_s = smem_u32(tv);
+  uint4 rk[kPerLane], rv[kPerLane];
+  auto fetch = [&](int blk) {
+    const int tb = t0 + blk * 16;
 #pragma unroll
-    for (int u = 0; u < kPerThread; u++) {
-      const int c = tid + u * blockDim.x;
+    for (int u = 0; u < kPerLane; u++) {
+      const int c = lane + 32 * u, r = c / (D / 8), ch = c - r * (D / 8);
       rk[u] = rv[u] = make_uint4(0, 0, 0, 0);
-      const int t = tile0 + c / LP;
-      if (c < kChunks && t <= p) {
-        const size_t off = base + static_cast<size_t>(t) * dkv + 8 * (c % LP);
+      if (tb + r <= p) {
+        const size_t off = base + static_cast<size_t>(tb + r) * dkv + 8 * ch;
         rk[u] = __ldg(reinterpret_cast<const uint4 *>(k_cache + off));
         rv[u] = __ldg(reinterpret_cast<const uint4 *>(v_cache + off));
       }
     }
   };
-  auto stash = [&](int buf) {
+  if (warp < n_blocks) fetch(warp);
+  for (int blk = warp; blk < n_blocks; blk += kAttnWarps) {
+    __syncwarp();  // the previous block's ldmatrix reads are done
 #pragma unroll
-    for (int u = 0; u < kPerThread; u++) {
-      const int c = tid + u * blockDim.x;
-      if (c < kChunks) {
-        tile_k[buf][c] = rk[u];
-        tile_v[buf][c] = rv[u];
-      }
+    for (int u = 0; u < kPerLane; u++) {
+      const int c = lane + 32 * u, r = c / (D / 8), ch = c - r * (D / 8);
+      *reinterpret_cast<uint4 *>(tk + r * RS + ch * 16) = rk[u];
+      *reinterpret_cast<uint4 *>(tv + r * RS + ch * 16) = rv[u];
     }
-  };
-  // blockDim may be smaller than 256 (few query heads per KV head): stage in several rounds
-  const int rounds = (kChunks + kPerThread * blockDim.x - 1) / (kPerThread * blockDim.x);
-  auto fetch_stash_all = [&](int tile0, int buf) {
-    for (int r = 0; r < rounds; r++) {
+    __syncwarp();
+    if (blk + kAttnWarps < n_blocks) fetch(blk + kAttnWarps);  // in flight during the math
+
+    // S = Q K^T for 16 positions: two n-tiles of 8
+    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int u = 0; u < kPerThread; u++) {
-        const int c = tid + (r * kPerThread + u) * blockDim.x;
-        if (c < kChunks) {
-          const int t = tile0 + c / LP;
-          uint4 a = make_uint4(0, 0, 0, 0), b = a;
-          if (t <= p) {
-            const size_t off = base + static_cast<size_t>(t) * dkv + 8 * (c % LP);
-            a = __ldg(reinterpret_cast<const uint4 *>(k_cache + off));
-            b = __ldg(reinterpret_cast<const uint4 *>(v_cache + off));
-          }
-          tile_k[buf][c] = a;
-          tile_v[buf][c] = b;
-        }
-      }
+    for (int kk = 0; kk < D / 16; kk++) {
+      uint32_t b[4];
+      const int prow = (lane >> 4) * 8 + (lane & 7), dch = kk * 2 + ((lane >> 3) & 1);
+      ldsm_x4(tk_s + prow * RS + dch * 16, b);
+      mma_16816(s0, qa[kk], b[0], b[1]);
+      mma_16816(s1, qa[kk], b[2], b[3]);
     }
-  };
-  const bool wide = rounds == 1;  // every chunk of a tile has its own thread slot
-  int buf = 0;
-  fetch_stash_all(t0, 0);
+    // this thread's four positions of head row hr: block offsets 2qd, 2qd+1, 8+2qd, 9+2qd
+    const int tb = t0 + blk * 16;
+    float sv[4] = {s0[0], s0[1], s1[0], s1[1]};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int t = tb + (i >> 1) * 8 + 2 * qd + (i & 1);
+      if (t > p) sv[i] = -INFINITY;
+    }
+    float bm = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
+    bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+    bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
+    const float m_new = fmaxf(m, bm);  // finite: the first position of a block is <= pos
+    const float corr = __expf(m - m_new);
+    float pr[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) pr[i] = __expf(sv[i] - m_new);
+    l = l * corr + (pr[0] + pr[1]) + (pr[2] + pr[3]);
+    m = m_new;
+#pragma unroll
+    for (int n = 0; n < D / 8; n++) {
+      o[n][0] *= corr;
+      o[n][1] *= corr;
+    }
+    // O += P V: P (16 heads x 16 positions) from the score fragments, V transposed on load
+    uint32_t pa[4] = {pack_bf16(pr[0], pr[1]), 0u, pack_bf16(pr[2], pr[3]), 0u};
+#pragma unroll
+    for (int n = 0; n < D / 8; n += 2) {
+      uint32_t b[4];
+      const int prow = ((lane >> 3) & 1) * 8 + (lane & 7), dch = n + (lane >> 4);
+      ldsm_x4_trans(tv_s + prow * RS + dch * 16, b);
+      float acc0[4] = {o[n][0], o[n][1], 0.f, 0.f}, acc1[4] = {o[n + 1][0], o[n + 1][1], 0.f, 0.f};
+      mma_16816(acc0, pa, b[0], b[1]);
+      mma_16816(acc1, pa, b[2], b[3]);
+      o[n][0] = acc0[0]; o[n][1] = acc0[1];
+      o[n + 1][0] = acc1[0]; o[n + 1][1] = acc1[1];
+    }
+  }
+  // the quad's partial sums of l -> one per head
+  l += __shfl_xor_sync(0xffffffffu, l, 1);
+  l += __shfl_xor_sync(0xffffffffu, l, 2);
+  if (qd == 0) {
+    sm_m[warp][hr] = m;
+    sm_l[warp][hr] = l;
+  }
+  // the warp's partial output [8 heads][D] goes where its K / V tiles were
+  __syncwarp();
+  {
+    float *my_o = reinterpret_cast<float *>(tiles[warp][0]);
+#pragma unroll
+    for (int n = 0; n < D / 8; n++) {
+      my_o[hr * D + n * 8 + 2 * qd] = o[n][0];
+      my_o[hr * D + n * 8 + 2 * qd + 1] = o[n][1];
+    }
+  }
   __syncthreads();
-  for (int tile0 = t0; tile0 <= p; tile0 += kAttnTile) {
-    const bool more = tile0 + kAttnTile <= p;
-    if (more && wide) fetch(tile0 + kAttnTile);  // next tile in flight during the math
-    if (warp < group) {
+  // merge the warps and the sink; one output element per thread and trip
+  for (int idx = tid; idx < group * D; idx += kAttnWarps * 32) {
+    const int hl = idx / D, d = idx - hl * D;
+    const int h = kvh * group + hl;
+    const float sink = sinks[h];
+    float m_all = sink;
 #pragma unroll
-      for (int j = 0; j < kAttnTile / PP; j++) {
-        const int c = (j * PP + grp) * LP + sub;
-        const int t = tile0 + j * PP + grp;
-        const uint4 kv = tile_k[buf][c], vv = tile_v[buf][c];
-        float s = qr[0] * bf16_lo(kv.x) + qr[1] * bf16_hi(kv.x) + qr[2] * bf16_lo(kv.y) +
-                  qr[3] * bf16_hi(kv.y) + qr[4] * bf16_lo(kv.z) + qr[5] * bf16_hi(kv.z) +
-                  qr[6] * bf16_lo(kv.w) + qr[7] * bf16_hi(kv.w);
+    for (int w = 0; w < kAttnWarps; w++) m_all = fmaxf(m_all, sm_m[w][hl]);
+    float lsum = __expf(sink - m_all), acc = 0.f;
 #pragma unroll
-        for (int off = 1; off < LP; off <<= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-        if (t <= p) {
-          const float m_new = fmaxf(m, s);
-          const float corr = __expf(m - m_new), pr = __expf(s - m_new);
-          l = l * corr + pr;
-          acc[0] = acc[0] * corr + pr * bf16_lo(vv.x);
-          acc[1] = acc[1] * corr + pr * bf16_hi(vv.x);
-          acc[2] = acc[2] * corr + pr * bf16_lo(vv.y);
-          acc[3] = acc[3] * corr + pr * bf16_hi(vv.y);
-          acc[4] = acc[4] * corr + pr * bf16_lo(vv.z);
-          acc[5] = acc[5] * corr + pr * bf16_hi(vv.z);
-          acc[6] = acc[6] * corr + pr * bf16_lo(vv.w);
-          acc[7] = acc[7] * corr + pr * bf16_hi(vv.w);
-          m = m_new;
-        }
-      }
+    for (int w = 0; w < kAttnWarps; w++) {
+      const float mw = sm_m[w][hl];
+      const float f = (mw == -INFINITY) ? 0.f : __expf(mw - m_all);
+      lsum += sm_l[w][hl] * f;
+      acc += reinterpret_cast<const float *>(tiles[w][0])[hl * D + d] * f;
     }
-    if (more) {
-      if (wide)
-        stash(buf ^ 1);
-      else
-        fetch_stash_all(tile0 + kAttnTile, buf ^ 1);
-    }
-    __syncthreads();
-    buf ^= 1;
-  }
-  if (warp >= group) return;
-  // merge the position groups: common maximum (the sink logit included), rescaled sums
-  float m_all = m;
-#pragma unroll
-  for (int off = LP; off < 32; off <<= 1) m_all = fmaxf(m_all, __shfl_xor_sync(0xffffffffu, m_all, off));
-  const float sink = sinks[h];
-  m_all = fmaxf(m_all, sink);
-  const float mine = (m == -INFINITY) ? 0.f : __expf(m - m_all);
-  l *= mine;
-#pragma unroll
-  for (int i = 0; i < 8; i++) acc[i] *= mine;
-#pragma unroll
-  for (int off = LP; off < 32; off <<= 1) {
-    l += __shfl_xor_sync(0xffffffffu, l, off);
-#pragma unroll
-    for (int i = 0; i < 8; i++) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], off);
-  }
-  l += __expf(sink - m_all);
-  if (grp == 0) {
-    const float inv = 1.0f / l;
-    uint4 o;
-    o.x = pack_bf16(acc[0] * inv, acc[1] * inv);
-    o.y = pack_bf16(acc[2] * inv, acc[3] * inv);
-    o.z = pack_bf16(acc[4] * inv, acc[5] * inv);
-    o.w = pack_bf16(acc[6] * inv, acc[7] * inv);
-    *reinterpret_cast<uint4 *>(out + (static_cast<size_t>(row) * Hq + h) * D + 8 * sub) = o;
+    out[(static_cast<size_t>(row) * Hq + h) * D + d] = __float2bfloat16_rn(acc / lsum);
   }
 }
 
@@ -727,8 +754,8 @@ int gptoss_decode_step(gptoss_decode_t *h, const int *tokens, const int *pos, in
     DCK(h, cudaGetLastError());
     // sliding window on even layers (run.cpp:619)
     const int window = (c.sliding_window > 0 && (l % 2 == 0)) ? c.sliding_window : 0;
-    // one CTA per (row, KV head), one warp per query head of the group
-    const int grid = B * Hkv, threads = 32 * (Hq / Hkv);
+    // one CTA per (row, KV head): the group's query heads are the rows of the MMA tiles
+    const int grid = B * Hkv, threads = kAttnWarps * 32;
     const float *sinks = h->sinks + static_cast<size_t>(l) * Hq;
     if (D == 32)
       attn_decode_kernel<32><<<grid, threads, 0, st>>>(h->q, kc, vc, sinks, h->d_pos, h->attn, B, Hq, Hkv, S, window);

@@ -103,17 +103,21 @@ def test_rows_are_independent_and_inactive_rows_idle(pkg, tmp_path):
         assert multi[r] == solo[0], f"row {r}"
 
 
-def test_live_reference_when_present(pkg, oracle, tmp_path):
-    """Fresh seed, full logits against the compiled reference where it travelled along."""
+@pytest.mark.parametrize("heads", [(4, 2), (8, 1), (6, 2)])
+def test_live_reference_when_present(pkg, oracle, tmp_path, heads):
+    """Fresh seed, full logits against the compiled reference where it travelled along;
+    2, 8 and 3 query heads per KV head, contexts longer than one 16-position block and a
+    window that cuts into them."""
     from gpt_oss_b200 import synth
 
     if not oracle.have_ref():
         pytest.skip("compiled reference not present")
-    # one layer and few positions: little room for a near-tie in the router, where a bf16
-    # pipeline and the fp32 reference would part ways
-    cfg = dict(synth.MINI_MODEL, vocab_size=777, sliding_window=5, n_layers=1)
-    rng = np.random.default_rng(77)
-    tokens = rng.integers(0, cfg["vocab_size"], size=12, dtype=np.int32)
+    # every expert is selected (top-4 of 4), so no near-tie in the router can make the bf16
+    # pipeline and the fp32 reference pick different experts
+    cfg = dict(synth.MINI_MODEL, vocab_size=777, sliding_window=21, n_layers=2,
+               n_attn_heads=heads[0], n_kv_heads=heads[1], n_experts=4, experts_per_token=4)
+    rng = np.random.default_rng(77 + heads[0])
+    tokens = rng.integers(0, cfg["vocab_size"], size=40, dtype=np.int32)
     logits, _ = _run_teacher_forced(pkg, cfg, 9, tokens, tmp_path)
     want = oracle.model_logits(tmp_path / "model.bin", tokens, cfg["vocab_size"])
     err = np.abs(logits - want)
