@@ -101,6 +101,7 @@ def load_library() -> ctypes.CDLL:
         "gptoss_moe_forward_host": (c_int, [vp, c_int, vp, vp, vp, c_int]),
         "gptoss_moe_forward_host_submit": (c_int, [vp, c_int, vp, vp, vp, c_int, ip]),
         "gptoss_moe_forward_host_wait": (c_int, [vp, c_int]),
+        "gptoss_moe_load_ffn_norm": (c_int, [vp, c_int, vp]),
         "gptoss_moe_route": (c_int, [vp, c_int, vp, vp, c_int, vp]),
         "gptoss_moe_permute": (c_int, [vp, vp, c_int, vp]),
         "gptoss_moe_experts": (c_int, [vp, c_int, vp]),
@@ -264,6 +265,10 @@ class MoeEngine:
             self.handle, layer, _ptr(t_host), _ptr(x_host), _ptr(pos_host), n_tokens,
             ctypes.byref(ticket)))
         return int(ticket.value)
+
+    def load_ffn_norm(self, layer, scale):
+        scale = np.ascontiguousarray(scale, dtype=np.float32)
+        self._check(self.lib.gptoss_moe_load_ffn_norm(self.handle, layer, _ptr(scale)))
 
     def forward_host_wait(self, ticket: int):
         self._check(self.lib.gptoss_moe_forward_host_wait(self.handle, ticket))

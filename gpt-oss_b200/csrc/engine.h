@@ -34,6 +34,7 @@ struct LayerWeights {
   uint8_t *w2_blocks = nullptr, *w2_scales = nullptr;
   CUtensorMap tmap_w1, tmap_w2;            // boxes of 240 weight rows (N operand)
   CUtensorMap tmap_w1_rows, tmap_w2_rows;  // boxes of 128 weight rows (M operand, CTA pairs)
+  float *rms_ffn = nullptr;   // [H] scale of the RMSNorm in front of the block (optional)
   bool loaded = false;
 };
 

@@ -164,7 +164,7 @@ int gptoss_moe_destroy(gptoss_moe_t *h) {
   for (auto &lw : h->layers) {
     cudaFree(lw.w_router); cudaFree(lw.b_router); cudaFree(lw.w1); cudaFree(lw.b1);
     cudaFree(lw.w2); cudaFree(lw.b2); cudaFree(lw.w1_blocks); cudaFree(lw.w1_scales);
-    cudaFree(lw.w2_blocks); cudaFree(lw.w2_scales);
+    cudaFree(lw.w2_blocks); cudaFree(lw.w2_scales); cudaFree(lw.rms_ffn);
   }
   cudaFree(h->topk_i); cudaFree(h->topk_v); cudaFree(h->logits); cudaFree(h->block_counts);
   cudaFree(h->expert_offsets); cudaFree(h->sorted_row); cudaFree(h->sorted_weight);
@@ -452,13 +452,25 @@ int gptoss_moe_forward_host(gptoss_moe_t *h, int layer, const void *t_host, void
   return GPTOSS_OK;
 }
 
+int gptoss_moe_load_ffn_norm(gptoss_moe_t *h, int layer, const float *scale_host) {
+  if (!h || !scale_host) return GPTOSS_E_INVALID;
+  if (layer < 0 || layer >= h->L) return fail(h, GPTOSS_E_INVALID, "layer out of range");
+  CK(h, cudaSetDevice(h->cfg.device));
+  LayerWeights &lw = h->layers[layer];
+  if (!lw.rms_ffn) CK(h, dev_alloc(&lw.rms_ffn, (size_t)h->H));
+  CK(h, cudaMemcpy(lw.rms_ffn, scale_host, sizeof(float) * h->H, cudaMemcpyHostToDevice));
+  return GPTOSS_OK;
+}
+
 int gptoss_moe_forward_host_submit(gptoss_moe_t *h, int layer, const void *t_host, void *x_host,
                                    const int *pos_host, int n_tokens, int *ticket) {
   if (!h || !ticket) return GPTOSS_E_INVALID;
-  if ((!t_host || !x_host) && n_tokens > 0)
-    return fail(h, GPTOSS_E_INVALID, "null activation pointer");
+  if (!x_host && n_tokens > 0) return fail(h, GPTOSS_E_INVALID, "null activation pointer");
   int rc = check_layer(h, layer, n_tokens);
   if (rc) return rc;
+  if (!t_host && !h->layers[layer].rms_ffn)
+    return fail(h, GPTOSS_E_STATE,
+                "t_host is NULL but the layer has no RMSNorm scale (gptoss_moe_load_ffn_norm)");
   if (h->ep_size > 1)
     return fail(h, GPTOSS_E_STATE, "the pipelined host path is for engines with all experts local");
   CK(h, cudaSetDevice(h->cfg.device));
@@ -484,7 +496,7 @@ int gptoss_moe_forward_host_submit(gptoss_moe_t *h, int layer, const void *t_hos
   }
   const size_t bytes = (size_t)n_tokens * h->H * sizeof(bf16);
   if (n_tokens > 0) {
-    CK(h, cudaMemcpyAsync(sl.t, t_host, bytes, cudaMemcpyHostToDevice, h->s_h2d));
+    if (t_host) CK(h, cudaMemcpyAsync(sl.t, t_host, bytes, cudaMemcpyHostToDevice, h->s_h2d));
     CK(h, cudaMemcpyAsync(sl.x, x_host, bytes, cudaMemcpyHostToDevice, h->s_h2d));
     if (pos_host)
       CK(h, cudaMemcpyAsync(sl.pos, pos_host, (size_t)n_tokens * 4, cudaMemcpyHostToDevice, h->s_h2d));
@@ -492,6 +504,9 @@ int gptoss_moe_forward_host_submit(gptoss_moe_t *h, int layer, const void *t_hos
   CK(h, cudaEventRecord(sl.h2d, h->s_h2d));
   CK(h, cudaStreamWaitEvent(h->s_comp, sl.h2d, 0));
   if (n_tokens > 0) {
+    if (!t_host)  // the block's own RMSNorm: t = scale * x / rms(x)
+      CK(h, launch_rmsnorm(sl.t, sl.x, h->layers[layer].rms_ffn, pos_host ? sl.pos : nullptr,
+                           n_tokens, h->H, h->s_comp, &h->launches));
     rc = gptoss_moe_forward(h, layer, sl.t, sl.x, pos_host ? sl.pos : nullptr, n_tokens, h->s_comp);
     if (rc) return rc;
   }

@@ -145,12 +145,18 @@ int gptoss_moe_forward_host(gptoss_moe_t *h, int layer, const void *t_host, void
  * time (one stream per direction and one for the kernels).  x_host is valid
  * after gptoss_moe_forward_host_wait(h, ticket); t_host, x_host and pos_host must
  * stay untouched until then.  A fourth submit waits for the oldest.  All experts
- * local only.  No counterpart in the reference, whose host loop copies, computes
+ * local only.  t_host may be NULL once gptoss_moe_load_ffn_norm gave the layer the
+ * scale of the RMSNorm that precedes the block in the model (run.cpp:664): the
+ * normalised input is then computed on the device from x, and only x crosses the
+ * bus in each direction.  No counterpart in the reference, whose host loop copies, computes
  * and copies back in turn (getp_run.cpp:956-961).
  */
 int gptoss_moe_forward_host_submit(gptoss_moe_t *h, int layer, const void *t_host, void *x_host,
                                    const int *pos_host, int n_tokens, int *ticket);
 int gptoss_moe_forward_host_wait(gptoss_moe_t *h, int ticket);
+/* fp32 [H] scale of the ffn RMSNorm of `layer` (rms_ffn_w, run.cpp:52, :664), host
+ * pointer; only needed for submits with t_host == NULL. */
+int gptoss_moe_load_ffn_norm(gptoss_moe_t *h, int layer, const float *scale_host);
 
 /* The stages of gptoss_moe_forward, individually (same order). */
 /* router linear + bias + top-k + softmax (matmul.cpp:945, utility.cpp:274). */

@@ -216,4 +216,22 @@ def test_streamed_host_path_matches_one_call_path(pkg):
         np.testing.assert_array_equal(a, b)
     with pytest.raises(pkg.MoeError):
         eng.forward_host_wait(10_000)
+    # without t: the block's RMSNorm runs on the device; same as sending rmsnorm(x) as t
+    t, x, pos = batches[0]
+    with pytest.raises(pkg.MoeError):  # no scale loaded yet
+        eng.forward_host_submit(0, None, x.copy(), pos, t.shape[0])
+    scale = synth.bf16_round(1.0 + 0.1 * rng.standard_normal(256).astype(np.float32))
+    eng.load_ffn_norm(0, scale)
+    import torch
+
+    xd = torch.from_numpy(x.view(np.int16)).cuda().view(torch.bfloat16)
+    td = torch.empty_like(xd)
+    eng.rmsnorm(td, xd, torch.from_numpy(scale).cuda(), torch.from_numpy(pos).cuda(), t.shape[0],
+                torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    t_norm = td.view(torch.int16).cpu().numpy().view(np.uint16)
+    a, b = x.copy(), x.copy()
+    eng.forward_host(0, t_norm, a, pos, t.shape[0])
+    eng.forward_host_wait(eng.forward_host_submit(0, None, b, pos, t.shape[0]))
+    np.testing.assert_array_equal(a, b)
     eng.close()
