@@ -132,6 +132,7 @@ def load_library() -> ctypes.CDLL:
                                             ctypes.POINTER(vp)]),
         "gptoss_decode_set_tensor": (c_int, [vp, c_char_p, c_int, vp, c_int, c_int]),
         "gptoss_decode_set_kv": (c_int, [vp, c_int, c_int, c_int, c_int, c_int, vp, vp]),
+        "gptoss_decode_get_kv": (c_int, [vp, c_int, c_int, c_int, c_int, c_int, vp, vp]),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(lib, name)
@@ -389,6 +390,11 @@ class DecodeEngine:
     def set_kv(self, layer: int, row0: int, pos0: int, k, v):
         """k, v: CUDA bf16 tensors [rows, positions, n_kv_heads * head_dim]."""
         self._check(self.lib.gptoss_decode_set_kv(self.handle, layer, row0, k.shape[0], pos0,
+                                                  k.shape[1], _ptr(k), _ptr(v)))
+
+    def get_kv(self, layer: int, row0: int, pos0: int, k, v):
+        """Fills the CUDA bf16 tensors k, v [rows, positions, n_kv_heads * head_dim]."""
+        self._check(self.lib.gptoss_decode_get_kv(self.handle, layer, row0, k.shape[0], pos0,
                                                   k.shape[1], _ptr(k), _ptr(v)))
 
     def moe(self, ep_rank: int = 0, ep_size: int = 1, device: int = 0) -> "MoeEngine":

@@ -680,6 +680,24 @@ int gptoss_decode_set_kv(gptoss_decode_t *h, int layer, int row0, int n_rows, in
   return GPTOSS_OK;
 }
 
+int gptoss_decode_get_kv(gptoss_decode_t *h, int layer, int row0, int n_rows, int pos0, int n_pos,
+                         void *k_dev, void *v_dev) {
+  if (!h || !k_dev || !v_dev) return GPTOSS_E_INVALID;
+  const gptoss_model_config_t &c = h->cfg;
+  if (layer < 0 || layer >= c.n_layers || row0 < 0 || n_rows < 0 || row0 + n_rows > h->max_batch ||
+      pos0 < 0 || n_pos < 0 || pos0 + n_pos > c.seq_len)
+    return dfail(h, GPTOSS_E_INVALID, "cache region out of range");
+  if (n_rows == 0 || n_pos == 0) return GPTOSS_OK;
+  DCK(h, cudaSetDevice(h->device));
+  const size_t dkv = static_cast<size_t>(c.n_kv_heads) * c.head_dim, S = c.seq_len;
+  const size_t off = ((static_cast<size_t>(layer) * h->max_batch + row0) * S + pos0) * dkv;
+  DCK(h, cudaMemcpy2D(k_dev, n_pos * dkv * sizeof(bf16), h->k_cache + off, S * dkv * sizeof(bf16),
+                      n_pos * dkv * sizeof(bf16), n_rows, cudaMemcpyDeviceToDevice));
+  DCK(h, cudaMemcpy2D(v_dev, n_pos * dkv * sizeof(bf16), h->v_cache + off, S * dkv * sizeof(bf16),
+                      n_pos * dkv * sizeof(bf16), n_rows, cudaMemcpyDeviceToDevice));
+  return GPTOSS_OK;
+}
+
 int gptoss_decode_load_bin(gptoss_decode_t *h, const float *p) {
   if (!h || !p) return GPTOSS_E_INVALID;
   const gptoss_model_config_t &c = h->cfg;

@@ -109,6 +109,10 @@ int gptoss_decode_set_tensor(gptoss_decode_t *h, const char *name, int layer, co
  * the prompt (benchmarks with synthetic contexts). */
 int gptoss_decode_set_kv(gptoss_decode_t *h, int layer, int row0, int n_rows, int pos0, int n_pos,
                          const void *k_dev, const void *v_dev);
+/* The reverse: copies that region of the cache out (moving a sequence to another row or
+ * another engine). */
+int gptoss_decode_get_kv(gptoss_decode_t *h, int layer, int row0, int n_rows, int pos0, int n_pos,
+                         void *k_dev, void *v_dev);
 
 /* One step.  tokens[i] / pos[i]: the token to feed to batch row i and its position
  * (host arrays); pos[i] < 0 marks a row that does no work (its cache is untouched

@@ -136,3 +136,58 @@ def test_decode_argument_errors(pkg):
         eng.step(np.zeros(2, np.int32), np.zeros(2, np.int32))
     assert ei.value.code == pkg.GPTOSS_E_STATE
     eng.close()
+
+
+def test_per_tensor_loading_and_cache_transfer(pkg, tmp_path):
+    """An engine filled tensor by tensor (fp32 from the host, or bf16 / fp32 already on the
+    device) and handed another engine's KV cache continues a sequence exactly as the engine
+    that loaded the .bin image and ran the sequence itself."""
+    import torch
+
+    from gpt_oss_b200 import synth
+
+    cfg = synth.MINI_MODEL
+    path = tmp_path / "model.bin"
+    W = synth.write_model_bin(path, cfg, 12)
+    a = pkg.DecodeEngine(cfg, 3)
+    a.load_bin(np.asarray(np.memmap(path, dtype=np.uint8, mode="r")))
+    rng = np.random.default_rng(8)
+    tokens = rng.integers(0, cfg["vocab_size"], size=11, dtype=np.int32)
+    idle = np.full(3, -1, np.int32)
+    for p, t in enumerate(tokens[:-1]):
+        tok, pos = idle.copy(), idle.copy()
+        tok[2], pos[2] = t, p
+        a.step(tok, pos)
+
+    b = pkg.DecodeEngine(cfg, 3)
+    dev = torch.device("cuda:0")
+    L = cfg["n_layers"]
+    for name in ("token_embedding_table", "out"):
+        b.set_tensor(name, 0, W[name])                                   # fp32 from the host
+    b.set_tensor("rms_out_w", 0, torch.from_numpy(W["rms_out_w"]).to(dev))  # fp32 on the device
+    for l in range(L):
+        b.set_tensor("w_qkv", l, torch.from_numpy(W["w_qkv"][l]).to(dev).bfloat16())  # bf16 on the device
+        b.set_tensor("w_o", l, np.ascontiguousarray(W["w_o"][l]))
+        for name in ("b_qkv", "b_o", "attn_sinks", "rms_attn_w", "rms_ffn_w"):
+            b.set_tensor(name, l, np.ascontiguousarray(W[name][l]))
+    with pytest.raises(pkg.MoeError):  # the MoE layers are still missing
+        b.step(np.zeros(3, np.int32), np.zeros(3, np.int32))
+    moe = b.moe()
+    for l in range(L):
+        moe.load_layer_f32(l, W["w_router"][l], W["b_router"][l], W["w_mlp1"][l], W["b_mlp1"][l],
+                           W["w_mlp2"][l], W["b_mlp2"][l])
+    dkv = cfg["n_kv_heads"] * cfg["head_dim"]
+    n_ctx = len(tokens) - 1
+    for l in range(L):
+        k = torch.empty((1, n_ctx, dkv), device=dev, dtype=torch.bfloat16)
+        v = torch.empty_like(k)
+        a.get_kv(l, 2, 0, k, v)       # row 2 of engine a ...
+        b.set_kv(l, 1, 0, k, v)       # ... becomes row 1 of engine b
+    tok, pos = idle.copy(), idle.copy()
+    tok[2], pos[2] = tokens[-1], n_ctx
+    na = a.step(tok, pos)
+    nb = b.step(np.array([-1, tokens[-1], -1], np.int32), np.array([-1, n_ctx, -1], np.int32))
+    assert na[2] == nb[1] and nb[0] == -1
+    np.testing.assert_array_equal(a.logits(2), b.logits(1))
+    a.close()
+    b.close()
