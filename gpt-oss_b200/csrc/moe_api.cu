@@ -424,9 +424,21 @@ int gptoss_moe_forward(gptoss_moe_t *h, int layer, const void *t, void *x, const
   return gptoss_moe_combine(h, x, n_tokens, stream);
 }
 
+// Submissions still in flight use the engine's workspaces: let them finish first.
+static int drain_host_slots(gptoss_moe *h) {
+  for (auto &sl : h->host_slots) {
+    if (sl.busy) {
+      CK(h, cudaEventSynchronize(sl.d2h));
+      sl.busy = false;
+    }
+  }
+  return GPTOSS_OK;
+}
+
 int gptoss_moe_forward_host(gptoss_moe_t *h, int layer, const void *t_host, void *x_host,
                             const int *pos_host, int n_tokens) {
   if (!h) return GPTOSS_E_INVALID;
+  if (int drc = drain_host_slots(h)) return drc;
   if ((!t_host || !x_host) && n_tokens > 0)
     return fail(h, GPTOSS_E_INVALID, "null activation pointer");
   int rc = check_layer(h, layer, n_tokens);

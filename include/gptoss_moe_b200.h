@@ -7,6 +7,9 @@
  * (cudaStream_t), every call returns 0 on success or a negative GPTOSS_E_* code
  * and gptoss_moe_last_error() gives the text.  There is no CPU fallback: every
  * compute entry point fails with GPTOSS_E_CUDA when no sm_100 device is usable.
+ * A handle is used by one host thread at a time (the reference drives one
+ * engine per GPU from one thread, getp_run.cpp:1038-1063); different handles are
+ * independent.
  *
  * Citations are file:line in the reference project (pmatuan/gpt-oss).
  */
@@ -145,7 +148,9 @@ int gptoss_moe_forward_host(gptoss_moe_t *h, int layer, const void *t_host, void
  * time (one stream per direction and one for the kernels).  x_host is valid
  * after gptoss_moe_forward_host_wait(h, ticket); t_host, x_host and pos_host must
  * stay untouched until then.  A fourth submit waits for the oldest.  All experts
- * local only.  t_host may be NULL once gptoss_moe_load_ffn_norm gave the layer the
+ * local only.  While submissions are in flight the handle's workspaces are theirs:
+ * wait for every ticket before calling gptoss_moe_forward or the stage entry points
+ * on the same handle (gptoss_moe_forward_host does that wait itself).  t_host may be NULL once gptoss_moe_load_ffn_norm gave the layer the
  * scale of the RMSNorm that precedes the block in the model (run.cpp:664): the
  * normalised input is then computed on the device from x, and only x crosses the
  * bus in each direction.  No counterpart in the reference, whose host loop copies, computes
