@@ -98,7 +98,11 @@ __device__ __forceinline__ float warp_exact_dot(const bf16 *a, const bf16 *b, in
 }
 
 // NT = 8-expert MMA tiles per warp; the CTA covers EPAD = 32*NT experts.
-template <int NT>
+// SPLIT = CTAs of a cluster that share one group of 32 tokens, each taking 1/SPLIT of the
+// K chunks (small batches: the K loop is a latency chain and there are SMs to spare); the
+// partial logits meet in the first CTA through distributed shared memory, added in rank
+// order, and the first CTA selects.
+template <int NT, int SPLIT>
 __global__ void __launch_bounds__(kRtThreads)
 router_topk_kernel(const __grid_constant__ CUtensorMap tmap_t,
                    const __grid_constant__ CUtensorMap tmap_w, const bf16 *__restrict__ t,
@@ -119,8 +123,10 @@ router_topk_kernel(const __grid_constant__ CUtensorMap tmap_t,
   float *lg = reinterpret_cast<float *>(smem + kRtStages * kStageBytes + 256);  // [32][EPAD]
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int tok0 = blockIdx.x * kRtTokens;
-  const int nk = (H + kRtKC - 1) / kRtKC;
+  const int crank = SPLIT > 1 ? static_cast<int>(blockIdx.x % SPLIT) : 0;  // rank in the cluster
+  const int tok0 = static_cast<int>(blockIdx.x / SPLIT) * kRtTokens;
+  const int nk_all = (H + kRtKC - 1) / kRtKC;
+  const int kc_lo = crank * nk_all / SPLIT, kc_hi = (crank + 1) * nk_all / SPLIT;
 
   if (tid == 0) {
     for (int s = 0; s < kRtStages; s++) {
@@ -147,7 +153,7 @@ router_topk_kernel(const __grid_constant__ CUtensorMap tmap_t,
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      for (int kc = 0; kc < nk; kc++) {
+      for (int kc = kc_lo; kc < kc_hi; kc++) {
         if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
           set_status(status, kStatusWaitTimeoutProducer);
           *abort_flag = 1;
@@ -166,7 +172,7 @@ router_topk_kernel(const __grid_constant__ CUtensorMap tmap_t,
   } else {
     int stage = 0;
     uint32_t phase = 0;
-    for (int kc = 0; kc < nk; kc++) {
+    for (int kc = kc_lo; kc < kc_hi; kc++) {
       if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
         set_status(status, kStatusWaitTimeoutMma);
         *abort_flag = 1;
@@ -204,20 +210,44 @@ router_topk_kernel(const __grid_constant__ CUtensorMap tmap_t,
       }
     }
   }
+  // accumulators -> shared logits [32][EPAD]
+  if (warp < kRtComputeWarps) {
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+      const int col = (sl * NT + nt) * 8 + (lane & 3) * 2;
+      const int r0 = tg * 16 + (lane >> 2);
+      lg[r0 * EPAD + col] = acc[nt][0];
+      lg[r0 * EPAD + col + 1] = acc[nt][1];
+      lg[(r0 + 8) * EPAD + col] = acc[nt][2];
+      lg[(r0 + 8) * EPAD + col + 1] = acc[nt][3];
+    }
+  }
+  if constexpr (SPLIT > 1) {
+    // every CTA's partial logits are in its shared memory; the first CTA adds the others'
+    // in rank order, then everybody may leave
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (crank == 0) {
+      const uint32_t lg_s = smem_u32(lg);
+      for (int i = tid; i < kRtTokens * EPAD; i += kRtThreads) {
+        float v = lg[i];
+#pragma unroll
+        for (int r = 1; r < SPLIT; r++) {
+          uint32_t remote;
+          float pv;
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(lg_s + 4 * i), "r"(r));
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pv) : "r"(remote) : "memory");
+          v += pv;
+        }
+        lg[i] = v;
+      }
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (crank != 0) return;
+  }
   __syncthreads();
   if (warp == kRtComputeWarps) return;  // the producer warp takes no part in the selection
-
-  // accumulators -> shared logits [32][EPAD]
-#pragma unroll
-  for (int nt = 0; nt < NT; nt++) {
-    const int col = (sl * NT + nt) * 8 + (lane & 3) * 2;
-    const int r0 = tg * 16 + (lane >> 2);
-    lg[r0 * EPAD + col] = acc[nt][0];
-    lg[r0 * EPAD + col + 1] = acc[nt][1];
-    lg[(r0 + 8) * EPAD + col] = acc[nt][2];
-    lg[(r0 + 8) * EPAD + col + 1] = acc[nt][3];
-  }
-  asm volatile("bar.sync 1, %0;" ::"n"(kRtComputeWarps * 32) : "memory");
 
   // selection: warp w owns tokens w*4 .. w*4+3 of the CTA
   const int rounds_sel = K;
@@ -329,17 +359,45 @@ router_topk_kernel(const __grid_constant__ CUtensorMap tmap_t,
   }
 }
 
-template <int NT>
-static cudaError_t launch_router_nt(const bf16 *t, const bf16 *w_router, const float *b_router,
-                                    const int *pos, int T, int H, int E, int K, int *topk_i,
-                                    float *topk_v, float *logits_opt, int exact_ties, int *status,
-                                    cudaStream_t stream) {
+template <int NT, int SPLIT>
+static cudaError_t launch_router_split(const CUtensorMap &tmap_t, const CUtensorMap &tmap_w,
+                                       const bf16 *t, const bf16 *w_router, const float *b_router,
+                                       const int *pos, int T, int H, int E, int K, int *topk_i,
+                                       float *topk_v, float *logits_opt, int exact_ties,
+                                       int *status, cudaStream_t stream) {
   constexpr int EPAD = 32 * NT;
   constexpr int kRtStages = RtStages<NT>::value;
   // alignment slack + ring + barriers + logits
   const size_t smem = 1024 + static_cast<size_t>(kRtStages) * (kRtTokens + EPAD) * kRtRowBytes +
                       256 + kRtTokens * EPAD * 4;
   static_assert(2 * RtStages<NT>::value * 8 + 4 <= 256, "barrier area");
+  cudaError_t e = cudaFuncSetAttribute(router_topk_kernel<NT, SPLIT>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  const int groups = (T + kRtTokens - 1) / kRtTokens;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(groups * SPLIT));
+  cfg.blockDim = dim3(kRtThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = SPLIT;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = SPLIT > 1 ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, router_topk_kernel<NT, SPLIT>, tmap_t, tmap_w, t, w_router,
+                            b_router, pos, T, H, E, K, topk_i, topk_v, logits_opt, exact_ties,
+                            status);
+}
+
+template <int NT>
+static cudaError_t launch_router_nt(const bf16 *t, const bf16 *w_router, const float *b_router,
+                                    const int *pos, int T, int H, int E, int K, int *topk_i,
+                                    float *topk_v, float *logits_opt, int exact_ties, int *status,
+                                    cudaStream_t stream) {
+  constexpr int EPAD = 32 * NT;
   // tiles of one 64-element K chunk: 32 token rows, EPAD expert rows (rows that do not
   // exist read as zeros)
   CUtensorMap tmap_t, tmap_w;
@@ -347,14 +405,19 @@ static cudaError_t launch_router_nt(const bf16 *t, const bf16 *w_router, const f
   if (make_tmap_2d_bf16(&tmap_t, t, H, T, kRtKC, kRtTokens, &err) ||
       make_tmap_2d_bf16(&tmap_w, w_router, H, E, kRtKC, EPAD, &err))
     return cudaErrorInvalidValue;
-  cudaError_t e = cudaFuncSetAttribute(router_topk_kernel<NT>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return e;
-  const int grid = (T + kRtTokens - 1) / kRtTokens;
-  router_topk_kernel<NT><<<grid, kRtThreads, smem, stream>>>(tmap_t, tmap_w, t, w_router, b_router,
-                                                             pos, T, H, E, K, topk_i, topk_v,
-                                                             logits_opt, exact_ties, status);
-  return cudaGetLastError();
+  // few token groups (decode batches): four CTAs per group split the K loop
+  static int num_sms = 0;
+  if (!num_sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const int groups = (T + kRtTokens - 1) / kRtTokens;
+  if (groups * 4 <= num_sms && H >= 16 * kRtKC)
+    return launch_router_split<NT, 4>(tmap_t, tmap_w, t, w_router, b_router, pos, T, H, E, K,
+                                      topk_i, topk_v, logits_opt, exact_ties, status, stream);
+  return launch_router_split<NT, 1>(tmap_t, tmap_w, t, w_router, b_router, pos, T, H, E, K,
+                                    topk_i, topk_v, logits_opt, exact_ties, status, stream);
 }
 
 cudaError_t launch_router_topk(const bf16 *t, const bf16 *w_router, const float *b_router,

@@ -59,6 +59,8 @@ EDGE_CASES = [
     (64, 128, 64, 16, 1, 0),     # top-1
     (64, 128, 64, 16, 8, 5),     # top-8
     (300, 2880, 2880, 8, 4, 0),  # the real hidden sizes: 45 K steps, 24 / 12 N tiles
+    (70, 2880, 64, 128, 4, 9),   # decode-sized batch, 128 experts: the router splits K over a cluster
+    (33, 1024, 64, 64, 4, 0),    # the shortest hidden size that does
 ]
 
 
