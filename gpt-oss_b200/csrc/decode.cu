@@ -6,10 +6,11 @@
 //   embed_rows_kernel                    x = E[token]                      (run.cpp:550-552)
 //   per layer:
 //     rmsnorm_rows_kernel                t = rmsnorm(x) * w                (run.cpp:556)
-//     cuBLAS GEMM                        qkv = t Wqkv^T                    (run.cpp:568)
-//     qkv_rope_cache_kernel              + bias, rotate q and k, append k,v (run.cpp:571-596)
+//     grouped_gemm_pair_kernel<down>     qkv = t Wqkv^T + bias (one group) (run.cpp:568-574)
+//     qkv_rope_cache_kernel              rotate q and k, append k,v        (run.cpp:575-596)
 //     attn_decode_kernel                 softmax(qK/sqrt(D) | sink) V      (run.cpp:601-647)
-//     cuBLAS GEMM + bias_residual_kernel x += o Wo^T + b_o                 (run.cpp:649-661)
+//     grouped_gemm_pair_kernel<down> + bias_residual_kernel
+//                                        x += o Wo^T + b_o                 (run.cpp:649-661)
 //     rmsnorm_rows_kernel, gptoss_moe_forward                              (run.cpp:664-750)
 //   rmsnorm_rows_kernel, cuBLAS GEMM     logits = rmsnorm(x) Wout^T        (run.cpp:752-757)
 //   argmax_rows_kernel                   next = argmax (lowest index on ties)
@@ -28,6 +29,7 @@
 #include "../../include/gptoss_decode_b200.h"
 #include "common.cuh"
 #include "engine.h"
+#include "gemm_epilogue.cuh"
 
 namespace gptoss {
 
@@ -89,8 +91,11 @@ embed_rows_kernel(bf16 *__restrict__ x, const bf16 *__restrict__ table,
 // (apply_rotary_emb, run.cpp:511-533: pairs (i, i + D/2), cos/sin of pos * inv_freq[i]
 // times the YaRN concentration); q stays fp32, k and v go to the row's cache slot at
 // position pos as bf16.  One CTA per row.
+// QKV_BF: the projection comes from this library's GEMM as bf16 with the bias already
+// added; otherwise fp32 from cuBLAS and the bias is added here.
+template <bool QKV_BF>
 __global__ void __launch_bounds__(256)
-qkv_rope_cache_kernel(const float *__restrict__ qkv, const float *__restrict__ bias,
+qkv_rope_cache_kernel(const void *__restrict__ qkv_any, const float *__restrict__ bias,
                       const int *__restrict__ pos, const float *__restrict__ inv_freq,
                       float concentration, float *__restrict__ q_out, bf16 *__restrict__ k_cache,
                       bf16 *__restrict__ v_cache, int B, int Hq, int Hkv, int D, int S) {
@@ -99,13 +104,17 @@ qkv_rope_cache_kernel(const float *__restrict__ qkv, const float *__restrict__ b
   if (p < 0) return;
   const int half = D >> 1;
   const int dq = Hq * D, dkv = Hkv * D, ld = dq + 2 * dkv;
-  const float *src = qkv + static_cast<size_t>(row) * ld;
+  auto val = [&](int i) -> float {
+    if (QKV_BF)
+      return __bfloat162float(static_cast<const bf16 *>(qkv_any)[static_cast<size_t>(row) * ld + i]);
+    return static_cast<const float *>(qkv_any)[static_cast<size_t>(row) * ld + i] + bias[i];
+  };
   // rotated pairs of q and k
   for (int i = threadIdx.x; i < (Hq + Hkv) * half; i += blockDim.x) {
     const int head = i / half, j = i - head * half;
     const int base = head * D;  // q heads first, then k heads: contiguous in qkv
-    const float x1 = src[base + j] + bias[base + j];
-    const float x2 = src[base + half + j] + bias[base + half + j];
+    const float x1 = val(base + j);
+    const float x2 = val(base + half + j);
     const float ang = static_cast<float>(p) * inv_freq[j];
     const float c = cosf(ang) * concentration, s = sinf(ang) * concentration;
     const float o1 = x1 * c - x2 * s, o2 = x2 * c + x1 * s;
@@ -121,7 +130,7 @@ qkv_rope_cache_kernel(const float *__restrict__ qkv, const float *__restrict__ b
   }
   for (int i = threadIdx.x; i < dkv; i += blockDim.x) {
     bf16 *dst = v_cache + (static_cast<size_t>(row) * S + p) * dkv;
-    dst[i] = __float2bfloat16_rn(src[dq + dkv + i] + bias[dq + dkv + i]);
+    dst[i] = __float2bfloat16_rn(val(dq + dkv + i));
   }
 }
 
@@ -316,15 +325,19 @@ attn_decode_kernel(const float *__restrict__ q, const bf16 *__restrict__ k_cache
   }
 }
 
-// x[row] = bf16(x[row] + proj[row] + bias) for active rows.
+// x[row] = bf16(x[row] + proj[row] + bias) for active rows (PROJ_BF: proj is bf16 with
+// the bias already added).
+template <bool PROJ_BF>
 __global__ void __launch_bounds__(256)
-bias_residual_kernel(bf16 *__restrict__ x, const float *__restrict__ proj,
+bias_residual_kernel(bf16 *__restrict__ x, const void *__restrict__ proj,
                      const float *__restrict__ bias, const int *__restrict__ pos, int B, int H) {
   const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= static_cast<size_t>(B) * H) return;
   const int row = static_cast<int>(i / H), c = static_cast<int>(i - static_cast<size_t>(row) * H);
   if (pos[row] < 0) return;
-  x[i] = __float2bfloat16_rn(__bfloat162float(x[i]) + proj[i] + bias[c]);
+  const float pv = PROJ_BF ? __bfloat162float(static_cast<const bf16 *>(proj)[i])
+                           : static_cast<const float *>(proj)[i] + bias[c];
+  x[i] = __float2bfloat16_rn(__bfloat162float(x[i]) + pv);
 }
 
 // next[row] = index of the largest logit, lowest index among equals; -1 on inactive rows.
@@ -406,6 +419,15 @@ struct gptoss_decode {
   float *qkv = nullptr, *q = nullptr, *proj = nullptr, *logits = nullptr;
   int *d_tokens = nullptr, *d_pos = nullptr, *d_next = nullptr, *status = nullptr;
   int *h_pinned = nullptr;  // tokens | pos | next, max_batch each
+  // QKV and output projections on this library's tcgen05 kernel (one "expert" = all rows)
+  bool own_gemm = true;
+  int num_sms = 0, sched_B = -1, sched_cap = 0;
+  int *lin_sched = nullptr;     // device: expert ids | first rows | row counts | tile count
+  float *ones = nullptr;        // [max_batch] row weights of a plain linear layer
+  bf16 *qkv_bf = nullptr, *proj_bf = nullptr;
+  std::vector<CUtensorMap> tm_wqkv, tm_wo;  // per layer, boxes of 128 weight rows
+  CUtensorMap tm_t[3], tm_attn[3];          // activations in boxes of 128 / 32 / 8 rows
+  bool maps_ready = false;
   std::string err;
 };
 
@@ -500,7 +522,8 @@ int gptoss_decode_destroy(gptoss_decode_t *h) {
   cudaFree(h->b_o); cudaFree(h->sinks); cudaFree(h->inv_freq); cudaFree(h->x); cudaFree(h->t);
   cudaFree(h->attn); cudaFree(h->k_cache); cudaFree(h->v_cache); cudaFree(h->qkv); cudaFree(h->q);
   cudaFree(h->proj); cudaFree(h->logits); cudaFree(h->d_tokens); cudaFree(h->d_pos);
-  cudaFree(h->d_next); cudaFree(h->status);
+  cudaFree(h->d_next); cudaFree(h->status); cudaFree(h->lin_sched); cudaFree(h->ones);
+  cudaFree(h->qkv_bf); cudaFree(h->proj_bf);
   if (h->h_pinned) cudaFreeHost(h->h_pinned);
   delete h;
   return GPTOSS_OK;
@@ -570,10 +593,21 @@ int gptoss_decode_create_ep(const gptoss_model_config_t *cfg, int max_batch, int
   A(dalloc(&h->logits, B * V));
   A(dalloc(&h->d_tokens, B)); A(dalloc(&h->d_pos, B)); A(dalloc(&h->d_next, B));
   A(dalloc(&h->status, 1));
+  h->sched_cap = (max_batch + 255) / 256 + 1;
+  A(dalloc(&h->lin_sched, 3 * static_cast<size_t>(h->sched_cap) + 1));
+  A(dalloc(&h->ones, B));
+  A(dalloc(&h->qkv_bf, B * (dq + 2 * dkv)));
+  A(dalloc(&h->proj_bf, B * H));
+  A(cudaDeviceGetAttribute(&h->num_sms, cudaDevAttrMultiProcessorCount, device));
   A(cudaMallocHost(reinterpret_cast<void **>(&h->h_pinned), 3 * B * sizeof(int)));
   if (e == cudaSuccess) e = cudaMemset(h->status, 0, sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(h->x, 0, B * H * sizeof(bf16));
   if (e != cudaSuccess) return bail(GPTOSS_E_CUDA, std::string("allocation: ") + cudaGetErrorString(e));
+  {
+    std::vector<float> one(B, 1.0f);
+    e = cudaMemcpy(h->ones, one.data(), B * sizeof(float), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return bail(GPTOSS_E_CUDA, cudaGetErrorString(e));
+  }
   std::vector<float> inv;
   rope_tables(c, &inv, &h->concentration);
   e = cudaMemcpy(h->inv_freq, inv.data(), inv.size() * 4, cudaMemcpyHostToDevice);
@@ -735,6 +769,70 @@ static int gemm_xwt(gptoss_decode *h, const bf16 *x, const bf16 *w, float *c, in
   return GPTOSS_OK;
 }
 
+// Tensor maps of the projections (weights per layer, the two activation buffers).
+static int build_linear_maps(gptoss_decode *h) {
+  const gptoss_model_config_t &c = h->cfg;
+  const uint64_t H = c.hidden_dim, D = c.head_dim, dq = c.n_attn_heads * D;
+  const uint64_t dqkv = dq + 2 * c.n_kv_heads * D;
+  std::string err;
+  h->tm_wqkv.resize(c.n_layers);
+  h->tm_wo.resize(c.n_layers);
+  int rc = 0;
+  for (int l = 0; l < c.n_layers && !rc; l++) {
+    rc = make_tmap_2d_bf16(&h->tm_wqkv[l], h->w_qkv + l * dqkv * H, H, dqkv, kTileK, 128, &err) ||
+         make_tmap_2d_bf16(&h->tm_wo[l], h->w_o + l * H * dq, dq, H, kTileK, 128, &err);
+  }
+  const uint32_t boxes[3] = {128, 32, 8};
+  for (int i = 0; i < 3 && !rc; i++) {
+    rc = make_tmap_2d_bf16(&h->tm_t[i], h->t, H, h->max_batch, kTileK, boxes[i], &err) ||
+         make_tmap_2d_bf16(&h->tm_attn[i], h->attn, dq, h->max_batch, kTileK, boxes[i], &err);
+  }
+  if (rc) return dfail(h, GPTOSS_E_CUDA, "tensor maps of the projections: %s", err.c_str());
+  h->maps_ready = true;
+  return GPTOSS_OK;
+}
+
+// Tile schedule of a plain linear layer over B rows: ceil(B / 256) tiles of equal size
+// (a multiple of 16), all of "expert" 0.
+static int build_linear_schedule(gptoss_decode *h, int B, cudaStream_t st) {
+  const int cap = h->sched_cap;
+  std::vector<int> sched(3 * cap + 1, 0);
+  const int cnt = (B + 255) / 256;
+  const int step = (((B + cnt - 1) / cnt) + 15) & ~15;
+  int n = 0;
+  for (int r = 0; r < B && n < cap; r += step, n++) {
+    sched[cap + n] = r;
+    sched[2 * cap + n] = std::min(step, B - r);
+  }
+  sched[3 * cap] = n;
+  DCK(h, cudaMemcpyAsync(h->lin_sched, sched.data(), sched.size() * sizeof(int),
+                         cudaMemcpyHostToDevice, st));
+  DCK(h, cudaStreamSynchronize(st));  // the host vector goes out of scope
+  h->sched_B = B;
+  return GPTOSS_OK;
+}
+
+// out[B, N] (bf16) = x[B, K] . W[N, K]^T + bias on the CTA-pair tcgen05 kernel
+static int linear_own(gptoss_decode *h, const CUtensorMap &tw, const CUtensorMap *tx,
+                      const float *bias, bf16 *out, int N, int K, cudaStream_t st) {
+  GemmArgs g;
+  g.bias = bias;
+  g.out = out;
+  g.row_weight = h->ones;
+  g.mtile_expert = h->lin_sched;
+  g.mtile_row0 = h->lin_sched + h->sched_cap;
+  g.mtile_rows = h->lin_sched + 2 * h->sched_cap;
+  g.num_mtiles = h->lin_sched + 3 * h->sched_cap;
+  g.k_dim = K;
+  g.n_cols = N;
+  g.out_ld = N;
+  g.limit = 0.f;
+  g.status = h->status;
+  g.skip_epilogue = 0;
+  DCK(h, launch_linear_pair(h->num_sms, tw, tx, g, st, nullptr));
+  return GPTOSS_OK;
+}
+
 int gptoss_decode_step(gptoss_decode_t *h, const int *tokens, const int *pos, int B, int *next,
                        void *stream) {
   if (!h || !tokens || !pos || !next) return GPTOSS_E_INVALID;
@@ -759,16 +857,30 @@ int gptoss_decode_step(gptoss_decode_t *h, const int *tokens, const int *pos, in
                                                                    h->d_pos, B, H, V, h->status);
   DCK(h, cudaGetLastError());
   int rc;
+  // the tcgen05 kernel writes whole 16-byte segments: row lengths must be multiples of 8
+  const bool own = h->own_gemm && ((dq + 2 * dkv) % 8 == 0) && (dq % 8 == 0);
+  if (own) {
+    if (!h->maps_ready && (rc = build_linear_maps(h))) return rc;
+    if (h->sched_B != B && (rc = build_linear_schedule(h, B, st))) return rc;
+  }
   for (int l = 0; l < c.n_layers; l++) {
     DCK(h, launch_rmsnorm(h->t, h->x, h->rms_attn + static_cast<size_t>(l) * H, h->d_pos, B, H, st, nullptr));
-    if ((rc = gemm_xwt(h, h->t, h->w_qkv + static_cast<size_t>(l) * (dq + 2 * dkv) * H, h->qkv, B,
-                       dq + 2 * dkv, H)))
-      return rc;
+    if (own)
+      rc = linear_own(h, h->tm_wqkv[l], h->tm_t, h->b_qkv + static_cast<size_t>(l) * (dq + 2 * dkv),
+                      h->qkv_bf, dq + 2 * dkv, H, st);
+    else
+      rc = gemm_xwt(h, h->t, h->w_qkv + static_cast<size_t>(l) * (dq + 2 * dkv) * H, h->qkv, B,
+                    dq + 2 * dkv, H);
+    if (rc) return rc;
     bf16 *kc = h->k_cache + static_cast<size_t>(l) * h->max_batch * S * dkv;
     bf16 *vc = h->v_cache + static_cast<size_t>(l) * h->max_batch * S * dkv;
-    qkv_rope_cache_kernel<<<B, 256, 0, st>>>(h->qkv, h->b_qkv + static_cast<size_t>(l) * (dq + 2 * dkv),
-                                             h->d_pos, h->inv_freq, h->concentration, h->q, kc, vc,
-                                             B, Hq, Hkv, D, S);
+    if (own)
+      qkv_rope_cache_kernel<true><<<B, 256, 0, st>>>(h->qkv_bf, nullptr, h->d_pos, h->inv_freq,
+                                                     h->concentration, h->q, kc, vc, B, Hq, Hkv, D, S);
+    else
+      qkv_rope_cache_kernel<false><<<B, 256, 0, st>>>(
+          h->qkv, h->b_qkv + static_cast<size_t>(l) * (dq + 2 * dkv), h->d_pos, h->inv_freq,
+          h->concentration, h->q, kc, vc, B, Hq, Hkv, D, S);
     DCK(h, cudaGetLastError());
     // sliding window on even layers (run.cpp:619)
     const int window = (c.sliding_window > 0 && (l % 2 == 0)) ? c.sliding_window : 0;
@@ -782,10 +894,19 @@ int gptoss_decode_step(gptoss_decode_t *h, const int *tokens, const int *pos, in
     else
       attn_decode_kernel<128><<<grid, threads, 0, st>>>(h->q, kc, vc, sinks, h->d_pos, h->attn, B, Hq, Hkv, S, window);
     DCK(h, cudaGetLastError());
-    if ((rc = gemm_xwt(h, h->attn, h->w_o + static_cast<size_t>(l) * H * dq, h->proj, B, H, dq))) return rc;
     const size_t n = static_cast<size_t>(B) * H;
-    bias_residual_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(
-        h->x, h->proj, h->b_o + static_cast<size_t>(l) * H, h->d_pos, B, H);
+    if (own) {
+      if ((rc = linear_own(h, h->tm_wo[l], h->tm_attn, h->b_o + static_cast<size_t>(l) * H,
+                           h->proj_bf, H, dq, st)))
+        return rc;
+      bias_residual_kernel<true><<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(
+          h->x, h->proj_bf, nullptr, h->d_pos, B, H);
+    } else {
+      if ((rc = gemm_xwt(h, h->attn, h->w_o + static_cast<size_t>(l) * H * dq, h->proj, B, H, dq)))
+        return rc;
+      bias_residual_kernel<false><<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(
+          h->x, h->proj, h->b_o + static_cast<size_t>(l) * H, h->d_pos, B, H);
+    }
     DCK(h, cudaGetLastError());
     DCK(h, launch_rmsnorm(h->t, h->x, h->rms_ffn + static_cast<size_t>(l) * H, h->d_pos, B, H, st, nullptr));
     rc = gptoss_moe_forward(h->moe, l, h->t, h->x, h->d_pos, B, st);

@@ -175,6 +175,9 @@ int gemm_tile_n(int which);  // N extent of one tile: 0 = gate_up, 1 = down
 // grouped_gemm_pair.cu
 cudaError_t launch_gate_up_pair(gptoss_moe *h, int layer, cudaStream_t stream, int part = 0);
 cudaError_t launch_down_pair(gptoss_moe *h, int layer, cudaStream_t stream);
+struct GemmArgs;
+cudaError_t launch_linear_pair(int num_sms, const CUtensorMap &tw, const CUtensorMap *tx,
+                               const GemmArgs &g, cudaStream_t stream, long long *launches);
 
 // moe_api.cu: error text for entry points that take no handle (read back with
 // gptoss_moe_last_error(NULL)); returns `code`

@@ -473,7 +473,8 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
 }
 
 template <int EPI, int STAGES, bool MX, int TOKB, int RAWS, int LUTREP>
-static cudaError_t launch_pair_stages(gptoss_moe *h, const CUtensorMap &tw, const CUtensorMap *tx,
+static cudaError_t launch_pair_stages(int num_sms, long long *launches, const CUtensorMap &tw,
+                                      const CUtensorMap *tx,
                                       const GemmArgs &g, cudaStream_t stream) {
   const size_t smem = 1024 + STAGES * (kPairOperandBytes + TOKB * kTileK * 2) + kPairBarrierBytes +
                       PairStage<EPI>::kTotalBytes +
@@ -482,7 +483,7 @@ static cudaError_t launch_pair_stages(gptoss_moe *h, const CUtensorMap &tw, cons
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(h->num_sms & ~1));
+  cfg.gridDim = dim3(static_cast<unsigned>(num_sms & ~1));
   cfg.blockDim = dim3(kPairThreads + (MX ? (kDequantWarps + 1) * 32 : 0));
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -493,7 +494,7 @@ static cudaError_t launch_pair_stages(gptoss_moe *h, const CUtensorMap &tw, cons
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  h->launches++;
+  if (launches) ++*launches;
   return cudaLaunchKernelEx(&cfg, grouped_gemm_pair_kernel<EPI, STAGES, MX, TOKB, RAWS, LUTREP>, tw, tx[0], tx[1], tx[2],
                             g);
 }
@@ -512,13 +513,13 @@ static cudaError_t launch_pair(gptoss_moe *h, const CUtensorMap &tw, const CUten
 #endif
     if (h->cur_tile_rows == 64)
       return launch_pair_stages<EPI, GPTOSS_NARROW_STAGES, true, 32, GPTOSS_NARROW_RAW,
-                                GPTOSS_NARROW_LUTREP>(h, tx[0], tx, g, stream);
-    return launch_pair_stages<EPI, 4, true, 128, 12, 1>(h, tx[0], tx, g, stream);
+                                GPTOSS_NARROW_LUTREP>(h->num_sms, &h->launches, tx[0], tx, g, stream);
+    return launch_pair_stages<EPI, 4, true, 128, 12, 1>(h->num_sms, &h->launches, tx[0], tx, g, stream);
   }
   switch (h->opt_pair_stages) {
-    case 4: return launch_pair_stages<EPI, 4, false, 128, 0, 1>(h, tw, tx, g, stream);
-    case 5: return launch_pair_stages<EPI, 5, false, 128, 0, 1>(h, tw, tx, g, stream);
-    default: return launch_pair_stages<EPI, 6, false, 128, 0, 1>(h, tw, tx, g, stream);
+    case 4: return launch_pair_stages<EPI, 4, false, 128, 0, 1>(h->num_sms, &h->launches, tw, tx, g, stream);
+    case 5: return launch_pair_stages<EPI, 5, false, 128, 0, 1>(h->num_sms, &h->launches, tw, tx, g, stream);
+    default: return launch_pair_stages<EPI, 6, false, 128, 0, 1>(h->num_sms, &h->launches, tw, tx, g, stream);
   }
 }
 
@@ -548,6 +549,15 @@ cudaError_t launch_gate_up_pair(gptoss_moe *h, int layer, cudaStream_t stream, i
   g.tile_part = part;
   g.tile_split = h->mtile_split;
   return launch_pair<kEpiSwiglu>(h, lw.tmap_w1_rows, tx, g, stream);
+}
+
+// A plain linear layer out[r, :] = (x[r, :] . W^T + bias) * row_weight[r] on the same kernel:
+// one "expert" whose rows are all the rows of x, schedule and tensor maps supplied by the
+// caller (tw: W [n_cols, k] in boxes of 128 rows; tx: x [rows, k] in boxes of 128, 32 and 8
+// rows).
+cudaError_t launch_linear_pair(int num_sms, const CUtensorMap &tw, const CUtensorMap *tx,
+                               const GemmArgs &g, cudaStream_t stream, long long *launches) {
+  return launch_pair_stages<kEpiDown, 6, false, 128, 0, 1>(num_sms, launches, tw, tx, g, stream);
 }
 
 cudaError_t launch_down_pair(gptoss_moe *h, int layer, cudaStream_t stream) {

@@ -10,12 +10,13 @@
  * (getp-csrc/getp_run.cpp:501-894) and computes what forward() computes for one
  * sequence (run.cpp:536-766), for every row of the batch.
  *
- * The dense projections (QKV, attention output, logits) are plain GEMMs and go
- * through cuBLAS (bf16 operands, fp32 accumulate and output), loaded with dlopen
- * at gptoss_decode_create.  Everything else is this library's own kernels.
- * Activations between kernels: the residual stream and the normalised rows are
- * bf16 (the MoE block's interface), q, the attention logits and the projection
- * outputs fp32, the KV cache bf16.
+ * The QKV and attention-output projections run on the library's tcgen05 CTA-pair
+ * kernel (the grouped GEMM of the MoE block with one group: bias in the epilogue,
+ * bf16 output); the logits, which the argmax needs in fp32, are a plain GEMM through
+ * cuBLAS (bf16 operands, fp32 accumulate and output), loaded with dlopen at
+ * gptoss_decode_create, as is the fallback for projections whose row length is not
+ * a multiple of 8.  Activations between kernels: the residual stream, the normalised
+ * rows and the projection outputs are bf16, q and the logits fp32, the KV cache bf16.
  */
 #ifndef GPTOSS_DECODE_B200_H
 #define GPTOSS_DECODE_B200_H
