@@ -12,7 +12,8 @@
 //     grouped_gemm_pair_kernel<down> + bias_residual_kernel
 //                                        x += o Wo^T + b_o                 (run.cpp:649-661)
 //     rmsnorm_rows_kernel, gptoss_moe_forward                              (run.cpp:664-750)
-//   rmsnorm_rows_kernel, cuBLAS GEMM     logits = rmsnorm(x) Wout^T        (run.cpp:752-757)
+//   rmsnorm_rows_kernel, grouped_gemm_pair_kernel<f32>
+//                                        logits = rmsnorm(x) Wout^T        (run.cpp:752-757)
 //   argmax_rows_kernel                   next = argmax (lowest index on ties)
 // Rows with pos < 0 are skipped by every kernel (the GEMMs compute them and the
 // results are ignored).
@@ -426,6 +427,7 @@ struct gptoss_decode {
   float *ones = nullptr;        // [max_batch] row weights of a plain linear layer
   bf16 *qkv_bf = nullptr, *proj_bf = nullptr;
   std::vector<CUtensorMap> tm_wqkv, tm_wo;  // per layer, boxes of 128 weight rows
+  CUtensorMap tm_unemb;                     // the unembedding, boxes of 128 rows
   CUtensorMap tm_t[3], tm_attn[3];          // activations in boxes of 128 / 32 / 8 rows
   bool maps_ready = false;
   std::string err;
@@ -576,8 +578,6 @@ int gptoss_decode_create_ep(const gptoss_model_config_t *cfg, int max_batch, int
     return code;
   };
   std::string err;
-  if (!load_cublas(&err)) return bail(GPTOSS_E_STATE, err);
-  if (g_blas.Create(&h->blas) != CUBLAS_STATUS_SUCCESS) return bail(GPTOSS_E_CUDA, "cublasCreate failed");
   const size_t V = c.vocab_size, H = c.hidden_dim, L = c.n_layers, D = c.head_dim;
   const size_t dq = c.n_attn_heads * D, dkv = c.n_kv_heads * D, B = max_batch, S = c.seq_len;
   cudaError_t e = cudaSuccess;
@@ -760,7 +760,14 @@ int gptoss_decode_load_bin(gptoss_decode_t *h, const float *p) {
 }
 
 // C[B, N] (fp32) = X[B, K] (bf16) . W[N, K]^T (bf16)
-static int gemm_xwt(gptoss_decode *h, const bf16 *x, const bf16 *w, float *c, int B, int N, int K) {
+static int gemm_xwt(gptoss_decode *h, const bf16 *x, const bf16 *w, float *c, int B, int N, int K,
+                    cudaStream_t st) {
+  if (!h->blas) {  // only shapes the library's own kernel does not take come here
+    std::string err;
+    if (!load_cublas(&err)) return dfail(h, GPTOSS_E_STATE, "%s", err.c_str());
+    if (g_blas.Create(&h->blas) != CUBLAS_STATUS_SUCCESS) return dfail(h, GPTOSS_E_CUDA, "cublasCreate failed");
+  }
+  if (g_blas.SetStream(h->blas, st) != CUBLAS_STATUS_SUCCESS) return dfail(h, GPTOSS_E_CUDA, "cublasSetStream failed");
   const float one = 1.f, zero = 0.f;
   cublasStatus_t s = g_blas.GemmEx(h->blas, CUBLAS_OP_T, CUBLAS_OP_N, N, B, K, &one, w,
                                    CUDA_R_16BF, K, x, CUDA_R_16BF, K, &zero, c, CUDA_R_32F, N,
@@ -782,6 +789,7 @@ static int build_linear_maps(gptoss_decode *h) {
     rc = make_tmap_2d_bf16(&h->tm_wqkv[l], h->w_qkv + l * dqkv * H, H, dqkv, kTileK, 128, &err) ||
          make_tmap_2d_bf16(&h->tm_wo[l], h->w_o + l * H * dq, dq, H, kTileK, 128, &err);
   }
+  if (!rc) rc = make_tmap_2d_bf16(&h->tm_unemb, h->unemb, H, c.vocab_size, kTileK, 128, &err);
   const uint32_t boxes[3] = {128, 32, 8};
   for (int i = 0; i < 3 && !rc; i++) {
     rc = make_tmap_2d_bf16(&h->tm_t[i], h->t, H, h->max_batch, kTileK, boxes[i], &err) ||
@@ -814,10 +822,11 @@ static int build_linear_schedule(gptoss_decode *h, int B, cudaStream_t st) {
 
 // out[B, N] (bf16) = x[B, K] . W[N, K]^T + bias on the CTA-pair tcgen05 kernel
 static int linear_own(gptoss_decode *h, const CUtensorMap &tw, const CUtensorMap *tx,
-                      const float *bias, bf16 *out, int N, int K, cudaStream_t st) {
+                      const float *bias, void *out, int N, int K, cudaStream_t st,
+                      bool f32_out = false) {
   GemmArgs g;
   g.bias = bias;
-  g.out = out;
+  g.out = static_cast<bf16 *>(out);
   g.row_weight = h->ones;
   g.mtile_expert = h->lin_sched;
   g.mtile_row0 = h->lin_sched + h->sched_cap;
@@ -829,7 +838,7 @@ static int linear_own(gptoss_decode *h, const CUtensorMap &tw, const CUtensorMap
   g.limit = 0.f;
   g.status = h->status;
   g.skip_epilogue = 0;
-  DCK(h, launch_linear_pair(h->num_sms, tw, tx, g, st, nullptr));
+  DCK(h, launch_linear_pair(h->num_sms, tw, tx, g, st, nullptr, f32_out));
   return GPTOSS_OK;
 }
 
@@ -844,7 +853,6 @@ int gptoss_decode_step(gptoss_decode_t *h, const int *tokens, const int *pos, in
     if (pos[i] >= c.seq_len) return dfail(h, GPTOSS_E_CAPACITY, "row %d: position %d >= seq_len %d", i, pos[i], c.seq_len);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   DCK(h, cudaSetDevice(h->device));
-  if (g_blas.SetStream(h->blas, st) != CUBLAS_STATUS_SUCCESS) return dfail(h, GPTOSS_E_CUDA, "cublasSetStream failed");
   const int H = c.hidden_dim, D = c.head_dim, Hq = c.n_attn_heads, Hkv = c.n_kv_heads;
   const int dq = Hq * D, dkv = Hkv * D, S = c.seq_len, V = c.vocab_size;
   int *hp = h->h_pinned;
@@ -870,7 +878,7 @@ int gptoss_decode_step(gptoss_decode_t *h, const int *tokens, const int *pos, in
                       h->qkv_bf, dq + 2 * dkv, H, st);
     else
       rc = gemm_xwt(h, h->t, h->w_qkv + static_cast<size_t>(l) * (dq + 2 * dkv) * H, h->qkv, B,
-                    dq + 2 * dkv, H);
+                    dq + 2 * dkv, H, st);
     if (rc) return rc;
     bf16 *kc = h->k_cache + static_cast<size_t>(l) * h->max_batch * S * dkv;
     bf16 *vc = h->v_cache + static_cast<size_t>(l) * h->max_batch * S * dkv;
@@ -902,7 +910,7 @@ int gptoss_decode_step(gptoss_decode_t *h, const int *tokens, const int *pos, in
       bias_residual_kernel<true><<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(
           h->x, h->proj_bf, nullptr, h->d_pos, B, H);
     } else {
-      if ((rc = gemm_xwt(h, h->attn, h->w_o + static_cast<size_t>(l) * H * dq, h->proj, B, H, dq)))
+      if ((rc = gemm_xwt(h, h->attn, h->w_o + static_cast<size_t>(l) * H * dq, h->proj, B, H, dq, st)))
         return rc;
       bias_residual_kernel<false><<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(
           h->x, h->proj, h->b_o + static_cast<size_t>(l) * H, h->d_pos, B, H);
@@ -913,7 +921,12 @@ int gptoss_decode_step(gptoss_decode_t *h, const int *tokens, const int *pos, in
     if (rc) return dfail(h, rc, "MoE layer %d: %s", l, gptoss_moe_last_error(h->moe));
   }
   DCK(h, launch_rmsnorm(h->t, h->x, h->rms_out, h->d_pos, B, H, st, nullptr));
-  if ((rc = gemm_xwt(h, h->t, h->unemb, h->logits, B, V, H))) return rc;
+  // fp32 logits: own kernel when the rows of the logits are 16-byte multiples, else cuBLAS
+  if (own && V % 4 == 0)
+    rc = linear_own(h, h->tm_unemb, h->tm_t, nullptr, h->logits, V, H, st, /*f32_out=*/true);
+  else
+    rc = gemm_xwt(h, h->t, h->unemb, h->logits, B, V, H, st);
+  if (rc) return rc;
   argmax_rows_kernel<<<B, 256, 0, st>>>(h->logits, h->d_pos, h->d_next, V);
   DCK(h, cudaGetLastError());
   DCK(h, cudaMemcpyAsync(hp + 2 * h->max_batch, h->d_next, B * sizeof(int), cudaMemcpyDeviceToHost, st));

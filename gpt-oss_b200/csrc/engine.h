@@ -177,7 +177,8 @@ cudaError_t launch_gate_up_pair(gptoss_moe *h, int layer, cudaStream_t stream, i
 cudaError_t launch_down_pair(gptoss_moe *h, int layer, cudaStream_t stream);
 struct GemmArgs;
 cudaError_t launch_linear_pair(int num_sms, const CUtensorMap &tw, const CUtensorMap *tx,
-                               const GemmArgs &g, cudaStream_t stream, long long *launches);
+                               const GemmArgs &g, cudaStream_t stream, long long *launches,
+                               bool f32_out = false);
 
 // moe_api.cu: error text for entry points that take no handle (read back with
 // gptoss_moe_last_error(NULL)); returns `code`

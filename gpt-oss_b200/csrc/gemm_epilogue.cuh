@@ -13,7 +13,8 @@
 
 namespace gptoss {
 
-enum { kEpiSwiglu = 0, kEpiDown = 1 };
+// kEpiF32 (CTA-pair kernel only): out = acc (+ bias when given) as fp32, no row weight
+enum { kEpiSwiglu = 0, kEpiDown = 1, kEpiF32 = 2 };
 
 constexpr int kEpiPitch = 144;                  // 128 B of payload + 16 B: conflict-free
 constexpr int kEpiStageBytes = 32 * kEpiPitch;  // per warp

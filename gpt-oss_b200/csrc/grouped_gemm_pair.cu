@@ -48,7 +48,8 @@ constexpr int kAccColsPair = 256;  // TMEM columns per accumulator (up to 256 to
 
 template <int EPI>
 struct PairStage {
-  static constexpr int kRowBytes = (EPI == kEpiSwiglu) ? 128 : 256;  // per token, per CTA
+  // per token, per CTA: 64 activations, 128 bf16 outputs or 128 fp32 outputs
+  static constexpr int kRowBytes = (EPI == kEpiSwiglu) ? 128 : (EPI == kEpiF32 ? 512 : 256);
   // 16 bytes of padding keep the 2-byte writes of the SwiGLU epilogue off each
   // other's banks; the 256-byte rows of the down epilogue go unpadded so that six
   // operand stages still fit
@@ -370,8 +371,9 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
       const int ntok = g.mtile_rows[tt];
       const int n_cta = wp * 256 + static_cast<int>(rank) * 128;  // first weight row of this CTA
       const int n_lane = n_cta + q * 32 + lane;
-      const float bias_v =
-          n_lane < g.n_cols ? __ldg(g.bias + static_cast<size_t>(e) * g.n_cols + n_lane) : 0.f;
+      const float bias_v = (g.bias != nullptr && n_lane < g.n_cols)
+                               ? __ldg(g.bias + static_cast<size_t>(e) * g.n_cols + n_lane)
+                               : 0.f;
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) {
         set_status(g.status, kStatusWaitTimeoutEpilogue);
         *abort_flag = 1;
@@ -402,6 +404,12 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
               *reinterpret_cast<bf16 *>(tile_s + j * ST::kPitch + q * 32 + (lane >> 1) * 2) =
                   __float2bfloat16_rn(a);
             }
+          } else if (EPI == kEpiF32) {
+            // lane = output column, register j = token: rows of 128 fp32 per CTA
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+              *reinterpret_cast<float *>(tile_s + j * ST::kPitch + q * 128 + lane * 4) =
+                  __uint_as_float(r[j]) + bias_v;
           } else {
             const int jt = c * 32 + lane;
             const float w_lane = jt < ntok ? g.row_weight[tok0 + jt] : 0.f;
@@ -431,10 +439,13 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
           const int col0 = (EPI == kEpiSwiglu) ? (n_cta >> 1) : n_cta;
           if (tg < 32 && !(g.skip_epilogue & 2)) {
             const int jt = c * 32 + tg;
-            int bytes = (g.out_ld - col0) * 2;
+            constexpr int kOutElem = (EPI == kEpiF32) ? 4 : 2;  // bytes per output element
+            int bytes = (g.out_ld - col0) * kOutElem;
             bytes = bytes < ST::kRowBytes ? bytes : ST::kRowBytes;
             if (jt < ntok && bytes > 0) {
-              bf16 *dst = g.out + static_cast<size_t>(tok0 + jt) * g.out_ld + col0;
+              unsigned char *dst =
+                  reinterpret_cast<unsigned char *>(g.out) +
+                  (static_cast<size_t>(tok0 + jt) * g.out_ld + col0) * kOutElem;
               asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
                            "r"(smem_u32(tile_s + tg * ST::kPitch)), "r"(bytes)
                            : "memory");
@@ -555,8 +566,13 @@ cudaError_t launch_gate_up_pair(gptoss_moe *h, int layer, cudaStream_t stream, i
 // one "expert" whose rows are all the rows of x, schedule and tensor maps supplied by the
 // caller (tw: W [n_cols, k] in boxes of 128 rows; tx: x [rows, k] in boxes of 128, 32 and 8
 // rows).
+// f32_out: g.out addresses fp32 [rows, out_ld] (out_ld a multiple of 4), no row weight, bias
+// optional; four operand stages make room for the wider output staging.
 cudaError_t launch_linear_pair(int num_sms, const CUtensorMap &tw, const CUtensorMap *tx,
-                               const GemmArgs &g, cudaStream_t stream, long long *launches) {
+                               const GemmArgs &g, cudaStream_t stream, long long *launches,
+                               bool f32_out) {
+  if (f32_out)
+    return launch_pair_stages<kEpiF32, 4, false, 128, 0, 1>(num_sms, launches, tw, tx, g, stream);
   return launch_pair_stages<kEpiDown, 6, false, 128, 0, 1>(num_sms, launches, tw, tx, g, stream);
 }
 

@@ -10,12 +10,12 @@
  * (getp-csrc/getp_run.cpp:501-894) and computes what forward() computes for one
  * sequence (run.cpp:536-766), for every row of the batch.
  *
- * The QKV and attention-output projections run on the library's tcgen05 CTA-pair
- * kernel (the grouped GEMM of the MoE block with one group: bias in the epilogue,
- * bf16 output); the logits, which the argmax needs in fp32, are a plain GEMM through
- * cuBLAS (bf16 operands, fp32 accumulate and output), loaded with dlopen at
- * gptoss_decode_create, as is the fallback for projections whose row length is not
- * a multiple of 8.  Activations between kernels: the residual stream, the normalised
+ * The QKV and attention-output projections and the logits run on the library's
+ * tcgen05 CTA-pair kernel (the grouped GEMM of the MoE block with one group: bias in
+ * the epilogue, bf16 output; fp32 output for the logits, which the argmax needs in
+ * fp32).  Shapes that kernel does not take (projection rows that are not multiples of
+ * 8 elements, a vocabulary that is not a multiple of 4) fall back to cuBLAS, loaded
+ * with dlopen on first need.  Activations between kernels: the residual stream, the normalised
  * rows and the projection outputs are bf16, q and the logits fp32, the KV cache bf16.
  */
 #ifndef GPTOSS_DECODE_B200_H
@@ -76,7 +76,7 @@ int gptoss_decode_device_count(void);
 
 /* Allocates everything for max_batch sequences of up to cfg->seq_len positions on
  * `device` (KV cache: L * max_batch * seq_len * Hkv * D * 2 bf16).  No CPU
- * fallback: fails unless the device is sm_100 and cuBLAS can be loaded. */
+ * fallback: fails unless the device is sm_100. */
 int gptoss_decode_create(const gptoss_model_config_t *cfg, int max_batch, int device,
                          gptoss_decode_t **out);
 /* The same with the experts sharded over ep_size ranks (expert e on rank e % ep_size,
