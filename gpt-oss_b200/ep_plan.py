@@ -40,3 +40,21 @@ def dispatch_plan(topk_i: np.ndarray, topk_v: np.ndarray, n_ranks: int):
 def local_expert_slice(n_experts: int, rank: int, n_ranks: int) -> np.ndarray:
     """Global ids of the experts a rank owns, in local-id order."""
     return np.arange(rank, n_experts, n_ranks, dtype=np.int32)
+
+
+def owner_view(all_topk_i: np.ndarray, all_topk_v: np.ndarray, rank: int, n_ranks: int):
+    """Peer-memory transport, owner side: what rank `rank` makes of every rank's routing
+    result.  all_topk_i / all_topk_v [N, max_t, K] (ids of rows past a rank's batch = -1).
+    Returns slot_expert, slot_weight [N * max_t, K] over global rows g = src * max_t + t:
+    owner-local ids of the slots whose expert lives here, -1 elsewhere."""
+    N, max_t, K = all_topk_i.shape
+    ids = all_topk_i.reshape(N * max_t, K)
+    mine = (ids >= 0) & (ids % n_ranks == rank)
+    se = np.where(mine, ids // n_ranks, -1).astype(np.int32)
+    sw = np.where(mine, all_topk_v.reshape(N * max_t, K), 0.0).astype(np.float32)
+    return se, sw
+
+
+def owners_of_token(topk_row: np.ndarray, n_ranks: int):
+    """Ranks a home pulls partial sums from for one token, in the order it adds them."""
+    return sorted({int(e) % n_ranks for e in topk_row if e >= 0})

@@ -87,6 +87,75 @@ def _worker(rank, world, port, tmp):
     dist.destroy_process_group()
 
 
+def _peer_worker(rank, world, port, tmp):
+    """The peer-memory protocol with gloo standing in for the mapped buffers: every rank
+    publishes activations and routing result; owners work on global rows src * max_t + t
+    and fill a row of sums only where they have a slot; homes add the owners' sums in
+    ascending owner order."""
+    sys.path.insert(0, str(ROOT))
+    import torch.distributed as dist
+
+    import __graft_entry__ as entry
+
+    entry.load_package()
+    from gpt_oss_b200 import ep_plan, synth
+
+    oracle = entry.load_oracle()
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    max_t, H, K, E = 48, 48, 4, 8
+    d = synth.make_layer(synth.MoeShape("ep", 8, H, 24, E, K, 7.0, 901))
+    T = 31 + 9 * rank
+    shape = synth.MoeShape("ep", T, H, 24, E, K, 7.0, 901)
+    rng = np.random.default_rng(4321 + rank)
+    d["t"] = synth.bf16_round(rng.standard_normal((T, H)).astype(np.float32))
+    d["x"] = synth.bf16_round(rng.standard_normal((T, H)).astype(np.float32))
+    d["pos"] = np.arange(T, dtype=np.int32)
+    d["pos"][2::7] = -1
+    want = oracle.moe_layer(d, shape)
+    # publish (rows past T: id -1, as the publishing kernel writes them)
+    ids = np.full((max_t, K), -1, np.int32)
+    wts = np.zeros((max_t, K), np.float32)
+    act = np.zeros((max_t, H), np.float32)
+    ids[:T], wts[:T], act[:T] = want["topk_i"], want["topk_v"], d["t"]
+    published = [None] * world
+    dist.all_gather_object(published, {"ids": ids, "wts": wts, "act": act})
+    all_i = np.stack([p["ids"] for p in published])
+    all_v = np.stack([p["wts"] for p in published])
+    all_t = np.concatenate([p["act"] for p in published])  # global rows
+    # owner
+    se, sw = ep_plan.owner_view(all_i, all_v, rank, world)
+    mine = ep_plan.local_expert_slice(E, rank, world)
+    rows = np.nonzero((se >= 0).any(axis=1))[0]
+    sums = np.zeros((world * max_t, H), np.float64)
+    sums[rows] = _expert_rows(all_t[rows], se[rows], sw[rows], d["w_mlp1"][mine], d["b_mlp1"][mine],
+                              d["w_mlp2"][mine], d["b_mlp2"][mine], shape.swiglu_limit)
+    everyone = [None] * world
+    dist.all_gather_object(everyone, sums)
+    # home: pull in owner order
+    e_agg = np.zeros((T, H), np.float64)
+    for t in range(T):
+        for o in ep_plan.owners_of_token(want["topk_i"][t], world):
+            e_agg[t] += everyone[o][rank * max_t + t]
+    ok = np.allclose(e_agg, want["e_agg"], rtol=0, atol=2e-5)
+    ok = ok and (e_agg[d["pos"] < 0] == 0).all()
+    # an owner touches exactly the global rows that have one of its experts
+    expect = {s * max_t + t for s in range(world) for t in range(max_t)
+              for e in all_i[s, t] if e >= 0 and e % world == rank}
+    ok = ok and set(rows.tolist()) == expect
+    (pathlib.Path(tmp) / f"peer{rank}.txt").write_text("ok" if ok else "mismatch")
+    dist.destroy_process_group()
+
+
+def test_peer_memory_protocol_two_cpu_ranks(tmp_path):
+    import torch.multiprocessing as mp
+
+    port = 31500 + os.getpid() % 2000
+    mp.spawn(_peer_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        assert (tmp_path / f"peer{r}.txt").read_text() == "ok"
+
+
 def test_ep_exchange_two_cpu_ranks(tmp_path):
     import torch.multiprocessing as mp
 
