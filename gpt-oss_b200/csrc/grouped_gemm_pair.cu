@@ -164,7 +164,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
   const int first_tile = tt_lo * w_pairs + (blockIdx.x >> 1);
   const int total_tiles = tt_hi * w_pairs;
   const int kb_count = (g.k_dim + kTileK - 1) / kTileK;
-  const int cl = blockIdx.x >> 1, ncl = gridDim.x >> 1;
+  const int ncl = gridDim.x >> 1;  // clusters of the launch; a cluster strides over the tiles
 
   if (warp == 0) {
     if (lane == 0) {
@@ -309,8 +309,9 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
       const int stage = grp;
       uint32_t phase = 0;
       for (int n = grp; n < total_kb; n += kPairStages, phase ^= 1u) {
-        const int rs = n % kRawStages;
-        const uint32_t rphase = (n / kRawStages) & 1;
+        constexpr int kRawDiv = kRawStages > 0 ? kRawStages : 1;  // (no raw ring without MX)
+        const int rs = n % kRawDiv;
+        const uint32_t rphase = (n / kRawDiv) & 1;
         if (!mbar_wait(&raw_full[rs], rphase, abort_flag) ||
             !mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
           set_status(g.status, kStatusWaitTimeoutProducer);
