@@ -1,33 +1,37 @@
 """Benchmark of the MoE block: tokens/s of one layer pass.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload c2|c3|c2s|c4|c5|tiny] [--no-extra] [--no-cpu-baseline]
+                    [--workload c3|c2|c2s|c3s|c4|c5|tiny] [--no-extra] [--no-cpu-baseline]
 
 A step is one pass of the block (router -> top-4 -> permutation -> grouped
 gate_up + SwiGLU -> grouped down -> combine + residual) over one batch of
 seeded synthetic tokens.  One JSON line is printed by rank 0.
 
-N=1 runs the gpt-oss-20b-shape layer at T=7168 ("c2"), the configuration the
-single-GPU metric is quoted on.  N>1 runs one such replica per GPU (the
-reference serves the 20b shape as data-parallel replicas, getp_run.cpp:1035-1060),
-so per-GPU work is fixed ("weak") and no data-path collective is involved.
-The same line carries "layer_120b": the 120b-shape layer (T=6144 per GPU, 128
-experts) measured in the same run, with the experts sharded over the ranks when
-N>1 (rows read from peer memory over NVLink, or NCCL send/recv; both timed), a
-strong-scaling reading (the 6144 tokens split over the ranks) beside the weak one.
+The default workload at every N is the gpt-oss-120b-shape layer ("c3": 128 experts,
+T = 6144 tokens per GPU), the configuration the target of the benchmark description is
+quoted on: all experts local at N = 1; at N > 1 the experts are sharded over the ranks
+(expert e on rank e % N) and every rank brings its own 6144 tokens (weak scaling), rows
+read from peer memory over NVLink or sent with NCCL.  The line then also carries the
+strong-scaling reading (the 6144 tokens split over the ranks), the NCCL transport, and
+"ep_parity": 32 tokens of every rank against the CPU code and the two transports
+against each other.  At N = 1 the same line carries "layer_20b" (configuration 2: 32
+experts, T = 7168) and "decode_mxfp4" (configuration 4: MXFP4 weights, T = 64 / 256 /
+1024, Zipf-skewed router), each with its own roofline.
 
 Other workloads (each prints its own line):
-  c3    the 120b-shape layer as the headline workload
-  c2s   a quarter-size 20b-shape layer (8 experts, T=1792) for profiler captures
-  c4    the 120b-shape layer with MXFP4 expert weights at decode batch sizes
-        T = 64 / 256 / 1024 under a Zipf-skewed router
+  c2    the 20b-shape layer as the headline workload (N > 1: not sharded, 32 experts
+        split like any other count that N divides)
+  c2s   a quarter-size 20b-shape layer (8 experts, T = 1792) for profiler captures
+  c3s   an eighth-size 120b-shape layer (16 experts, T = 768: the same 192 rows per
+        expert) for profiler captures
+  c4    the MXFP4 decode shapes as their own line
   c5    one decode step of the full 120b-architecture model (36 layers, 6144
         sequences with 512 positions of KV context), experts sharded over N >= 2 GPUs,
         with the MoE share of the step time
   tiny  a 16-token layer (smoke runs)
 
 --impl reference times the reference's own CPU code (oracle/_ref when it was
-built from the reference tree, else the C port in oracle/) on the host cores, on
+built from the reference tree, else the C port in oracle/) on all host cores, on
 a bounded sample of the same workload per step.
 """
 from __future__ import annotations
@@ -35,6 +39,12 @@ from __future__ import annotations
 import argparse
 import json
 import os
+
+# The CPU legs (reference arm, CPU baseline, parity checks) use every core this process may
+# run on; a launcher that pins OMP_NUM_THREADS to 1 (torch.distributed.run does) must not
+# decide that, and the OpenMP runtime reads the variable when it is first loaded - which
+# importing numpy or torch may already do - so it is set before any other import.
+os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
 import pathlib
 import statistics
 import sys
@@ -49,8 +59,6 @@ import __graft_entry__ as entry  # noqa: E402
 
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
-# workloads whose gate_up DRAM traffic is covered by the ncu capture of the small 20b-shape case
-C2S_RATIO_WORKLOADS = ("gpt-oss-20b-moe-layer-T7168", "gpt-oss-20b-moe-layer-8experts-T1792")
 
 
 def read_peaks():
@@ -158,33 +166,62 @@ def cpu_sample(shape, w_host, t_host, x_host, n_tokens, kind):
     return time.perf_counter() - t0
 
 
-def run_reference_arm(args, shape):
-    """The reference's CPU implementation on the host cores (rank 0 only)."""
-    import torch
+def oracle_router_np(oracle, t, w_router, b_router, K):
+    """Top-K expert ids of every row of t by the CPU oracle's router (cheap)."""
+    import ctypes
 
+    T, H = t.shape
+    E = w_router.shape[0]
+    lib = ctypes.CDLL(str(oracle.ORACLE_LIB))
+    fp, ip = ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_int)
+    lg = np.zeros((T, E), np.float32)
+    ti = np.full((T, K), -1, np.int32)
+    tv = np.zeros((T, K), np.float32)
+    lib.oracle_router.argtypes = [fp, ip] + [ctypes.c_int] * 4 + [fp, fp, fp, ip, fp]
+    t = np.ascontiguousarray(t, np.float32)
+    w_router = np.ascontiguousarray(w_router, np.float32)
+    b_router = np.ascontiguousarray(b_router, np.float32)
+    rc = lib.oracle_router(t.ctypes.data_as(fp), None, T, H, E, K, w_router.ctypes.data_as(fp),
+                           b_router.ctypes.data_as(fp), lg.ctypes.data_as(fp),
+                           ti.ctypes.data_as(ip), tv.ctypes.data_as(fp))
+    if rc != 0:
+        raise RuntimeError("oracle_router failed")
+    return ti
+
+
+def run_reference_arm(args, shape):
+    """The reference's CPU implementation on the host cores (rank 0 only).  The sample's
+    tokens are routed first; only the experts they select get weights drawn (the CPU code
+    never reads the others, which stay untouched zero pages)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    # all the host cores this process may use (torchrun pins OMP_NUM_THREADS to 1)
-    os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
+    import torch
+
     oracle = entry.load_oracle()
     if not oracle.ORACLE_LIB.exists():
         oracle.build(native=True)
     kind = "reference" if oracle.have_ref() else "port"
     cores = oracle.num_threads("ref" if kind == "reference" else "oracle")
+    if cores < 2 and len(os.sched_getaffinity(0)) > 1:
+        raise SystemExit("the CPU baseline would run on one thread although the box has more cores")
     g = torch.Generator().manual_seed(shape.seed)
-    # weights drawn on the CPU here (same distributions); the sample is what matters
-    H, IM, E = shape.hidden_dim, shape.intermediate_dim, shape.n_experts
+    H, IM, E, K = shape.hidden_dim, shape.intermediate_dim, shape.n_experts, shape.experts_per_token
 
     def normal(size, std):
         return (torch.randn(size, generator=g) * std).bfloat16().float().numpy()
 
-    w = {"w_router": normal((E, H), 0.02), "b_router": normal((E,), 0.02),
-         "w_mlp1": normal((E, 2 * IM, H), 0.02), "b_mlp1": normal((E, 2 * IM), 0.01),
-         "w_mlp2": normal((E, H, IM), 0.02), "b_mlp2": normal((E, H), 0.01)}
     n_sample = args.cpu_tokens
+    w = {"w_router": normal((E, H), 0.02), "b_router": normal((E,), 0.02),
+         "b_mlp1": normal((E, 2 * IM), 0.01), "b_mlp2": normal((E, H), 0.01)}
     t = normal((n_sample, H), 1.0)
     x = normal((n_sample, H), 1.0)
+    used = np.unique(oracle_router_np(oracle, t, w["w_router"], w["b_router"], K))
+    w["w_mlp1"] = np.zeros((E, 2 * IM, H), np.float32)
+    w["w_mlp2"] = np.zeros((E, H, IM), np.float32)
+    for e in used:
+        w["w_mlp1"][e] = normal((2 * IM, H), 0.02)
+        w["w_mlp2"][e] = normal((H, IM), 0.02)
     for _ in range(min(args.warmup, 1)):
         cpu_sample(shape, w, t, x, n_sample, kind)
     times = [cpu_sample(shape, w, t, x, n_sample, kind) for _ in range(args.steps)]
@@ -205,178 +242,222 @@ def run_reference_arm(args, shape):
     print(json.dumps(line), flush=True)
 
 
-def measure_c3_layer(args, pkg, dev, rank, world, local_rank, barrier):
-    """The 120b-shape layer (T=6144 tokens per GPU, 128 experts) beside the headline
-    workload: all experts local at N=1, expert parallel (owner = e % N) at N>1.  Weak
-    scaling: every rank brings its own 6144 tokens."""
+def host_weights_for(w, used, shape):
+    """fp32 host copies of the layer for the CPU code: router and biases whole, expert
+    matrices only for the experts in `used` (the others stay untouched zero pages)."""
+    H, IM, E = shape.hidden_dim, shape.intermediate_dim, shape.n_experts
+    d = {k: w[k].float().cpu().numpy() for k in ("w_router", "b_router", "b_mlp1", "b_mlp2")}
+    d["w_mlp1"] = np.zeros((E, 2 * IM, H), np.float32)
+    d["w_mlp2"] = np.zeros((E, H, IM), np.float32)
+    for e in used:
+        d["w_mlp1"][e] = w["w_mlp1"][e].float().cpu().numpy()
+        d["w_mlp2"][e] = w["w_mlp2"][e].float().cpu().numpy()
+    return d
+
+
+def cpu_baseline_for(args, shape, w, t, x0, routing_topk_i):
+    """Times the CPU code on the first tokens of the batch (about 12 s of work)."""
+    oracle = entry.load_oracle()
+    if not oracle.ORACLE_LIB.exists():
+        oracle.build(native=True)
+    kind = "reference" if oracle.have_ref() else "port"
+    T, K = shape.n_tokens, shape.experts_per_token
+
+    def sample(n):
+        w_host = host_weights_for(w, np.unique(routing_topk_i[:n]), shape)
+        return cpu_sample(shape, w_host, t[:n].float().cpu().numpy(), x0[:n].float().cpu().numpy(),
+                          n, kind)
+
+    if args.cpu_tokens:
+        n_cpu = min(T, args.cpu_tokens)
+        sec = sample(n_cpu)
+    else:
+        n_cpu = min(T, 64)
+        sec = sample(n_cpu)
+        want = min(T, max(64, int(12.0 / (sec / n_cpu)) // 64 * 64))
+        if want > 2 * n_cpu:
+            n_cpu = want
+            sec = sample(n_cpu)
+    return {"value": n_cpu / sec, "unit": UNIT,
+            "cores": oracle.num_threads("ref" if kind == "reference" else "oracle"), "kind": kind,
+            "sample": f"first {n_cpu} tokens of the batch, {K} experts each, {sec:.1f} s"}
+
+
+def timed_forward(eng, t, x, T, steps, stream, barrier, world, dev, names, warm=3):
+    """`steps` passes of the layer between CUDA events on the launching stream (barrier and
+    synchronize on both sides, max over ranks), with per-stage event pairs."""
     import torch
     import torch.distributed as dist
 
-    shape = workload_shape("c3")
+    for _ in range(warm):
+        eng.forward(0, t, x, None, T, stream)
+    barrier()
+    if eng.device_status() != 0:
+        raise SystemExit("device status non-zero after warm-up")
+    eng.set_option("time_stages", 1)
+    barrier()
+    launches0 = eng.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(steps):
+        eng.forward(0, t, x, None, T, stream)
+    ev1.record()
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    launches = eng.launch_count() - launches0
+    if world > 1:
+        tt = torch.tensor([ms], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms = float(tt.item())
+    stage_ms = {s: eng.stage_ms(s) for s in names}
+    eng.set_option("time_stages", 0)
+    return {"ms": ms, "stage_ms": stage_ms, "launches": launches}
+
+
+def measure_layer(args, pkg, shape, dev, rank, world, local_rank, barrier, with_e2e, with_cpu,
+                  with_parity):
+    """One MoE layer workload: all experts local at world 1, expert parallel (owner =
+    e % world, every rank its own `shape.n_tokens` tokens: weak scaling) otherwise."""
+    import torch
+    import torch.distributed as dist
+
     T, H, IM, E, K = (shape.n_tokens, shape.hidden_dim, shape.intermediate_dim, shape.n_experts,
                       shape.experts_per_token)
+    ep = world > 1
     eng = pkg.MoeEngine(H, IM, E, K, n_layers=1, max_tokens=T, swiglu_limit=shape.swiglu_limit,
-                        ep_rank=rank, ep_size=world, device=local_rank)
+                        ep_rank=rank if ep else 0, ep_size=world if ep else 1, device=local_rank)
     w = device_weights(shape, dev)  # same seed on every rank: one set of weights, sharded
     eng.load_layer_bf16(0, w["w_router"], w["b_router"], w["w_mlp1"], w["b_mlp1"], w["w_mlp2"],
                         w["b_mlp2"], on_device=True)
-    del w
-    torch.cuda.empty_cache()
-    if os.environ.get("GPTOSS_GEMM_IMPL"):
-        eng.set_option("gemm_impl", int(os.environ["GPTOSS_GEMM_IMPL"]))
-    if world > 1:
+    if ep:
         uid = torch.zeros(128, dtype=torch.uint8, device=dev)
         if rank == 0:
             uid.copy_(torch.frombuffer(bytearray(pkg.MoeEngine.ep_unique_id()), dtype=torch.uint8))
         dist.broadcast(uid, 0)
         eng.ep_init(bytes(uid.cpu().numpy().tobytes()))
     g = torch.Generator(device=dev)
-    g.manual_seed(shape.seed + 2000 + rank)
-    t = torch.randn((T, H), generator=g, device=dev).bfloat16()
-    x = torch.randn((T, H), generator=g, device=dev).bfloat16()
-    stream = torch.cuda.current_stream().cuda_stream
-    steps = max(3, min(args.steps, 30))
-    names = ["route", "permute", "gate_up", "down", "combine"]
-    if world > 1:
-        names += ["dispatch", "return"]
-
-    def timed(T=T):
-        for _ in range(3):
-            eng.forward(0, t, x, None, T, stream)
-        barrier()
-        if eng.device_status() != 0:
-            raise SystemExit("device status non-zero in the 120b-shape layer")
-        eng.set_option("time_stages", 1)
-        barrier()
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        ev0.record()
-        for _ in range(steps):
-            eng.forward(0, t, x, None, T, stream)
-        ev1.record()
-        barrier()
-        ms = ev0.elapsed_time(ev1)
-        if world > 1:
-            tt = torch.tensor([ms], device=dev)
-            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            ms = float(tt.item())
-        stage_ms = {s: eng.stage_ms(s) for s in names}
-        eng.set_option("time_stages", 0)
-        return {"value": world * T * steps / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms / steps,
-                "steps": steps, "stage_ms": stage_ms}
-
-    # expert parallelism: rows read from the peers' memory where the ranks could map each
-    # other (the default then), and over NCCL send / recv for comparison
-    transport = eng.ep_transport if world > 1 else -1
-    res = timed()
-    other = strong = None
-    if world > 1:
-        # strong-scaling reading: the same 6144 tokens split over the ranks
-        strong = timed(T // world)
-        strong["tokens_per_gpu"] = T // world
-    overlap = None
-    if transport == 1:
-        eng.set_option("ep_overlap", 1)
-        overlap = timed()
-        eng.set_option("ep_overlap", 0)
-        eng.set_option("ep_transport", 0)
-        other = timed()
-    eng.close()
-    how = {-1: "all experts local", 0: f"expert parallel x{world} (NCCL send/recv)",
-           1: f"expert parallel x{world} (rows read from peer memory over NVLink)"}[transport]
-    out = {"workload": shape.name, "tokens_per_gpu": T, "experts": E, "parallelism": how}
-    out.update(res)
-    # rank 0's own gate_up launch; under expert parallelism its row count varies a little
-    # around T*K per rank
-    out["gate_up_tflops"] = 2.0 * T * K * 2 * IM * H / (res["stage_ms"]["gate_up"] * 1e-3) / 1e12
-    if strong is not None:
-        out["strong_scaling"] = strong
-    if overlap is not None:
-        out["peer_memory_with_gather_overlap"] = overlap
-    if other is not None:
-        out["nccl_send_recv"] = other
-    return out
-
-
-def run_ours(args, shape):
-    import torch
-    import torch.distributed as dist
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-
-    pkg = entry.load_package()
-    T, H, IM, E, K = (shape.n_tokens, shape.hidden_dim, shape.intermediate_dim, shape.n_experts,
-                      shape.experts_per_token)
-    eng = pkg.MoeEngine(H, IM, E, K, n_layers=1, max_tokens=T, swiglu_limit=shape.swiglu_limit,
-                        device=local_rank)
-    w = device_weights(shape, dev)
-    eng.load_layer_bf16(0, w["w_router"], w["b_router"], w["w_mlp1"], w["b_mlp1"], w["w_mlp2"],
-                        w["b_mlp2"], on_device=True)
-    if os.environ.get("GPTOSS_GEMM_IMPL"):  # 0 = single-CTA tcgen05, 2 = CTA pairs
-        eng.set_option("gemm_impl", int(os.environ["GPTOSS_GEMM_IMPL"]))
-    if os.environ.get("GPTOSS_PAIR_STAGES"):  # tuning aid
-        eng.set_option("pair_stages", int(os.environ["GPTOSS_PAIR_STAGES"]))
-    if os.environ.get("GPTOSS_SKIP_EPILOGUE"):  # measurement aid: main loop only
-        eng.set_option("skip_epilogue", int(os.environ["GPTOSS_SKIP_EPILOGUE"]))
-    g = torch.Generator(device=dev)
     g.manual_seed(shape.seed + 1000 + rank)
     t = torch.randn((T, H), generator=g, device=dev).bfloat16()
     x0 = torch.randn((T, H), generator=g, device=dev).bfloat16()
     x = x0.clone()
     stream = torch.cuda.current_stream().cuda_stream
+    names = ["route", "permute", "gate_up", "down", "combine"] + (["dispatch", "return"] if ep else [])
+    transport = eng.ep_transport if ep else -1
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
+    # warm-up, then the timed region of the line
     for _ in range(args.warmup):
         eng.forward(0, t, x, None, T, stream)
-    barrier()
-    if eng.device_status() != 0:
-        raise SystemExit("device status non-zero after warm-up")
     x.copy_(x0)
-    eng.set_option("time_stages", 1)
     sampler = ClockSampler(local_rank)
     sampler.start()
-    barrier()
-    launches0 = eng.launch_count()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for _ in range(args.steps):
-        eng.forward(0, t, x, None, T, stream)
-    ev1.record()
-    barrier()
+    main = timed_forward(eng, t, x, T, args.steps, stream, barrier, world, dev, names, warm=0)
     clocks = sampler.result()
-    elapsed_ms = ev0.elapsed_time(ev1)
-    launches = eng.launch_count() - launches0
-    stage_ms = {s: eng.stage_ms(s) for s in ("route", "permute", "gate_up", "down", "combine")}
-    eng.set_option("time_stages", 0)
-    if world > 1:
-        tt = torch.tensor([elapsed_ms], device=dev)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        elapsed_ms = float(tt.item())
-    value = world * T * args.steps / (elapsed_ms * 1e-3)
+    out = {"ms_per_step": main["ms"] / args.steps, "stage_ms": main["stage_ms"],
+           "launches": main["launches"], "clocks": clocks, "transport": transport,
+           "value": world * T * args.steps / (main["ms"] * 1e-3)}
+    routing = eng.get_routing(T)
 
-    # end to end through the host-buffer entry point: pinned host inputs copied in,
-    # result copied out, every step
-    # (a) one call per step that copies in, computes, copies out and returns;
-    # (b) the streaming pair submit / wait: three batches in flight, each in its own pinned
-    #     buffers, so the copies of neighbouring steps overlap the kernels.  Every step still
-    #     moves its own inputs in and its own result out.
+    if ep:
+        side_steps = max(3, min(args.steps, 20))
+        strong = timed_forward(eng, t, x, T // world, side_steps, stream, barrier, world, dev, names)
+        out["strong_scaling"] = {"tokens_per_gpu": T // world,
+                                 "value": world * (T // world) * side_steps / (strong["ms"] * 1e-3),
+                                 "unit": UNIT, "ms_per_step": strong["ms"] / side_steps,
+                                 "stage_ms": strong["stage_ms"]}
+        if transport == 1:
+            eng.set_option("ep_transport", 0)
+            other = timed_forward(eng, t, x, T, side_steps, stream, barrier, world, dev, names)
+            eng.set_option("ep_transport", 1)
+            out["nccl_send_recv"] = {"value": world * T * side_steps / (other["ms"] * 1e-3),
+                                     "unit": UNIT, "ms_per_step": other["ms"] / side_steps,
+                                     "stage_ms": other["stage_ms"]}
+
+    if with_parity:
+        out["parity"] = parity_check(pkg, eng, shape, w, t, x0, rank, world, dev, stream, barrier,
+                                     transport)
+
+    if with_e2e:
+        out["e2e"] = measure_e2e(args, eng, shape, t, x0, world, dev, barrier, ep)
+
+    if with_cpu and rank == 0:
+        out["cpu_baseline"] = cpu_baseline_for(args, shape, w, t, x0, routing["topk_i"])
+    eng.close()
+    del w
+    torch.cuda.empty_cache()
+    return out
+
+
+def parity_check(pkg, eng, shape, w, t, x0, rank, world, dev, stream, barrier, transport):
+    """Untimed.  One pass on this rank's tokens with a zero residual; 32 seeded tokens of it
+    against the CPU code (all experts), expert ids exactly, block output within the stated
+    tolerance; under expert parallelism also the two transports against each other bit for
+    bit.  The worst figures over the ranks are returned."""
+    import torch
+    import torch.distributed as dist
+
+    T, K = shape.n_tokens, shape.experts_per_token
+    oracle = entry.load_oracle()
+    if not oracle.ORACLE_LIB.exists():
+        oracle.build(native=True)
+    kind = "ref" if oracle.have_ref() else "oracle"
+
+    def one_pass():
+        x = torch.zeros_like(x0)
+        eng.forward(0, t, x, None, T, stream)
+        barrier()
+        if eng.device_status() != 0:
+            raise SystemExit("device status non-zero in the parity pass")
+        return x
+
+    x_a = one_pass()
+    routing = eng.get_routing(T)
+    bitwise = None
+    if transport == 1:
+        eng.set_option("ep_transport", 0)
+        x_b = one_pass()
+        eng.set_option("ep_transport", 1)
+        bitwise = bool(torch.equal(x_a, x_b))
+    rng = np.random.default_rng(shape.seed + rank)
+    idx = np.sort(rng.choice(T, 32, replace=False))
+    d = host_weights_for(w, np.unique(routing["topk_i"][idx]), shape)
+    d["t"] = t[idx].float().cpu().numpy()
+    d["x"] = np.zeros_like(d["t"])
+    d["pos"] = None
+    sub = type(shape)(shape.name, 32, shape.hidden_dim, shape.intermediate_dim, shape.n_experts, K,
+                      shape.swiglu_limit, shape.seed)
+    want = oracle.moe_layer(d, sub, which=kind)
+    got = x_a[idx].float().cpu().numpy()
+    err = np.abs(got - want["e_agg"])
+    res = [float(err.max()), float(err.mean() / np.abs(want["e_agg"]).mean()),
+           float(not np.array_equal(routing["topk_i"][idx], want["topk_i"])),
+           0.0 if bitwise in (None, True) else 1.0]
+    if world > 1:
+        tt = torch.tensor(res, device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        res = [float(v) for v in tt.tolist()]
+    return {"checker": "oracle/_ref (the reference's CPU code)" if kind == "ref" else "oracle port",
+            "tokens_per_rank": 32, "max_abs": res[0], "mean_rel": res[1],
+            "indices_exact": res[2] == 0.0,
+            "transports_bitwise_equal": None if bitwise is None else res[3] == 0.0,
+            "within_tolerance": res[0] <= 2e-2 and res[1] <= 1e-2 and res[2] == 0.0}
+
+
+def measure_e2e(args, eng, shape, t, x0, world, dev, barrier, ep):
+    """The same layer through the host-buffer entry points: every step copies its inputs in
+    from pinned host memory and its result back out.  The streamed pair submit / wait
+    keeps three batches in flight, each in its own pinned buffers, so the copies of
+    neighbouring steps overlap the kernels; with the RMSNorm of the block on the device
+    only the residual stream crosses the bus."""
+    import torch
+    import torch.distributed as dist
+
+    T, H = shape.n_tokens, shape.hidden_dim
     t_h = t.cpu().pin_memory()
     x_h = x0.cpu().pin_memory()
     e2e_steps = max(3, min(args.steps, 20))
 
     def timed_host(fn):
-        fn(2)
+        fn(3)
         barrier()
         t0 = time.perf_counter()
         fn(e2e_steps)
@@ -406,16 +487,92 @@ def run_ours(args, shape):
                 eng.forward_host_wait(tk)
         return steps
 
-    e2e_sync_value = timed_host(sync_steps)
-    e2e_streamed_t = timed_host(streamed(True))
-    # (c) as (b), but only the residual stream crosses the bus: the block's RMSNorm (scale 1
-    #     here) runs on the device, as in the model, instead of the caller sending t as well
+    one_call = timed_host(sync_steps)
+    res = {"unit": UNIT, "steps": e2e_steps,
+           "one_call_per_step": {"value": one_call, "h2d_bytes_per_step": 2 * T * H * 2,
+                                 "d2h_bytes_per_step": T * H * 2}}
+    if ep and eng.ep_transport != 1:
+        # the NCCL transport synchronises with the host in every layer: no streamed variant
+        res.update(value=one_call, h2d_bytes_per_step=2 * T * H * 2, d2h_bytes_per_step=T * H * 2,
+                   how="gptoss_moe_forward_host: t and x in, block on the device, x out, per step")
+        return res
+    with_t = timed_host(streamed(True))
     eng.load_ffn_norm(0, np.ones(H, dtype=np.float32))
-    e2e_value = timed_host(streamed(False))
+    value = timed_host(streamed(False))
+    res.update(value=value, h2d_bytes_per_step=T * H * 2, d2h_bytes_per_step=T * H * 2,
+               how="gptoss_moe_forward_host_submit / _wait, three batches in flight; x in, "
+                   "RMSNorm + block on the device, x out",
+               streamed_with_t_from_host={"value": with_t, "h2d_bytes_per_step": 2 * T * H * 2})
+    return res
 
-    extra = None
-    if not args.no_extra and args.workload == "c2":
-        extra = measure_c3_layer(args, pkg, dev, rank, world, local_rank, barrier)
+
+def layer_rooflines(shape, stage_ms, peaks, timed_s, rows_per_rank_scale=1.0, local_experts=None):
+    """Roofline entries of the dominant kernel (gate_up GEMM) of a layer measurement:
+    against the tensor peak (algorithmic flops 2*A*2IM*H) and against the HBM copy
+    bandwidth (weights once, gathered rows in, activations out)."""
+    T, H, IM, E, K = (shape.n_tokens, shape.hidden_dim, shape.intermediate_dim, shape.n_experts,
+                      shape.experts_per_token)
+    El = E if local_experts is None else local_experts
+    n_assign = T * K * rows_per_rank_scale
+    flops = 2.0 * n_assign * 2 * IM * H
+    peak_kind = "bf16_tflops" if timed_s < 1.0 else "bf16_tflops_sustained"
+    sec = stage_ms["gate_up"] * 1e-3
+    tflops = flops / sec / 1e12
+    alg_bytes = El * 2 * IM * H * 2 + n_assign * H * 2 + n_assign * IM * 2
+    gbs = alg_bytes / sec / 1e9
+    tensor = {"kernel": "grouped_gemm_pair_kernel<swiglu> (gate_up, CTA pairs)", "bound": "tensor",
+              "achieved": tflops, "peak": peaks[peak_kind], "unit": "TFLOP/s",
+              "frac": tflops / peaks[peak_kind], "peak_source": f"{peaks['source']} {peak_kind}",
+              "algorithmic_flops_per_launch": flops, "kernel_ms": stage_ms["gate_up"]}
+    hbm = {"kernel": tensor["kernel"], "bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"],
+           "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+           "peak_source": f"{peaks['source']} hbm_gbs",
+           "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": stage_ms["gate_up"]}
+    return tensor, hbm, alg_bytes
+
+
+def run_ours(args, shape):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    pkg = entry.load_package()
+    T, H, IM, E, K = (shape.n_tokens, shape.hidden_dim, shape.intermediate_dim, shape.n_experts,
+                      shape.experts_per_token)
+    if world > 1 and E % world:
+        raise SystemExit(f"{E} experts do not split over {world} GPUs")
+    res = measure_layer(args, pkg, shape, dev, rank, world, local_rank, barrier, with_e2e=True,
+                        with_cpu=(world == 1 and not args.no_cpu_baseline), with_parity=not args.no_extra)
+
+    extras = {}
+    if not args.no_extra and world == 1 and args.workload == "c3":
+        # the 20b-shape layer (configuration 2) and the MXFP4 decode shapes (configuration 4)
+        # ride in the same line
+        import copy
+
+        side = copy.copy(args)
+        side.steps = max(3, min(args.steps, 30))
+        side.warmup = 3
+        c2 = measure_layer(side, pkg, workload_shape("c2"), dev, 0, 1, local_rank, barrier,
+                           with_e2e=False, with_cpu=False, with_parity=False)
+        extras["layer_20b"] = c2
+        side.steps = max(3, min(args.steps, 30))
+        extras["decode_mxfp4"] = measure_decode_mxfp4(side, pkg, dev)
 
     if rank != 0:
         if world > 1:
@@ -423,106 +580,96 @@ def run_ours(args, shape):
         return
 
     peaks = read_peaks()
+    timed_s = res["ms_per_step"] * args.steps * 1e-3
+    tensor, hbm, alg_bytes = layer_rooflines(shape, res["stage_ms"], peaks, timed_s,
+                                             local_experts=E // world)
+    # DRAM traffic of one gate_up launch, from the ncu capture named in profiles/: the ratio
+    # of measured to algorithmic bytes of the captured small case applied to this launch
+    ratio = TRAFFIC_RATIO.get(shape.name if world == 1 else None)
+    tensor["traffic"] = hbm["traffic"] = ratio * alg_bytes if ratio else None
+    tensor["traffic_unit"] = hbm["traffic_unit"] = "bytes/launch"
+    tensor["traffic_source"] = hbm["traffic_source"] = TRAFFIC_SOURCE if ratio else None
+    stage = res["stage_ms"]
     n_assign = T * K
-    flops_gate_up = 2.0 * n_assign * 2 * IM * H
-    timed_s = elapsed_ms * 1e-3
-    peak_kind = "bf16_tflops" if timed_s < 1.0 else "bf16_tflops_sustained"
-    achieved = flops_gate_up / (stage_ms["gate_up"] * 1e-3) / 1e12
-    # DRAM traffic of one gate_up launch: the ncu capture of the small case c2s read and wrote
-    # 377.2 MB against 348.0 MB algorithmic (weights once, rows in, activations out); c2 has four
-    # times the rows and four times the experts, so the same ratio is applied to its bytes.
-    alg_bytes = E * 2 * IM * H * 2 + n_assign * H * 2 + n_assign * IM * 2
-    gate_up_traffic = (377.2 / 348.0) * alg_bytes if shape.name in C2S_RATIO_WORKLOADS else None
-    roofline = {
-        "kernel": ("grouped_gemm_tc_kernel<240, swiglu> (gate_up, single CTA)"
-                   if os.environ.get("GPTOSS_GEMM_IMPL") == "0"
-                   else "grouped_gemm_pair_kernel<swiglu, 6> (gate_up, CTA pairs)"),
-        "bound": "tensor",
-        "achieved": achieved, "peak": peaks[peak_kind], "unit": "TFLOP/s",
-        "frac": achieved / peaks[peak_kind], "peak_source": f"{peaks['source']} {peak_kind}",
-        "traffic": gate_up_traffic, "traffic_unit": "bytes/launch",
-        "traffic_source": "ncu dram__bytes_read+write of the c2s capture (377.2 MB, a quarter of the "
-                          "rows and of the experts), scaled by rows x experts",
-        "kernel_ms": stage_ms["gate_up"],
-        "stage_ms": stage_ms,
-        "down_tflops": 2.0 * n_assign * H * IM / (stage_ms["down"] * 1e-3) / 1e12,
-        "route_gbs": (T * H * 2 + E * H * 2 + T * K * 8) / (stage_ms["route"] * 1e-3) / 1e9,
-        "combine_gbs": (n_assign * H * 2 + 2 * T * H * 2) / (stage_ms["combine"] * 1e-3) / 1e9,
-        "hbm_peak_gbs": peaks["hbm_gbs"],
-    }
+    tensor["stage_ms"] = stage
+    tensor["down_tflops"] = 2.0 * n_assign * H * IM / (stage["down"] * 1e-3) / 1e12
+    tensor["route_gbs"] = (T * H * 2 + E * H * 2 + T * K * 8) / (stage["route"] * 1e-3) / 1e9
+    tensor["route_frac_of_hbm"] = tensor["route_gbs"] / peaks["hbm_gbs"]
+    tensor["combine_gbs"] = ((n_assign * H * 2 + 2 * T * H * 2) / (stage["combine"] * 1e-3) / 1e9
+                             if world == 1 else None)
+    tensor["hbm_peak_gbs"] = peaks["hbm_gbs"]
+    # the whole layer against both ceilings
+    layer_flops = 2.0 * n_assign * 3 * IM * H
+    layer_bytes = (E // world) * 3 * IM * H * 2 + T * H * 2 + 2 * n_assign * IM * 2 + 2 * T * H * 2
+    tensor["layer_tflops"] = layer_flops / (res["ms_per_step"] * 1e-3) / 1e12
+    tensor["layer_frac_of_tensor_peak"] = tensor["layer_tflops"] / peaks["bf16_tflops"]
+    tensor["layer_frac_of_hbm_streaming"] = (layer_bytes / peaks["hbm_gbs"] / 1e9) / (res["ms_per_step"] * 1e-3)
 
-    cpu_baseline = None
-    if not args.no_cpu_baseline and world == 1:  # the CPU figure is a 1-process measurement
-        oracle = entry.load_oracle()
-        if not oracle.ORACLE_LIB.exists():
-            oracle.build(native=True)
-        kind = "reference" if oracle.have_ref() else "port"
-        w_host = host_weights_f32(w)
-
-        def sample(n):
-            return cpu_sample(shape, w_host, t[:n].float().cpu().numpy(),
-                              x0[:n].float().cpu().numpy(), n, kind)
-
-        if args.cpu_tokens:
-            n_cpu = min(T, args.cpu_tokens)
-            sec = sample(n_cpu)
-        else:
-            # size the sample for about 12 s of CPU work on this box's cores
-            n_cpu = min(T, 64)
-            sec = sample(n_cpu)
-            want = min(T, max(64, int(12.0 / (sec / n_cpu)) // 64 * 64))
-            if want > 2 * n_cpu:
-                n_cpu = want
-                sec = sample(n_cpu)
-        cpu_baseline = {"value": n_cpu / sec, "unit": UNIT,
-                        "cores": oracle.num_threads("ref" if kind == "reference" else "oracle"),
-                        "kind": kind,
-                        "sample": f"first {n_cpu} tokens of the batch, {K} experts each, {sec:.1f} s"}
-
+    how = {-1: "all experts local", 0: f"expert parallel x{world} (NCCL send/recv)",
+           1: f"expert parallel x{world} (rows read from peer memory over NVLink)"}[res["transport"]]
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
+        "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": shape.name, "tokens_per_gpu": T, "hidden": H, "intermediate": IM,
-                   "experts": E, "top_k": K, "parallelism": f"replicas x{world}",
-                   "l2": "inputs larger than L2 (expert weights %.2f GB streamed every step)"
-                         % ((E * 3 * IM * H * 2) / 1e9)},
-        "roofline": roofline, "cpu_baseline": cpu_baseline,
-        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": T * H * 2,
-                "d2h_bytes_per_step": T * H * 2, "steps": e2e_steps,
-                "how": "gptoss_moe_forward_host_submit / _wait, three batches in flight; x in, "
-                       "RMSNorm + block on the device, x out",
-                "streamed_with_t_from_host": {"value": e2e_streamed_t,
-                                              "h2d_bytes_per_step": 2 * T * H * 2},
-                "one_call_per_step": {"value": e2e_sync_value,
-                                      "h2d_bytes_per_step": 2 * T * H * 2}},
-        "gpu_launches": launches, "clocks": clocks,
+                   "experts": E, "experts_per_gpu": E // world, "top_k": K, "parallelism": how,
+                   "l2": "inputs larger than L2 (expert weights %.2f GB per GPU streamed every step)"
+                         % (((E // world) * 3 * IM * H * 2) / 1e9)},
+        "roofline": tensor, "roofline_hbm": hbm, "cpu_baseline": res.get("cpu_baseline"),
+        "e2e": res["e2e"], "gpu_launches": res["launches"], "clocks": res["clocks"],
+        "stage_ms": stage,
     }
-    if extra is not None:
-        extra["gate_up_frac_of_peak"] = extra["gate_up_tflops"] / peaks["bf16_tflops"]
-        line["layer_120b"] = extra
+    for key in ("strong_scaling", "nccl_send_recv", "parity"):
+        if key in res:
+            line["ep_parity" if (key == "parity" and world > 1) else key] = res[key]
+    for name, ex in extras.items():
+        if name == "layer_20b":
+            s20 = workload_shape("c2")
+            t20, h20, _ = layer_rooflines(s20, ex["stage_ms"], peaks, ex["ms_per_step"] * 30e-3)
+            line[name] = {"workload": s20.name, "value": ex["value"], "unit": UNIT,
+                          "ms_per_step": ex["ms_per_step"], "stage_ms": ex["stage_ms"],
+                          "roofline": t20, "roofline_hbm": h20,
+                          "route_gbs": (s20.n_tokens * H * 2 + s20.n_experts * H * 2 + s20.n_tokens * K * 8)
+                                       / (ex["stage_ms"]["route"] * 1e-3) / 1e9}
+        else:
+            line[name] = ex
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
 
-def run_decode_mxfp4(args):
-    """--workload c4: the 120b-shape layer with MXFP4 expert weights at decode batch
-    sizes T = 64 / 256 / 1024, router biased so that expert popularity is skewed
-    (Zipf(1.1) weights over a seeded permutation of the experts).  Bound by HBM: the
-    packed weights of every touched expert are streamed once per layer pass."""
+# ratio of measured DRAM traffic (ncu dram__bytes_read.sum + dram__bytes_write.sum) to the
+# algorithmic bytes of the gate_up launch, per workload the capture covers
+TRAFFIC_RATIO = {"gpt-oss-20b-moe-layer-T7168": 377.2 / 348.0,
+                 "gpt-oss-20b-moe-layer-8experts-T1792": 377.2 / 348.0}
+TRAFFIC_SOURCE = ("ncu dram__bytes_read+write of the small-case capture under profiles/ scaled to "
+                  "this launch by its algorithmic bytes")
+
+
+def c4_tokens(T, H, g, dev):
+    """Decode-batch activations of configuration 4: t with sigma 0.25 (the weights' rms is
+    0.094, so pre-activations stay around the clamp), a N(0,1) residual."""
     import torch
 
-    pkg = entry.load_package()
+    t = (torch.randn((T, H), generator=g, device=dev) * 0.25).bfloat16()
+    x = torch.randn((T, H), generator=g, device=dev).bfloat16()
+    return t, x
+
+
+def c4_layer(pkg, dev, max_tokens=1024, n_experts=None):
+    """Configuration 4: the 120b-shape layer with MXFP4 expert weights - e2m1 codes uniform
+    over the 16 values, e8m0 scales uniform in 2^-8 .. 2^-4 - and a router whose bias
+    makes expert popularity follow Zipf(1.1) over a seeded permutation of the experts.
+    Returns the loaded engine and the tensors it was loaded from."""
+    import torch
+
     shape = workload_shape("c3")
-    H, IM, E, K = shape.hidden_dim, shape.intermediate_dim, shape.n_experts, shape.experts_per_token
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(0)
+    H, IM, K = shape.hidden_dim, shape.intermediate_dim, shape.experts_per_token
+    E = n_experts or shape.n_experts
     g = torch.Generator(device=dev)
     g.manual_seed(4)
-    eng = pkg.MoeEngine(H, IM, E, K, max_tokens=1024, weight_format=pkg.WEIGHTS_MXFP4)
-    if os.environ.get("GPTOSS_SKIP_EPILOGUE"):  # measurement aid
-        eng.set_option("skip_epilogue", int(os.environ["GPTOSS_SKIP_EPILOGUE"]))
+    eng = pkg.MoeEngine(H, IM, E, K, max_tokens=max_tokens, weight_format=pkg.WEIGHTS_MXFP4,
+                        device=dev.index or 0)
 
     def codes(rows, k):
         return torch.randint(0, 256, (E, rows, k // 2), generator=g, device=dev, dtype=torch.uint8)
@@ -536,23 +683,34 @@ def run_decode_mxfp4(args):
     # logits = bias + noise with sigma ~1.07 (t has sigma 0.25, router weights 0.08); a
     # Gaussian of that width selects about like Gumbel noise of scale 0.83, for which
     # P(expert) is proportional to exp(bias / 0.83): bias = 0.83 * log(Zipf weight)
-    b_router = (zipf / zipf.sum()).log().float() * 0.83
-    w_router = (torch.randn((E, H), generator=g, device=dev) * 0.08).bfloat16()
-    b1 = (torch.randn((E, 2 * IM), generator=g, device=dev) * 0.01).float()
-    b2 = (torch.randn((E, H), generator=g, device=dev) * 0.01).float()
-    eng.load_layer_mxfp4(0, w_router, b_router, codes(2 * IM, H), scales(2 * IM, H), b1,
-                         codes(H, IM), scales(H, IM), b2, on_device=True)
+    w = {"b_router": ((zipf / zipf.sum()).log().float() * 0.83).contiguous(),
+         "w_router": (torch.randn((E, H), generator=g, device=dev) * 0.08).bfloat16(),
+         "b_mlp1": (torch.randn((E, 2 * IM), generator=g, device=dev) * 0.01).float(),
+         "b_mlp2": (torch.randn((E, H), generator=g, device=dev) * 0.01).float(),
+         "w1_codes": codes(2 * IM, H), "w1_scales": scales(2 * IM, H),
+         "w2_codes": codes(H, IM), "w2_scales": scales(H, IM)}
+    eng.load_layer_mxfp4(0, w["w_router"], w["b_router"], w["w1_codes"], w["w1_scales"], w["b_mlp1"],
+                         w["w2_codes"], w["w2_scales"], w["b_mlp2"], on_device=True)
+    return {"engine": eng, "weights": w, "H": H, "IM": IM, "E": E, "K": K}
+
+
+def measure_decode_mxfp4(args, pkg, dev):
+    """Configuration 4 at T = 64 / 256 / 1024: tokens/s, stage times and the rate at which
+    the packed weights of the touched experts stream from HBM (the kernel's roofline)."""
+    import torch
+
+    case = c4_layer(pkg, dev)
+    eng, H, IM, E = case["engine"], case["H"], case["IM"], case["E"]
     torch.cuda.empty_cache()
     peaks = read_peaks()
     stream = torch.cuda.current_stream().cuda_stream
     per_expert_bytes = 3 * IM * H // 2 + 3 * IM * H // 32
+    g = torch.Generator(device=dev)
+    g.manual_seed(44)
     results = {}
-    sampler = ClockSampler(0)
-    sampler.start()
     for T in (64, 256, 1024):
-        t = (torch.randn((T, H), generator=g, device=dev) * 0.25).bfloat16()
-        x = torch.randn((T, H), generator=g, device=dev).bfloat16()
-        for _ in range(args.warmup):
+        t, x = c4_tokens(T, H, g, dev)
+        for _ in range(max(3, args.warmup)):
             eng.forward(0, t, x, None, T, stream)
         torch.cuda.synchronize()
         if eng.device_status() != 0:
@@ -571,31 +729,49 @@ def run_decode_mxfp4(args):
         counts = np.bincount(r["topk_i"].ravel(), minlength=E)
         touched = int((counts > 0).sum())
         gemm_ms = stage_ms["gate_up"] + stage_ms["down"]
-        results[T] = {
+        gbs = touched * per_expert_bytes / (gemm_ms * 1e-3) / 1e9
+        results[str(T)] = {
             "tokens_per_s": T / (ms * 1e-3), "ms_per_step": ms, "stage_ms": stage_ms,
             "experts_touched": touched, "busiest_expert_share": float(counts.max() / counts.sum()),
-            "weight_gbs": touched * per_expert_bytes / (gemm_ms * 1e-3) / 1e9,
+            "roofline": {"kernel": "grouped_gemm_pair_kernel<*, mxfp4> (gate_up + down)",
+                         "bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / peaks["hbm_gbs"], "peak_source": f"{peaks['source']} hbm_gbs",
+                         "algorithmic_bytes_per_step": touched * per_expert_bytes},
         }
+    out = {"workload": "gpt-oss-120b-moe-layer-mxfp4-decode", "weights": "MXFP4 (e2m1 + e8m0/32)",
+           "routing": "Zipf(1.1)-biased router", "launches": eng.launch_count(), "decode": results}
+    eng.close()
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_decode_mxfp4(args):
+    """--workload c4: configuration 4 as its own line (the T = 1024 figures on top)."""
+    import torch
+
+    pkg = entry.load_package()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    sampler = ClockSampler(0)
+    sampler.start()
+    res = measure_decode_mxfp4(args, pkg, dev)
     clocks = sampler.result()
-    top = results[1024]
+    top = res["decode"]["1024"]
+    shape = workload_shape("c3")
     line = {
         "metric": METRIC, "value": top["tokens_per_s"], "unit": UNIT, "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": top["ms_per_step"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": "gpt-oss-120b-moe-layer-mxfp4-decode-T1024", "hidden": H,
-                   "intermediate": IM, "experts": E, "top_k": K, "weights": "MXFP4 (e2m1 + e8m0/32)",
-                   "routing": "Zipf(1.1)-biased router", "l2": "inputs larger than L2 (1.69 GB of "
+        "config": {"workload": "gpt-oss-120b-moe-layer-mxfp4-decode-T1024", "hidden": shape.hidden_dim,
+                   "intermediate": shape.intermediate_dim, "experts": shape.n_experts,
+                   "top_k": shape.experts_per_token, "weights": res["weights"],
+                   "routing": res["routing"], "l2": "inputs larger than L2 (1.69 GB of "
                    "packed expert weights streamed every step)"},
-        "roofline": {"kernel": "grouped_gemm_pair_kernel<*, 5, mxfp4> (gate_up + down)",
-                     "bound": "hbm", "achieved": top["weight_gbs"], "peak": peaks["hbm_gbs"],
-                     "unit": "GB/s", "frac": top["weight_gbs"] / peaks["hbm_gbs"],
-                     "peak_source": f"{peaks['source']} hbm_gbs", "traffic": None},
-        "decode": {str(k): v for k, v in results.items()}, "cpu_baseline": None,
-        "e2e": None, "gpu_launches": eng.launch_count(), "clocks": clocks,
+        "roofline": dict(top["roofline"], traffic=None), "decode": res["decode"],
+        "cpu_baseline": None, "e2e": None, "gpu_launches": res["launches"], "clocks": clocks,
     }
     print(json.dumps(line), flush=True)
-    eng.close()
 
 
 def run_decode_120b(args):
@@ -755,12 +931,13 @@ def main():
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c2s", "c4", "c5", "tiny"])
+    ap.add_argument("--workload", default="c3",
+                    choices=["c3", "c2", "c2s", "c3s", "c4", "c5", "tiny"])
     ap.add_argument("--cpu-tokens", type=int, default=None,
                     help="tokens in the CPU sample (default 256 for ours, 64 for reference)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true",
-                    help="skip the 120b-shape layer measured beside the headline workload")
+                    help="skip the parity pass and the workloads measured beside the headline one")
     args = ap.parse_args()
     entry.load_package()
     if args.workload == "c4" and args.impl == "ours":
@@ -782,6 +959,8 @@ def main():
     else:
         args.steps = args.steps if args.steps is not None else 100
         args.warmup = max(3, args.warmup if args.warmup is not None else 10)
+        if args.workload in ("c2s", "c3s", "tiny"):
+            args.no_extra = True
         run_ours(args, shape)
 
 

@@ -116,6 +116,8 @@ def load_library() -> ctypes.CDLL:
         "gptoss_moe_ep_unique_id": (c_int, [vp]),
         "gptoss_moe_ep_init": (c_int, [vp, vp]),
         "gptoss_moe_ep_transport": (c_int, [vp]),
+        "gptoss_moe_ep_init_local": (c_int, [ctypes.POINTER(vp), c_int]),
+        "gptoss_moe_forward_part": (c_int, [vp, c_int, c_int, vp, vp, vp, c_int, vp]),
         "gptoss_moe_version": (c_char_p, []),
         "gptoss_moe_permute_static": (c_int, [vp, vp, c_int, c_int, c_int, vp, vp, vp, vp, vp]),
         "gptoss_decode_create": (c_int, [ctypes.POINTER(ModelConfig), c_int, c_int,
@@ -344,6 +346,25 @@ class MoeEngine:
     def ep_init(self, unique_id: bytes):
         buf = (ctypes.c_ubyte * 128).from_buffer_copy(unique_id)
         self._check(self.lib.gptoss_moe_ep_init(self.handle, ctypes.cast(buf, ctypes.c_void_p)))
+
+    @staticmethod
+    def ep_init_local(engines):
+        """gptoss_moe_ep_init_local: engines[r] was created with ep_rank r, ep_size len(engines);
+        all of them live in this process."""
+        lib = load_library()
+        arr = (ctypes.c_void_p * len(engines))(*[e.handle for e in engines])
+        rc = lib.gptoss_moe_ep_init_local(arr, len(engines))
+        if rc != GPTOSS_OK:
+            text = lib.gptoss_moe_last_error(engines[0].handle).decode()
+            for e in engines:
+                t2 = lib.gptoss_moe_last_error(e.handle).decode()
+                if t2:
+                    text = t2
+            raise MoeError(rc, text or lib.gptoss_moe_last_error(None).decode())
+
+    def forward_part(self, layer, part, t, x, pos, n_tokens, stream=0):
+        self._check(self.lib.gptoss_moe_forward_part(self.handle, layer, part, _ptr(t), _ptr(x),
+                                                     _ptr(pos), n_tokens, ctypes.c_void_p(stream)))
 
     @property
     def ep_transport(self) -> int:

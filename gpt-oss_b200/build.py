@@ -19,7 +19,7 @@ CU_SOURCES = ["moe_api.cu", "router.cu", "permute.cu", "grouped_gemm.cu", "group
 HEADERS = ["common.cuh", "engine.h", "ep.h", "gemm_epilogue.cuh", "umma_2sm.cuh"]
 
 NVCC_FLAGS = [
-    "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+    "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "--threads", "0",
     "-Xcompiler", "-fPIC,-fvisibility=default", "-shared",
 ]
 
@@ -62,16 +62,20 @@ def build_library(force: bool = False, verbose: bool = False) -> pathlib.Path:
 
 HOST_LIB = PKG_DIR / "libgptoss_getp_b200.so"
 HARNESS = PKG_DIR.parent / "tests" / "host" / "_build" / "getp_harness"
+AGREEMENT_TEST = PKG_DIR.parent / "tests" / "host" / "_build" / "step_agreement_test"
 
 
 def build_host(force: bool = False) -> pathlib.Path:
     """Compile the C++17 getp entry points (host/getp_run_b200.cpp, no CUDA in it) into
     libgptoss_getp_b200.so next to the CUDA library, and the test host program that calls
-    them (tests/host/getp_harness.cpp).  `encode` stays undefined in the library: the
+    them (tests/host/getp_harness.cpp), plus the CPU test program of the step agreement
+    (tests/host/step_agreement_test.cpp).  `encode` stays undefined in the library: the
     host program supplies its tokenizer."""
     gxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else (shutil.which("g++") or "g++")
     src = PKG_DIR / "host" / "getp_run_b200.cpp"
-    deps = [src, PKG_DIR / "host" / "getp_abi.h", PKG_DIR.parent / "include" / "gptoss_decode_b200.h"]
+    deps = [src, PKG_DIR / "host" / "getp_abi.h", PKG_DIR / "host" / "step_agreement.h",
+            PKG_DIR.parent / "include" / "gptoss_decode_b200.h",
+            PKG_DIR.parent / "include" / "gptoss_moe_b200.h"]
     if force or _stale(HOST_LIB, deps):
         cmd = [gxx, "-std=c++17", "-O2", "-fPIC", "-shared", "-pthread", "-Wall", "-o", str(HOST_LIB),
                str(src), "-L", str(PKG_DIR), "-lgptoss_moe_b200", "-Wl,-rpath,$ORIGIN"]
@@ -84,6 +88,13 @@ def build_host(force: bool = False) -> pathlib.Path:
         cmd = [gxx, "-std=c++17", "-O2", "-pthread", "-Wall", "-o", str(HARNESS), str(hsrc),
                "-L", str(PKG_DIR), "-lgptoss_getp_b200", "-lgptoss_moe_b200",
                "-Wl,-rpath," + str(PKG_DIR), "-Wl,-rpath,$ORIGIN/../../../gpt-oss_b200"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError("g++ failed:\n" + res.stdout + res.stderr)
+    tsrc = PKG_DIR.parent / "tests" / "host" / "step_agreement_test.cpp"
+    if tsrc.exists() and (force or _stale(AGREEMENT_TEST, [tsrc, PKG_DIR / "host" / "step_agreement.h"])):
+        AGREEMENT_TEST.parent.mkdir(parents=True, exist_ok=True)
+        cmd = [gxx, "-std=c++17", "-O2", "-pthread", "-Wall", "-o", str(AGREEMENT_TEST), str(tsrc)]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError("g++ failed:\n" + res.stdout + res.stderr)

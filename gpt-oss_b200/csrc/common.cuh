@@ -34,6 +34,19 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
+// Programmatic dependent launch.  A kernel launched with the stream-serialization
+// attribute may start while its predecessor in the stream is still running; it must
+// call grid_dependency_wait() before it reads anything the predecessor wrote (the wait
+// returns once the predecessor has finished and its writes are visible).  Without the
+// attribute both are no-ops.  grid_launch_dependents() lets the successor's CTAs be
+// scheduled as soon as SMs have room for them.
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- bf16 utils
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
@@ -64,11 +77,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
-#ifdef GPTOSS_TEST_WAIT
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#else
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#endif
       "selp.u32 %0, 1, 0, p;\n\t"
       "}"
       : "=r"(ok)

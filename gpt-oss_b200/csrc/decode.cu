@@ -642,6 +642,8 @@ int gptoss_decode_load_weights(gptoss_decode_t *h, const gptoss_model_weights_t 
                                    w->b_mlp2 + l * E * H);
     if (rc) return dfail(h, rc, "MoE layer %d: %s", static_cast<int>(l), gptoss_moe_last_error(h->moe));
   }
+  if ((rc = upload_finish(h->moe))) return dfail(h, rc, "weight upload: %s", gptoss_moe_last_error(h->moe));
+  gptoss_moe_release_upload_staging(h->moe);  // the model is in place: 128 MB of staging go back
   h->loaded = true;
   return GPTOSS_OK;
 }
@@ -676,6 +678,7 @@ int gptoss_decode_set_tensor(gptoss_decode_t *h, const char *name, int layer, co
         DCK(h, cudaMemcpy(dst, src, sl.n * sizeof(bf16), cudaMemcpyDeviceToDevice));
       } else if (!on_device && !is_bf16) {
         int rc = upload_f32_as_bf16(h->moe, dst, static_cast<const float *>(src), sl.n);
+        if (!rc) rc = upload_finish(h->moe);
         if (rc) return dfail(h, rc, "upload: %s", gptoss_moe_last_error(h->moe));
       } else {
         return dfail(h, GPTOSS_E_INVALID, "%s takes fp32 host data or bf16 device data", name);
@@ -837,7 +840,6 @@ static int linear_own(gptoss_decode *h, const CUtensorMap &tw, const CUtensorMap
   g.out_ld = N;
   g.limit = 0.f;
   g.status = h->status;
-  g.skip_epilogue = 0;
   DCK(h, launch_linear_pair(h->num_sms, tw, tx, g, st, nullptr, f32_out));
   return GPTOSS_OK;
 }
@@ -938,6 +940,9 @@ int gptoss_decode_step(gptoss_decode_t *h, const int *tokens, const int *pos, in
     cudaMemset(h->status, 0, sizeof(int));
     return dfail(h, GPTOSS_E_DEVICE, "a decode kernel reported status %d (token id out of range?)", dev_status);
   }
+  // the MoE engine keeps its own status word: pipeline and peer-flag waits that ran out
+  if (gptoss_moe_take_status(h->moe) != GPTOSS_OK)
+    return dfail(h, GPTOSS_E_DEVICE, "MoE block: %s", gptoss_moe_last_error(h->moe));
   return GPTOSS_OK;
 }
 

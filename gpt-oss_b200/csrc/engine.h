@@ -30,10 +30,11 @@ struct LayerWeights {
   bf16 *w2 = nullptr;         // [E_local, H, IM]
   float *b2 = nullptr;        // [E_local, H]
   // MXFP4 storage, tiled: [expert][128-row block][64-k block][4096 B codes + 256 B scales]
-  uint8_t *w1_blocks = nullptr, *w1_scales = nullptr;  // (scales pointers unused: kept in the tile)
-  uint8_t *w2_blocks = nullptr, *w2_scales = nullptr;
+  uint8_t *w1_blocks = nullptr, *w2_blocks = nullptr;
   CUtensorMap tmap_w1, tmap_w2;            // boxes of 240 weight rows (N operand)
   CUtensorMap tmap_w1_rows, tmap_w2_rows;  // boxes of 128 weight rows (M operand, CTA pairs)
+  CUtensorMap tmap_router;                 // router rows in boxes of one K chunk (made on first use)
+  bool tmap_router_ready = false;
   float *rms_ffn = nullptr;   // [H] scale of the RMSNorm in front of the block (optional)
   bool loaded = false;
 };
@@ -108,14 +109,28 @@ struct gptoss_moe {
   cudaStream_t s_h2d = nullptr, s_comp = nullptr, s_d2h = nullptr;
   long long host_submitted = 0;
 
+  // router: tensor map of the caller's activations, kept while the same buffer comes back
+  CUtensorMap tmap_router_t;
+  const void *router_t_ptr = nullptr;
+  int router_t_rows = 0;
+
+  // weight upload: fp32 host tensors through pinned and device staging, converted on the device
+  static constexpr size_t kUploadChunk = (size_t)8 << 20;  // elements per chunk (32 MB of fp32)
+  cudaStream_t up_stream = nullptr;
+  float *up_pinned[2] = {nullptr, nullptr}, *up_dev[2] = {nullptr, nullptr};
+  cudaEvent_t up_done[2] = {nullptr, nullptr};
+  int up_next = 0;
+
   int *status = nullptr;  // device status word
   int opt_gemm_impl = GPTOSS_GEMM_PAIR;
   int opt_keep_logits = 0;
   int opt_exact_ties = 1;
   int opt_time_stages = 0;
-  int opt_skip_epilogue = 0;
   int opt_ep_overlap = 0;  // peer transport: second half of the experts gathered under the first half's GEMM
-  int opt_pair_stages = 6;  // operand ring depth of the CTA-pair GEMM (4, 5 or 6)
+  int opt_router_impl = 0;  // 0 = tcgen05 router, 1 = mma.sync router
+  int opt_pair_rings = 8;   // CTA-pair GEMM: weight slots of the twelve 16 KB operand slots (6..9)
+  int opt_dependent_launch = 0;  // programmatic dependent launch between the layer's kernels
+  int opt_wait_limit_ms = 2000;  // longest wait for another rank's flag (peer-memory transport)
   gptoss::StageTimer timers[8];
   long long launches = 0;
   mutable std::string err;
@@ -127,10 +142,8 @@ struct gptoss_moe {
 namespace gptoss {
 
 // router.cu
-cudaError_t launch_router_topk(const bf16 *t, const bf16 *w_router, const float *b_router,
-                               const int *pos, int T, int H, int E, int K, int *topk_i,
-                               float *topk_v, float *logits_opt, int exact_ties, int *status,
-                               cudaStream_t stream, long long *launches);
+cudaError_t launch_router_topk(gptoss_moe *h, int layer, const bf16 *t, const int *pos, int T,
+                               float *logits_opt, cudaStream_t stream);
 cudaError_t launch_rmsnorm(bf16 *out, const bf16 *x, const float *w, const int *pos, int T, int H,
                            cudaStream_t stream, long long *launches);
 
@@ -190,6 +203,12 @@ cudaError_t launch_f32_to_bf16(bf16 *dst, const float *src, size_t n, cudaStream
 
 }  // namespace gptoss
 
+// moe_api.cu: after a stream synchronisation, GPTOSS_E_DEVICE (and the word cleared) when a
+// kernel of this engine reported a problem
+extern "C" int gptoss_moe_take_status(gptoss_moe *h);
 // moe_api.cu: fp32 host tensor -> bf16 device tensor (round to nearest even) through a
 // pinned double buffer; errors go to the handle's error text
 extern "C" int upload_f32_as_bf16(gptoss_moe *h, gptoss::bf16 *dst, const float *src, size_t n);
+// waits for the uploads queued so far / gives the staging buffers back
+extern "C" int upload_finish(gptoss_moe *h);
+extern "C" void gptoss_moe_release_upload_staging(gptoss_moe *h);

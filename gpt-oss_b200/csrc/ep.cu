@@ -44,6 +44,12 @@
 // first flags of the next layer (every peer has combined).  The two transports add
 // the same values in the same order, so their results are equal bit for bit.
 //
+// The peer-memory transport has two ways to learn the peers' addresses: CUDA IPC handles
+// exchanged over the NCCL communicator (one process per rank, gptoss_moe_ep_init), or
+// plain pointers when one process drives all GPUs with a host thread each, as the
+// reference's getp engine does (gptoss_moe_ep_init_local: peer access enabled between
+// the devices, no NCCL, no IPC).
+//
 // NCCL is loaded with dlopen on first use, so single-GPU users of the library do
 // not need it; in a process that already loaded NCCL (PyTorch) the same copy is
 // picked up.
@@ -130,6 +136,7 @@ struct EpState {
   // peer-memory transport
   int transport = 0;            // 0 = NCCL send / recv, 1 = peer loads
   bool peer_ok = false;
+  bool local = false;           // peers wired inside one process (no IPC mappings to close)
   std::string peer_why;         // why the peer transport is not available
   int max_t = 0;
   bf16 *pub_t = nullptr;        // [max_t, H] this rank's activations, mapped by the peers
@@ -164,7 +171,8 @@ __global__ void ep_signal_kernel(const PeerCtl ctl, int N, int which, int rank, 
 
 // Waits until every rank's flag of this round is here; false (and a status) after
 // kWaitLimitNs.  Called by the first warp of a CTA, followed by a CTA barrier.
-__device__ __forceinline__ bool ep_wait_flags(const int *flags, int N, int round, int *status) {
+__device__ __forceinline__ bool ep_wait_flags(const int *flags, int N, int round, int *status,
+                                              uint64_t limit_ns) {
   const int lane = threadIdx.x & 31;
   bool ok = true;
   if (lane < N) {
@@ -179,7 +187,7 @@ __device__ __forceinline__ bool ep_wait_flags(const int *flags, int N, int round
         const uint64_t now = global_timer_ns();
         if (t0 == 0) {
           t0 = now;
-        } else if (now - t0 > kWaitLimitNs) {
+        } else if (now - t0 > limit_ns) {
           set_status(status, kStatusWaitTimeoutPeer);
           ok = false;
           break;
@@ -216,9 +224,9 @@ ep_publish_meta_kernel(const int *__restrict__ topk_i, const float *__restrict__
 __global__ void __launch_bounds__(256)
 ep_owner_slots_kernel(const int *all_meta, const int *flags, int round, int N, int rank,
                       int max_t, int K, int *__restrict__ stage_e, float *__restrict__ stage_w,
-                      int *status) {
+                      int *status, uint64_t limit_ns) {
   // every rank's routing result (and, by the order of its stream, its activations)
-  if (threadIdx.x < 32) ep_wait_flags(flags, N, round, status);
+  if (threadIdx.x < 32) ep_wait_flags(flags, N, round, status, limit_ns);
   __syncthreads();
   const int per = max_t * K;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -265,14 +273,28 @@ gather_rows_peer_kernel(bf16 *__restrict__ xs, const PeerRows src, int max_t,
   }
 }
 
+// 16 bytes that another GPU may have written while this kernel was already running (it
+// spins on the flag that announces them): an ordinary relaxed load at system scope, not
+// the read-only path, which is only defined for data that never changes under a kernel.
+__device__ __forceinline__ uint4 ld_peer_v4(const uint4 *p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
 // x[t] += sum over the owners o (ascending) of token t of the owner's pre-reduced row
 // (rank * max_t + t) in its out_rows, read from the owner's memory.  One warp per token.
 __global__ void __launch_bounds__(256)
 combine_peer_kernel(bf16 *__restrict__ x, const PeerRows outs, const int *__restrict__ topk_i,
                     int T, int K, int N, int rank, int max_t, int H, const int *flags, int round,
-                    int *status) {
-  // every owner's sums are complete (and every peer is done with this rank's activations)
-  if (threadIdx.x < 32) ep_wait_flags(flags, N, round, status);
+                    int *status, uint64_t limit_ns) {
+  // every owner's sums are complete (and every peer is done with this rank's activations);
+  // a rank without tokens still takes this wait (one CTA): it is what allows it to
+  // overwrite its published buffers in the next layer
+  if (threadIdx.x < 32) ep_wait_flags(flags, N, round, status, limit_ns);
   __syncthreads();
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -291,7 +313,7 @@ combine_peer_kernel(bf16 *__restrict__ x, const PeerRows outs, const int *__rest
 #pragma unroll
     for (int o = 0; o < GPTOSS_MAX_TOPK; o++)
       if (o < N && ((owners >> o) & 1u))
-        v[o] = __ldg(reinterpret_cast<const uint4 *>(outs.p[o] + row) + p);
+        v[o] = ld_peer_v4(reinterpret_cast<const uint4 *>(outs.p[o] + row) + p);
     const uint4 xv = o4[p];
     float s[8];
 #pragma unroll
@@ -365,6 +387,24 @@ ep_pack_kernel(const bf16 *__restrict__ t, const int *__restrict__ topk_i,
   }
 }
 
+// Checks the all-gathered row counts counts[src * N + dst] against the capacities every
+// rank was created with; NULL when every rank can take part.
+const char *ep_counts_problem(const int *counts, int N, int max_tokens, int send_cap,
+                              int rows_cap) {
+  for (int a = 0; a < N; a++) {
+    long long sent = 0, received = 0;
+    for (int b = 0; b < N; b++) {
+      const int s = counts[a * N + b], r = counts[b * N + a];
+      if (s < 0 || s > max_tokens) return "row counts exchanged between ranks are out of range";
+      sent += s;
+      received += r;
+    }
+    if (sent > send_cap || received > rows_cap)
+      return "more rows routed than the engines were created for";
+  }
+  return nullptr;
+}
+
 static int ep_fail(gptoss_moe *h, int code, const std::string &msg) {
   h->err = msg;
   return code;
@@ -412,29 +452,51 @@ struct EpStageScope {
   }
 };
 
-// The layer over peer memory (see the head of this file).
-static int ep_forward_peer(gptoss_moe *h, EpState *ep, int layer, const bf16 *t, void *x_io, int T,
-                           cudaStream_t st) {
+// The layer over peer memory (see the head of this file), in three parts that one stream
+// runs back to back.  A host that drives several ranks from ONE stream of one GPU (ranks as
+// engines on the same device) can interleave them part by part - every rank's part 0, then
+// every rank's part 1, then every rank's part 2 - and no kernel ever waits for a later
+// launch; separate launches that wait for one another must never share a GPU otherwise.
+static void peer_ctl_of(const EpState *ep, PeerCtl *ctl) {
+  for (int p = 0; p < GPTOSS_MAX_TOPK; p++)
+    ctl->p[p] = static_cast<int *>(p < ep->N ? ep->peer_ctl[p] : nullptr);
+}
+
+// part 0: publish - activations where the peers can read them, routing result into every
+// rank's memory, then the flag "rank r of this round is in place"
+static int ep_peer_publish(gptoss_moe *h, EpState *ep, const bf16 *t, int T, cudaStream_t st) {
   const int N = ep->N, K = h->K, H = h->H, max_t = ep->max_t;
   const int per = max_t * K;
   PeerCtl ctl;
-  for (int p = 0; p < GPTOSS_MAX_TOPK; p++) ctl.p[p] = static_cast<int *>(p < N ? ep->peer_ctl[p] : nullptr);
+  peer_ctl_of(ep, &ctl);
   const int round = ++ep->round;
+  EpStageScope sc(h, 5, st);
+  if (T > 0)
+    EP_CUDA(h, cudaMemcpyAsync(ep->pub_t, t, static_cast<size_t>(T) * H * sizeof(bf16),
+                               cudaMemcpyDeviceToDevice, st));
+  ep_publish_meta_kernel<<<(per + 255) / 256, 256, 0, st>>>(h->topk_i, h->topk_v, T, max_t, K,
+                                                            ctl, N, ep->rank);
+  ep_signal_kernel<<<1, 32, 0, st>>>(ctl, N, 0, ep->rank, round);
+  h->launches += 2;
+  EP_CUDA(h, cudaGetLastError());
+  return GPTOSS_OK;
+}
+
+// part 1: owner - wait for every rank's flag, sort all N * max_t rows by local expert, pull
+// the rows out of the homes' memory (dispatch and gather in one kernel), both GEMMs, per-row
+// sums, then the flag "my sums are complete"
+static int ep_peer_owner(gptoss_moe *h, EpState *ep, int layer, const bf16 *t, cudaStream_t st) {
+  const int N = ep->N, K = h->K, H = h->H, max_t = ep->max_t;
+  const int per = max_t * K;
+  const int round = ep->round;
+  const uint64_t limit_ns = static_cast<uint64_t>(h->opt_wait_limit_ms) * 1000000ull;
+  PeerCtl ctl;
+  peer_ctl_of(ep, &ctl);
   {
     EpStageScope sc(h, 5, st);
-    // 1. publish: activations where the peers can read them, routing result into every
-    //    rank's memory, then the flag "rank r of this round is in place"
-    if (T > 0)
-      EP_CUDA(h, cudaMemcpyAsync(ep->pub_t, t, static_cast<size_t>(T) * H * sizeof(bf16),
-                                 cudaMemcpyDeviceToDevice, st));
-    ep_publish_meta_kernel<<<(per + 255) / 256, 256, 0, st>>>(h->topk_i, h->topk_v, T, max_t, K,
-                                                              ctl, N, ep->rank);
-    ep_signal_kernel<<<1, 32, 0, st>>>(ctl, N, 0, ep->rank, round);
-    h->launches += 2;
-    EP_CUDA(h, cudaGetLastError());
-    // 2. owner view of all N * max_t rows, once every rank's flag is here
     ep_owner_slots_kernel<<<(N * per + 255) / 256, 256, 0, st>>>(
-        ep->all_meta, ep->ctl, round, N, ep->rank, max_t, K, ep->recv_e, ep->recv_w, h->status);
+        ep->all_meta, ep->ctl, round, N, ep->rank, max_t, K, ep->recv_e, ep->recv_w, h->status,
+        limit_ns);
     h->launches++;
     EP_CUDA(h, cudaGetLastError());
   }
@@ -443,16 +505,14 @@ static int ep_forward_peer(gptoss_moe *h, EpState *ep, int layer, const bf16 *t,
   h->stage_expert = ep->recv_e;
   h->stage_weight = ep->recv_w;
   h->stage_R = R;
-  PeerRows src, outs;
-  for (int p = 0; p < GPTOSS_MAX_TOPK; p++) {
+  PeerRows src;
+  for (int p = 0; p < GPTOSS_MAX_TOPK; p++)
     src.p[p] = static_cast<const bf16 *>(p < N ? ep->peer_t[p] : nullptr);
-    outs.p[p] = static_cast<const bf16 *>(p < N ? ep->peer_out[p] : nullptr);
-  }
-  src.p[ep->rank] = t;  // own rows straight from the caller's buffer
-  // 3. sort by local expert; dispatch and gather in one kernel.  With the CTA-pair GEMM
-  //    the experts are taken in two halves: the rows of the second half are pulled on a
-  //    second stream while the first half is already being multiplied (the gather kernel
-  //    uses no shared memory and few registers, so its CTAs share the SMs with the GEMM's).
+  if (t) src.p[ep->rank] = t;  // own rows straight from the caller's buffer
+  // With the CTA-pair GEMM the experts can be taken in two halves: the rows of the second
+  // half are pulled on a second stream while the first half is already being multiplied
+  // (the gather kernel uses no shared memory and few registers, so its CTAs share the SMs
+  // with the GEMM's).
   const bool halves = h->opt_ep_overlap && h->opt_gemm_impl == GPTOSS_GEMM_PAIR && h->El >= 2 && ep->s2;
   const int e_mid = halves ? h->El / 2 : h->El;
   {
@@ -488,26 +548,56 @@ static int ep_forward_peer(gptoss_moe *h, EpState *ep, int layer, const bf16 *t,
     EP_CUDA(h, launch_down(h, layer, st));
   }
   {
-    // 4. per-row sums over this rank's experts, then "my sums are complete" to everyone
     EpStageScope sc(h, 6, st);
     EP_CUDA(h, launch_reduce_rows(h, ep->out_rows, R, st, /*skip_empty=*/true));
     ep_signal_kernel<<<1, 32, 0, st>>>(ctl, N, 1, ep->rank, round);
     h->launches++;
     EP_CUDA(h, cudaGetLastError());
   }
-  {
-    // 5. return and combine in one kernel
-    EpStageScope sc(h, 4, st);
-    if (T > 0) {
-      const int warps = 8;
-      combine_peer_kernel<<<(T + warps - 1) / warps, warps * 32, 0, st>>>(
-          static_cast<bf16 *>(x_io), outs, h->topk_i, T, K, N, ep->rank, max_t, H, ep->ctl + N, round,
-          h->status);
-      h->launches++;
-      EP_CUDA(h, cudaGetLastError());
-    }
-  }
   return GPTOSS_OK;
+}
+
+// part 2: home - wait for every owner's flag, pull the sums of this rank's tokens and add
+// them and the residual (return and combine in one kernel).  Without tokens the kernel is
+// still launched, with one CTA, for its wait: the second flags are also the proof that
+// every peer has finished reading this rank's published buffers.
+static int ep_peer_combine(gptoss_moe *h, EpState *ep, void *x_io, int T, cudaStream_t st) {
+  const int N = ep->N, K = h->K, H = h->H, max_t = ep->max_t;
+  const uint64_t limit_ns = static_cast<uint64_t>(h->opt_wait_limit_ms) * 1000000ull;
+  PeerRows outs;
+  for (int p = 0; p < GPTOSS_MAX_TOPK; p++)
+    outs.p[p] = static_cast<const bf16 *>(p < N ? ep->peer_out[p] : nullptr);
+  EpStageScope sc(h, 4, st);
+  const int warps = 8;
+  const int grid = T > 0 ? (T + warps - 1) / warps : 1;
+  combine_peer_kernel<<<grid, warps * 32, 0, st>>>(static_cast<bf16 *>(x_io), outs, h->topk_i, T, K,
+                                                   N, ep->rank, max_t, H, ep->ctl + N, ep->round,
+                                                   h->status, limit_ns);
+  h->launches++;
+  EP_CUDA(h, cudaGetLastError());
+  return GPTOSS_OK;
+}
+
+static int ep_forward_peer(gptoss_moe *h, EpState *ep, int layer, const bf16 *t, void *x_io, int T,
+                           cudaStream_t st) {
+  int rc = ep_peer_publish(h, ep, t, T, st);
+  if (rc) return rc;
+  if ((rc = ep_peer_owner(h, ep, layer, t, st))) return rc;
+  return ep_peer_combine(h, ep, x_io, T, st);
+}
+
+int ep_forward_part(gptoss_moe *h, int layer, int part, const void *t, void *x_io, int T,
+                    void *stream) {
+  EpState *ep = static_cast<EpState *>(h->ep);
+  if (!ep || !ep->peer_ok || ep->transport != 1)
+    return ep_fail(h, GPTOSS_E_STATE, "the layer runs in parts only over the peer-memory transport");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (part) {
+    case 0: return ep_peer_publish(h, ep, static_cast<const bf16 *>(t), T, st);
+    case 1: return ep_peer_owner(h, ep, layer, static_cast<const bf16 *>(t), st);
+    case 2: return ep_peer_combine(h, ep, x_io, T, st);
+    default: return ep_fail(h, GPTOSS_E_INVALID, "part must be 0, 1 or 2");
+  }
 }
 
 int ep_set_transport(gptoss_moe *h, int transport) {
@@ -517,6 +607,9 @@ int ep_set_transport(gptoss_moe *h, int transport) {
     return ep_fail(h, GPTOSS_E_INVALID, "ep_transport: 0 = NCCL send/recv, 1 = peer memory");
   if (transport == 1 && !ep->peer_ok)
     return ep_fail(h, GPTOSS_E_STATE, "peer-memory transport unavailable: " + ep->peer_why);
+  if (transport == 0 && !ep->comm)
+    return ep_fail(h, GPTOSS_E_STATE, "NCCL transport unavailable: the ranks were wired inside "
+                                      "one process without a communicator");
   ep->transport = transport;
   return GPTOSS_OK;
 }
@@ -528,12 +621,13 @@ int ep_get_transport(const gptoss_moe *h) {
 
 int ep_forward(gptoss_moe *h, int layer, const void *t_in, void *x_io, int T, void *stream) {
   EpState *ep = static_cast<EpState *>(h->ep);
-  if (!ep || !ep->comm)
+  if (!ep || (!ep->comm && !ep->peer_ok))
     return ep_fail(h, GPTOSS_E_STATE,
                    "expert parallelism is not set up: call gptoss_moe_ep_init first");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (ep->transport == 1)
     return ep_forward_peer(h, ep, layer, static_cast<const bf16 *>(t_in), x_io, T, st);
+  if (!ep->comm) return ep_fail(h, GPTOSS_E_STATE, "no NCCL communicator on this engine");
   const int N = ep->N, K = h->K, H = h->H;
   const bf16 *t = static_cast<const bf16 *>(t_in);
   std::vector<int> soff(N + 1, 0), roff(N + 1, 0);
@@ -575,16 +669,18 @@ int ep_forward(gptoss_moe *h, int layer, const void *t_in, void *x_io, int T, vo
     EP_CUDA(h, cudaMemcpyAsync(ep->counts_host, ep->counts_dev, sizeof(int) * N * N,
                                cudaMemcpyDeviceToHost, st));
     EP_CUDA(h, cudaStreamSynchronize(st));
-    for (int p2 = 0; p2 < N; p2++) {
-      const int s = ep->counts_host[ep->rank * N + p2];
-      const int r = ep->counts_host[p2 * N + ep->rank];
-      if (s < 0 || r < 0 || s > h->max_tokens || r > h->max_tokens)
-        return ep_fail(h, GPTOSS_E_COMM, "row counts exchanged between ranks are out of range");
-      soff[p2 + 1] = soff[p2] + s;
-      roff[p2 + 1] = roff[p2] + r;
+    // go / no-go from the whole N x N matrix, which every rank holds: all ranks decide
+    // alike (max_tokens is the same everywhere, gptoss_moe_ep_init checked it), so none
+    // leaves the others inside a grouped send / recv that can never be matched
+    {
+      const char *why = ep_counts_problem(ep->counts_host, N, h->max_tokens, ep->send_cap,
+                                          h->rows_cap);
+      if (why) return ep_fail(h, GPTOSS_E_CAPACITY, why);
     }
-    if (soff[N] > ep->send_cap || roff[N] > h->rows_cap)
-      return ep_fail(h, GPTOSS_E_CAPACITY, "more rows routed than the engine was created for");
+    for (int p2 = 0; p2 < N; p2++) {
+      soff[p2 + 1] = soff[p2] + ep->counts_host[ep->rank * N + p2];
+      roff[p2 + 1] = roff[p2] + ep->counts_host[p2 * N + ep->rank];
+    }
     // 3. dispatch
     EP_NCCL(h, g_nccl.GroupStart());
     for (int p2 = 0; p2 < N; p2++) {
@@ -653,7 +749,7 @@ int ep_forward(gptoss_moe *h, int layer, const void *t_in, void *x_io, int T, vo
 
 struct PeerBlob {  // what a rank tells the others at start-up
   cudaIpcMemHandle_t t, out, ctl;
-  int ok, max_t, hidden, pid;
+  int ok, max_t, hidden, pid, top_k, experts;
 };
 
 static int ep_map_peers(gptoss_moe *h, EpState *ep) {
@@ -661,6 +757,8 @@ static int ep_map_peers(gptoss_moe *h, EpState *ep) {
   PeerBlob mine = {};
   mine.max_t = ep->max_t;
   mine.hidden = h->H;
+  mine.top_k = h->K;
+  mine.experts = h->E;
   mine.pid = static_cast<int>(getpid());
   mine.ok = cudaIpcGetMemHandle(&mine.t, ep->pub_t) == cudaSuccess &&
             cudaIpcGetMemHandle(&mine.out, ep->out_rows) == cudaSuccess &&
@@ -677,14 +775,22 @@ static int ep_map_peers(gptoss_moe *h, EpState *ep) {
                               ep->comm, nullptr));
   EP_CUDA(h, cudaStreamSynchronize(nullptr));
   EP_CUDA(h, cudaMemcpy(blobs.data(), blobs_dev, sizeof(PeerBlob) * N, cudaMemcpyDeviceToHost));
+  // engines that do not agree on their sizes cannot work together over either transport:
+  // every rank sees the same blobs, so every rank fails here, before any other exchange
+  for (int p = 0; p < N; p++) {
+    if (blobs[p].max_t != ep->max_t || blobs[p].hidden != h->H || blobs[p].top_k != h->K ||
+        blobs[p].experts != h->E) {
+      cudaFree(blobs_dev);
+      return ep_fail(h, GPTOSS_E_INVALID,
+                     "ranks were created with different max_tokens, hidden size, expert count "
+                     "or top-k");
+    }
+  }
   bool ok = true;
   for (int p = 0; p < N && ok; p++) {
     if (!blobs[p].ok) {
       ok = false;
       if (ep->peer_why.empty()) ep->peer_why = "a peer rank could not export its buffers";
-    } else if (blobs[p].max_t != ep->max_t || blobs[p].hidden != h->H) {
-      ok = false;
-      ep->peer_why = "ranks were created with different max_tokens or hidden sizes";
     } else if (p != ep->rank && blobs[p].pid == mine.pid) {
       ok = false;
       ep->peer_why = "ranks share a process (IPC mappings need one process per rank)";
@@ -730,7 +836,7 @@ static int ep_map_peers(gptoss_moe *h, EpState *ep) {
 void ep_destroy(gptoss_moe *h) {
   EpState *ep = static_cast<EpState *>(h->ep);
   if (!ep) return;
-  for (int p = 0; p < ep->N; p++) {
+  for (int p = 0; p < ep->N && !ep->local; p++) {
     if (p == ep->rank) continue;
     if (ep->peer_t[p]) cudaIpcCloseMemHandle(ep->peer_t[p]);
     if (ep->peer_out[p]) cudaIpcCloseMemHandle(ep->peer_out[p]);
@@ -767,6 +873,26 @@ extern "C" int gptoss_moe_ep_unique_id(void *id128) {
   return GPTOSS_OK;
 }
 
+// Buffers of the peer-memory transport (also the owner-side staging both transports use).
+static int ep_alloc_peer_side(gptoss_moe *h, EpState *ep) {
+  const int N = ep->N, K = h->K, H = h->H;
+  const size_t T = h->max_tokens;
+  ep->max_t = static_cast<int>(T);
+  EP_CUDA(h, ep_alloc(&ep->recv_e, (size_t)h->rows_cap * K));
+  EP_CUDA(h, ep_alloc(&ep->recv_w, (size_t)h->rows_cap * K));
+  EP_CUDA(h, ep_alloc(&ep->out_rows, (size_t)h->rows_cap * H));
+  EP_CUDA(h, ep_alloc(&ep->pub_t, T * H));
+  EP_CUDA(h, ep_alloc(&ep->ctl, (size_t)kCtlHeader + (size_t)N * 2 * T * K));
+  EP_CUDA(h, cudaMemset(ep->ctl, 0, sizeof(int) * kCtlHeader));
+  ep->all_meta = ep->ctl + kCtlHeader;
+  // expert ids of a rank that has not published yet read as -1 (no row), not as garbage
+  EP_CUDA(h, cudaMemset(ep->all_meta, 0xFF, sizeof(int) * (size_t)N * 2 * T * K));
+  EP_CUDA(h, cudaStreamCreateWithFlags(&ep->s2, cudaStreamNonBlocking));
+  EP_CUDA(h, cudaEventCreateWithFlags(&ep->ev_plan, cudaEventDisableTiming));
+  EP_CUDA(h, cudaEventCreateWithFlags(&ep->ev_second, cudaEventDisableTiming));
+  return GPTOSS_OK;
+}
+
 extern "C" int gptoss_moe_ep_init(gptoss_moe_t *h, const void *id128) {
   if (!h || !id128) return GPTOSS_E_INVALID;
   if (h->ep_size <= 1) return ep_fail(h, GPTOSS_E_STATE, "engine was created with ep_size <= 1");
@@ -798,9 +924,6 @@ extern "C" int gptoss_moe_ep_init(gptoss_moe_t *h, const void *id128) {
   EP_CUDA(h, ep_alloc(&ep->send_w, (size_t)ep->send_cap * K));
   EP_CUDA(h, ep_alloc(&ep->ret_rows, (size_t)ep->send_cap * H));
   EP_CUDA(h, ep_alloc(&ep->recv_rows, (size_t)h->rows_cap * H));
-  EP_CUDA(h, ep_alloc(&ep->recv_e, (size_t)h->rows_cap * K));
-  EP_CUDA(h, ep_alloc(&ep->recv_w, (size_t)h->rows_cap * K));
-  EP_CUDA(h, ep_alloc(&ep->out_rows, (size_t)h->rows_cap * H));
   EP_CUDA(h, ep_alloc(&ep->counts_dev, (size_t)N * N));
   EP_CUDA(h, cudaMemset(ep->counts_dev, 0, sizeof(int) * N * N));
   EP_CUDA(h, cudaMemset(ep->s_offsets, 0, sizeof(int) * (N + 1)));
@@ -812,15 +935,112 @@ extern "C" int gptoss_moe_ep_init(gptoss_moe_t *h, const void *id128) {
   // communicator.  Every rank takes part in the exchange whatever happens locally, so a
   // rank that cannot export or map memory does not leave the others waiting; the
   // transport is offered only when every rank mapped every peer.
-  ep->max_t = static_cast<int>(T);
-  EP_CUDA(h, ep_alloc(&ep->pub_t, T * H));
-  EP_CUDA(h, ep_alloc(&ep->ctl, (size_t)kCtlHeader + (size_t)N * 2 * T * K));
-  EP_CUDA(h, cudaMemset(ep->ctl, 0, sizeof(int) * kCtlHeader));
-  ep->all_meta = ep->ctl + kCtlHeader;
-  EP_CUDA(h, cudaStreamCreateWithFlags(&ep->s2, cudaStreamNonBlocking));
-  EP_CUDA(h, cudaEventCreateWithFlags(&ep->ev_plan, cudaEventDisableTiming));
-  EP_CUDA(h, cudaEventCreateWithFlags(&ep->ev_second, cudaEventDisableTiming));
+  int rc = ep_alloc_peer_side(h, ep);
+  if (rc) return rc;
   return ep_map_peers(h, ep);
+}
+
+// All ranks live in this process (one host thread per GPU, the reference's own host shape,
+// getp_run.cpp:1038-1063): no communicator and no IPC handles are needed, the engines learn
+// each other's buffers as plain pointers once peer access between their devices is on.
+extern "C" int gptoss_moe_ep_init_local(gptoss_moe_t *const *engines, int n_engines) {
+  if (!engines || n_engines < 2 || n_engines > GPTOSS_MAX_TOPK)
+    return set_global_error(GPTOSS_E_INVALID, "gptoss_moe_ep_init_local: 2 to 8 engines");
+  const int N = n_engines;
+  for (int r = 0; r < N; r++) {
+    gptoss_moe *h = engines[r];
+    if (!h) return set_global_error(GPTOSS_E_INVALID, "gptoss_moe_ep_init_local: null engine");
+    if (h->ep) return ep_fail(h, GPTOSS_E_STATE, "expert parallelism already set up");
+    if (h->ep_size != N || h->ep_rank != r)
+      return ep_fail(h, GPTOSS_E_INVALID, "engines[r] must have been created with ep_rank r and "
+                                          "ep_size n_engines");
+    const gptoss_moe *h0 = engines[0];
+    if (h->max_tokens != h0->max_tokens || h->H != h0->H || h->K != h0->K || h->E != h0->E)
+      return ep_fail(h, GPTOSS_E_INVALID,
+                     "ranks were created with different max_tokens, hidden size, expert count "
+                     "or top-k");
+  }
+  // peer access between every pair of distinct devices
+  for (int a = 0; a < N; a++) {
+    for (int b = 0; b < N; b++) {
+      const int da = engines[a]->cfg.device, db = engines[b]->cfg.device;
+      if (da == db) continue;
+      int can = 0;
+      cudaError_t e = cudaDeviceCanAccessPeer(&can, da, db);
+      if (e != cudaSuccess || !can)
+        return ep_fail(engines[a], GPTOSS_E_CUDA, "no peer access between the engines' devices");
+      if ((e = cudaSetDevice(da)) != cudaSuccess)
+        return ep_fail(engines[a], GPTOSS_E_CUDA, cudaGetErrorString(e));
+      e = cudaDeviceEnablePeerAccess(db, 0);
+      if (e == cudaErrorPeerAccessAlreadyEnabled) {
+        cudaGetLastError();
+      } else if (e != cudaSuccess) {
+        return ep_fail(engines[a], GPTOSS_E_CUDA,
+                       std::string("cudaDeviceEnablePeerAccess: ") + cudaGetErrorString(e));
+      }
+    }
+  }
+  int rc = GPTOSS_OK;
+  for (int r = 0; r < N && rc == GPTOSS_OK; r++) {
+    gptoss_moe *h = engines[r];
+    if (cudaSetDevice(h->cfg.device) != cudaSuccess) {
+      rc = ep_fail(h, GPTOSS_E_CUDA, "cudaSetDevice");
+      break;
+    }
+    EpState *ep = new EpState();
+    h->ep = ep;
+    ep->N = N;
+    ep->rank = r;
+    ep->local = true;
+    rc = ep_alloc_peer_side(h, ep);
+    if (rc == GPTOSS_OK && cudaDeviceSynchronize() != cudaSuccess)
+      rc = ep_fail(h, GPTOSS_E_CUDA, "cudaDeviceSynchronize");
+  }
+  if (rc != GPTOSS_OK) {
+    for (int r = 0; r < N; r++)
+      if (engines[r]->ep) {
+        cudaSetDevice(engines[r]->cfg.device);
+        ep_destroy(engines[r]);
+      }
+    return rc;
+  }
+  for (int r = 0; r < N; r++) {
+    EpState *ep = static_cast<EpState *>(engines[r]->ep);
+    for (int p = 0; p < N; p++) {
+      EpState *peer = static_cast<EpState *>(engines[p]->ep);
+      ep->peer_t[p] = peer->pub_t;
+      ep->peer_out[p] = peer->out_rows;
+      ep->peer_ctl[p] = peer->ctl;
+    }
+    ep->peer_ok = true;
+    ep->transport = 1;
+  }
+  return GPTOSS_OK;
+}
+
+extern "C" int gptoss_moe_forward_part(gptoss_moe_t *h, int layer, int part, const void *t, void *x,
+                                       const int *pos, int n_tokens, void *stream) {
+  if (!h) return GPTOSS_E_INVALID;
+  if (layer < 0 || layer >= h->L || !h->layers[layer].loaded)
+    return ep_fail(h, GPTOSS_E_STATE, "layer out of range or not loaded");
+  if (n_tokens < 0 || n_tokens > h->max_tokens)
+    return ep_fail(h, GPTOSS_E_CAPACITY, "n_tokens out of range");
+  if ((part == 0 && !t && n_tokens > 0) || (part == 2 && !x && n_tokens > 0))
+    return ep_fail(h, GPTOSS_E_INVALID, "null activation pointer");
+  EP_CUDA(h, cudaSetDevice(h->cfg.device));
+  if (part == 0) {
+    int rc = gptoss_moe_route(h, layer, t, pos, n_tokens, stream);
+    if (rc) return rc;
+  }
+  return ep_forward_part(h, layer, part, t, x, n_tokens, stream);
+}
+
+// Not part of the public header: lets host-side tests put the capacity check of the NCCL
+// transport in front of count matrices of their own (pure host code, no GPU needed).
+extern "C" const char *gptoss_internal_ep_counts_problem(const int *counts, int n_ranks,
+                                                         int max_tokens, int top_k) {
+  const int send_cap = max_tokens * (n_ranks < top_k ? n_ranks : top_k);
+  return ep_counts_problem(counts, n_ranks, max_tokens, send_cap, max_tokens * n_ranks);
 }
 
 extern "C" int gptoss_moe_ep_transport(const gptoss_moe_t *h) {

@@ -29,9 +29,6 @@ struct GemmArgs {
   int out_ld;   // leading dimension of out
   float limit;
   int *status;
-  int skip_epilogue;  // measurement aid, bit mask: 1 = do not read the accumulator,
-                      // 2 = compute but do not store, 4 = no proxy fence after the
-                      // MXFP4 conversion, 8 = no conversion, 16 = no MMA issue
   const uint8_t *wq = nullptr;  // MXFP4: tiled packed codes + scales of the weight operand
   // (CTA-pair kernel) 0 = every token tile; 1 / 2 = only the tiles before / from
   // *tile_split, so that a launch can start on the first experts while the rows of the
@@ -148,18 +145,16 @@ __device__ __forceinline__ void epilogue_pass(uint32_t taddr, int n0, const floa
   const int sub = lane / kLanes, piece = lane - sub * kLanes;
   const int out_col0 = (EPI == kEpiSwiglu) ? (n0 >> 1) : n0;
   const bool piece_ok = sub < kRowsPerInstr && out_col0 + piece * 8 + 8 <= g.out_ld;
-  if (!(g.skip_epilogue & 2)) {
 #pragma unroll
-    for (int r0 = 0; r0 < 32; r0 += kRowsPerInstr) {
-      const int r = r0 + sub;
-      if (piece_ok && r < 32 && r < rows_left) {
-        const uint4 v = *reinterpret_cast<const uint4 *>(stage + r * kEpiPitch + piece * 16);
-        // streaming store: the output is read once by the next kernel and must not
-        // push the weight and activation tiles this kernel re-reads out of L2
-        __stcs(reinterpret_cast<uint4 *>(g.out + static_cast<size_t>(row_base + r) * g.out_ld +
-                                         out_col0 + piece * 8),
-               v);
-      }
+  for (int r0 = 0; r0 < 32; r0 += kRowsPerInstr) {
+    const int r = r0 + sub;
+    if (piece_ok && r < 32 && r < rows_left) {
+      const uint4 v = *reinterpret_cast<const uint4 *>(stage + r * kEpiPitch + piece * 16);
+      // streaming store: the output is read once by the next kernel and must not
+      // push the weight and activation tiles this kernel re-reads out of L2
+      __stcs(reinterpret_cast<uint4 *>(g.out + static_cast<size_t>(row_base + r) * g.out_ld +
+                                       out_col0 + piece * 8),
+             v);
     }
   }
   __syncwarp();

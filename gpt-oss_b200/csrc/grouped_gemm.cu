@@ -204,7 +204,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kAccCols;
-      if (!(g.skip_epilogue & 1)) {
+      {
         // two warps share a lane quarter and split the tile's columns
         constexpr int kSplit = ((BN / 16 + 1) / 2) * 16;
         unsigned char *stage = epi_stage + (warp - 2) * kEpiStageBytes;
@@ -392,7 +392,6 @@ cudaError_t launch_gate_up(gptoss_moe *h, int layer, cudaStream_t stream, int pa
   g.out_ld = h->IM;
   g.limit = h->cfg.swiglu_limit;
   g.status = h->status;
-  g.skip_epilogue = h->opt_skip_epilogue;
   if (h->opt_gemm_impl == GPTOSS_GEMM_SIMT) {
     dim3 grid((g.n_cols + 63) / 64, h->mtiles_cap);
     grouped_gemm_simt_kernel<kEpiSwiglu><<<grid, 256, 0, stream>>>(h->xs, h->H, lw.w1, g);
@@ -418,7 +417,6 @@ cudaError_t launch_down(gptoss_moe *h, int layer, cudaStream_t stream) {
   g.out_ld = h->H;
   g.limit = h->cfg.swiglu_limit;
   g.status = h->status;
-  g.skip_epilogue = h->opt_skip_epilogue;
   if (h->opt_gemm_impl == GPTOSS_GEMM_SIMT) {
     dim3 grid((g.n_cols + 63) / 64, h->mtiles_cap);
     grouped_gemm_simt_kernel<kEpiDown><<<grid, 256, 0, stream>>>(h->hact, h->IM, lw.w2, g);

@@ -163,8 +163,8 @@ int gptoss_moe_destroy(gptoss_moe_t *h) {
   ep_destroy(h);
   for (auto &lw : h->layers) {
     cudaFree(lw.w_router); cudaFree(lw.b_router); cudaFree(lw.w1); cudaFree(lw.b1);
-    cudaFree(lw.w2); cudaFree(lw.b2); cudaFree(lw.w1_blocks); cudaFree(lw.w1_scales);
-    cudaFree(lw.w2_blocks); cudaFree(lw.w2_scales); cudaFree(lw.rms_ffn);
+    cudaFree(lw.w2); cudaFree(lw.b2); cudaFree(lw.w1_blocks); cudaFree(lw.w2_blocks);
+    cudaFree(lw.rms_ffn);
   }
   cudaFree(h->topk_i); cudaFree(h->topk_v); cudaFree(h->logits); cudaFree(h->block_counts);
   cudaFree(h->expert_offsets); cudaFree(h->sorted_row); cudaFree(h->sorted_weight);
@@ -182,12 +182,25 @@ int gptoss_moe_destroy(gptoss_moe_t *h) {
   if (h->s_h2d) cudaStreamDestroy(h->s_h2d);
   if (h->s_comp) cudaStreamDestroy(h->s_comp);
   if (h->s_d2h) cudaStreamDestroy(h->s_d2h);
+  gptoss_moe_release_upload_staging(h);
   for (auto &t : h->timers) {
     for (auto e : t.beg) cudaEventDestroy(e);
     for (auto e : t.end) cudaEventDestroy(e);
   }
   delete h;
   return GPTOSS_OK;
+}
+
+// Reads the device status word after the caller has synchronised the stream the kernels ran
+// on; a non-zero word is cleared and reported as GPTOSS_E_DEVICE.
+int gptoss_moe_take_status(gptoss_moe *h) {
+  int s = 0;
+  CK(h, cudaMemcpy(&s, h->status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (!s) return GPTOSS_OK;
+  CK(h, cudaMemset(h->status, 0, sizeof(int)));
+  return fail(h, GPTOSS_E_DEVICE,
+              "a kernel reported status %d (101-103: a pipeline wait ran out, 104: index out of "
+              "range, 105: tensor memory, 106: another rank's flag did not arrive in time)", s);
 }
 
 // ------------------------------------------------------------------ weights
@@ -218,34 +231,60 @@ static int finish_layer(gptoss_moe *h, LayerWeights &lw) {
 }
 
 // fp32 host -> bf16 device through a pinned double buffer (not part of the public
-// header; the decode engine's loader uses it too).
+// header; the decode engine's loader uses it too).  The stream, the two pinned and the
+// two device staging buffers and their events belong to the engine: made on the first
+// upload, reused by every later one, released by gptoss_moe_release_upload_staging (the
+// loaders call it when a model is in place) or with the engine.
+static int upload_staging(gptoss_moe *h) {
+  if (h->up_stream) return GPTOSS_OK;
+  CK(h, cudaStreamCreateWithFlags(&h->up_stream, cudaStreamNonBlocking));
+  for (int i = 0; i < 2; i++) {
+    CK(h, cudaMallocHost(reinterpret_cast<void **>(&h->up_pinned[i]), gptoss_moe::kUploadChunk * 4));
+    CK(h, dev_alloc(&h->up_dev[i], gptoss_moe::kUploadChunk));
+    CK(h, cudaEventCreateWithFlags(&h->up_done[i], cudaEventDisableTiming));
+  }
+  return GPTOSS_OK;
+}
+
+void gptoss_moe_release_upload_staging(gptoss_moe *h) {
+  if (!h) return;
+  if (h->up_stream) cudaStreamSynchronize(h->up_stream);
+  for (int i = 0; i < 2; i++) {
+    if (h->up_pinned[i]) cudaFreeHost(h->up_pinned[i]);
+    if (h->up_dev[i]) cudaFree(h->up_dev[i]);
+    if (h->up_done[i]) cudaEventDestroy(h->up_done[i]);
+    h->up_pinned[i] = nullptr;
+    h->up_dev[i] = nullptr;
+    h->up_done[i] = nullptr;
+  }
+  if (h->up_stream) cudaStreamDestroy(h->up_stream);
+  h->up_stream = nullptr;
+  h->up_next = 0;
+}
+
 int upload_f32_as_bf16(gptoss_moe *h, bf16 *dst, const float *src, size_t n) {
-  const size_t chunk = (size_t)8 << 20;  // elements per chunk (32 MB of fp32)
-  float *pinned[2] = {nullptr, nullptr}, *dtmp[2] = {nullptr, nullptr};
-  cudaStream_t st;
-  cudaEvent_t done[2];
-  CK(h, cudaStreamCreate(&st));
-  for (int i = 0; i < 2; i++) {
-    CK(h, cudaMallocHost(reinterpret_cast<void **>(&pinned[i]), std::min(chunk, n) * 4));
-    CK(h, dev_alloc(&dtmp[i], std::min(chunk, n)));
-    CK(h, cudaEventCreate(&done[i]));
+  int rc = upload_staging(h);
+  if (rc) {
+    gptoss_moe_release_upload_staging(h);
+    return rc;
   }
-  int b = 0;
-  for (size_t off = 0; off < n; off += chunk, b ^= 1) {
+  const size_t chunk = gptoss_moe::kUploadChunk;
+  for (size_t off = 0; off < n; off += chunk) {
+    const int b = h->up_next;
+    h->up_next ^= 1;
     const size_t m = std::min(chunk, n - off);
-    CK(h, cudaEventSynchronize(done[b]));  // buffer free again (no-op the first time)
-    memcpy(pinned[b], src + off, m * 4);
-    CK(h, cudaMemcpyAsync(dtmp[b], pinned[b], m * 4, cudaMemcpyHostToDevice, st));
-    CK(h, launch_f32_to_bf16(dst + off, dtmp[b], m, st, &h->launches));
-    CK(h, cudaEventRecord(done[b], st));
+    CK(h, cudaEventSynchronize(h->up_done[b]));  // buffer free again (no-op the first time)
+    memcpy(h->up_pinned[b], src + off, m * 4);
+    CK(h, cudaMemcpyAsync(h->up_dev[b], h->up_pinned[b], m * 4, cudaMemcpyHostToDevice, h->up_stream));
+    CK(h, launch_f32_to_bf16(dst + off, h->up_dev[b], m, h->up_stream, &h->launches));
+    CK(h, cudaEventRecord(h->up_done[b], h->up_stream));
   }
-  CK(h, cudaStreamSynchronize(st));
-  for (int i = 0; i < 2; i++) {
-    cudaFreeHost(pinned[i]);
-    cudaFree(dtmp[i]);
-    cudaEventDestroy(done[i]);
-  }
-  cudaStreamDestroy(st);
+  return GPTOSS_OK;
+}
+
+// Everything queued by upload_f32_as_bf16 has landed.
+int upload_finish(gptoss_moe *h) {
+  if (h->up_stream) CK(h, cudaStreamSynchronize(h->up_stream));
   return GPTOSS_OK;
 }
 
@@ -273,6 +312,7 @@ int gptoss_moe_load_layer_f32(gptoss_moe_t *h, int layer, const float *w_router,
     CK(h, cudaMemcpy(lw.b1 + j * 2 * IM, b_mlp1 + e * 2 * IM, 2 * IM * 4, cudaMemcpyHostToDevice));
     CK(h, cudaMemcpy(lw.b2 + j * H, b_mlp2 + e * H, H * 4, cudaMemcpyHostToDevice));
   }
+  if ((rc = upload_finish(h))) return rc;
   return finish_layer(h, lw);
 }
 
@@ -352,12 +392,9 @@ int gptoss_moe_route(gptoss_moe_t *h, int layer, const void *t, const int *pos, 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (h->opt_keep_logits && !h->logits)
     CK(h, dev_alloc(&h->logits, (size_t)h->max_tokens * h->E));
-  LayerWeights &lw = h->layers[layer];
   StageScope sc(h, 0, st);
-  CK(h, launch_router_topk(static_cast<const bf16 *>(t), lw.w_router, lw.b_router, pos, n_tokens,
-                           h->H, h->E, h->K, h->topk_i, h->topk_v,
-                           h->opt_keep_logits ? h->logits : nullptr, h->opt_exact_ties, h->status, st,
-                           &h->launches));
+  CK(h, launch_router_topk(h, layer, static_cast<const bf16 *>(t), pos, n_tokens,
+                           h->opt_keep_logits ? h->logits : nullptr, st));
   return GPTOSS_OK;
 }
 
@@ -461,7 +498,7 @@ int gptoss_moe_forward_host(gptoss_moe_t *h, int layer, const void *t_host, void
   if (rc) return rc;
   CK(h, cudaMemcpyAsync(x_host, h->x_dev, bytes, cudaMemcpyDeviceToHost, st));
   CK(h, cudaStreamSynchronize(st));
-  return GPTOSS_OK;
+  return gptoss_moe_take_status(h);
 }
 
 int gptoss_moe_load_ffn_norm(gptoss_moe_t *h, int layer, const float *scale_host) {
@@ -483,8 +520,10 @@ int gptoss_moe_forward_host_submit(gptoss_moe_t *h, int layer, const void *t_hos
   if (!t_host && !h->layers[layer].rms_ffn)
     return fail(h, GPTOSS_E_STATE,
                 "t_host is NULL but the layer has no RMSNorm scale (gptoss_moe_load_ffn_norm)");
-  if (h->ep_size > 1)
-    return fail(h, GPTOSS_E_STATE, "the pipelined host path is for engines with all experts local");
+  if (h->ep_size > 1 && ep_get_transport(h) != 1)
+    return fail(h, GPTOSS_E_STATE,
+                "under expert parallelism the pipelined host path needs the peer-memory transport "
+                "(the NCCL transport synchronises with the host inside every layer)");
   CK(h, cudaSetDevice(h->cfg.device));
   if (!h->s_comp) {
     CK(h, cudaStreamCreateWithFlags(&h->s_h2d, cudaStreamNonBlocking));
@@ -544,6 +583,9 @@ int gptoss_moe_forward_host_wait(gptoss_moe_t *h, int ticket) {
     CK(h, cudaSetDevice(h->cfg.device));
     CK(h, cudaEventSynchronize(sl.d2h));
     sl.busy = false;
+    // the status word is the engine's, not the ticket's: a problem in a later submission
+    // that has already run shows up here too
+    return gptoss_moe_take_status(h);
   }
   return GPTOSS_OK;
 }
@@ -605,15 +647,22 @@ int gptoss_moe_set_option(gptoss_moe_t *h, const char *name, int value) {
     h->opt_keep_logits = value != 0;
   } else if (!strcmp(name, "exact_ties")) {
     h->opt_exact_ties = value != 0;
-  } else if (!strcmp(name, "pair_stages")) {
-    if (value < 4 || value > 6) return fail(h, GPTOSS_E_INVALID, "pair_stages must be 4, 5 or 6");
-    h->opt_pair_stages = value;
+  } else if (!strcmp(name, "router_impl")) {
+    if (value != 0 && value != 1) return fail(h, GPTOSS_E_INVALID, "router_impl must be 0 or 1");
+    h->opt_router_impl = value;
+  } else if (!strcmp(name, "pair_rings")) {
+    if (value < 6 || value > 9) return fail(h, GPTOSS_E_INVALID, "pair_rings must be 6..9");
+    h->opt_pair_rings = value;
+  } else if (!strcmp(name, "dependent_launch")) {
+    h->opt_dependent_launch = value != 0;
+  } else if (!strcmp(name, "wait_limit_ms")) {
+    if (value < 1 || value > 60000)
+      return fail(h, GPTOSS_E_INVALID, "wait_limit_ms must be 1..60000");
+    h->opt_wait_limit_ms = value;
   } else if (!strcmp(name, "ep_overlap")) {
     h->opt_ep_overlap = value != 0;
   } else if (!strcmp(name, "ep_transport")) {
     return ep_set_transport(h, value);
-  } else if (!strcmp(name, "skip_epilogue")) {
-    h->opt_skip_epilogue = value;
   } else if (!strcmp(name, "time_stages")) {
     // value 1 starts a fresh series of measurements (event pairs are reused)
     h->opt_time_stages = value != 0;

@@ -77,9 +77,9 @@ mxfp4_tile_scales_kernel(uint8_t *__restrict__ s, const uint8_t *__restrict__ sc
 size_t mxfp4_blocks_per_expert(int rows) { return static_cast<size_t>((rows + 255) / 256) * 2; }
 
 // Tiles one tensor ([E, rows, k] codes + scales, host or device pointers) into
-// freshly allocated device buffers *q_out / *s_out for the experts this rank owns.
+// a freshly allocated device buffer *q_out for the experts this rank owns.
 static int tile_tensor(gptoss_moe *h, const uint8_t *blocks, const uint8_t *scales, int rows, int k,
-                       int on_device, uint8_t **q_out, uint8_t **s_out) {
+                       int on_device, uint8_t **q_out) {
   const int k_bytes = k / 2, k_groups = k / 32;
   const int kb_count = (k + kTileK - 1) / kTileK;
   const int nb = static_cast<int>(mxfp4_blocks_per_expert(rows));
@@ -168,11 +168,9 @@ extern "C" int gptoss_moe_load_layer_mxfp4(gptoss_moe_t *h, int layer, const voi
         (e = cudaMemcpy(lw.b2 + j * H, b_mlp2 + eg * H, H * 4, kind)) != cudaSuccess)
       return fail(GPTOSS_E_CUDA, std::string("bias upload: ") + cudaGetErrorString(e));
   }
-  int rc = tile_tensor(h, w_mlp1_blocks, w_mlp1_scales, 2 * h->IM, h->H, on_device, &lw.w1_blocks,
-                       &lw.w1_scales);
+  int rc = tile_tensor(h, w_mlp1_blocks, w_mlp1_scales, 2 * h->IM, h->H, on_device, &lw.w1_blocks);
   if (rc) return rc;
-  rc = tile_tensor(h, w_mlp2_blocks, w_mlp2_scales, h->H, h->IM, on_device, &lw.w2_blocks,
-                   &lw.w2_scales);
+  rc = tile_tensor(h, w_mlp2_blocks, w_mlp2_scales, h->H, h->IM, on_device, &lw.w2_blocks);
   if (rc) return rc;
   lw.loaded = true;
   return GPTOSS_OK;

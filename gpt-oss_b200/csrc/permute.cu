@@ -16,6 +16,8 @@
 //                 schedule of the grouped GEMMs
 //   gather:       copies the source rows into sorted order (16-byte accesses)
 // All kernels are bound by latency (<= 200k items) or HBM (gather, combine).
+#include <atomic>
+
 #include "common.cuh"
 #include "engine.h"
 
@@ -454,28 +456,30 @@ constexpr int kStaticMaxRows = 8192;
 constexpr int kStaticMaxExperts = 256;
 constexpr int kStaticBlocks = kStaticMaxRows / kPermTokens;  // 64 CTAs at most
 constexpr int kStaticMtilesPad = 1024;  // >= 8192 * 8 / 128 + 256 + 1 M tiles
-// ints: [block counts: 64 x 256][mtile_expert | mtile_row0 | mtile_rows: 3 x 1024][num_mtiles, status, pad]
+// ints: [block counts: 64 x 256][mtile_expert | mtile_row0 | mtile_rows: 3 x 1024][num_mtiles, pad]
 constexpr int kStaticCountsInts = kStaticBlocks * kStaticMaxExperts;
 constexpr int kStaticInts = kStaticCountsInts + 3 * kStaticMtilesPad + 64;
 
 static __device__ __align__(256) int g_perm_scratch[kStaticInts];
 
 // In host code `g_perm_scratch` is only a handle for the runtime, not an address
-// a kernel can use; the device address is looked up once per device.
-static int *g_perm_scratch_dev[64] = {nullptr};
+// a kernel can use; the device address is looked up once per device.  Several host
+// threads may make the first call on a device at the same time: each looks the address
+// up and stores the same value.
+static std::atomic<int *> g_perm_scratch_dev[64];
 
 static cudaError_t static_scratch(int **out) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-  if (!g_perm_scratch_dev[dev]) {
-    int *p = nullptr;
+  int *p = g_perm_scratch_dev[dev].load(std::memory_order_acquire);
+  if (!p) {
     e = cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_perm_scratch);
     if (e != cudaSuccess) return e;
-    g_perm_scratch_dev[dev] = p;
+    g_perm_scratch_dev[dev].store(p, std::memory_order_release);
   }
-  *out = g_perm_scratch_dev[dev];
+  *out = p;
   return cudaSuccess;
 }
 
@@ -507,10 +511,12 @@ extern "C" int gptoss_moe_permute_static(const int *slot_expert, const float *sl
   int *mtile_row0 = mtile_expert + kStaticMtilesPad;
   int *mtile_rows = mtile_row0 + kStaticMtilesPad;
   int *num_mtiles = mtile_rows + kStaticMtilesPad;
-  int *status = num_mtiles + 1;
-  // the array keeps what the previous call left: the two words that are only ever
-  // OR-ed / compared start from zero again; everything else is fully rewritten
-  e = cudaMemsetAsync(num_mtiles, 0, 2 * sizeof(int), st);
+  // No status word: slots whose expert id is out of range are skipped, as documented, and
+  // the sizes were checked above, so the kernels have nothing to report.
+  int *status = nullptr;
+  // the array keeps what the previous call left: the tile count starts from zero again;
+  // everything else the kernels read is fully rewritten first
+  e = cudaMemsetAsync(num_mtiles, 0, sizeof(int), st);
   if (e != cudaSuccess) return set_global_error(GPTOSS_E_CUDA, cudaGetErrorString(e));
   const int nblocks = (n_rows + kPermTokens - 1) / kPermTokens;
   perm_count_kernel<<<nblocks, 256, n_experts * sizeof(int), st>>>(slot_expert, n_rows, top_k,

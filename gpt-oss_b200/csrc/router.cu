@@ -63,24 +63,25 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
 // (run.cpp:356-369): exact float products summed in double, rounded to float
 // once at the end.  Whole warp cooperates; every lane returns the result.
 __device__ __forceinline__ float warp_exact_dot(const bf16 *a, const bf16 *b, int H, int lane) {
-  // Loads of up to 4 pieces per lane are issued together (their latency overlaps)
-  // and four independent accumulators keep the fp64 add chains short.  The order
+  // Loads of up to 12 pieces per lane and operand (one round trip for H <= 3072) are
+  // issued together and four independent accumulators keep the fp64 add chains short.  The order
   // of the fp64 additions differs from the reference's left-to-right sum by
   // rounding errors ~1e-16 relative, which the final rounding to float hides.
   double acc0 = 0.0, acc1 = 0.0, acc2 = 0.0, acc3 = 0.0;
   const uint4 *a4 = reinterpret_cast<const uint4 *>(a);
   const uint4 *b4 = reinterpret_cast<const uint4 *>(b);
   const int n4 = H >> 3;
-  for (int p0 = lane; p0 < n4; p0 += 128) {
-    uint4 av[4], bv[4];
+  constexpr int kU = 12;
+  for (int p0 = lane; p0 < n4; p0 += 32 * kU) {
+    uint4 av[kU], bv[kU];
 #pragma unroll
-    for (int u = 0; u < 4; u++) {
+    for (int u = 0; u < kU; u++) {
       const int p = p0 + u * 32;
       av[u] = p < n4 ? __ldg(a4 + p) : make_uint4(0, 0, 0, 0);
       bv[u] = p < n4 ? __ldg(b4 + p) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
-    for (int u = 0; u < 4; u++) {
+    for (int u = 0; u < kU; u++) {
       acc0 += static_cast<double>(__fmul_rn(bf16_lo(av[u].x), bf16_lo(bv[u].x)));
       acc1 += static_cast<double>(__fmul_rn(bf16_hi(av[u].x), bf16_hi(bv[u].x)));
       acc2 += static_cast<double>(__fmul_rn(bf16_lo(av[u].y), bf16_lo(bv[u].y)));
@@ -359,6 +360,415 @@ router_topk_kernel(const __grid_constant__ CUtensorMap tmap_t,
   }
 }
 
+// ---------------------------------------------------------------------------
+// The router on the 5th-generation tensor cores.
+//
+// A CTA owns 128 consecutive tokens (the MMA's M) and all experts (the MMA's N, padded
+// to EPAD = 32 / 64 / 128 / 256); tcgen05.mma (M=128, N=EPAD, K=16, bf16 -> fp32)
+// accumulates the logits in EPAD columns of TMEM.  Both operands arrive through one
+// TMA ring: per 64-deep K chunk a box of 128 token rows (the only stream that comes
+// from HBM) and a box of EPAD router rows (L2).  Warp 0 = producer, warp 1 = TMEM
+// allocation and MMA issue, warps 2-5 = selection: a TMEM lane is a token, so every
+// thread reads the logits of its own token with tcgen05.ld and keeps a sorted list of
+// the best K+1 in registers - no shuffles, no shared-memory round trip.
+//
+// With fewer than one 128-token tile per SM (always: T <= 148 * 128 would need 18944
+// tokens) a cluster of `split` CTAs shares a tile, each taking 1/split of the K chunks;
+// when all of them are done each pushes its partial logits (remote shared-memory stores)
+// to the CTA that selects for that token - the tile's tokens are dealt out evenly over
+// the cluster - where the partials are added in rank order.
+//
+// Exact selection as before: a token whose best K+1 logits contain two neighbours closer
+// than kTieGuard lists every expert within 2 * kTieGuard of its K-th value; after the
+// CTA's threads are through, its warps take those tokens one by one, recompute the
+// listed logits the way the reference's CPU matmul does (float products summed in
+// double) and select again.
+constexpr int kRcTokens = 128;
+constexpr int kRcThreads = 192;
+constexpr int kRcSelWarps = 4;
+constexpr int kRcCand = 16;  // listed contenders per token; more than that: all experts
+template <int EPAD> struct RcStages {
+  static constexpr int value = EPAD <= 32 ? 9 : (EPAD <= 64 ? 8 : (EPAD <= 128 ? 6 : 4));
+};
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_size() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// NS = length of the sorted list every thread keeps (K + 1 <= NS)
+template <int EPAD, int NS>
+__global__ void __launch_bounds__(kRcThreads, 1)
+router_tc_kernel(const __grid_constant__ CUtensorMap tmap_t,
+                 const __grid_constant__ CUtensorMap tmap_w, const bf16 *__restrict__ t,
+                 const bf16 *__restrict__ w_router, const float *__restrict__ b_router,
+                 const int *__restrict__ pos, int T, int H, int E, int K,
+                 int *__restrict__ topk_i, float *__restrict__ topk_v,
+                 float *__restrict__ logits_out, int exact_ties, int *status) {
+  constexpr int kStages = RcStages<EPAD>::value;
+  constexpr int kTokBytes = kRcTokens * kRtRowBytes;          // 16 KB
+  constexpr int kStageBytes = kTokBytes + EPAD * kRtRowBytes;
+  constexpr int NT = EPAD / 32;
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  unsigned char *smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
+  unsigned char *after = smem + kStages * kStageBytes;
+  uint64_t *full_bar = reinterpret_cast<uint64_t *>(after);
+  uint64_t *empty_bar = full_bar + kStages;
+  uint64_t *tfull_bar = empty_bar + kStages;
+  uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(tfull_bar + 1);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
+  int *n_flagged = const_cast<int *>(abort_flag) + 1;
+  float *bias_s = reinterpret_cast<float *>(after + 256);               // [EPAD]
+  int *flag_tok = reinterpret_cast<int *>(after + 256 + EPAD * 4);      // [128] token row in the tile
+  int *cand_cnt = flag_tok + kRcTokens;                                 // [128]
+  int *cand_e = cand_cnt + kRcTokens;                                   // [128][kRcCand]
+  // partial logits pushed by the cluster's CTAs, over the ring once everybody is done
+  // with it: part[source rank][expert][token of this CTA's share]
+  float *part = reinterpret_cast<float *>(smem);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int split = static_cast<int>(cluster_size());
+  const int crank = static_cast<int>(cluster_rank());
+  const int tok0 = static_cast<int>(blockIdx.x / split) * kRcTokens;
+  const int nk_all = (H + kRtKC - 1) / kRtKC;
+  const int kc_lo = crank * nk_all / split, kc_hi = (crank + 1) * nk_all / split;
+  const int share = (kRcTokens + split - 1) / split;  // tokens each CTA selects for
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; s++) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(tfull_bar, 1);
+    *abort_flag = 0;
+    *n_flagged = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_t);
+    tma_prefetch_desc(&tmap_w);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, EPAD);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  grid_dependency_wait();
+  grid_launch_dependents();
+  for (int e = tid; e < EPAD; e += kRcThreads) bias_s[e] = e < E ? __ldg(b_router + e) : 0.f;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kc = kc_lo; kc < kc_hi; kc++) {
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+          set_status(status, kStatusWaitTimeoutProducer);
+          *abort_flag = 1;
+          break;
+        }
+        unsigned char *dst = smem + stage * kStageBytes;
+        mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
+        tma_load_2d(dst, &tmap_t, &full_bar[stage], kc * kRtKC, tok0);
+        tma_load_2d(dst + kTokBytes, &tmap_w, &full_bar[stage], kc * kRtKC, 0);
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(kRcTokens, EPAD);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kc = kc_lo; kc < kc_hi; kc++) {
+        if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+          set_status(status, kStatusWaitTimeoutMma);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + stage * kStageBytes);
+        const uint64_t da = umma_smem_desc_sw128(sa);
+        const uint64_t db = umma_smem_desc_sw128(sa + kTokBytes);
+#pragma unroll
+        for (int k = 0; k < kRtKC / 16; k++)
+          umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (kc > kc_lo || k > 0) ? 1u : 0u);
+        umma_commit(&empty_bar[stage]);
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      umma_commit(tfull_bar);  // also when this CTA had no K chunk: nothing to wait for
+    }
+  }
+  __syncwarp();
+
+  const bool selector = warp >= 2;
+  const int q = warp & 3;             // TMEM lanes [32q, 32q+32) are this warp's
+  const int row = q * 32 + lane;      // token row of the tile held by this thread's TMEM lane
+  bool acc_ok = true;
+  if (selector) {
+    if (!mbar_wait(tfull_bar, 0, abort_flag)) {
+      set_status(status, kStatusWaitTimeoutEpilogue);
+      *abort_flag = 1;
+      acc_ok = false;
+    }
+    tc_fence_after();
+  }
+  const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+  const bool has_acc = kc_hi > kc_lo;  // a CTA without K chunks holds no partial sums
+
+  if (split > 1) {
+    // 1. every CTA of the cluster is done with its ring
+    cluster_sync_all();
+    // 2. push this CTA's partial logits of token `row` to the CTA that selects for it
+    if (selector) {
+      const int dst_cta = row / share, tl = row - dst_cta * share;
+#pragma unroll 1
+      for (int c0 = 0; c0 < EPAD; c0 += 32) {
+        uint32_t r[32];
+        if (has_acc && acc_ok) {
+          tmem_ld32(taddr + c0, r);
+          tmem_ld_wait32(r);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; j++) r[j] = 0u;
+        }
+        const uint32_t local =
+            smem_u32(part + (static_cast<size_t>(crank) * EPAD + c0) * share + tl);
+        uint32_t remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(dst_cta));
+#pragma unroll
+        for (int j = 0; j < 32; j++)
+          asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(remote + j * share * 4), "r"(r[j])
+                       : "memory");
+      }
+    }
+    // 3. all partials are in place
+    cluster_sync_all();
+  }
+
+  // which token this thread selects for
+  const int sel_row = split > 1 ? crank * share + (tid - 64) : row;
+  const bool sel_active = selector && (split == 1 || ((tid - 64) < share && sel_row < kRcTokens));
+  const int tok = tok0 + sel_row;
+  const bool live = sel_active && tok < T && !(pos && pos[tok] < 0);
+  const int rounds_chk = (K + 1 <= E) ? K + 1 : E;
+
+  float bv[NS];
+  int bi[NS];
+#pragma unroll
+  for (int p = 0; p < NS; p++) {
+    bv[p] = -INFINITY;
+    bi[p] = 0x7fffffff;
+  }
+  // pass over the token's logits, 32 at a time; f(e, value) per expert
+  auto for_each_logit = [&](auto &&f) {
+#pragma unroll 1
+    for (int c0 = 0; c0 < EPAD; c0 += 32) {
+      float r[32];
+      if (split == 1) {
+        uint32_t u[32];
+        tmem_ld32(taddr + c0, u);  // the whole warp, also for rows without a token
+        tmem_ld_wait32(u);
+#pragma unroll
+        for (int j = 0; j < 32; j++) r[j] = __uint_as_float(u[j]);
+      } else {
+        const int tl = tid - 64;
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+          float v = 0.f;
+          if (sel_active)
+            for (int s = 0; s < split; s++)
+              v += part[(static_cast<size_t>(s) * EPAD + c0 + j) * share + tl];
+          r[j] = v;
+        }
+      }
+      if (live) {
+#pragma unroll
+        for (int j = 0; j < 32; j++)
+          if (c0 + j < E) f(c0 + j, r[j] + bias_s[c0 + j]);
+      }
+    }
+  };
+
+  bool flagged = false;
+  if (selector) {
+    for_each_logit([&](int e, float v) {
+      if (logits_out) logits_out[static_cast<size_t>(tok) * E + e] = v;
+      if (v > bv[NS - 1]) {
+        // insert: the new value goes in front of the first smaller one (equal values keep
+        // the lower index in front), everything behind moves down one place
+        float cv = v;
+        int ci = e;
+        bool carrying = false;
+#pragma unroll
+        for (int p = 0; p < NS; p++) {
+          if (carrying || cv > bv[p]) {
+            const float tv = bv[p];
+            const int ti = bi[p];
+            bv[p] = cv;
+            bi[p] = ci;
+            cv = tv;
+            ci = ti;
+            carrying = true;
+          }
+        }
+      }
+    });
+    if (live && exact_ties) {
+#pragma unroll
+      for (int r = 0; r + 1 < NS; r++)
+        if (r + 1 < rounds_chk && bv[r] - bv[r + 1] < kTieGuard) flagged = true;
+    }
+    // second pass for the tokens with a near tie: list the contenders
+    if (__any_sync(0xffffffffu, flagged)) {
+      float kth = bv[0];
+#pragma unroll
+      for (int r = 1; r < NS; r++)
+        if (r < K) kth = bv[r];
+      const float thr = kth - 2.f * kTieGuard;
+      int slot = -1, cnt = 0;
+      if (flagged) {
+        slot = atomicAdd(n_flagged, 1);
+        flag_tok[slot] = sel_row;
+      }
+      const bool was_live = live;
+      for_each_logit([&](int e, float v) {
+        if (flagged && v >= thr) {
+          if (cnt < kRcCand) cand_e[slot * kRcCand + cnt] = e;
+          cnt++;
+        }
+      });
+      (void)was_live;
+      if (flagged) cand_cnt[slot] = cnt;
+    }
+    if (live && !flagged) {
+      // softmax over the K selected values (run.cpp:336-354: double max/sum)
+      float ev[NS];
+      double sum = 0.0;
+      const double mx = static_cast<double>(bv[0]);
+#pragma unroll
+      for (int r = 0; r < NS; r++) {
+        if (r < K) {
+          ev[r] = expf(static_cast<float>(static_cast<double>(bv[r]) - mx));
+          sum += static_cast<double>(ev[r]);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < NS; r++) {
+        if (r < K) {
+          topk_i[static_cast<size_t>(tok) * K + r] = bi[r];
+          topk_v[static_cast<size_t>(tok) * K + r] =
+              static_cast<float>(static_cast<double>(ev[r]) / sum);
+        }
+      }
+    } else if (sel_active && tok < T && !live) {
+      for (int r = 0; r < K; r++) {
+        topk_i[static_cast<size_t>(tok) * K + r] = -1;
+        topk_v[static_cast<size_t>(tok) * K + r] = 0.f;
+      }
+    }
+  }
+  __syncthreads();
+
+  // near ties: one warp per listed token
+  const int n_flag = *n_flagged;
+  for (int s = warp; s < n_flag; s += kRcThreads / 32) {
+    const int tk = tok0 + flag_tok[s];
+    const int cnt = cand_cnt[s];
+    const bool all = cnt > kRcCand;
+    const int n = all ? E : cnt;
+    const bf16 *trow = t + static_cast<size_t>(tk) * H;
+    float v[NT];
+#pragma unroll
+    for (int j = 0; j < NT; j++) v[j] = -INFINITY;
+    for (int i = 0; i < n; i++) {
+      const int e = all ? i : cand_e[s * kRcCand + i];
+      const float ex = warp_exact_dot(trow, w_router + static_cast<size_t>(e) * H, H, lane) + bias_s[e];
+#pragma unroll
+      for (int j = 0; j < NT; j++)
+        if (e == lane + 32 * j) v[j] = ex;
+      if (logits_out && lane == 0) logits_out[static_cast<size_t>(tk) * E + e] = ex;
+    }
+    float selv[GPTOSS_MAX_TOPK];
+    int seli[GPTOSS_MAX_TOPK];
+    uint32_t taken = 0;
+#pragma unroll
+    for (int r = 0; r < GPTOSS_MAX_TOPK; r++) {
+      if (r < K) {
+        float xv = -INFINITY;
+        int xi = 0x7fffffff;
+#pragma unroll
+        for (int j = 0; j < NT; j++) {
+          const int e = lane + 32 * j;
+          if (!((taken >> j) & 1u) && e < E && v[j] > -INFINITY && (v[j] > xv || xi == 0x7fffffff)) {
+            xv = v[j];
+            xi = e;
+          }
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+          const float ov = __shfl_xor_sync(0xffffffffu, xv, off);
+          const int oi = __shfl_xor_sync(0xffffffffu, xi, off);
+          if (oi != 0x7fffffff && (xi == 0x7fffffff || ov > xv || (ov == xv && oi < xi))) {
+            xv = ov;
+            xi = oi;
+          }
+        }
+        selv[r] = xv;
+        seli[r] = xi;
+        if (xi != 0x7fffffff && (xi & 31) == lane) taken |= 1u << (xi >> 5);
+      }
+    }
+    float ev[GPTOSS_MAX_TOPK];
+    double sum = 0.0;
+    const double mx = static_cast<double>(selv[0]);
+#pragma unroll
+    for (int r = 0; r < GPTOSS_MAX_TOPK; r++) {
+      if (r < K) {
+        ev[r] = expf(static_cast<float>(static_cast<double>(selv[r]) - mx));
+        sum += static_cast<double>(ev[r]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < GPTOSS_MAX_TOPK; r++) {
+      if (r < K && lane == r) {
+        topk_i[static_cast<size_t>(tk) * K + r] = seli[r];
+        topk_v[static_cast<size_t>(tk) * K + r] = static_cast<float>(static_cast<double>(ev[r]) / sum);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 2000000ull) {
+    }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, EPAD);
+  }
+}
+
 template <int NT, int SPLIT>
 static cudaError_t launch_router_split(const CUtensorMap &tmap_t, const CUtensorMap &tmap_w,
                                        const bf16 *t, const bf16 *w_router, const float *b_router,
@@ -392,12 +802,13 @@ static cudaError_t launch_router_split(const CUtensorMap &tmap_t, const CUtensor
                             status);
 }
 
+// The CUDA-core-MMA router (router_impl 1): kept selectable beside the tcgen05 one.
 template <int NT>
-static cudaError_t launch_router_nt(const bf16 *t, const bf16 *w_router, const float *b_router,
-                                    const int *pos, int T, int H, int E, int K, int *topk_i,
-                                    float *topk_v, float *logits_opt, int exact_ties, int *status,
-                                    cudaStream_t stream) {
+static cudaError_t launch_router_nt(gptoss_moe *h, const bf16 *t, const bf16 *w_router,
+                                    const float *b_router, const int *pos, int T, int *topk_i,
+                                    float *topk_v, float *logits_opt, cudaStream_t stream) {
   constexpr int EPAD = 32 * NT;
+  const int H = h->H, E = h->E, K = h->K;
   // tiles of one 64-element K chunk: 32 token rows, EPAD expert rows (rows that do not
   // exist read as zeros)
   CUtensorMap tmap_t, tmap_w;
@@ -406,38 +817,113 @@ static cudaError_t launch_router_nt(const bf16 *t, const bf16 *w_router, const f
       make_tmap_2d_bf16(&tmap_w, w_router, H, E, kRtKC, EPAD, &err))
     return cudaErrorInvalidValue;
   // few token groups (decode batches): four CTAs per group split the K loop
-  static int num_sms = 0;
-  if (!num_sms) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-  }
   const int groups = (T + kRtTokens - 1) / kRtTokens;
-  if (groups * 4 <= num_sms && H >= 16 * kRtKC)
+  if (groups * 4 <= h->num_sms && H >= 16 * kRtKC)
     return launch_router_split<NT, 4>(tmap_t, tmap_w, t, w_router, b_router, pos, T, H, E, K,
-                                      topk_i, topk_v, logits_opt, exact_ties, status, stream);
+                                      topk_i, topk_v, logits_opt, h->opt_exact_ties, h->status,
+                                      stream);
   return launch_router_split<NT, 1>(tmap_t, tmap_w, t, w_router, b_router, pos, T, H, E, K,
-                                    topk_i, topk_v, logits_opt, exact_ties, status, stream);
+                                    topk_i, topk_v, logits_opt, h->opt_exact_ties, h->status, stream);
 }
 
-cudaError_t launch_router_topk(const bf16 *t, const bf16 *w_router, const float *b_router,
-                               const int *pos, int T, int H, int E, int K, int *topk_i,
-                               float *topk_v, float *logits_opt, int exact_ties, int *status,
-                               cudaStream_t stream, long long *launches) {
+template <int EPAD, int NS>
+static cudaError_t launch_router_tc(gptoss_moe *h, LayerWeights &lw, const bf16 *t, const int *pos,
+                                    int T, int *topk_i, float *topk_v, float *logits_opt,
+                                    cudaStream_t stream) {
+  constexpr int kStages = RcStages<EPAD>::value;
+  const int H = h->H, E = h->E, K = h->K;
+  auto kernel = router_tc_kernel<EPAD, NS>;
+  const size_t smem = 1024 + static_cast<size_t>(kStages) * (kRcTokens + EPAD) * kRtRowBytes + 256 +
+                      EPAD * 4 + kRcTokens * 4 * (2 + kRcCand);
+  static_assert((2 * kStages + 1) * 8 + 16 <= 256, "barrier area");
+  std::string err;
+  // the router rows never move: their map is made once per layer; the token map is kept
+  // while the caller hands the same buffer and batch size
+  if (!lw.tmap_router_ready) {
+    if (make_tmap_2d_bf16(&lw.tmap_router, lw.w_router, H, E, kRtKC, EPAD, &err))
+      return cudaErrorInvalidValue;
+    lw.tmap_router_ready = true;
+  }
+  if (h->router_t_ptr != t || h->router_t_rows != T) {
+    if (make_tmap_2d_bf16(&h->tmap_router_t, t, H, T, kRtKC, kRcTokens, &err))
+      return cudaErrorInvalidValue;
+    h->router_t_ptr = t;
+    h->router_t_rows = T;
+  }
+  const int tiles = (T + kRcTokens - 1) / kRcTokens;
+  const int nk_all = (H + kRtKC - 1) / kRtKC;
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(kRcThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = h->opt_dependent_launch ? 2 : 1;
+  // CTAs per tile: as many as fill the GPU in one wave (a cluster shares the tile's K
+  // chunks); how many clusters of a size fit at once is asked of the runtime, once
+  // (the answer is the same on every GPU of one kind: concurrent first calls from several
+  // host threads write equal values)
+  static int fit[9] = {0};  // [cluster size] -> co-resident clusters of this kernel
+  // per device, cheap: set on every launch so every GPU a process drives has it
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)smem);
+  if (e != cudaSuccess) return e;
+  int split = h->num_sms / tiles;
+  if (split > 8) split = 8;
+  if (split > nk_all) split = nk_all;
+  if (split < 1) split = 1;
+  for (; split > 1; split--) {
+    if (!fit[split]) {
+      cfg.gridDim = dim3(static_cast<unsigned>(split * 8));
+      attr[0].val.clusterDim.x = split;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        n = -1;
+      }
+      fit[split] = n > 0 ? n : -1;
+    }
+    if (fit[split] >= tiles) break;
+  }
+  cfg.gridDim = dim3(static_cast<unsigned>(tiles * split));
+  attr[0].val.clusterDim.x = split;
+  return cudaLaunchKernelEx(&cfg, kernel, h->tmap_router_t, lw.tmap_router, t,
+                            static_cast<const bf16 *>(lw.w_router),
+                            static_cast<const float *>(lw.b_router), pos, T, H, E, K, topk_i,
+                            topk_v, logits_opt, h->opt_exact_ties, h->status);
+}
+
+cudaError_t launch_router_topk(gptoss_moe *h, int layer, const bf16 *t, const int *pos, int T,
+                               float *logits_opt, cudaStream_t stream) {
   if (T <= 0) return cudaSuccess;
-  if (launches) ++*launches;
-  if (E <= 32)
-    return launch_router_nt<1>(t, w_router, b_router, pos, T, H, E, K, topk_i, topk_v, logits_opt,
-                               exact_ties, status, stream);
-  if (E <= 64)
-    return launch_router_nt<2>(t, w_router, b_router, pos, T, H, E, K, topk_i, topk_v, logits_opt,
-                               exact_ties, status, stream);
-  if (E <= 128)
-    return launch_router_nt<4>(t, w_router, b_router, pos, T, H, E, K, topk_i, topk_v, logits_opt,
-                               exact_ties, status, stream);
-  if (E <= 256)
-    return launch_router_nt<8>(t, w_router, b_router, pos, T, H, E, K, topk_i, topk_v, logits_opt,
-                               exact_ties, status, stream);
+  h->launches++;
+  LayerWeights &lw = h->layers[layer];
+  const int E = h->E;
+  if (E > 256) return cudaErrorInvalidValue;
+  if (h->opt_router_impl == 1) {
+    const bf16 *w = lw.w_router;
+    const float *b = lw.b_router;
+    if (E <= 32) return launch_router_nt<1>(h, t, w, b, pos, T, h->topk_i, h->topk_v, logits_opt, stream);
+    if (E <= 64) return launch_router_nt<2>(h, t, w, b, pos, T, h->topk_i, h->topk_v, logits_opt, stream);
+    if (E <= 128) return launch_router_nt<4>(h, t, w, b, pos, T, h->topk_i, h->topk_v, logits_opt, stream);
+    return launch_router_nt<8>(h, t, w, b, pos, T, h->topk_i, h->topk_v, logits_opt, stream);
+  }
+#define GPTOSS_ROUTER_CASE(EP)                                                                   \
+  if (E <= EP)                                                                                   \
+    return h->K <= 4 ? launch_router_tc<EP, 5>(h, lw, t, pos, T, h->topk_i, h->topk_v,           \
+                                               logits_opt, stream)                               \
+                     : launch_router_tc<EP, 9>(h, lw, t, pos, T, h->topk_i, h->topk_v,           \
+                                               logits_opt, stream);
+  GPTOSS_ROUTER_CASE(32)
+  GPTOSS_ROUTER_CASE(64)
+  GPTOSS_ROUTER_CASE(128)
+  GPTOSS_ROUTER_CASE(256)
+#undef GPTOSS_ROUTER_CASE
   return cudaErrorInvalidValue;
 }
 

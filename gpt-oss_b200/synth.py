@@ -57,6 +57,9 @@ SHAPES = {
     # and the same tiles, 0.4 GB of weights (still larger than L2); the case that
     # profiler captures with many passes are taken on
     "c2s": MoeShape("gpt-oss-20b-moe-layer-8experts-T1792", 1792, 2880, 2880, 8, 4, 7.0, 1),
+    # c3 cut to 16 experts and an eighth of the tokens: the same 192 rows per expert,
+    # 0.8 GB of weights (larger than L2); the weight-streaming case for profiler captures
+    "c3s": MoeShape("gpt-oss-120b-moe-layer-16experts-T768", 768, 2880, 2880, 16, 4, 7.0, 2),
 }
 
 

@@ -148,7 +148,8 @@ int gptoss_moe_forward_host(gptoss_moe_t *h, int layer, const void *t_host, void
  * time (one stream per direction and one for the kernels).  x_host is valid
  * after gptoss_moe_forward_host_wait(h, ticket); t_host, x_host and pos_host must
  * stay untouched until then.  A fourth submit waits for the oldest.  All experts
- * local only.  While submissions are in flight the handle's workspaces are theirs:
+ * local, or expert parallel over the peer-memory transport (every rank then makes
+ * the same sequence of submits).  While submissions are in flight the handle's workspaces are theirs:
  * wait for every ticket before calling gptoss_moe_forward or the stage entry points
  * on the same handle (gptoss_moe_forward_host does that wait itself).  t_host may be NULL once gptoss_moe_load_ffn_norm gave the layer the
  * scale of the RMSNorm that precedes the block in the model (run.cpp:664): the
@@ -196,20 +197,26 @@ int gptoss_moe_get_activations(gptoss_moe_t *h, void *act_host, size_t bytes);
 
 /* Options: "gemm_impl" (GPTOSS_GEMM_*), "keep_logits" (0/1),
  * "exact_ties" (0/1, default 1: re-evaluate near-tied router logits in fp64),
+ * "router_impl" (0 = tcgen05 router, the default; 1 = the mma.sync router),
  * "ep_transport" (0/1, see gptoss_moe_ep_transport), "ep_overlap" (0/1, default 0;
  * peer-memory transport only: the owner pulls the rows of the second half of its
  * experts on a second stream while the gate_up GEMM of the first half runs),
- * "time_stages" (0/1, see gptoss_moe_stage_ms), "pair_stages" (4..6, operand
- * ring depth of the CTA-pair GEMM with bf16 weights), "skip_epilogue" (a bit
- * mask, default 0, measurement aid only - results are garbage while any bit is
- * set: 1 = the grouped GEMMs do not read their accumulators, 2 = compute but do
- * not store, 4 = MXFP4 path without the proxy fence, 8 = MXFP4 path without the
- * code -> bf16 conversion, 16 = no MMA issue). */
+ * "time_stages" (0/1, see gptoss_moe_stage_ms), "pair_rings" (6..9: how many of
+ * the CTA-pair GEMM's twelve 16 KB operand slots hold weight tiles, the rest
+ * token tiles; bf16 weights), "dependent_launch" (0/1: the layer's kernels are
+ * launched with programmatic stream serialization, so a kernel's set-up overlaps
+ * its predecessor's tail), "wait_limit_ms" (1..60000, default 2000: how long a
+ * kernel of the peer-memory transport waits for another rank's flag before it
+ * gives up with status 106).  Every option leaves the results unchanged. */
 int gptoss_moe_set_option(gptoss_moe_t *h, const char *name, int value);
 /* Kernels launched by this handle since creation. */
 long long gptoss_moe_launch_count(const gptoss_moe_t *h);
 /* Reads (and clears) the device status word; 0 = no kernel reported a problem.
- * Synchronises the device. */
+ * Synchronises the device.  Codes: 101-103 a bounded wait inside a kernel's
+ * pipeline ran out, 104 an index was out of range, 105 tensor-memory allocation,
+ * 106 another rank's flag did not arrive within "wait_limit_ms".  The calls that
+ * synchronise by themselves (gptoss_moe_forward_host, gptoss_moe_forward_host_wait,
+ * gptoss_decode_step) check the word and return GPTOSS_E_DEVICE when it is set. */
 int gptoss_moe_device_status(gptoss_moe_t *h);
 /* Average duration in milliseconds of one stage, measured with CUDA events
  * recorded on the launching stream around the stage's kernels in every call
@@ -226,6 +233,31 @@ int gptoss_moe_stage_ms(gptoss_moe_t *h, int stage, float *ms);
  */
 int gptoss_moe_ep_unique_id(void *id128);
 int gptoss_moe_ep_init(gptoss_moe_t *h, const void *id128);
+/*
+ * The same for a host that drives all GPUs from one process with a thread per GPU,
+ * as the reference does (getp_run.cpp:1038-1063, warm_up_ep expert.cpp:1176-1231):
+ * engines[r] was created with ep_rank r and ep_size n_engines, each on its own
+ * device.  Called once, from one thread, before any forward: enables peer access
+ * between the devices and hands every engine the others' buffers as plain
+ * pointers - no NCCL, no IPC.  Only the peer-memory transport exists then.  The
+ * engines must be destroyed together, after all of their streams are idle.
+ * Fails (on every engine alike) when the engines differ in max_tokens, hidden
+ * size, expert count or top-k; gptoss_moe_ep_init makes the same check across
+ * processes.
+ */
+int gptoss_moe_ep_init_local(gptoss_moe_t *const *engines, int n_engines);
+/*
+ * gptoss_moe_forward under expert parallelism over peer memory, one part at a time:
+ * part 0 = router + publish (needs t, pos), 1 = owner stage (waits for every
+ * rank's part 0), 2 = combine into x (waits for every rank's part 1).  For a host
+ * that runs several ranks through ONE stream - every rank's part 0, then every
+ * rank's part 1, then every rank's part 2 - so that no kernel is ever launched
+ * before the kernels whose flags it polls; that is also the only way ranks may
+ * share a GPU.  (The reference's counterpart is the three phases of
+ * gpu_forward_device_batch_ep, expert.cpp:1432-1478, :1480-1552, :1554-1605.)
+ */
+int gptoss_moe_forward_part(gptoss_moe_t *h, int layer, int part, const void *t, void *x,
+                            const int *pos, int n_tokens, void *stream);
 /* How rows travel between ranks: 0 = NCCL send / recv (dispatch, owner experts,
  * return, combine as separate steps, one host synchronisation per layer for the
  * row counts), 1 = peer memory (each owner's gather kernel reads the rows it
@@ -233,7 +265,7 @@ int gptoss_moe_ep_init(gptoss_moe_t *h, const void *id128);
  * reads the owners' per-row sums the same way; routing results are written into
  * the peers' memory and the two rendezvous of a layer are flags in peer memory
  * with bounded polls - no NCCL call and no host synchronisation in the layer; a
- * flag that does not arrive within 2 s leaves GPTOSS_E_DEVICE in
+ * flag that does not arrive within "wait_limit_ms" (2 s) leaves status 106 in
  * gptoss_moe_device_status; the reference's counterpart is the peer copies of
  * expert.cpp:1520-1535 and :1577).  gptoss_moe_ep_init selects 1 when every rank could map
  * every peer's buffers through CUDA IPC (one process per rank, one node), else 0;
@@ -256,7 +288,8 @@ int gptoss_moe_ep_transport(const gptoss_moe_t *h);
  *
  * Same result as gptoss_moe_permute without the row gather: for n_rows rows with
  * top_k slots each (slot_expert: expert id or -1 to skip the slot; ids >=
- * n_experts are skipped too), a stable counting sort by expert.  All pointers
+ * n_experts are skipped too, silently: this call has no status word to report
+ * them in), a stable counting sort by expert.  All pointers
  * are device pointers owned by the caller:
  *   expert_offsets [n_experts+1], sorted_row / sorted_weight [n_rows*top_k]
  *   (first expert_offsets[n_experts] entries valid), row_of [n_rows*top_k]
@@ -264,8 +297,9 @@ int gptoss_moe_ep_transport(const gptoss_moe_t *h);
  * Limits: n_rows <= 8192, n_experts <= 256, top_k <= 8; anything larger is
  * rejected with GPTOSS_E_CAPACITY (text via gptoss_moe_last_error(NULL)).
  *
- * The first call on each device looks up the array's device address; make that
- * first call before starting any stream capture.  All calls on one GPU share
+ * The first call on each device looks up the array's device address (several host
+ * threads may make it at once); make that first call before starting any stream
+ * capture.  All calls on one GPU share
  * the one array, which keeps the previous call's contents (the call clears the
  * words that must start at zero): two calls whose kernels overlap on the GPU,
  * from different streams or threads, race - serialise them.

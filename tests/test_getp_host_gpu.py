@@ -64,3 +64,69 @@ def test_getp_entry_points_on_tiny_model(pkg, tmp_path):
         break  # the sequences differ from here on by construction
     else:
         assert len(got) == len(want)
+
+
+def _run_host(native_build, bin_path, req, out, env_extra):
+    env = dict(os.environ, **env_extra)
+    res = subprocess.run([str(native_build.HARNESS), str(bin_path), str(req), str(out)],
+                         capture_output=True, text=True, env=env, timeout=900)
+    assert res.returncode == 0, res.stdout + res.stderr
+    rows = [[int(t) for t in line.split()] for line in out.read_text().splitlines()]
+    return rows, res.stdout
+
+
+def test_getp_entry_points_expert_parallel(pkg, tmp_path):
+    """warm_up / inference / finish with the experts sharded over 2 GPUs (the reference's
+    GETP_FORCE_EP switch), one host thread per GPU.  The second GPU's requests end after
+    two steps (an end-of-sequence id in the prompt) while the first GPU decodes two full
+    batches: the idle GPU must keep stepping for its experts' sake and all threads must
+    stop together.  The generated ids must equal the one-GPU run's; where they part, the
+    one-GPU engine's own logits at that step must be a near tie (sharding adds one bf16
+    rounding per owner to the block's output)."""
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    from gpt_oss_b200 import build as native_build
+    from gpt_oss_b200 import synth
+
+    if not native_build.HARNESS.exists():
+        native_build.build_host()
+    g = np.load(ROOT / "tests" / "golden" / "model_tiny.npz")
+    cfg = synth.TINY_MODEL
+    n_prompt = int(g["n_prompt"])
+    bin_path = tmp_path / "tiny.bin"
+    synth.write_model_bin(bin_path, cfg, int(g["seed"]))
+    rng = np.random.default_rng(11)
+    prompts = [list(g["tokens"][:n_prompt]),
+               list(rng.integers(0, cfg["vocab_size"], size=5)),
+               [23, 199999, 7],      # these two go to the second GPU and end at once
+               [1234, 200002]]
+    req = tmp_path / "requests.txt"
+    req.write_text(f"{len(prompts)}\n" + "\n".join(" ".join(str(int(t)) for t in p) for p in prompts) + "\n")
+    one, _ = _run_host(native_build, bin_path, req, tmp_path / "one.txt",
+                       {"GPTOSS_GETP_GPUS": "1", "GPTOSS_GETP_BATCH": "1"})
+    two, log = _run_host(native_build, bin_path, req, tmp_path / "two.txt",
+                         {"GPTOSS_GETP_GPUS": "2", "GPTOSS_GETP_BATCH": "1", "GETP_FORCE_EP": "1",
+                          "NCCL_NVLS_ENABLE": "0"})
+    assert "experts sharded over the GPUs" in log
+    assert len(one) == len(two) == len(prompts)
+    assert two[2] == [] and two[3] == []
+    assert len(prompts[0]) + len(two[0]) == cfg["seq_len"] or any(t in (199999, 200002) for t in two[0])
+    image = np.fromfile(bin_path, dtype=np.uint8)
+    eng = pkg.DecodeEngine(cfg, 1)
+    eng.load_bin(image)
+    try:
+        for p, a, b in zip(prompts, one, two):
+            if a == b:
+                continue
+            i = next(k for k in range(min(len(a), len(b))) if a[k] != b[k])
+            seq = list(p) + a[:i]
+            for pos_i, tok in enumerate(seq):
+                eng.step(np.array([tok], np.int32), np.array([pos_i], np.int32))
+            lg = eng.logits(0)
+            gap = abs(float(lg[a[i]]) - float(lg[b[i]]))
+            assert gap <= 2e-2, (f"generated token {i}: {a[i]} on one GPU, {b[i]} with sharded "
+                                 f"experts, logits {gap:.4f} apart")
+    finally:
+        eng.close()

@@ -54,10 +54,11 @@ def _case(pkg, oracle, T, H, IM, E, K, inactive=0, on_device=False, scale_range=
     active = d["pos"] >= 0
     np.testing.assert_array_equal(r["topk_i"][active], want["topk_i"][active])
     # block output (zero residual); its magnitude here is larger than in the bf16 cases, so
-    # the absolute limit is scaled to it the same way (2e-2 at |y| ~ 0.6)
-    scale = max(1.0, float(np.abs(want["e_agg"]).std()) / 0.6)
+    # the absolute limit is the stated 2e-2 scaled to it (the stated figure goes with outputs
+    # of std 0.6)
+    scale = max(1.0, float(want["e_agg"][active].std()) / 0.6)
     helpers.check_activations(got[active], want["e_agg"][active], "mxfp4 block output",
-                              max_abs=2e-2 * scale * 2, mean_rel=1e-2)
+                              max_abs=helpers.MAX_ABS * scale, mean_rel=helpers.MEAN_REL)
     assert (got[~active] == 0).all()
 
 

@@ -62,6 +62,60 @@ def test_static_permutation_matches_engine_permutation_twice(pkg):
     _one_call(pkg, synth.MoeShape("static_small", 300, 128, 64, 8, 2, 7.0, 52), inactive_every=0)
 
 
+def _numpy_permutation(slot_expert, n_experts):
+    """Stable counting sort of the flat (row, slot) pairs by expert; ids outside
+    [0, n_experts) are skipped."""
+    flat = slot_expert.reshape(-1)
+    valid = (flat >= 0) & (flat < n_experts)
+    order = np.nonzero(valid)[0]
+    order = order[np.argsort(flat[order], kind="stable")]
+    offsets = np.zeros(n_experts + 1, np.int64)
+    np.add.at(offsets, flat[valid] + 1, 1)
+    offsets = np.cumsum(offsets)
+    row_of = np.full(flat.shape, -1, np.int64)
+    row_of[order] = np.arange(order.size)
+    return offsets, order, row_of
+
+
+@pytest.mark.parametrize("rows,k,e", [(8192, 8, 256), (8192, 1, 256), (8191, 8, 255), (1, 8, 256)])
+def test_static_permutation_at_its_limits(pkg, rows, k, e):
+    """The largest sizes the fixed scratch takes, against a numpy counting sort; some
+    slots empty (-1) and some with ids past the last expert (skipped without a report)."""
+    import torch
+
+    rng = np.random.default_rng(rows + k + e)
+    slot_expert = rng.integers(-1, e + 3, size=(rows, k)).astype(np.int32)
+    slot_weight = rng.random((rows, k), dtype=np.float32)
+    dev = torch.device("cuda:0")
+    se, sw = torch.from_numpy(slot_expert).to(dev), torch.from_numpy(slot_weight).to(dev)
+    offsets = torch.full((e + 1,), -7, dtype=torch.int32, device=dev)
+    sorted_row = torch.full((rows * k,), -7, dtype=torch.int32, device=dev)
+    sorted_weight = torch.full((rows * k,), -7.0, dtype=torch.float32, device=dev)
+    row_of = torch.full((rows * k,), -7, dtype=torch.int32, device=dev)
+    for _ in range(2):  # twice in a row: the scratch keeps the first call's contents
+        pkg.permute_static(se, sw, rows, k, e, offsets, sorted_row, sorted_weight, row_of,
+                           torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    want_off, want_order, want_row_of = _numpy_permutation(slot_expert, e)
+    n = int(want_off[-1])
+    np.testing.assert_array_equal(offsets.cpu().numpy(), want_off)
+    np.testing.assert_array_equal(sorted_row.cpu().numpy()[:n], want_order // k)
+    np.testing.assert_array_equal(sorted_weight.cpu().numpy()[:n], slot_weight.reshape(-1)[want_order])
+    np.testing.assert_array_equal(row_of.cpu().numpy(), want_row_of)
+    assert (sorted_row.cpu().numpy()[n:] == -7).all()
+
+
+def test_static_permutation_of_nothing(pkg):
+    import torch
+
+    dev = torch.device("cuda:0")
+    offsets = torch.full((33,), -7, dtype=torch.int32, device=dev)
+    pkg.permute_static(None, None, 0, 4, 32, offsets, None, None, None,
+                       torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert (offsets.cpu().numpy() == 0).all()
+
+
 def test_static_permutation_rejects_sizes_beyond_its_scratch(pkg):
     import torch
 
