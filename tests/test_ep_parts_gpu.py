@@ -6,7 +6,8 @@ every rank's owner stage, then every rank's combine (gptoss_moe_forward_part) - 
 kernel is launched before the kernels whose flags it polls: the flag waits inside the
 kernels always find their flags set.  That is the whole data path of the peer-memory
 transport (routing results written into every rank's control block, owners sorting all
-ranks' rows and pulling them from the homes' buffers, homes pulling the owners' sums),
+ranks' rows and pulling them from the homes' buffers, homes pulling the expert outputs
+of their tokens' slots from the owners' buffers),
 checked against the CPU oracle on every rank's own tokens, on a box with one GPU.
 
 Also here: a bounded wait that runs out.  One rank runs its owner stage although the
@@ -88,6 +89,9 @@ def test_ranks_on_one_gpu_match_the_oracle(pkg, oracle, world, H, IM, E, K, size
                 helpers.check_activations(got[active], want["x_out"][active], f"rank {r} x_out",
                                           bf16_quantum=True)
                 np.testing.assert_array_equal(got[~active], x[~active])
+                # the homes add the same K expert outputs in the same order as one GPU with
+                # all experts does: sharding does not change a bit of the result
+                np.testing.assert_array_equal(got, helpers.run_gpu_layer(pkg, shape, d)["x_out"])
                 mine = ep_plan.local_expert_slice(E, r, world)
                 assert routing["expert_offsets"].shape[0] == len(mine) + 1
     finally:
