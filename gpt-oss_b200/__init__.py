@@ -301,8 +301,10 @@ class MoeEngine:
         topk_i = np.empty((n_tokens, K), dtype=np.int32)
         topk_v = np.empty((n_tokens, K), dtype=np.float32)
         offsets = np.empty((El + 1,), dtype=np.int32)
-        sorted_token = np.full((max(1, n_tokens * K * max(1, self.cfg.ep_size)),), -1,
-                               dtype=np.int32)
+        # under expert parallelism the owner's sorted order holds rows of every rank's batch,
+        # whatever this rank's own n_tokens is: size for the engine's capacity
+        rows_cap = self.cfg.max_tokens * max(1, self.cfg.ep_size) if self.cfg.ep_size > 1 else n_tokens
+        sorted_token = np.full((max(1, rows_cap * K),), -1, dtype=np.int32)
         logits = np.empty((n_tokens, E), dtype=np.float32) if want_logits else None
         self._check(self.lib.gptoss_moe_get_routing(self.handle, n_tokens, _ptr(topk_i),
                                                     _ptr(topk_v), _ptr(offsets),

@@ -128,6 +128,7 @@ struct gptoss_moe {
   int opt_time_stages = 0;
   int opt_ep_overlap = 0;  // peer transport: second half of the experts gathered under the first half's GEMM
   int opt_router_impl = 0;  // 0 = tcgen05 router, 1 = mma.sync router
+  int opt_router_split = 0; // tcgen05 router: CTAs that share a 128-token tile (0 = fill the GPU)
   int opt_pair_rings = 8;   // CTA-pair GEMM: weight slots of the twelve 16 KB operand slots (6..9)
   int opt_dependent_launch = 0;  // programmatic dependent launch between the layer's kernels
   int opt_wait_limit_ms = 2000;  // longest wait for another rank's flag (peer-memory transport)

@@ -24,8 +24,8 @@
 // each of a token's K slots, the weighted expert output from the owner's buffer (the
 // position from the owner's inverse permutation), adds the K rows in slot order in
 // fp32 and adds the residual - return and combine are one kernel, and the sum is the
-// single-GPU combine's, value for value: sharding does not change a bit of the
-// result.  (The reference's owner first sums its experts' outputs per row and rounds
+// single-GPU combine's, the same K rows in the same order: sharding adds no rounding
+// of its own.  (The reference's owner first sums its experts' outputs per row and rounds
 // that to bf16, expert.cpp:394-410: one more rounding per owner and one more pass over
 // the outputs, for a little less traffic.)  A rank reuses a buffer only after the flags that prove
 // its readers are done: activations and routing slots after the second flags of the
@@ -298,8 +298,8 @@ __device__ __forceinline__ uint4 ld_peer_v4(const uint4 *p) {
 // that the slot's owner holds for it).  Slot k of token t went to owner o = e % N, whose
 // permutation put it at row_of[o][(rank * max_t + t) * K + k] of its sorted order; the
 // owner's down GEMM left the weighted bf16 output there (ys).  Position and row are read
-// from the owner's memory.  This is, value for value and in the same order, the sum the
-// single-GPU combine makes, so sharding the experts does not change a bit of the result.
+// from the owner's memory.  This is the sum the single-GPU combine makes, the same K rows
+// in the same order, so sharding the experts adds no rounding of its own.
 // One warp per token, two 16-byte columns per lane and trip.
 __global__ void __launch_bounds__(256)
 combine_peer_kernel(bf16 *__restrict__ x, const PeerRows ys, const PeerInts rowof,

@@ -650,6 +650,9 @@ int gptoss_moe_set_option(gptoss_moe_t *h, const char *name, int value) {
   } else if (!strcmp(name, "router_impl")) {
     if (value != 0 && value != 1) return fail(h, GPTOSS_E_INVALID, "router_impl must be 0 or 1");
     h->opt_router_impl = value;
+  } else if (!strcmp(name, "router_split")) {
+    if (value < 0 || value > 8) return fail(h, GPTOSS_E_INVALID, "router_split must be 0..8");
+    h->opt_router_split = value;
   } else if (!strcmp(name, "pair_rings")) {
     if (value < 6 || value > 9) return fail(h, GPTOSS_E_INVALID, "pair_rings must be 6..9");
     h->opt_pair_rings = value;

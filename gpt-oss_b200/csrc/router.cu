@@ -467,7 +467,6 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmap_t,
   const uint32_t tmem_base = *tmem_holder;
   grid_dependency_wait();
   grid_launch_dependents();
-  for (int e = tid; e < EPAD; e += kRcThreads) bias_s[e] = e < E ? __ldg(b_router + e) : 0.f;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -523,11 +522,15 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmap_t,
   const int row = q * 32 + lane;      // token row of the tile held by this thread's TMEM lane
   bool acc_ok = true;
   if (selector) {
+    // the selecting warps fetch the bias while the main loop runs
+    for (int e = tid - 64; e < EPAD; e += kRcSelWarps * 32) bias_s[e] = e < E ? __ldg(b_router + e) : 0.f;
+    asm volatile("bar.sync 1, %0;" ::"n"(kRcSelWarps * 32) : "memory");
     if (!mbar_wait(tfull_bar, 0, abort_flag)) {
       set_status(status, kStatusWaitTimeoutEpilogue);
       *abort_flag = 1;
       acc_ok = false;
     }
+    acc_ok = __all_sync(0xffffffffu, acc_ok);
     tc_fence_after();
   }
   const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
@@ -873,7 +876,7 @@ static cudaError_t launch_router_tc(gptoss_moe *h, LayerWeights &lw, const bf16 
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem);
   if (e != cudaSuccess) return e;
-  int split = h->num_sms / tiles;
+  int split = h->opt_router_split > 0 ? h->opt_router_split : h->num_sms / tiles;
   if (split > 8) split = 8;
   if (split > nk_all) split = nk_all;
   if (split < 1) split = 1;

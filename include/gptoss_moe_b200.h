@@ -187,7 +187,8 @@ int gptoss_moe_rmsnorm(gptoss_moe_t *h, void *out, const void *x, const float *w
  * Debug taps of the last forward (host destination buffers, any may be NULL;
  * synchronises the device).  topk_i / topk_v [n_tokens,K] (inactive rows: -1 /
  * 0), expert_offsets [E_local+1], sorted_token [n_assignments] (row of t, in
- * per-expert order), logits [n_tokens,E] only when enabled with
+ * per-expert order; under expert parallelism the owner's order holds rows of every
+ * rank's batch: room for max_tokens * ep_size * K entries), logits [n_tokens,E] only when enabled with
  * gptoss_moe_set_option("keep_logits", 1).
  */
 int gptoss_moe_get_routing(gptoss_moe_t *h, int n_tokens, int *topk_i, float *topk_v,
@@ -198,6 +199,8 @@ int gptoss_moe_get_activations(gptoss_moe_t *h, void *act_host, size_t bytes);
 /* Options: "gemm_impl" (GPTOSS_GEMM_*), "keep_logits" (0/1),
  * "exact_ties" (0/1, default 1: re-evaluate near-tied router logits in fp64),
  * "router_impl" (0 = tcgen05 router, the default; 1 = the mma.sync router),
+ * "router_split" (0..8: CTAs that share one 128-token tile of the tcgen05 router,
+ * each taking a part of the hidden dimension; 0 = as many as fill the GPU),
  * "ep_transport" (0/1, see gptoss_moe_ep_transport), "ep_overlap" (0/1, default 0;
  * peer-memory transport only: the owner pulls the rows of the second half of its
  * experts on a second stream while the gate_up GEMM of the first half runs),

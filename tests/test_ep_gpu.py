@@ -81,10 +81,12 @@ def _worker(rank, world, uid, tmp):
                 helpers.check_activations(outs[0][d["pos"] >= 0], outs[1][d["pos"] >= 0],
                                           "NCCL transport vs peer memory", bf16_quantum=True)
             got = outs[-1]
-            # one GPU with all experts gives the same bits as the peer-memory transport
+            # one GPU with all experts: the same sum of the same K rows per token; only the
+            # GEMMs' own last bits differ (other tile widths)
             if len(outs) == 3:
                 single = helpers.run_gpu_layer(pkg, shape, d)["x_out"]
-                np.testing.assert_array_equal(got, single)
+                helpers.check_activations(got, single, "peer memory vs one GPU", max_abs=4e-2,
+                                          mean_rel=1e-3)
             active = d["pos"] >= 0
             r = eng.get_routing(T)
             helpers.check_indices(r["topk_i"], want["topk_i"], want["logits"], active)
