@@ -23,7 +23,9 @@ Other workloads (each prints its own line):
         split like any other count that N divides)
   c2s   a quarter-size 20b-shape layer (8 experts, T = 1792) for profiler captures
   c3s   an eighth-size 120b-shape layer (16 experts, T = 768: the same 192 rows per
-        expert) for profiler captures
+        expert) for profiler captures of the GEMMs
+  c3r   the 120b-shape routing problem (T = 6144, 128 experts) with narrow experts, for
+        profiler captures of the router, permutation and combine kernels
   c4    the MXFP4 decode shapes as their own line
   c5    one decode step of the full 120b-architecture model (36 layers, 6144
         sequences with 512 positions of KV context), experts sharded over N >= 2 GPUs,
@@ -933,7 +935,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3",
-                    choices=["c3", "c2", "c2s", "c3s", "c4", "c5", "tiny"])
+                    choices=["c3", "c2", "c2s", "c3s", "c3r", "c4", "c5", "tiny"])
     ap.add_argument("--cpu-tokens", type=int, default=None,
                     help="tokens in the CPU sample (default 256 for ours, 64 for reference)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -960,7 +962,7 @@ def main():
     else:
         args.steps = args.steps if args.steps is not None else 100
         args.warmup = max(3, args.warmup if args.warmup is not None else 10)
-        if args.workload in ("c2s", "c3s", "tiny"):
+        if args.workload in ("c2s", "c3s", "c3r", "tiny"):
             args.no_extra = True
         run_ours(args, shape)
 

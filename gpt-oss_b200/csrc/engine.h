@@ -33,8 +33,10 @@ struct LayerWeights {
   uint8_t *w1_blocks = nullptr, *w2_blocks = nullptr;
   CUtensorMap tmap_w1, tmap_w2;            // boxes of 240 weight rows (N operand)
   CUtensorMap tmap_w1_rows, tmap_w2_rows;  // boxes of 128 weight rows (M operand, CTA pairs)
-  CUtensorMap tmap_router;                 // router rows in boxes of one K chunk (made on first use)
-  bool tmap_router_ready = false;
+  // router rows tile by tile (128 rows x 64 k, zero padded; weights.cu's layout): the
+  // tcgen05 router's M operand, one box per K chunk
+  bf16 *router_tiled = nullptr;
+  CUtensorMap tmap_router_tiled;
   float *rms_ffn = nullptr;   // [H] scale of the RMSNorm in front of the block (optional)
   bool loaded = false;
 };
@@ -112,7 +114,7 @@ struct gptoss_moe {
   // router: tensor map of the caller's activations, kept while the same buffer comes back
   CUtensorMap tmap_router_t;
   const void *router_t_ptr = nullptr;
-  int router_t_rows = 0;
+  int router_t_rows = 0, router_t_box = 0;
 
   // weight upload: fp32 host tensors through pinned and device staging, converted on the device
   static constexpr size_t kUploadChunk = (size_t)8 << 20;  // elements per chunk (32 MB of fp32)
@@ -127,10 +129,10 @@ struct gptoss_moe {
   int opt_exact_ties = 1;
   int opt_time_stages = 0;
   int opt_ep_overlap = 0;  // peer transport: second half of the experts gathered under the first half's GEMM
+  int opt_ep_gather_ctas = 64;  // CTAs of that overlapped gather
   int opt_router_impl = 0;  // 0 = tcgen05 router, 1 = mma.sync router
-  int opt_router_split = 0; // tcgen05 router: CTAs that share a 128-token tile (0 = fill the GPU)
-  int opt_pair_rings = 8;   // CTA-pair GEMM: weight slots of the twelve 16 KB operand slots (6..9)
-  int opt_dependent_launch = 0;  // programmatic dependent launch between the layer's kernels
+  int opt_dependent_launch = 1;  // programmatic dependent launch between the layer's kernels
+  int opt_l2_hints = 1;     // CTA-pair GEMM: weights evict-first, token tiles evict-last
   int opt_wait_limit_ms = 2000;  // longest wait for another rank's flag (peer-memory transport)
   gptoss::StageTimer timers[8];
   long long launches = 0;
@@ -145,6 +147,8 @@ namespace gptoss {
 // router.cu
 cudaError_t launch_router_topk(gptoss_moe *h, int layer, const bf16 *t, const int *pos, int T,
                                float *logits_opt, cudaStream_t stream);
+// the router rows re-tiled for the tcgen05 router (after w_router is in place)
+int build_router_tiles(gptoss_moe *h, LayerWeights &lw);
 cudaError_t launch_rmsnorm(bf16 *out, const bf16 *x, const float *w, const int *pos, int T, int H,
                            cudaStream_t stream, long long *launches);
 
@@ -201,6 +205,11 @@ int set_global_error(int code, const char *text);
 // weights.cu
 cudaError_t launch_f32_to_bf16(bf16 *dst, const float *src, size_t n, cudaStream_t stream,
                                long long *launches);
+size_t tiled_weight_elems(int rows, int k, int n_experts);
+cudaError_t launch_retile_weights(bf16 *dst, const bf16 *src, int rows, int k, int n_experts,
+                                  cudaStream_t stream, long long *launches);
+// a tensor of 16 KB tiles as rows of 512 bytes, one tile per box of 32 rows, no swizzle
+int make_tmap_tiles_bf16(CUtensorMap *map, const void *base, uint64_t n_tiles, std::string *err);
 
 }  // namespace gptoss
 

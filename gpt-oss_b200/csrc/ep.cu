@@ -570,7 +570,8 @@ static int ep_peer_owner(gptoss_moe *h, EpState *ep, int layer, const bf16 *t, c
       // the second half starts when the first has the links to itself no longer
       EP_CUDA(h, cudaEventRecord(ep->ev_plan, st));
       EP_CUDA(h, cudaStreamWaitEvent(ep->s2, ep->ev_plan, 0));
-      gather_rows_peer_kernel<<<h->num_sms * 2, 256, 0, ep->s2>>>(
+      // few CTAs: the copy has to keep the links busy, not the SMs, which the GEMM needs
+      gather_rows_peer_kernel<<<h->opt_ep_gather_ctas, 256, 0, ep->s2>>>(
           h->xs, src, max_t, h->sorted_row, h->expert_offsets, e_mid, h->El, H, R, h->status);
       EP_CUDA(h, cudaGetLastError());
       EP_CUDA(h, cudaEventRecord(ep->ev_second, ep->s2));

@@ -35,6 +35,8 @@ struct GemmArgs {
   // others are still on their way
   int tile_part = 0;
   const int *tile_split = nullptr;
+  // (CTA-pair kernel) the loads carry L2 eviction hints: weights first out, token tiles last
+  int l2_hints = 0;
 };
 
 // gate * sigmoid(alpha * gate) * (up + 1) with the reference CPU path's clamps

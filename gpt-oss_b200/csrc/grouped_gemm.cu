@@ -359,6 +359,23 @@ int make_tmap_2d_bf16(CUtensorMap *map, const void *base, uint64_t inner, uint64
   return GPTOSS_OK;
 }
 
+int make_tmap_tiles_bf16(CUtensorMap *map, const void *base, uint64_t n_tiles, std::string *err) {
+  EncodeTiledFn fn = get_encode_fn(err);
+  if (!fn) return GPTOSS_E_CUDA;
+  cuuint64_t dims[2] = {256, n_tiles * 32};
+  cuuint64_t strides[1] = {512};
+  cuuint32_t box[2] = {256, 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims,
+                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    if (err) *err = "cuTensorMapEncodeTiled (tiles) failed with CUresult " + std::to_string((int)r);
+    return GPTOSS_E_CUDA;
+  }
+  return GPTOSS_OK;
+}
+
 template <int EPI>
 static cudaError_t launch_tc(gptoss_moe *h, const CUtensorMap &ta, const CUtensorMap &tb,
                              const GemmArgs &g, cudaStream_t stream) {

@@ -19,21 +19,12 @@
 // No TMA load uses multicast: the halves of the shared operand are loaded by the
 // CTA that holds them.
 //
-// Two operand rings per CTA instead of one ring of (weights, tokens) pairs: the
-// weight tiles are the stream that comes from HBM (every byte read once, latency
-// of a microsecond and more under load), the token tiles are re-read by every
-// weight-row pair of the expert and come from L2.  A weight ring of kW slots and a
-// token ring of kX slots (kW > kX, same shared memory as kW = kX) keeps half as
-// many more weight bytes in flight, which is what a weight-streaming shape (few
-// rows per expert) is bound by.
-//
-// Warp roles per CTA (352 threads): warp 0 lane 0 = TMA producer of the weight ring,
-// warp 2 lane 0 = TMA producer of the token ring (both CTAs; the odd CTA's loads
-// complete on the even CTA's full barriers), warp 1 lane 0 of the even CTA = MMA
-// issuer, warp 1 = paired TMEM allocation, warps 3-10 = epilogue.  tcgen05.commit
-// with a 2-CTA mask releases the slots / publishes the accumulator in both CTAs;
-// the odd CTA's epilogue warps release the accumulator with a remote mbarrier
-// arrive.
+// Warp roles per CTA (320 threads): warp 0 lane 0 = TMA producer (both CTAs; the
+// odd CTA's loads complete on the even CTA's full barrier), warp 1 lane 0 of the
+// even CTA = MMA issuer, warp 1 = paired TMEM allocation, warps 2-9 = epilogue.
+// tcgen05.commit with a 2-CTA mask releases the stage / publishes the accumulator
+// in both CTAs; the odd CTA's epilogue warps release the accumulator with a
+// remote mbarrier arrive.
 //
 // Epilogue (transposed): a TMEM lane is an output feature, a column a token.  A
 // warp reads 32 lanes x 32 tokens, adds the lane's bias, pairs gate/up rows
@@ -50,9 +41,9 @@
 
 namespace gptoss {
 
-constexpr int kPairThreads = 352;
+constexpr int kPairThreads = 320;
 constexpr int kPairOperandBytes = 128 * kTileK * 2;          // 16 KB: 128 rows x 64 k
-constexpr int kPairEpiWarps = kPairThreads / 32 - 3;
+constexpr int kPairEpiWarps = kPairThreads / 32 - 2;
 constexpr int kAccColsPair = 256;  // TMEM columns per accumulator (up to 256 tokens), two of them
 
 template <int EPI>
@@ -89,38 +80,41 @@ __device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
   return *reinterpret_cast<uint32_t *>(&r);
 }
 
-// kW / kX = slots of the weight ring and of the token ring.
-// TOKB = token rows a slot of the token ring holds (128: token tiles of up to 256; 32:
-// tiles of up to 64 for decode-sized batches, which buys deeper rings)
+// Linear tile index -> (token tile, weight-row pair): the pairs of one token tile are
+// consecutive, so the clusters of one wave share one or two token tiles (L2 hits) and stream
+// each weight block once.  (Spreading a wave over several token tiles measured no faster.)
+__device__ __forceinline__ void decode_tile(int tile, int w_pairs, int tt_lo, int *tt, int *wp) {
+  const int q = tile / w_pairs;
+  *tt = tt_lo + q;
+  *wp = tile - q * w_pairs;
+}
+
+// TOKB = token rows a CTA's operand slot holds (128: token tiles of up to 256; 32:
+// tiles of up to 64 for decode-sized batches, which buys a deeper ring)
 // kRawStages = depth of the raw (packed) weight ring, 0 without MX; LUTREP = copies of the
 // code table, a power of two (32: one per bank, every lane reads its own copy and no
 // lookup conflicts; 16: lanes l and l + 16 share one)
-template <int EPI, int kW, int kX, bool MX, int TOKB, int kRawStages, int LUTREP>
+template <int EPI, int kPairStages, bool MX, int TOKB, int kRawStages, int LUTREP>
 __global__ void __launch_bounds__(kPairThreads + (MX ? (kDequantWarps + 1) * 32 : 0), 1)
 grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
                          const __grid_constant__ CUtensorMap tmap_x,
                          const __grid_constant__ CUtensorMap tmap_x32,
                          const __grid_constant__ CUtensorMap tmap_x8, const GemmArgs g) {
-  constexpr int kXBytes = TOKB * kTileK * 2;  // one slot of the token ring (this CTA's half)
-  static_assert(kXBytes % 1024 == 0, "token slots must stay 1024-byte aligned (128-byte swizzle)");
+  constexpr int kPairStageBytes = kPairOperandBytes + TOKB * kTileK * 2;  // weights + token half
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   unsigned char *smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
-  unsigned char *w_ring = smem;
-  unsigned char *x_ring = smem + kW * kPairOperandBytes;
-  uint64_t *wfull_bar = reinterpret_cast<uint64_t *>(x_ring + kX * kXBytes);
-  uint64_t *wempty_bar = wfull_bar + kW;
-  uint64_t *xfull_bar = wempty_bar + kW;
-  uint64_t *xempty_bar = xfull_bar + kX;
-  uint64_t *tfull_bar = xempty_bar + kX;          // [2]
+  uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + kPairStages * kPairStageBytes);
+  uint64_t *empty_bar = full_bar + kPairStages;
+  uint64_t *tfull_bar = empty_bar + kPairStages;  // [2]
   uint64_t *tempty_bar = tfull_bar + 2;           // [2], used in the even CTA
   uint64_t *raw_full = tempty_bar + 2;            // [kRawStages] (MX)
   uint64_t *raw_empty = raw_full + kRawStages;    // [kRawStages] (MX)
   uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(raw_empty + kRawStages);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
-  static_assert((2 * kW + 2 * kX + 4 + 2 * kRawStages) * 8 + 8 <= kPairBarrierBytes,
+  static_assert((2 * kPairStages + 4 + 2 * kRawStages) * 8 + 8 <= kPairBarrierBytes,
                 "barrier region too small");
-  unsigned char *epi_stage = reinterpret_cast<unsigned char *>(wfull_bar) + kPairBarrierBytes;
+  unsigned char *epi_stage = smem + kPairStages * kPairStageBytes + kPairBarrierBytes;
   unsigned char *raw_ring = epi_stage + PairStage<EPI>::kTotalBytes;  // (MX)
   // (MX) byte of two e2m1 codes -> the two values as bf16 (normal numbers; the
   // subnormal detour of the bit trick is paid 256 times here, not per element)
@@ -132,24 +126,20 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_cta_rank();
-  // (MX) weight slot s is always filled by the same kWarpsPerBlock dequantising warps,
+  // (MX) operand stage s is always filled by the same kWarpsPerBlock dequantising warps,
   // and a raw stage always drained by the same ones: every warp then meets the phases of
   // its barriers one by one, in order, and a parity wait can never be a whole turn of
   // the ring ahead of the barrier it polls
-  constexpr int kWarpsPerBlock = MX ? (kDequantWarps / kW > 0 ? kDequantWarps / kW : 1) : 1;
-  static_assert(!MX || (kRawStages % kW == 0 && kWarpsPerBlock * kW <= kDequantWarps &&
+  constexpr int kWarpsPerBlock = MX ? (kDequantWarps / kPairStages > 0 ? kDequantWarps / kPairStages : 1) : 1;
+  static_assert(!MX || (kRawStages % kPairStages == 0 && kWarpsPerBlock * kPairStages <= kDequantWarps &&
                         8 % kWarpsPerBlock == 0),
-                "dequantising warps must map to fixed ring slots");
+                "dequantising warps must map to fixed ring stages");
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kW; s++) {
-      // MX: the dequantising warps of the block in each CTA arrive; else the TMA bytes
-      mbar_init(&wfull_bar[s], MX ? 2 * kWarpsPerBlock : 1);
-      mbar_init(&wempty_bar[s], 1);
-    }
-    for (int s = 0; s < kX; s++) {
-      mbar_init(&xfull_bar[s], 1);
-      mbar_init(&xempty_bar[s], 1);
+    for (int s = 0; s < kPairStages; s++) {
+      // MX: the leader's producer plus the dequantising warps of the block in each CTA
+      mbar_init(&full_bar[s], MX ? 1 + 2 * kWarpsPerBlock : 1);
+      mbar_init(&empty_bar[s], 1);
     }
     for (int s = 0; s < kRawStages; s++) {
       mbar_init(&raw_full[s], 1);
@@ -184,61 +174,41 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
   int tt_lo = 0, tt_hi = *g.num_mtiles;
   if (g.tile_part == 1) tt_hi = *g.tile_split;
   if (g.tile_part == 2) tt_lo = *g.tile_split;
-  const int first_tile = tt_lo * w_pairs + (blockIdx.x >> 1);
-  const int total_tiles = tt_hi * w_pairs;
+  const int n_tt = tt_hi - tt_lo;
+  const int first_tile = blockIdx.x >> 1;
+  const int total_tiles = n_tt * w_pairs;
   const int kb_count = (g.k_dim + kTileK - 1) / kTileK;
   const int ncl = gridDim.x >> 1;  // clusters of the launch; a cluster strides over the tiles
 
   if (warp == 0) {
-    // weight ring: this CTA's 128 weight rows of the tile, one box per K block
-    if (!MX && lane == 0) {
-      int ws = 0;
-      uint32_t wphase = 0;
-      bool ok = true;
-      int e_next = 0;
-      if (first_tile < total_tiles) e_next = g.mtile_expert[first_tile / w_pairs];
-      for (int tile = first_tile; ok && tile < total_tiles; tile += ncl) {
-        const int tt = tile / w_pairs, wp = tile - tt * w_pairs;
-        const int e = e_next;
-        if (tile + ncl < total_tiles) e_next = g.mtile_expert[(tile + ncl) / w_pairs];
-        const int wrow = e * g.n_cols + wp * 256 + static_cast<int>(rank) * 128;
-        for (int kb = 0; kb < kb_count; kb++) {
-          if (!mbar_wait(&wempty_bar[ws], wphase ^ 1u, abort_flag)) {
-            set_status(g.status, kStatusWaitTimeoutProducer);
-            *abort_flag = 1;
-            ok = false;
-            break;
-          }
-          if (rank == 0) mbar_arrive_expect_tx(&wfull_bar[ws], 2 * kPairOperandBytes);
-          tma_load_2d_pair(w_ring + ws * kPairOperandBytes, &tmap_w, &wfull_bar[ws], kb * kTileK,
-                           wrow);
-          if (++ws == kW) {
-            ws = 0;
-            wphase ^= 1u;
-          }
-        }
-      }
-    }
-  } else if (warp == 2) {
-    // token ring: this CTA's half of the token tile
     if (lane == 0) {
-      int xs = 0;
-      uint32_t xphase = 0;
+      int stage = 0;
+      uint32_t phase = 0;
       bool ok = true;
-      int tok0_next = 0, ntok_next = 0;
+      int e_next = 0, tok0_next = 0, ntok_next = 0;
+      int tt, wp, tt2, wp2;
+      // weights pass through L2 once: first out; token tiles are re-read by every weight-row
+      // pair of the expert: last out
+      const uint64_t pol_w = g.l2_hints ? l2_policy_evict_first() : l2_policy_normal();
+      const uint64_t pol_x = g.l2_hints ? l2_policy_evict_last() : l2_policy_normal();
       if (first_tile < total_tiles) {
-        const int tt = first_tile / w_pairs;
+        decode_tile(first_tile, w_pairs, tt_lo, &tt, &wp);
+        e_next = g.mtile_expert[tt];
         tok0_next = g.mtile_row0[tt];
         ntok_next = g.mtile_rows[tt];
       }
       for (int tile = first_tile; ok && tile < total_tiles; tile += ncl) {
-        const int tok0 = tok0_next, ntok = ntok_next;
-        if (tile + ncl < total_tiles) {
-          const int tt2 = (tile + ncl) / w_pairs;
+        decode_tile(tile, w_pairs, tt_lo, &tt, &wp);
+        const int e = e_next, tok0 = tok0_next, ntok = ntok_next;
+        const int tile2 = tile + ncl;
+        if (tile2 < total_tiles) {
+          decode_tile(tile2, w_pairs, tt_lo, &tt2, &wp2);
+          e_next = g.mtile_expert[tt2];
           tok0_next = g.mtile_row0[tt2];
           ntok_next = g.mtile_rows[tt2];
         }
         const int half_n = ((ntok + 15) & ~15) >> 1;  // token rows each CTA contributes
+        const int wrow = e * g.n_cols + wp * 256 + static_cast<int>(rank) * 128;
         const int trow = tok0 + static_cast<int>(rank) * half_n;
         // narrow token tiles are loaded with a narrower box: 8, 32 or 128 rows per CTA
         const CUtensorMap *tx =
@@ -246,17 +216,26 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
         const uint32_t tok_bytes =
             (half_n <= 8 ? 8 : ((half_n <= 32 || TOKB == 32) ? 32 : 128)) * kTileK * 2;
         for (int kb = 0; kb < kb_count; kb++) {
-          if (!mbar_wait(&xempty_bar[xs], xphase ^ 1u, abort_flag)) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
             set_status(g.status, kStatusWaitTimeoutProducer);
             *abort_flag = 1;
             ok = false;
             break;
           }
-          if (rank == 0) mbar_arrive_expect_tx(&xfull_bar[xs], 2 * tok_bytes);
-          tma_load_2d_pair(x_ring + xs * kXBytes, tx, &xfull_bar[xs], kb * kTileK, trow);
-          if (++xs == kX) {
-            xs = 0;
-            xphase ^= 1u;
+          unsigned char *sa = smem + stage * kPairStageBytes;
+          if (!MX) {
+            if (rank == 0)
+              mbar_arrive_expect_tx(&full_bar[stage], 2 * (kPairOperandBytes + tok_bytes));
+            tma_load_2d_pair_hint(sa, &tmap_w, &full_bar[stage], kb * kTileK, wrow, pol_w);
+          } else if (rank == 0) {
+            // the weights arrive through the raw ring and the dequantising warps
+            mbar_arrive_expect_tx(&full_bar[stage], 2 * tok_bytes);
+          }
+          tma_load_2d_pair_hint(sa + kPairOperandBytes, tx, &full_bar[stage], kb * kTileK, trow,
+                                pol_x);
+          if (++stage == kPairStages) {
+            stage = 0;
+            phase ^= 1u;
           }
         }
       }
@@ -269,7 +248,8 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
       uint32_t rphase = 0;
       bool ok = true;
       for (int tile = first_tile; ok && tile < total_tiles; tile += ncl) {
-        const int tt = tile / w_pairs, wp = tile - tt * w_pairs;
+        int tt, wp;
+        decode_tile(tile, w_pairs, tt_lo, &tt, &wp);
         const int e = g.mtile_expert[tt];
         const size_t blk0 =
             (static_cast<size_t>(e) * (2 * w_pairs) + 2 * wp + rank) * kb_count;
@@ -292,13 +272,15 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
     }
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {
-      int ws = 0, xs = 0;
-      uint32_t wphase = 0, xphase = 0;
+      int stage = 0;
+      uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int tile = first_tile; ok && tile < total_tiles; tile += ncl) {
-        const int ntok = g.mtile_rows[tile / w_pairs];
+        int tt, wp;
+        decode_tile(tile, w_pairs, tt_lo, &tt, &wp);
+        const int ntok = g.mtile_rows[tt];
         const uint32_t idesc = umma_idesc_bf16(256, (ntok + 15) & ~15);
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_flag)) {
           set_status(g.status, kStatusWaitTimeoutMma);
@@ -308,29 +290,23 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kAccColsPair;
         for (int kb = 0; kb < kb_count; kb++) {
-          if (!mbar_wait(&xfull_bar[xs], xphase, abort_flag) ||
-              !mbar_wait(&wfull_bar[ws], wphase, abort_flag)) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
             set_status(g.status, kStatusWaitTimeoutMma);
             *abort_flag = 1;
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint64_t da = umma_smem_desc_sw128(smem_u32(w_ring + ws * kPairOperandBytes));
-          const uint64_t db = umma_smem_desc_sw128(smem_u32(x_ring + xs * kXBytes));
+          const uint32_t sa = smem_u32(smem + stage * kPairStageBytes);
+          const uint64_t da = umma_smem_desc_sw128(sa);
+          const uint64_t db = umma_smem_desc_sw128(sa + kPairOperandBytes);
 #pragma unroll
           for (int k = 0; k < kTileK / 16; k++)
             umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
-          // both slots are free, in both CTAs, once these MMAs have read them
-          umma_commit_pair(&wempty_bar[ws], 3);
-          umma_commit_pair(&xempty_bar[xs], 3);
-          if (++ws == kW) {
-            ws = 0;
-            wphase ^= 1u;
-          }
-          if (++xs == kX) {
-            xs = 0;
-            xphase ^= 1u;
+          umma_commit_pair(&empty_bar[stage], 3);  // frees the stage in both CTAs
+          if (++stage == kPairStages) {
+            stage = 0;
+            phase ^= 1u;
           }
         }
         if (!ok) break;
@@ -341,7 +317,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
     }
   } else if (MX && warp >= kPairThreads / 32) {
     // dequantising warps: group j = dw / kWarpsPerBlock expands the K blocks n = j, j + S,
-    // j + 2S, ... of the CTA's sequence (S = weight slots) into weight slot j, each
+    // j + 2S, ... of the CTA's sequence (S = operand stages) into operand stage j, each
     // warp of the group a share of the block's 16-byte chunks, so that the waits, the
     // fence and the arrivals of one block overlap the table lookups of the others.  Chunk
     // c = half (c & 1) of weight row c >> 1: 32 codes under one scale byte.
@@ -351,43 +327,45 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
     const int total_kb = my_tiles * kb_count;
     const uint32_t *lutl = lut + (lane & (LUTREP - 1));
     constexpr int kChunkIters = 8 / kWarpsPerBlock;
-    if (grp < kW) {
+    if (grp < kPairStages) {
       const int stage = grp;
       uint32_t phase = 0;
-      for (int n = grp; n < total_kb; n += kW, phase ^= 1u) {
+      for (int n = grp; n < total_kb; n += kPairStages, phase ^= 1u) {
         constexpr int kRawDiv = kRawStages > 0 ? kRawStages : 1;  // (no raw ring without MX)
         const int rs = n % kRawDiv;
         const uint32_t rphase = (n / kRawDiv) & 1;
         if (!mbar_wait(&raw_full[rs], rphase, abort_flag) ||
-            !mbar_wait(&wempty_bar[stage], phase ^ 1u, abort_flag)) {
+            !mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
           set_status(g.status, kStatusWaitTimeoutProducer);
           *abort_flag = 1;
           break;
         }
         tc_fence_after();  // the MMAs that read this operand slot are done
         const unsigned char *rq = raw_ring + rs * kRawStageBytes;
-        unsigned char *slot = w_ring + stage * kPairOperandBytes;
+        unsigned char *slot = smem + stage * kPairStageBytes;
+        {
 #pragma unroll 2
-        for (int i = 0; i < kChunkIters; i++) {
-          const int c = (sub * kChunkIters + i) * 32 + lane;
-          const int wr = c >> 1, hf = c & 1;
-          const uint4 q0 = *reinterpret_cast<const uint4 *>(rq + c * 16);
-          uint32_t sc = rq[kRawCodeBytes + c];
-          // codes come out of the table as bf16 values; times 2^(s-127), exact
-          sc = sc ? (sc << 7) : 0x0040u;  // e8m0 0 = 2^-127, a bf16 subnormal
-          const uint32_t mul = sc | (sc << 16);
-          unsigned char *row = slot + wr * 128;
-          const uint32_t words[4] = {q0.x, q0.y, q0.z, q0.w};
+          for (int i = 0; i < kChunkIters; i++) {
+            const int c = (sub * kChunkIters + i) * 32 + lane;
+            const int wr = c >> 1, hf = c & 1;
+            const uint4 q0 = *reinterpret_cast<const uint4 *>(rq + c * 16);
+            uint32_t sc = rq[kRawCodeBytes + c];
+            // codes come out of the table as bf16 values; times 2^(s-127), exact
+            sc = sc ? (sc << 7) : 0x0040u;  // e8m0 0 = 2^-127, a bf16 subnormal
+            const uint32_t mul = sc | (sc << 16);
+            unsigned char *row = slot + wr * 128;
+            const uint32_t words[4] = {q0.x, q0.y, q0.z, q0.w};
 #pragma unroll
-          for (int j = 0; j < 4; j++) {  // 8 elements (one packed word) -> one 16-byte chunk
-            const uint32_t w = words[j];
-            uint4 o;
-            o.x = bf16x2_mul(lutl[(w & 0xffu) * LUTREP], mul);
-            o.y = bf16x2_mul(lutl[((w >> 8) & 0xffu) * LUTREP], mul);
-            o.z = bf16x2_mul(lutl[((w >> 16) & 0xffu) * LUTREP], mul);
-            o.w = bf16x2_mul(lutl[(w >> 24) * LUTREP], mul);
-            // 128-byte swizzle: 16-byte chunk j of row r sits at chunk j ^ (r & 7)
-            *reinterpret_cast<uint4 *>(row + (((hf * 4 + j) ^ (wr & 7)) << 4)) = o;
+            for (int j = 0; j < 4; j++) {  // 8 elements (one packed word) -> one 16-byte chunk
+              const uint32_t w = words[j];
+              uint4 o;
+              o.x = bf16x2_mul(lutl[(w & 0xffu) * LUTREP], mul);
+              o.y = bf16x2_mul(lutl[((w >> 8) & 0xffu) * LUTREP], mul);
+              o.z = bf16x2_mul(lutl[((w >> 16) & 0xffu) * LUTREP], mul);
+              o.w = bf16x2_mul(lutl[(w >> 24) * LUTREP], mul);
+              // 128-byte swizzle: 16-byte chunk j of row r sits at chunk j ^ (r & 7)
+              *reinterpret_cast<uint4 *>(row + (((hf * 4 + j) ^ (wr & 7)) << 4)) = o;
+            }
           }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -395,22 +373,23 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
         if (lane == 0) {
           mbar_arrive(&raw_empty[rs]);
           if (rank == 0)
-            mbar_arrive(&wfull_bar[stage]);
+            mbar_arrive(&full_bar[stage]);
           else
-            mbar_arrive_cluster(&wfull_bar[stage], 0);
+            mbar_arrive_cluster(&full_bar[stage], 0);
         }
       }
     }
-  } else if (warp >= 3 && warp < kPairThreads / 32) {
+  } else {
     using ST = PairStage<EPI>;
     const int q = warp & 3;            // TMEM lanes [32q, 32q+32)
-    const int half = (warp - 3) >> 2;  // token chunks c with (c & 1) == half
-    const int tg = ((warp - 3) & 3) * 32 + lane;  // thread index among the half's 4 warps
+    const int half = (warp - 2) >> 2;  // token chunks c with (c & 1) == half
+    const int tg = ((warp - 2) & 3) * 32 + lane;  // thread index among the half's 4 warps
     const bool odd = (lane & 1) != 0;
     int acc = 0, buf = 0;
     uint32_t acc_phase = 0;
     for (int tile = first_tile; tile < total_tiles; tile += ncl) {
-      const int tt = tile / w_pairs, wp = tile - tt * w_pairs;
+      int tt, wp;
+      decode_tile(tile, w_pairs, tt_lo, &tt, &wp);
       const int e = g.mtile_expert[tt];
       const int tok0 = g.mtile_row0[tt];
       const int ntok = g.mtile_rows[tt];
@@ -428,75 +407,77 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
       const uint32_t taddr =
           tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kAccColsPair;
       const int n_chunks = (ntok + 31) >> 5;
-      for (int c = half; c < n_chunks; c += 2) {
-        uint32_t r[32];
-        tmem_ld32(taddr + c * 32, r);
-        tmem_ld_wait32(r);
-        unsigned char *tile_s = epi_stage + (half * 2 + buf) * ST::kTileBytes;
-        if (EPI == kEpiSwiglu) {
-          // lanes (2i, 2i+1) hold gate and up of feature i; each of the two takes
-          // every other token
+      {
+        for (int c = half; c < n_chunks; c += 2) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c * 32, r);
+          tmem_ld_wait32(r);
+          unsigned char *tile_s = epi_stage + (half * 2 + buf) * ST::kTileBytes;
+          if (EPI == kEpiSwiglu) {
+            // lanes (2i, 2i+1) hold gate and up of feature i; each of the two takes
+            // every other token
 #pragma unroll
-          for (int m = 0; m < 16; m++) {
-            const float lo = __uint_as_float(r[2 * m]) + bias_v;
-            const float hi = __uint_as_float(r[2 * m + 1]) + bias_v;
-            const float own = odd ? hi : lo;
-            const float send = odd ? lo : hi;
-            const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
-            const float a = swiglu_act(odd ? recv : own, odd ? own : recv, g.limit);
-            const int j = 2 * m + (odd ? 1 : 0);
-            *reinterpret_cast<bf16 *>(tile_s + j * ST::kPitch + q * 32 + (lane >> 1) * 2) =
-                __float2bfloat16_rn(a);
+            for (int m = 0; m < 16; m++) {
+              const float lo = __uint_as_float(r[2 * m]) + bias_v;
+              const float hi = __uint_as_float(r[2 * m + 1]) + bias_v;
+              const float own = odd ? hi : lo;
+              const float send = odd ? lo : hi;
+              const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+              const float a = swiglu_act(odd ? recv : own, odd ? own : recv, g.limit);
+              const int j = 2 * m + (odd ? 1 : 0);
+              *reinterpret_cast<bf16 *>(tile_s + j * ST::kPitch + q * 32 + (lane >> 1) * 2) =
+                  __float2bfloat16_rn(a);
+            }
+          } else if (EPI == kEpiF32) {
+            // lane = output column, register j = token: rows of 128 fp32 per CTA
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+              *reinterpret_cast<float *>(tile_s + j * ST::kPitch + q * 128 + lane * 4) =
+                  __uint_as_float(r[j]) + bias_v;
+          } else {
+            const int jt = c * 32 + lane;
+            const float w_lane = jt < ntok ? g.row_weight[tok0 + jt] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+              r[j] = __float_as_uint((__uint_as_float(r[j]) + bias_v) *
+                                     __shfl_sync(0xffffffffu, w_lane, j));
+            // lanes (2i, 2i+1) hold columns (2i, 2i+1); each takes every other token
+            // and stores both columns as one 32-bit word
+#pragma unroll
+            for (int m = 0; m < 16; m++) {
+              const float own = __uint_as_float(odd ? r[2 * m + 1] : r[2 * m]);
+              const float send = __uint_as_float(odd ? r[2 * m] : r[2 * m + 1]);
+              const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+              const int j = 2 * m + (odd ? 1 : 0);
+              *reinterpret_cast<uint32_t *>(tile_s + j * ST::kPitch + q * 64 + (lane >> 1) * 4) =
+                  pack_bf16(odd ? recv : own, odd ? own : recv);
+            }
           }
-        } else if (EPI == kEpiF32) {
-          // lane = output column, register j = token: rows of 128 fp32 per CTA
-#pragma unroll
-          for (int j = 0; j < 32; j++)
-            *reinterpret_cast<float *>(tile_s + j * ST::kPitch + q * 128 + lane * 4) =
-                __uint_as_float(r[j]) + bias_v;
-        } else {
-          const int jt = c * 32 + lane;
-          const float w_lane = jt < ntok ? g.row_weight[tok0 + jt] : 0.f;
-#pragma unroll
-          for (int j = 0; j < 32; j++)
-            r[j] = __float_as_uint((__uint_as_float(r[j]) + bias_v) *
-                                   __shfl_sync(0xffffffffu, w_lane, j));
-          // lanes (2i, 2i+1) hold columns (2i, 2i+1); each takes every other token
-          // and stores both columns as one 32-bit word
-#pragma unroll
-          for (int m = 0; m < 16; m++) {
-            const float own = __uint_as_float(odd ? r[2 * m + 1] : r[2 * m]);
-            const float send = __uint_as_float(odd ? r[2 * m] : r[2 * m + 1]);
-            const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
-            const int j = 2 * m + (odd ? 1 : 0);
-            *reinterpret_cast<uint32_t *>(tile_s + j * ST::kPitch + q * 64 + (lane >> 1) * 4) =
-                pack_bf16(odd ? recv : own, odd ? own : recv);
+          // make the tile visible to the bulk-copy engine; the first warp of the half
+          // also makes sure the copy that last read the other buffer is done before
+          // anyone passes the barrier and starts to refill it
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          if (tg < 32) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          named_barrier_sync(1 + half, 128);
+          // write out: one bulk copy per token row (a whole 128- / 256-byte segment)
+          const int col0 = (EPI == kEpiSwiglu) ? (n_cta >> 1) : n_cta;
+          if (tg < 32) {
+            const int jt = c * 32 + tg;
+            constexpr int kOutElem = (EPI == kEpiF32) ? 4 : 2;  // bytes per output element
+            int bytes = (g.out_ld - col0) * kOutElem;
+            bytes = bytes < ST::kRowBytes ? bytes : ST::kRowBytes;
+            if (jt < ntok && bytes > 0) {
+              unsigned char *dst =
+                  reinterpret_cast<unsigned char *>(g.out) +
+                  (static_cast<size_t>(tok0 + jt) * g.out_ld + col0) * kOutElem;
+              asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
+                           "r"(smem_u32(tile_s + tg * ST::kPitch)), "r"(bytes)
+                           : "memory");
+            }
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
+          buf ^= 1;
         }
-        // make the tile visible to the bulk-copy engine; the first warp of the half
-        // also makes sure the copy that last read the other buffer is done before
-        // anyone passes the barrier and starts to refill it
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        if (tg < 32) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-        named_barrier_sync(1 + half, 128);
-        // write out: one bulk copy per token row (a whole 128- / 256-byte segment)
-        const int col0 = (EPI == kEpiSwiglu) ? (n_cta >> 1) : n_cta;
-        if (tg < 32) {
-          const int jt = c * 32 + tg;
-          constexpr int kOutElem = (EPI == kEpiF32) ? 4 : 2;  // bytes per output element
-          int bytes = (g.out_ld - col0) * kOutElem;
-          bytes = bytes < ST::kRowBytes ? bytes : ST::kRowBytes;
-          if (jt < ntok && bytes > 0) {
-            unsigned char *dst =
-                reinterpret_cast<unsigned char *>(g.out) +
-                (static_cast<size_t>(tok0 + jt) * g.out_ld + col0) * kOutElem;
-            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
-                         "r"(smem_u32(tile_s + tg * ST::kPitch)), "r"(bytes)
-                         : "memory");
-          }
-          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        }
-        buf ^= 1;
       }
       tc_fence_before();
       __syncwarp();
@@ -526,21 +507,15 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
   }
 }
 
-template <int EPI, int KW, int KX, bool MX, int TOKB, int RAWS, int LUTREP>
-static cudaError_t launch_pair_rings(int num_sms, long long *launches, const CUtensorMap &tw,
-                                     const CUtensorMap *tx, const GemmArgs &g,
-                                     cudaStream_t stream, bool dependent) {
-  const size_t smem = 1024 + KW * kPairOperandBytes + KX * (TOKB * kTileK * 2) +
-                      kPairBarrierBytes + PairStage<EPI>::kTotalBytes +
+template <int EPI, int STAGES, bool MX, int TOKB, int RAWS, int LUTREP>
+static cudaError_t launch_pair_stages(int num_sms, long long *launches, const CUtensorMap &tw,
+                                      const CUtensorMap *tx, const GemmArgs &g,
+                                      cudaStream_t stream, bool dependent = false) {
+  const size_t smem = 1024 + STAGES * (kPairOperandBytes + TOKB * kTileK * 2) + kPairBarrierBytes +
+                      PairStage<EPI>::kTotalBytes +
                       (MX ? RAWS * kRawStageBytes + 1024 * LUTREP : 0);
-  static_assert(1024 + KW * kPairOperandBytes + KX * (TOKB * kTileK * 2) + kPairBarrierBytes +
-                        PairStage<EPI>::kTotalBytes +
-                        (MX ? RAWS * kRawStageBytes + 1024 * LUTREP : 0) <=
-                    232448,
-                "more shared memory than one CTA can have");
-  auto kernel = grouped_gemm_pair_kernel<EPI, KW, KX, MX, TOKB, RAWS, LUTREP>;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)smem);
+  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_pair_kernel<EPI, STAGES, MX, TOKB, RAWS, LUTREP>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(num_sms & ~1));
@@ -557,7 +532,8 @@ static cudaError_t launch_pair_rings(int num_sms, long long *launches, const CUt
   cfg.attrs = attr;
   cfg.numAttrs = dependent ? 2 : 1;
   if (launches) ++*launches;
-  return cudaLaunchKernelEx(&cfg, kernel, tw, tx[0], tx[1], tx[2], g);
+  return cudaLaunchKernelEx(&cfg, grouped_gemm_pair_kernel<EPI, STAGES, MX, TOKB, RAWS, LUTREP>, tw, tx[0], tx[1], tx[2],
+                            g);
 }
 
 template <int EPI>
@@ -569,18 +545,13 @@ static cudaError_t launch_pair(gptoss_moe *h, const CUtensorMap &tw, const CUten
   // with 64-token tiles, whose small token slots leave room for one code table per bank
   if (h->cfg.weight_format == GPTOSS_WEIGHTS_MXFP4) {
     if (h->cur_tile_rows == 64)
-      return launch_pair_rings<EPI, 6, 6, true, 32, 12, 16>(h->num_sms, &h->launches, tx[0], tx, g,
-                                                            stream, dep);
-    return launch_pair_rings<EPI, 4, 4, true, 128, 12, 1>(h->num_sms, &h->launches, tx[0], tx, g,
+      return launch_pair_stages<EPI, 6, true, 32, 12, 16>(h->num_sms, &h->launches, tx[0], tx, g,
                                                           stream, dep);
+    return launch_pair_stages<EPI, 4, true, 128, 12, 1>(h->num_sms, &h->launches, tx[0], tx, g,
+                                                        stream, dep);
   }
-  // twelve 16 KB slots in all; how many of them hold weights
-  switch (h->opt_pair_rings) {
-    case 6: return launch_pair_rings<EPI, 6, 6, false, 128, 0, 1>(h->num_sms, &h->launches, tw, tx, g, stream, dep);
-    case 7: return launch_pair_rings<EPI, 7, 5, false, 128, 0, 1>(h->num_sms, &h->launches, tw, tx, g, stream, dep);
-    case 9: return launch_pair_rings<EPI, 9, 3, false, 128, 0, 1>(h->num_sms, &h->launches, tw, tx, g, stream, dep);
-    default: return launch_pair_rings<EPI, 8, 4, false, 128, 0, 1>(h->num_sms, &h->launches, tw, tx, g, stream, dep);
-  }
+  return launch_pair_stages<EPI, 6, false, 128, 0, 1>(h->num_sms, &h->launches, tw, tx, g, stream,
+                                                      dep);
 }
 
 static GemmArgs pair_args(gptoss_moe *h, bool down, const LayerWeights &lw) {
@@ -598,6 +569,7 @@ static GemmArgs pair_args(gptoss_moe *h, bool down, const LayerWeights &lw) {
   g.limit = h->cfg.swiglu_limit;
   g.status = h->status;
   g.wq = down ? lw.w2_blocks : lw.w1_blocks;
+  g.l2_hints = h->opt_l2_hints;
   return g;
 }
 
@@ -615,15 +587,13 @@ cudaError_t launch_gate_up_pair(gptoss_moe *h, int layer, cudaStream_t stream, i
 // caller (tw: W [n_cols, k] in boxes of 128 rows; tx: x [rows, k] in boxes of 128, 32 and 8
 // rows).
 // f32_out: g.out addresses fp32 [rows, out_ld] (out_ld a multiple of 4), no row weight, bias
-// optional; fewer operand slots make room for the wider output staging.
+// optional; four operand stages make room for the wider output staging.
 cudaError_t launch_linear_pair(int num_sms, const CUtensorMap &tw, const CUtensorMap *tx,
                                const GemmArgs &g, cudaStream_t stream, long long *launches,
                                bool f32_out) {
   if (f32_out)
-    return launch_pair_rings<kEpiF32, 5, 5, false, 128, 0, 1>(num_sms, launches, tw, tx, g, stream,
-                                                              false);
-  return launch_pair_rings<kEpiDown, 6, 6, false, 128, 0, 1>(num_sms, launches, tw, tx, g, stream,
-                                                             false);
+    return launch_pair_stages<kEpiF32, 4, false, 128, 0, 1>(num_sms, launches, tw, tx, g, stream);
+  return launch_pair_stages<kEpiDown, 6, false, 128, 0, 1>(num_sms, launches, tw, tx, g, stream);
 }
 
 cudaError_t launch_down_pair(gptoss_moe *h, int layer, cudaStream_t stream) {

@@ -164,6 +164,7 @@ int gptoss_moe_destroy(gptoss_moe_t *h) {
   for (auto &lw : h->layers) {
     cudaFree(lw.w_router); cudaFree(lw.b_router); cudaFree(lw.w1); cudaFree(lw.b1);
     cudaFree(lw.w2); cudaFree(lw.b2); cudaFree(lw.w1_blocks); cudaFree(lw.w2_blocks);
+    cudaFree(lw.router_tiled);
     cudaFree(lw.rms_ffn);
   }
   cudaFree(h->topk_i); cudaFree(h->topk_v); cudaFree(h->logits); cudaFree(h->block_counts);
@@ -226,6 +227,7 @@ static int finish_layer(gptoss_moe *h, LayerWeights &lw) {
       make_tmap_2d_bf16(&lw.tmap_w2_rows, lw.w2, h->IM, (uint64_t)h->El * h->H, kTileK, 128,
                         &terr))
     return fail(h, GPTOSS_E_CUDA, "%s", terr.c_str());
+  if (int rc = build_router_tiles(h, lw)) return rc;
   lw.loaded = true;
   return GPTOSS_OK;
 }
@@ -650,12 +652,8 @@ int gptoss_moe_set_option(gptoss_moe_t *h, const char *name, int value) {
   } else if (!strcmp(name, "router_impl")) {
     if (value != 0 && value != 1) return fail(h, GPTOSS_E_INVALID, "router_impl must be 0 or 1");
     h->opt_router_impl = value;
-  } else if (!strcmp(name, "router_split")) {
-    if (value < 0 || value > 8) return fail(h, GPTOSS_E_INVALID, "router_split must be 0..8");
-    h->opt_router_split = value;
-  } else if (!strcmp(name, "pair_rings")) {
-    if (value < 6 || value > 9) return fail(h, GPTOSS_E_INVALID, "pair_rings must be 6..9");
-    h->opt_pair_rings = value;
+  } else if (!strcmp(name, "l2_hints")) {
+    h->opt_l2_hints = value != 0;
   } else if (!strcmp(name, "dependent_launch")) {
     h->opt_dependent_launch = value != 0;
   } else if (!strcmp(name, "wait_limit_ms")) {
@@ -664,6 +662,9 @@ int gptoss_moe_set_option(gptoss_moe_t *h, const char *name, int value) {
     h->opt_wait_limit_ms = value;
   } else if (!strcmp(name, "ep_overlap")) {
     h->opt_ep_overlap = value != 0;
+  } else if (!strcmp(name, "ep_gather_ctas")) {
+    if (value < 1 || value > 4096) return fail(h, GPTOSS_E_INVALID, "ep_gather_ctas must be 1..4096");
+    h->opt_ep_gather_ctas = value;
   } else if (!strcmp(name, "ep_transport")) {
     return ep_set_transport(h, value);
   } else if (!strcmp(name, "time_stages")) {

@@ -172,6 +172,7 @@ extern "C" int gptoss_moe_load_layer_mxfp4(gptoss_moe_t *h, int layer, const voi
   if (rc) return rc;
   rc = tile_tensor(h, w_mlp2_blocks, w_mlp2_scales, h->H, h->IM, on_device, &lw.w2_blocks);
   if (rc) return rc;
+  if ((rc = build_router_tiles(h, lw))) return rc;
   lw.loaded = true;
   return GPTOSS_OK;
 }

@@ -361,64 +361,53 @@ router_topk_kernel(const __grid_constant__ CUtensorMap tmap_t,
 }
 
 // ---------------------------------------------------------------------------
-// The router on the 5th-generation tensor cores.
+// The router on the 5th-generation tensor cores, computed transposed.
 //
-// A CTA owns 128 consecutive tokens (the MMA's M) and all experts (the MMA's N, padded
-// to EPAD = 32 / 64 / 128 / 256); tcgen05.mma (M=128, N=EPAD, K=16, bf16 -> fp32)
-// accumulates the logits in EPAD columns of TMEM.  Both operands arrive through one
-// TMA ring: per 64-deep K chunk a box of 128 token rows (the only stream that comes
-// from HBM) and a box of EPAD router rows (L2).  Warp 0 = producer, warp 1 = TMEM
-// allocation and MMA issue, warps 2-5 = selection: a TMEM lane is a token, so every
-// thread reads the logits of its own token with tcgen05.ld and keeps a sorted list of
-// the best K+1 in registers - no shuffles, no shared-memory round trip.
+//   logits^T[e, j] = sum_k Wr[e, k] * t[tok0 + j, k]
+// The router rows are the MMA's M (128 per instruction, padded with zero rows; two
+// instructions for more than 128 experts) and a CTA's tokens its N: any multiple of 16 up
+// to 64, chosen by the launcher so that the token tiles fill the GPU in one wave - no
+// split of the hidden dimension, no cluster, no reduction between CTAs.  The router rows
+// come as one pre-tiled 16 KB piece per K chunk (weights.cu's layout, made once at load
+// time) and stay in L2; the CTA's token rows are the only stream from HBM.
 //
-// With fewer than one 128-token tile per SM (always: T <= 148 * 128 would need 18944
-// tokens) a cluster of `split` CTAs shares a tile, each taking 1/split of the K chunks;
-// when all of them are done each pushes its partial logits (remote shared-memory stores)
-// to the CTA that selects for that token - the tile's tokens are dealt out evenly over
-// the cluster - where the partials are added in rank order.
+// Warp 0 = TMA producer, warp 1 = TMEM allocation + MMA issue (tcgen05.mma M=128, N=tokens,
+// K=16, bf16 -> fp32 in TMEM).  Then warps 2-5 read the accumulator (a TMEM lane is an
+// expert, a column a token), add the bias and transpose it into shared memory, and ONE
+// THREAD PER TOKEN selects: it walks its token's row keeping the best K+1 logits sorted in
+// registers (a warp per token with shuffles, as the mma.sync kernel does it, costs about a
+// thousand dependent instructions per token and was 30 of that kernel's 45 microseconds).
 //
-// Exact selection as before: a token whose best K+1 logits contain two neighbours closer
-// than kTieGuard lists every expert within 2 * kTieGuard of its K-th value; after the
-// CTA's threads are through, its warps take those tokens one by one, recompute the
-// listed logits the way the reference's CPU matmul does (float products summed in
-// double) and select again.
-constexpr int kRcTokens = 128;
-constexpr int kRcThreads = 192;
-constexpr int kRcSelWarps = 4;
-constexpr int kRcCand = 16;  // listed contenders per token; more than that: all experts
-template <int EPAD> struct RcStages {
-  static constexpr int value = EPAD <= 32 ? 9 : (EPAD <= 64 ? 8 : (EPAD <= 128 ? 6 : 4));
-};
+// Exact selection: a token whose best K+1 logits contain two neighbours closer than the
+// guard lists every expert within twice the guard of its K-th value; the CTA's warps then
+// recompute the listed logits the way the reference's CPU matmul does (float products
+// summed in double), one (token, expert) pair per warp at a time, and the token's thread
+// selects again from the corrected row.  The guard is tighter than the mma.sync kernel's:
+// the tensor core's fp32 accumulation was measured within 3e-6 of the reference's double
+// sums at H = 2880.
+constexpr int kRxThreads = 192;
+constexpr int kRxMaxTok = 64;
+constexpr int kRxTileBytes = 128 * kRtRowBytes;  // one 128-row x 64-k router tile: 16 KB
+constexpr int kRxPairs = 1024;                   // (token, expert) pairs a CTA recomputes
+constexpr float kTieGuardTc = 3e-5f;
+constexpr int kRxAccs = 2;  // accumulators the K chunks alternate between
 
-__device__ __forceinline__ uint32_t cluster_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ uint32_t cluster_size() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-
-// NS = length of the sorted list every thread keeps (K + 1 <= NS)
-template <int EPAD, int NS>
-__global__ void __launch_bounds__(kRcThreads, 1)
-router_tc_kernel(const __grid_constant__ CUtensorMap tmap_t,
-                 const __grid_constant__ CUtensorMap tmap_w, const bf16 *__restrict__ t,
+// NT = 32-expert groups (EPAD = 32 * NT); NS = length of the sorted list a thread keeps
+template <int NT, int NS>
+__global__ void __launch_bounds__(kRxThreads, 1)
+router_tx_kernel(const __grid_constant__ CUtensorMap tmap_t,
+                 const __grid_constant__ CUtensorMap tmap_wr, const bf16 *__restrict__ t,
                  const bf16 *__restrict__ w_router, const float *__restrict__ b_router,
-                 const int *__restrict__ pos, int T, int H, int E, int K,
+                 const int *__restrict__ pos, int T, int H, int E, int K, int ntok,
                  int *__restrict__ topk_i, float *__restrict__ topk_v,
                  float *__restrict__ logits_out, int exact_ties, int *status) {
-  constexpr int kStages = RcStages<EPAD>::value;
-  constexpr int kTokBytes = kRcTokens * kRtRowBytes;          // 16 KB
-  constexpr int kStageBytes = kTokBytes + EPAD * kRtRowBytes;
-  constexpr int NT = EPAD / 32;
+  constexpr int EPAD = 32 * NT;
+  constexpr int EM = EPAD > 128 ? 2 : 1;           // 128-row MMA tiles of router rows
+  constexpr int kPitch = EPAD + 1;                  // logits row pitch: a thread per row, no conflicts
+  constexpr int kTokBytes = kRxMaxTok * kRtRowBytes;            // 8 KB slot for up to 64 tokens
+  constexpr int kStageBytes = EM * kRxTileBytes + kTokBytes;
+  constexpr int kStages = EM == 1 ? 8 : 4;
+  constexpr int kAccCols = 64;                                   // TMEM columns per router tile
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   unsigned char *smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
@@ -428,22 +417,17 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmap_t,
   uint64_t *tfull_bar = empty_bar + kStages;
   uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(tfull_bar + 1);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
-  int *n_flagged = const_cast<int *>(abort_flag) + 1;
-  float *bias_s = reinterpret_cast<float *>(after + 256);               // [EPAD]
-  int *flag_tok = reinterpret_cast<int *>(after + 256 + EPAD * 4);      // [128] token row in the tile
-  int *cand_cnt = flag_tok + kRcTokens;                                 // [128]
-  int *cand_e = cand_cnt + kRcTokens;                                   // [128][kRcCand]
-  // partial logits pushed by the cluster's CTAs, over the ring once everybody is done
-  // with it: part[source rank][expert][token of this CTA's share]
-  float *part = reinterpret_cast<float *>(smem);
+  int *n_pairs = const_cast<int *>(abort_flag) + 1;
+  int *n_whole = n_pairs + 1;
+  int *pairs = reinterpret_cast<int *>(after + 256);  // [kRxPairs] row << 16 | expert
+  int *whole = pairs + kRxPairs;                      // [kRxMaxTok] rows recomputed entirely
+  // the logits of the CTA's tokens, [token][expert], over the ring once the MMAs are done
+  float *lg = reinterpret_cast<float *>(smem);
+  static_assert(kRxMaxTok * kPitch * 4 <= kStages * kStageBytes, "logits must fit the ring");
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int split = static_cast<int>(cluster_size());
-  const int crank = static_cast<int>(cluster_rank());
-  const int tok0 = static_cast<int>(blockIdx.x / split) * kRcTokens;
-  const int nk_all = (H + kRtKC - 1) / kRtKC;
-  const int kc_lo = crank * nk_all / split, kc_hi = (crank + 1) * nk_all / split;
-  const int share = (kRcTokens + split - 1) / split;  // tokens each CTA selects for
+  const int tok0 = static_cast<int>(blockIdx.x) * ntok;
+  const int nk = (H + kRtKC - 1) / kRtKC;
 
   if (tid == 0) {
     for (int s = 0; s < kStages; s++) {
@@ -452,13 +436,14 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmap_t,
     }
     mbar_init(tfull_bar, 1);
     *abort_flag = 0;
-    *n_flagged = 0;
+    *n_pairs = 0;
+    *n_whole = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmap_t);
-    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_wr);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_holder, EPAD);
+    tmem_alloc(tmem_holder, kRxAccs * EM * kAccCols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -472,16 +457,19 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmap_t,
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      for (int kc = kc_lo; kc < kc_hi; kc++) {
+      const uint32_t bytes = EM * kRxTileBytes + ntok * kRtRowBytes;
+      for (int kc = 0; kc < nk; kc++) {
         if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
           set_status(status, kStatusWaitTimeoutProducer);
           *abort_flag = 1;
           break;
         }
         unsigned char *dst = smem + stage * kStageBytes;
-        mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
-        tma_load_2d(dst, &tmap_t, &full_bar[stage], kc * kRtKC, tok0);
-        tma_load_2d(dst + kTokBytes, &tmap_w, &full_bar[stage], kc * kRtKC, 0);
+        mbar_arrive_expect_tx(&full_bar[stage], bytes);
+        tma_load_2d(dst + EM * kRxTileBytes, &tmap_t, &full_bar[stage], kc * kRtKC, tok0);
+#pragma unroll
+        for (int m = 0; m < EM; m++)
+          tma_load_2d(dst + m * kRxTileBytes, &tmap_wr, &full_bar[stage], 0, (m * nk + kc) * 32);
         if (++stage == kStages) {
           stage = 0;
           phase ^= 1u;
@@ -490,10 +478,10 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmap_t,
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(kRcTokens, EPAD);
+      const uint32_t idesc = umma_idesc_bf16(128, ntok);
       int stage = 0;
       uint32_t phase = 0;
-      for (int kc = kc_lo; kc < kc_hi; kc++) {
+      for (int kc = 0; kc < nk; kc++) {
         if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
           set_status(status, kStatusWaitTimeoutMma);
           *abort_flag = 1;
@@ -501,260 +489,195 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmap_t,
         }
         tc_fence_after();
         const uint32_t sa = smem_u32(smem + stage * kStageBytes);
-        const uint64_t da = umma_smem_desc_sw128(sa);
-        const uint64_t db = umma_smem_desc_sw128(sa + kTokBytes);
+        const uint64_t db = umma_smem_desc_sw128(sa + EM * kRxTileBytes);
+        // consecutive MMAs into one accumulator wait for each other; with so few columns
+        // that wait, not the tensor pipe, sets the pace: the chunks alternate between
+        // kRxAccs accumulators, added up when the logits are read
+        const int a = kc % kRxAccs;
 #pragma unroll
-        for (int k = 0; k < kRtKC / 16; k++)
-          umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (kc > kc_lo || k > 0) ? 1u : 0u);
+        for (int m = 0; m < EM; m++) {
+          const uint64_t da = umma_smem_desc_sw128(sa + m * kRxTileBytes);
+#pragma unroll
+          for (int k = 0; k < kRtKC / 16; k++)
+            umma_bf16(tmem_base + (a * EM + m) * kAccCols, da + 2 * k, db + 2 * k, idesc,
+                      (kc >= kRxAccs || k > 0) ? 1u : 0u);
+        }
         umma_commit(&empty_bar[stage]);
         if (++stage == kStages) {
           stage = 0;
           phase ^= 1u;
         }
       }
-      umma_commit(tfull_bar);  // also when this CTA had no K chunk: nothing to wait for
+      umma_commit(tfull_bar);
     }
-  }
-  __syncwarp();
-
-  const bool selector = warp >= 2;
-  const int q = warp & 3;             // TMEM lanes [32q, 32q+32) are this warp's
-  const int row = q * 32 + lane;      // token row of the tile held by this thread's TMEM lane
-  bool acc_ok = true;
-  if (selector) {
-    // the selecting warps fetch the bias while the main loop runs
-    for (int e = tid - 64; e < EPAD; e += kRcSelWarps * 32) bias_s[e] = e < E ? __ldg(b_router + e) : 0.f;
-    asm volatile("bar.sync 1, %0;" ::"n"(kRcSelWarps * 32) : "memory");
+  } else {
+    // accumulator -> logits [token][expert] in shared memory, bias added
     if (!mbar_wait(tfull_bar, 0, abort_flag)) {
       set_status(status, kStatusWaitTimeoutEpilogue);
       *abort_flag = 1;
-      acc_ok = false;
     }
-    acc_ok = __all_sync(0xffffffffu, acc_ok);
+    __syncwarp();
     tc_fence_after();
-  }
-  const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-  const bool has_acc = kc_hi > kc_lo;  // a CTA without K chunks holds no partial sums
-
-  if (split > 1) {
-    // 1. every CTA of the cluster is done with its ring
-    cluster_sync_all();
-    // 2. push this CTA's partial logits of token `row` to the CTA that selects for it
-    if (selector) {
-      const int dst_cta = row / share, tl = row - dst_cta * share;
-#pragma unroll 1
-      for (int c0 = 0; c0 < EPAD; c0 += 32) {
-        uint32_t r[32];
-        if (has_acc && acc_ok) {
-          tmem_ld32(taddr + c0, r);
-          tmem_ld_wait32(r);
-        } else {
+    const int q = warp & 3;  // TMEM lanes [32q, 32q+32) are this warp's
 #pragma unroll
-          for (int j = 0; j < 32; j++) r[j] = 0u;
+    for (int m = 0; m < EM; m++) {
+      const int e = m * 128 + q * 32 + lane;
+      const float bias = e < E ? __ldg(b_router + e) : 0.f;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + m * kAccCols;
+      const int accs = nk < kRxAccs ? nk : kRxAccs;  // accumulators that were written at all
+      for (int c0 = 0; c0 < ntok; c0 += 16) {
+        uint32_t r[16];
+        float sum[16];
+#pragma unroll
+        for (int j = 0; j < 16; j++) sum[j] = bias;
+        for (int a = 0; a < accs; a++) {
+          tmem_ld16(taddr + a * EM * kAccCols + c0, r);
+          tmem_ld_wait16(r);
+#pragma unroll
+          for (int j = 0; j < 16; j++) sum[j] += __uint_as_float(r[j]);
         }
-        const uint32_t local =
-            smem_u32(part + (static_cast<size_t>(crank) * EPAD + c0) * share + tl);
-        uint32_t remote;
-        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(dst_cta));
+        if (e < EPAD) {
 #pragma unroll
-        for (int j = 0; j < 32; j++)
-          asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(remote + j * share * 4), "r"(r[j])
-                       : "memory");
+          for (int j = 0; j < 16; j++) lg[(c0 + j) * kPitch + e] = sum[j];
+        }
       }
     }
-    // 3. all partials are in place
-    cluster_sync_all();
+    tc_fence_before();
   }
+  __syncthreads();
 
-  // which token this thread selects for
-  const int sel_row = split > 1 ? crank * share + (tid - 64) : row;
-  const bool sel_active = selector && (split == 1 || ((tid - 64) < share && sel_row < kRcTokens));
-  const int tok = tok0 + sel_row;
-  const bool live = sel_active && tok < T && !(pos && pos[tok] < 0);
+  // ---- selection: thread `tid` owns token row `tid`
+  const int tok = tok0 + tid;
+  const bool mine = tid < ntok && tok < T;
+  const bool live = mine && !(pos && pos[tok] < 0);
   const int rounds_chk = (K + 1 <= E) ? K + 1 : E;
-
+  const float *my = lg + tid * kPitch;
   float bv[NS];
   int bi[NS];
+  // the best NS logits of the row, sorted (value descending, lower index first on equal values)
+  auto scan_row = [&]() {
 #pragma unroll
-  for (int p = 0; p < NS; p++) {
-    bv[p] = -INFINITY;
-    bi[p] = 0x7fffffff;
-  }
-  // pass over the token's logits, 32 at a time; f(e, value) per expert
-  auto for_each_logit = [&](auto &&f) {
-#pragma unroll 1
-    for (int c0 = 0; c0 < EPAD; c0 += 32) {
-      float r[32];
-      if (split == 1) {
-        uint32_t u[32];
-        tmem_ld32(taddr + c0, u);  // the whole warp, also for rows without a token
-        tmem_ld_wait32(u);
-#pragma unroll
-        for (int j = 0; j < 32; j++) r[j] = __uint_as_float(u[j]);
-      } else {
-        const int tl = tid - 64;
-#pragma unroll
-        for (int j = 0; j < 32; j++) {
-          float v = 0.f;
-          if (sel_active)
-            for (int s = 0; s < split; s++)
-              v += part[(static_cast<size_t>(s) * EPAD + c0 + j) * share + tl];
-          r[j] = v;
-        }
-      }
-      if (live) {
-#pragma unroll
-        for (int j = 0; j < 32; j++)
-          if (c0 + j < E) f(c0 + j, r[j] + bias_s[c0 + j]);
-      }
+    for (int p = 0; p < NS; p++) {
+      bv[p] = -INFINITY;
+      bi[p] = 0x7fffffff;
     }
-  };
-
-  bool flagged = false;
-  if (selector) {
-    for_each_logit([&](int e, float v) {
-      if (logits_out) logits_out[static_cast<size_t>(tok) * E + e] = v;
-      if (v > bv[NS - 1]) {
-        // insert: the new value goes in front of the first smaller one (equal values keep
-        // the lower index in front), everything behind moves down one place
-        float cv = v;
-        int ci = e;
-        bool carrying = false;
+    // eight loads in flight before the first compare: the row walk is a chain of
+    // shared-memory latencies otherwise
+    for (int e0 = 0; e0 < E; e0 += 8) {
+      float v8[8];
 #pragma unroll
-        for (int p = 0; p < NS; p++) {
-          if (carrying || cv > bv[p]) {
-            const float tv = bv[p];
-            const int ti = bi[p];
-            bv[p] = cv;
-            bi[p] = ci;
-            cv = tv;
-            ci = ti;
-            carrying = true;
+      for (int u = 0; u < 8; u++) v8[u] = e0 + u < E ? my[e0 + u] : -INFINITY;
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        const float v = v8[u];
+        if (v > bv[NS - 1]) {
+          float cv = v;
+          int ci = e0 + u;
+          bool carrying = false;
+#pragma unroll
+          for (int p = 0; p < NS; p++) {
+            if (carrying || cv > bv[p]) {
+              const float tv = bv[p];
+              const int ti = bi[p];
+              bv[p] = cv;
+              bi[p] = ci;
+              cv = tv;
+              ci = ti;
+              carrying = true;
+            }
           }
         }
       }
-    });
-    if (live && exact_ties) {
+    }
+  };
+  // softmax over the K selected values (run.cpp:336-354) and the token's outputs
+  auto write_out = [&]() {
+    float ev[NS];
+    float sum = 0.f;
+#pragma unroll
+    for (int r = 0; r < NS; r++) {
+      if (r < K) {
+        ev[r] = expf(bv[r] - bv[0]);
+        sum += ev[r];
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < NS; r++) {
+      if (r < K) {
+        topk_i[static_cast<size_t>(tok) * K + r] = bi[r];
+        topk_v[static_cast<size_t>(tok) * K + r] = ev[r] / sum;
+      }
+    }
+    if (logits_out)
+      for (int e = 0; e < E; e++) logits_out[static_cast<size_t>(tok) * E + e] = my[e];
+  };
+
+  bool flagged = false;
+  if (live) {
+    scan_row();
+    if (exact_ties) {
 #pragma unroll
       for (int r = 0; r + 1 < NS; r++)
-        if (r + 1 < rounds_chk && bv[r] - bv[r + 1] < kTieGuard) flagged = true;
+        if (r + 1 < rounds_chk && bv[r] - bv[r + 1] < kTieGuardTc) flagged = true;
     }
-    // second pass for the tokens with a near tie: list the contenders
-    if (__any_sync(0xffffffffu, flagged)) {
+    if (flagged) {
+      // list the contenders: everything within twice the guard of the K-th value
       float kth = bv[0];
 #pragma unroll
       for (int r = 1; r < NS; r++)
         if (r < K) kth = bv[r];
-      const float thr = kth - 2.f * kTieGuard;
-      int slot = -1, cnt = 0;
-      if (flagged) {
-        slot = atomicAdd(n_flagged, 1);
-        flag_tok[slot] = sel_row;
-      }
-      const bool was_live = live;
-      for_each_logit([&](int e, float v) {
-        if (flagged && v >= thr) {
-          if (cnt < kRcCand) cand_e[slot * kRcCand + cnt] = e;
-          cnt++;
+      const float thr = kth - 2.f * kTieGuardTc;
+      bool full = false;
+      for (int e0 = 0; e0 < E && !full; e0 += 8) {
+        float v8[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) v8[u] = e0 + u < E ? my[e0 + u] : -INFINITY;
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+          if (v8[u] >= thr && !full) {
+            const int at = atomicAdd(n_pairs, 1);
+            if (at < kRxPairs)
+              pairs[at] = (tid << 16) | (e0 + u);
+            else
+              full = true;
+          }
         }
-      });
-      (void)was_live;
-      if (flagged) cand_cnt[slot] = cnt;
+      }
+      // the list is full (hundreds of near ties in one tile): this row is recomputed whole
+      if (full) whole[atomicAdd(n_whole, 1)] = tid;
+    } else {
+      write_out();
     }
-    if (live && !flagged) {
-      // softmax over the K selected values (run.cpp:336-354: double max/sum)
-      float ev[NS];
-      double sum = 0.0;
-      const double mx = static_cast<double>(bv[0]);
-#pragma unroll
-      for (int r = 0; r < NS; r++) {
-        if (r < K) {
-          ev[r] = expf(static_cast<float>(static_cast<double>(bv[r]) - mx));
-          sum += static_cast<double>(ev[r]);
-        }
-      }
-#pragma unroll
-      for (int r = 0; r < NS; r++) {
-        if (r < K) {
-          topk_i[static_cast<size_t>(tok) * K + r] = bi[r];
-          topk_v[static_cast<size_t>(tok) * K + r] =
-              static_cast<float>(static_cast<double>(ev[r]) / sum);
-        }
-      }
-    } else if (sel_active && tok < T && !live) {
-      for (int r = 0; r < K; r++) {
-        topk_i[static_cast<size_t>(tok) * K + r] = -1;
-        topk_v[static_cast<size_t>(tok) * K + r] = 0.f;
-      }
+  } else if (mine) {
+    for (int r = 0; r < K; r++) {
+      topk_i[static_cast<size_t>(tok) * K + r] = -1;
+      topk_v[static_cast<size_t>(tok) * K + r] = 0.f;
     }
   }
   __syncthreads();
 
-  // near ties: one warp per listed token
-  const int n_flag = *n_flagged;
-  for (int s = warp; s < n_flag; s += kRcThreads / 32) {
-    const int tk = tok0 + flag_tok[s];
-    const int cnt = cand_cnt[s];
-    const bool all = cnt > kRcCand;
-    const int n = all ? E : cnt;
-    const bf16 *trow = t + static_cast<size_t>(tk) * H;
-    float v[NT];
-#pragma unroll
-    for (int j = 0; j < NT; j++) v[j] = -INFINITY;
-    for (int i = 0; i < n; i++) {
-      const int e = all ? i : cand_e[s * kRcCand + i];
-      const float ex = warp_exact_dot(trow, w_router + static_cast<size_t>(e) * H, H, lane) + bias_s[e];
-#pragma unroll
-      for (int j = 0; j < NT; j++)
-        if (e == lane + 32 * j) v[j] = ex;
-      if (logits_out && lane == 0) logits_out[static_cast<size_t>(tk) * E + e] = ex;
+  // ---- near ties: the exact logits, one (token, expert) pair per warp at a time
+  const int np = *n_pairs < kRxPairs ? *n_pairs : kRxPairs;
+  const int nw = *n_whole;
+  if (np + nw > 0) {
+    for (int p = warp; p < np; p += kRxThreads / 32) {
+      const int row = pairs[p] >> 16, e = pairs[p] & 0xffff;
+      const float ex = warp_exact_dot(t + static_cast<size_t>(tok0 + row) * H,
+                                      w_router + static_cast<size_t>(e) * H, H, lane);
+      if (lane == 0) lg[row * kPitch + e] = ex + __ldg(b_router + e);
     }
-    float selv[GPTOSS_MAX_TOPK];
-    int seli[GPTOSS_MAX_TOPK];
-    uint32_t taken = 0;
-#pragma unroll
-    for (int r = 0; r < GPTOSS_MAX_TOPK; r++) {
-      if (r < K) {
-        float xv = -INFINITY;
-        int xi = 0x7fffffff;
-#pragma unroll
-        for (int j = 0; j < NT; j++) {
-          const int e = lane + 32 * j;
-          if (!((taken >> j) & 1u) && e < E && v[j] > -INFINITY && (v[j] > xv || xi == 0x7fffffff)) {
-            xv = v[j];
-            xi = e;
-          }
-        }
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) {
-          const float ov = __shfl_xor_sync(0xffffffffu, xv, off);
-          const int oi = __shfl_xor_sync(0xffffffffu, xi, off);
-          if (oi != 0x7fffffff && (xi == 0x7fffffff || ov > xv || (ov == xv && oi < xi))) {
-            xv = ov;
-            xi = oi;
-          }
-        }
-        selv[r] = xv;
-        seli[r] = xi;
-        if (xi != 0x7fffffff && (xi & 31) == lane) taken |= 1u << (xi >> 5);
+    for (int i = 0; i < nw; i++) {
+      const int row = whole[i];
+      for (int e = warp; e < E; e += kRxThreads / 32) {
+        const float ex = warp_exact_dot(t + static_cast<size_t>(tok0 + row) * H,
+                                        w_router + static_cast<size_t>(e) * H, H, lane);
+        if (lane == 0) lg[row * kPitch + e] = ex + __ldg(b_router + e);
       }
     }
-    float ev[GPTOSS_MAX_TOPK];
-    double sum = 0.0;
-    const double mx = static_cast<double>(selv[0]);
-#pragma unroll
-    for (int r = 0; r < GPTOSS_MAX_TOPK; r++) {
-      if (r < K) {
-        ev[r] = expf(static_cast<float>(static_cast<double>(selv[r]) - mx));
-        sum += static_cast<double>(ev[r]);
-      }
-    }
-#pragma unroll
-    for (int r = 0; r < GPTOSS_MAX_TOPK; r++) {
-      if (r < K && lane == r) {
-        topk_i[static_cast<size_t>(tk) * K + r] = seli[r];
-        topk_v[static_cast<size_t>(tk) * K + r] = static_cast<float>(static_cast<double>(ev[r]) / sum);
-      }
+    __syncthreads();
+    if (flagged) {
+      scan_row();
+      write_out();
     }
   }
 
@@ -768,7 +691,7 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmap_t,
   }
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, EPAD);
+    tmem_dealloc(tmem_base, kRxAccs * EM * kAccCols);
   }
 }
 
@@ -829,76 +752,69 @@ static cudaError_t launch_router_nt(gptoss_moe *h, const bf16 *t, const bf16 *w_
                                     topk_i, topk_v, logits_opt, h->opt_exact_ties, h->status, stream);
 }
 
-template <int EPAD, int NS>
-static cudaError_t launch_router_tc(gptoss_moe *h, LayerWeights &lw, const bf16 *t, const int *pos,
+template <int NT, int NS>
+static cudaError_t launch_router_tx(gptoss_moe *h, LayerWeights &lw, const bf16 *t, const int *pos,
                                     int T, int *topk_i, float *topk_v, float *logits_opt,
                                     cudaStream_t stream) {
-  constexpr int kStages = RcStages<EPAD>::value;
+  constexpr int EPAD = 32 * NT;
+  constexpr int EM = EPAD > 128 ? 2 : 1;
+  constexpr int kStages = EM == 1 ? 8 : 4;
   const int H = h->H, E = h->E, K = h->K;
-  auto kernel = router_tc_kernel<EPAD, NS>;
-  const size_t smem = 1024 + static_cast<size_t>(kStages) * (kRcTokens + EPAD) * kRtRowBytes + 256 +
-                      EPAD * 4 + kRcTokens * 4 * (2 + kRcCand);
+  auto kernel = router_tx_kernel<NT, NS>;
+  const size_t smem = 1024 + static_cast<size_t>(kStages) * (EM * kRxTileBytes + kRxMaxTok * kRtRowBytes) +
+                      256 + (kRxPairs + kRxMaxTok) * sizeof(int);
   static_assert((2 * kStages + 1) * 8 + 16 <= 256, "barrier area");
+  // tokens per CTA: the token tiles fill the GPU in one wave
+  int ntok = (((T + h->num_sms - 1) / h->num_sms) + 15) & ~15;
+  if (ntok < 16) ntok = 16;
+  if (ntok > kRxMaxTok) ntok = kRxMaxTok;
   std::string err;
-  // the router rows never move: their map is made once per layer; the token map is kept
-  // while the caller hands the same buffer and batch size
-  if (!lw.tmap_router_ready) {
-    if (make_tmap_2d_bf16(&lw.tmap_router, lw.w_router, H, E, kRtKC, EPAD, &err))
-      return cudaErrorInvalidValue;
-    lw.tmap_router_ready = true;
-  }
-  if (h->router_t_ptr != t || h->router_t_rows != T) {
-    if (make_tmap_2d_bf16(&h->tmap_router_t, t, H, T, kRtKC, kRcTokens, &err))
+  // the token map is kept while the caller hands the same buffer and batch size
+  if (h->router_t_ptr != t || h->router_t_rows != T || h->router_t_box != ntok) {
+    if (make_tmap_2d_bf16(&h->tmap_router_t, t, H, T, kRtKC, ntok, &err))
       return cudaErrorInvalidValue;
     h->router_t_ptr = t;
     h->router_t_rows = T;
+    h->router_t_box = ntok;
   }
-  const int tiles = (T + kRcTokens - 1) / kRcTokens;
-  const int nk_all = (H + kRtKC - 1) / kRtKC;
-  cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(kRcThreads);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[2];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[1].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = h->opt_dependent_launch ? 2 : 1;
-  // CTAs per tile: as many as fill the GPU in one wave (a cluster shares the tile's K
-  // chunks); how many clusters of a size fit at once is asked of the runtime, once
-  // (the answer is the same on every GPU of one kind: concurrent first calls from several
-  // host threads write equal values)
-  static int fit[9] = {0};  // [cluster size] -> co-resident clusters of this kernel
   // per device, cheap: set on every launch so every GPU a process drives has it
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem);
   if (e != cudaSuccess) return e;
-  int split = h->opt_router_split > 0 ? h->opt_router_split : h->num_sms / tiles;
-  if (split > 8) split = 8;
-  if (split > nk_all) split = nk_all;
-  if (split < 1) split = 1;
-  for (; split > 1; split--) {
-    if (!fit[split]) {
-      cfg.gridDim = dim3(static_cast<unsigned>(split * 8));
-      attr[0].val.clusterDim.x = split;
-      int n = 0;
-      if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
-        cudaGetLastError();
-        n = -1;
-      }
-      fit[split] = n > 0 ? n : -1;
-    }
-    if (fit[split] >= tiles) break;
-  }
-  cfg.gridDim = dim3(static_cast<unsigned>(tiles * split));
-  attr[0].val.clusterDim.x = split;
-  return cudaLaunchKernelEx(&cfg, kernel, h->tmap_router_t, lw.tmap_router, t,
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>((T + ntok - 1) / ntok));
+  cfg.blockDim = dim3(kRxThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = h->opt_dependent_launch ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, h->tmap_router_t, lw.tmap_router_tiled, t,
                             static_cast<const bf16 *>(lw.w_router),
-                            static_cast<const float *>(lw.b_router), pos, T, H, E, K, topk_i,
+                            static_cast<const float *>(lw.b_router), pos, T, H, E, K, ntok, topk_i,
                             topk_v, logits_opt, h->opt_exact_ties, h->status);
+}
+
+int build_router_tiles(gptoss_moe *h, LayerWeights &lw) {
+  const size_t n = tiled_weight_elems(h->E, h->H, 1);
+  auto fail = [&](const std::string &what) {
+    h->err = what;
+    return GPTOSS_E_CUDA;
+  };
+  cudaError_t e;
+  if (!lw.router_tiled &&
+      (e = cudaMalloc(reinterpret_cast<void **>(&lw.router_tiled), n * sizeof(bf16))) != cudaSuccess)
+    return fail(std::string("cudaMalloc(router tiles): ") + cudaGetErrorString(e));
+  if ((e = launch_retile_weights(lw.router_tiled, lw.w_router, h->E, h->H, 1, nullptr,
+                                 &h->launches)) != cudaSuccess ||
+      (e = cudaStreamSynchronize(nullptr)) != cudaSuccess)
+    return fail(std::string("router tiles: ") + cudaGetErrorString(e));
+  std::string err;
+  if (make_tmap_tiles_bf16(&lw.tmap_router_tiled, lw.router_tiled, n / (128 * kTileK), &err))
+    return fail(err);
+  return GPTOSS_OK;
 }
 
 cudaError_t launch_router_topk(gptoss_moe *h, int layer, const bf16 *t, const int *pos, int T,
@@ -916,16 +832,16 @@ cudaError_t launch_router_topk(gptoss_moe *h, int layer, const bf16 *t, const in
     if (E <= 128) return launch_router_nt<4>(h, t, w, b, pos, T, h->topk_i, h->topk_v, logits_opt, stream);
     return launch_router_nt<8>(h, t, w, b, pos, T, h->topk_i, h->topk_v, logits_opt, stream);
   }
-#define GPTOSS_ROUTER_CASE(EP)                                                                   \
-  if (E <= EP)                                                                                   \
-    return h->K <= 4 ? launch_router_tc<EP, 5>(h, lw, t, pos, T, h->topk_i, h->topk_v,           \
-                                               logits_opt, stream)                               \
-                     : launch_router_tc<EP, 9>(h, lw, t, pos, T, h->topk_i, h->topk_v,           \
-                                               logits_opt, stream);
-  GPTOSS_ROUTER_CASE(32)
-  GPTOSS_ROUTER_CASE(64)
-  GPTOSS_ROUTER_CASE(128)
-  GPTOSS_ROUTER_CASE(256)
+#define GPTOSS_ROUTER_CASE(NTV)                                                                  \
+  if (E <= 32 * NTV)                                                                             \
+    return h->K <= 4 ? launch_router_tx<NTV, 5>(h, lw, t, pos, T, h->topk_i, h->topk_v,          \
+                                                logits_opt, stream)                              \
+                     : launch_router_tx<NTV, 9>(h, lw, t, pos, T, h->topk_i, h->topk_v,          \
+                                                logits_opt, stream);
+  GPTOSS_ROUTER_CASE(1)
+  GPTOSS_ROUTER_CASE(2)
+  GPTOSS_ROUTER_CASE(4)
+  GPTOSS_ROUTER_CASE(8)
 #undef GPTOSS_ROUTER_CASE
   return cudaErrorInvalidValue;
 }

@@ -60,6 +60,10 @@ SHAPES = {
     # c3 cut to 16 experts and an eighth of the tokens: the same 192 rows per expert,
     # 0.8 GB of weights (larger than L2); the weight-streaming case for profiler captures
     "c3s": MoeShape("gpt-oss-120b-moe-layer-16experts-T768", 768, 2880, 2880, 16, 4, 7.0, 2),
+    # c3's routing problem (6144 tokens, 128 experts, hidden 2880) with narrow experts
+    # (intermediate 64: 0.14 GB of weights): the case that captures of the router,
+    # permutation and combine kernels are taken on
+    "c3r": MoeShape("gpt-oss-120b-routing-T6144-narrow-experts", 6144, 2880, 64, 128, 4, 7.0, 2),
 }
 
 

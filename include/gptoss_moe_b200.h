@@ -199,16 +199,15 @@ int gptoss_moe_get_activations(gptoss_moe_t *h, void *act_host, size_t bytes);
 /* Options: "gemm_impl" (GPTOSS_GEMM_*), "keep_logits" (0/1),
  * "exact_ties" (0/1, default 1: re-evaluate near-tied router logits in fp64),
  * "router_impl" (0 = tcgen05 router, the default; 1 = the mma.sync router),
- * "router_split" (0..8: CTAs that share one 128-token tile of the tcgen05 router,
- * each taking a part of the hidden dimension; 0 = as many as fill the GPU),
  * "ep_transport" (0/1, see gptoss_moe_ep_transport), "ep_overlap" (0/1, default 0;
  * peer-memory transport only: the owner pulls the rows of the second half of its
- * experts on a second stream while the gate_up GEMM of the first half runs),
- * "time_stages" (0/1, see gptoss_moe_stage_ms), "pair_rings" (6..9: how many of
- * the CTA-pair GEMM's twelve 16 KB operand slots hold weight tiles, the rest
- * token tiles; bf16 weights), "dependent_launch" (0/1: the layer's kernels are
- * launched with programmatic stream serialization, so a kernel's set-up overlaps
- * its predecessor's tail), "wait_limit_ms" (1..60000, default 2000: how long a
+ * experts on a second stream while the gate_up GEMM of the first half runs;
+ * "ep_gather_ctas", default 64, is the size of that second gather's grid),
+ * "time_stages" (0/1, see gptoss_moe_stage_ms), "dependent_launch" (0/1, default 1:
+ * the layer's kernels are launched with programmatic stream serialization, so a
+ * kernel's set-up overlaps its predecessor's tail), "l2_hints" (0/1, default 1:
+ * the CTA-pair GEMM marks its weight loads evict-first and its token loads
+ * evict-last in L2), "wait_limit_ms" (1..60000, default 2000: how long a
  * kernel of the peer-memory transport waits for another rank's flag before it
  * gives up with status 106).  Every option leaves the results unchanged. */
 int gptoss_moe_set_option(gptoss_moe_t *h, const char *name, int value);
