@@ -11,12 +11,14 @@
 //              getp_run.cpp:426-432, expert.cpp:1176-1231) and everything else is
 //              replicated; otherwise every GPU holds the whole model.
 //   inference  prompts encoded with the host program's tokenizer; requests split evenly
-//              over the GPUs, one host thread per GPU; each GPU works through its
-//              requests in static batches, one decode step per iteration for every
-//              unfinished sequence of the batch, finished sequences staying in place as
-//              inactive rows; greedy (argmax) decoding; tok_gens row i = generated ids
-//              terminated by -1; returns the number of generated tokens
-//              (getp_run.cpp:457-499, :896-1009, :1011-1074)
+//              over the GPUs, one host thread per GPU; one decode step per iteration for
+//              every running sequence of the GPU; greedy (argmax) decoding; tok_gens row
+//              i = generated ids terminated by -1; returns the number of generated tokens
+//              (getp_run.cpp:457-499, :896-1009, :1011-1074).  A row that ends is given to
+//              the next waiting request at once (continuous batching); GPTOSS_GETP_STATIC=1
+//              keeps the reference's static batches, where finished sequences stay in
+//              place as inactive rows until the whole batch is done.  The generated
+//              tokens are the same either way.
 //   finish     frees everything (getp_run.cpp:448-455)
 // Under expert parallelism the GPUs step in lock step: before every decode step the
 // threads agree on whether anybody still has work (step_agreement.h), and a GPU that has
@@ -29,7 +31,8 @@
 // Environment: GPTOSS_GETP_GPUS (default: all sm_100 devices), GPTOSS_GETP_BATCH
 // (sequences per GPU batch; default 896, or 768 with 128 experts, the reference's
 // MAX_BATCH_SIZE / MAX_BATCH_SIZE_120B, defines.h:30-31), GETP_FORCE_EP (expert
-// parallelism also with fewer than 128 experts, getp_run.cpp:426).
+// parallelism also with fewer than 128 experts, getp_run.cpp:426), GPTOSS_GETP_STATIC
+// (1 = the reference's static batches instead of continuous batching).
 #include "getp_abi.h"
 
 #include <algorithm>
@@ -57,7 +60,6 @@ struct Sequence {
   int *out = nullptr;  // the request's row of tok_gens
   int out_cap = 0;     // ids that fit before the terminator
   int pos = 0, token = 0, generated = 0;
-  bool finished = false;
 };
 
 struct Device {
@@ -78,42 +80,56 @@ int env_int(const char *name, int fallback) {
   return (v && *v) ? std::atoi(v) : fallback;
 }
 
-// One GPU's share of the requests, batch after batch.  `agree` (expert parallelism) makes
-// the GPUs step together; without it the GPU runs on its own.
+// One GPU's share of the requests.  The GPU's rows are slots: a request takes a free slot,
+// decodes there one position per step, and gives the slot back when it ends; the next
+// waiting request starts in it at position 0 in the following step (continuous batching:
+// a row's KV-cache slot simply starts over).  With `static_batches` the reference's
+// schedule is kept instead: a new batch starts only when every sequence of the previous
+// one has ended (getp_run.cpp:896-1009), finished sequences idling as inactive rows.
+// The tokens a request generates are the same either way - rows do not see each other.
+// `agree` (expert parallelism) makes the GPUs step together; without it the GPU runs on
+// its own.
 long long run_on_device(Device &dev, const Config &cfg, Sequence *seqs, int count,
-                        gptoss_host::StepAgreement *agree) {
+                        gptoss_host::StepAgreement *agree, bool static_batches) {
   long long total = 0;
-  std::vector<int> tokens(dev.batch), pos(dev.batch), next(dev.batch);
-  int first = 0, B = 0, unfinished = 0;
-  Sequence *batch = nullptr;
-  auto close_batch = [&]() {
-    for (int i = 0; i < B; i++) {
-      Sequence &s = batch[i];
-      const int n = std::min(s.generated, s.out_cap);
-      s.out[n] = -1;
-      total += n;
-    }
-    first += B;
-    B = 0;
-    batch = nullptr;
+  const int slots = dev.batch;
+  std::vector<int> tokens(slots), pos(slots), next(slots);
+  std::vector<Sequence *> row(slots, nullptr);
+  int next_request = 0, running = 0, rows_in_use = 0;
+  auto retire = [&](int i) {
+    Sequence &s = *row[i];
+    const int n = std::min(s.generated, s.out_cap);
+    s.out[n] = -1;
+    total += n;
+    row[i] = nullptr;
+    running--;
   };
   while (true) {
-    if (unfinished == 0) {
-      if (batch) close_batch();
-      if (first < count) {
-        B = std::min(dev.batch, count - first);
-        batch = seqs + first;
-        unfinished = B;
+    // hand free slots to waiting requests
+    if (static_batches) {
+      if (running == 0 && next_request < count) {
+        rows_in_use = std::min(slots, count - next_request);
+        for (int i = 0; i < rows_in_use; i++) row[i] = &seqs[next_request++];
+        running = rows_in_use;
       }
+    } else {
+      for (int i = 0; i < slots && next_request < count; i++) {
+        if (!row[i]) {
+          row[i] = &seqs[next_request++];
+          running++;
+          rows_in_use = std::max(rows_in_use, i + 1);
+        }
+      }
+      while (rows_in_use > 0 && !row[rows_in_use - 1]) rows_in_use--;
     }
-    const bool have_work = unfinished > 0;
+    const bool have_work = running > 0;
     if (agree ? !agree->another_step(have_work) : !have_work) break;
     int rows;
     if (have_work) {
-      rows = B;
-      for (int i = 0; i < B; i++) {
-        tokens[i] = batch[i].finished ? -1 : batch[i].token;
-        pos[i] = batch[i].finished ? -1 : batch[i].pos;
+      rows = rows_in_use;
+      for (int i = 0; i < rows; i++) {
+        tokens[i] = row[i] ? row[i]->token : -1;
+        pos[i] = row[i] ? row[i]->pos : -1;
       }
     } else {
       // nothing of its own left: one inactive row, so that this GPU's experts still
@@ -128,9 +144,9 @@ long long run_on_device(Device &dev, const Config &cfg, Sequence *seqs, int coun
       die("decode step", gptoss_decode_last_error(dev.engine));
     }
     if (!have_work) continue;
-    for (int i = 0; i < B; i++) {
-      Sequence &s = batch[i];
-      if (s.finished) continue;
+    for (int i = 0; i < rows; i++) {
+      if (!row[i]) continue;
+      Sequence &s = *row[i];
       s.pos++;
       int tok;
       if (s.pos < static_cast<int>(s.prompt.size())) {
@@ -144,13 +160,10 @@ long long run_on_device(Device &dev, const Config &cfg, Sequence *seqs, int coun
       const bool eos = tok == kEosA || tok == kEosB;
       // also stop where the caller's output row or the KV cache would overflow
       // (the reference checks neither)
-      if (eos || s.pos + 1 >= kMaxSteps || s.pos + 1 >= cfg.seq_len || s.generated >= s.out_cap) {
-        s.finished = true;
-        unfinished--;
-      }
+      if (eos || s.pos + 1 >= kMaxSteps || s.pos + 1 >= cfg.seq_len || s.generated >= s.out_cap)
+        retire(i);
     }
   }
-  if (batch) close_batch();
   return total;
 }
 
@@ -236,13 +249,15 @@ long long inference(Transformer *transformer, Tokenizer *tokenizer, Sampler *, R
   std::vector<std::thread> workers;
   std::unique_ptr<gptoss_host::StepAgreement> agree;
   if (g_expert_parallel) agree.reset(new gptoss_host::StepAgreement(gpus));
+  const bool static_batches = env_int("GPTOSS_GETP_STATIC", 0) != 0;
   int start = 0;
   for (int d = 0; d < gpus; d++) {
     const int share = n / gpus + (d < n % gpus ? 1 : 0);
     // under expert parallelism a GPU without requests still steps with the others
     if (share > 0 || g_expert_parallel)
       workers.emplace_back([&, d, start, share]() {
-        totals[d] = run_on_device(g_devices[d], cfg, seqs.data() + start, share, agree.get());
+        totals[d] = run_on_device(g_devices[d], cfg, seqs.data() + start, share, agree.get(),
+                                  static_batches);
       });
     start += share;
   }

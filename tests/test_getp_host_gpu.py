@@ -64,6 +64,15 @@ def test_getp_entry_points_on_tiny_model(pkg, tmp_path):
         break  # the sequences differ from here on by construction
     else:
         assert len(got) == len(want)
+    # the reference's static batches (a batch starts when the previous one is all done) give
+    # every request the same tokens as the default schedule, where a finished row is handed
+    # to the next waiting request at once
+    out_static = tmp_path / "out_static.txt"
+    res = subprocess.run([str(native_build.HARNESS), str(bin_path), str(req), str(out_static)],
+                         capture_output=True, text=True, env=dict(env, GPTOSS_GETP_STATIC="1"),
+                         timeout=600)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert out_static.read_text() == out.read_text()
 
 
 def _run_host(native_build, bin_path, req, out, env_extra):
