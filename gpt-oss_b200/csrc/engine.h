@@ -153,7 +153,6 @@ cudaError_t launch_rmsnorm(bf16 *out, const bf16 *x, const float *w, const int *
                            cudaStream_t stream, long long *launches);
 
 // permute.cu
-void set_small_kernel_carveout(int on);
 cudaError_t launch_permute(gptoss_moe *h, cudaStream_t stream);
 cudaError_t launch_permute_plan_only(gptoss_moe *h, cudaStream_t stream);
 // h->mtile_split = index of the first token tile whose expert is >= e_split

@@ -652,8 +652,6 @@ int gptoss_moe_set_option(gptoss_moe_t *h, const char *name, int value) {
   } else if (!strcmp(name, "router_impl")) {
     if (value != 0 && value != 1) return fail(h, GPTOSS_E_INVALID, "router_impl must be 0 or 1");
     h->opt_router_impl = value;
-  } else if (!strcmp(name, "smem_carveout")) {
-    set_small_kernel_carveout(value != 0);
   } else if (!strcmp(name, "l2_hints")) {
     h->opt_l2_hints = value != 0;
   } else if (!strcmp(name, "dependent_launch")) {

@@ -28,18 +28,9 @@ constexpr int kScanThreads = 512;
 // <<<grid, block, smem, stream>>> with the stream-serialization attribute when the engine
 // runs its layer with programmatic dependent launches (every kernel launched this way
 // starts with grid_dependency_wait()).
-// g_carveout != 0: the small kernels ask for the same shared-memory carve-out as the router
-// and the GEMMs that run around them, so that the SMs do not switch their L1 / shared-memory
-// split between every two kernels of the layer.
-static int g_carveout = 0;
-void set_small_kernel_carveout(int on) { g_carveout = on; }
-
 template <typename... KArgs, typename... Args>
 static cudaError_t launch_kernel(void (*kernel)(KArgs...), unsigned grid, unsigned block,
                                  size_t smem, cudaStream_t stream, bool dependent, Args... args) {
-  if (g_carveout)
-    cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                         cudaSharedmemCarveoutMaxShared);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(block);
