@@ -111,6 +111,20 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity,
   }
 }
 
+// One lane of a converged warp (the same one every time); the branch on the result is
+// warp-uniform control flow to the compiler, unlike a test of the lane index.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const void *tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");

@@ -98,8 +98,10 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int total_tiles = *g.num_mtiles * n_tiles;
   const int kb_count = (g.k_dim + kTileK - 1) / kTileK;
 
+  // the producer and the MMA warp walk the ring whole and one elected lane issues (a loop
+  // that only one lane runs makes every load and MMA several times dearer to issue)
   if (warp == 0) {
-    if (lane == 0) {
+    {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -129,9 +131,11 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
             break;
           }
           unsigned char *sa = smem + stage * kStageBytes;
-          mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
-          tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * kTileK, row0);
-          tma_load_2d(sa + kABytes, &tmap_b, &full_bar[stage], kb * kTileK, brow);
+          if (elect_one()) {
+            mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
+            tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * kTileK, row0);
+            tma_load_2d(sa + kABytes, &tmap_b, &full_bar[stage], kb * kTileK, brow);
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -140,7 +144,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {
       constexpr uint32_t idesc = umma_idesc_bf16(kTileM, BN);
       int stage = 0;
       uint32_t phase = 0;
@@ -166,20 +170,22 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t sa = smem_u32(smem + stage * kStageBytes);
           const uint64_t da = umma_smem_desc_sw128(sa);
           const uint64_t db = umma_smem_desc_sw128(sa + kABytes);
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < kTileK / 16; k++) {
-            // +32 bytes along K inside the 128-byte swizzle row = +2 in the
-            // descriptor's (address >> 4) field
-            umma_bf16(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < kTileK / 16; k++) {
+              // +32 bytes along K inside the 128-byte swizzle row = +2 in the
+              // descriptor's (address >> 4) field
+              umma_bf16(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+            umma_commit(&empty_bar[stage]);
           }
-          umma_commit(&empty_bar[stage]);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!ok) break;
-        umma_commit(&tfull_bar[acc]);
+        if (elect_one()) umma_commit(&tfull_bar[acc]);
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }

@@ -59,20 +59,22 @@ struct PairStage {
 };
 
 // MXFP4 weights (MX = true): a producer warp bulk-copies the packed codes (4 KB) and
-// scales (256 B) of the CTA's 128 rows x 64 k into a raw ring; eight extra warps, each
-// taking every eighth K block whole, expand them to bf16 straight into the operand
-// ring, in the 128-byte-swizzled layout TMA would have written, and count as one
-// arrival per CTA on the even CTA's full barrier beside the token tiles' bytes.
+// scales (256 B) of the CTA's 128 rows x 64 k into a raw ring; eight extra warps expand
+// them to bf16 straight into the operand ring, in the 128-byte-swizzled layout TMA would
+// have written, and count as arrivals on the even CTA's full barrier beside the token
+// tiles' bytes.  The expansion is register arithmetic only (a table in shared memory cost
+// more shared-memory cycles per K block than the MMAs' own operand reads).
 constexpr int kPairBarrierBytes = 1024;  // mbarriers, TMEM address holder, abort flag
 constexpr int kRawCodeBytes = 128 * 32;
 constexpr int kRawStageBytes = kRawCodeBytes + 128 * 2;
 constexpr int kDequantWarps = 8;  // two threads per weight row
 
-// two e2m1 codes (one byte, low nibble = even element) -> two bf16 whose value is
-// code * 2^-126: sign to bit 15, the three magnitude bits to exponent bit 0-1 and
-// mantissa bit 6 (for magnitude 1 this is the bf16 subnormal 2^-127)
-__device__ __forceinline__ uint32_t e2m1x2_to_bf16x2_raw(uint32_t x) {
-  return ((x & 0x08u) << 12) | ((x & 0x07u) << 6) | ((x & 0x80u) << 24) | ((x & 0x70u) << 18);
+// two e2m1 codes, one in bits 0-3 and one in bits 16-19 (other bits: anything) -> two bf16
+// whose value is code * 2^-126: sign to bit 15 of its half, the three magnitude bits to
+// exponent bits 0-1 and mantissa bit 6 (magnitude code 1 becomes the bf16 subnormal
+// 2^-127, which bf16 multiplies take at full rate)
+__device__ __forceinline__ uint32_t e2m1_pair_to_bf16x2_raw(uint32_t u) {
+  return ((u << 6) & 0x01C001C0u) | ((u << 12) & 0x80008000u);
 }
 __device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
   __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162 *>(&a),
@@ -91,10 +93,8 @@ __device__ __forceinline__ void decode_tile(int tile, int w_pairs, int tt_lo, in
 
 // TOKB = token rows a CTA's operand slot holds (128: token tiles of up to 256; 32:
 // tiles of up to 64 for decode-sized batches, which buys a deeper ring)
-// kRawStages = depth of the raw (packed) weight ring, 0 without MX; LUTREP = copies of the
-// code table, a power of two (32: one per bank, every lane reads its own copy and no
-// lookup conflicts; 16: lanes l and l + 16 share one)
-template <int EPI, int kPairStages, bool MX, int TOKB, int kRawStages, int LUTREP>
+// kRawStages = depth of the raw (packed) weight ring, 0 without MX
+template <int EPI, int kPairStages, bool MX, int TOKB, int kRawStages>
 __global__ void __launch_bounds__(kPairThreads + (MX ? (kDequantWarps + 1) * 32 : 0), 1)
 grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
                          const __grid_constant__ CUtensorMap tmap_x,
@@ -116,13 +116,6 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
                 "barrier region too small");
   unsigned char *epi_stage = smem + kPairStages * kPairStageBytes + kPairBarrierBytes;
   unsigned char *raw_ring = epi_stage + PairStage<EPI>::kTotalBytes;  // (MX)
-  // (MX) byte of two e2m1 codes -> the two values as bf16 (normal numbers; the
-  // subnormal detour of the bit trick is paid 256 times here, not per element)
-  uint32_t *lut = reinterpret_cast<uint32_t *>(raw_ring + kRawStages * kRawStageBytes);
-  if (MX) {
-    for (uint32_t x = threadIdx.x; x < 256 * LUTREP; x += blockDim.x)
-      lut[x] = bf16x2_mul(e2m1x2_to_bf16x2_raw(x / LUTREP), 0x7E807E80u);  // * (2^126, 2^126)
-  }
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_cta_rank();
@@ -181,7 +174,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
   const int ncl = gridDim.x >> 1;  // clusters of the launch; a cluster strides over the tiles
 
   if (warp == 0) {
-    if (lane == 0) {
+    {  // the whole warp walks the ring; one elected lane issues the loads
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -223,16 +216,18 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
             break;
           }
           unsigned char *sa = smem + stage * kPairStageBytes;
-          if (!MX) {
-            if (rank == 0)
-              mbar_arrive_expect_tx(&full_bar[stage], 2 * (kPairOperandBytes + tok_bytes));
-            tma_load_2d_pair_hint(sa, &tmap_w, &full_bar[stage], kb * kTileK, wrow, pol_w);
-          } else if (rank == 0) {
-            // the weights arrive through the raw ring and the dequantising warps
-            mbar_arrive_expect_tx(&full_bar[stage], 2 * tok_bytes);
+          if (elect_one()) {
+            if (!MX) {
+              if (rank == 0)
+                mbar_arrive_expect_tx(&full_bar[stage], 2 * (kPairOperandBytes + tok_bytes));
+              tma_load_2d_pair_hint(sa, &tmap_w, &full_bar[stage], kb * kTileK, wrow, pol_w);
+            } else if (rank == 0) {
+              // the weights arrive through the raw ring and the dequantising warps
+              mbar_arrive_expect_tx(&full_bar[stage], 2 * tok_bytes);
+            }
+            tma_load_2d_pair_hint(sa + kPairOperandBytes, tx, &full_bar[stage], kb * kTileK, trow,
+                                  pol_x);
           }
-          tma_load_2d_pair_hint(sa + kPairOperandBytes, tx, &full_bar[stage], kb * kTileK, trow,
-                                pol_x);
           if (++stage == kPairStages) {
             stage = 0;
             phase ^= 1u;
@@ -243,7 +238,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
   } else if (MX && warp == kPairThreads / 32 + kDequantWarps) {
     // raw-weight producer: one bulk copy (packed codes + scales of 128 rows x 64 k) per
     // K block into a ring deep enough to cover HBM latency at HBM bandwidth
-    if (lane == 0) {
+    {
       int rs = 0;
       uint32_t rphase = 0;
       bool ok = true;
@@ -260,9 +255,11 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(&raw_full[rs], kRawStageBytes);
-          bulk_load(raw_ring + rs * kRawStageBytes, g.wq + (blk0 + kb) * kRawStageBytes,
-                    kRawStageBytes, &raw_full[rs]);
+          if (elect_one()) {
+            mbar_arrive_expect_tx(&raw_full[rs], kRawStageBytes);
+            bulk_load(raw_ring + rs * kRawStageBytes, g.wq + (blk0 + kb) * kRawStageBytes,
+                      kRawStageBytes, &raw_full[rs]);
+          }
           if (++rs == kRawStages) {
             rs = 0;
             rphase ^= 1u;
@@ -271,7 +268,8 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && rank == 0) {
+    // the whole warp walks the ring (every lane polls the barriers); one elected lane issues
+    if (rank == 0) {
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -300,17 +298,19 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
           const uint32_t sa = smem_u32(smem + stage * kPairStageBytes);
           const uint64_t da = umma_smem_desc_sw128(sa);
           const uint64_t db = umma_smem_desc_sw128(sa + kPairOperandBytes);
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < kTileK / 16; k++)
-            umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
-          umma_commit_pair(&empty_bar[stage], 3);  // frees the stage in both CTAs
+            for (int k = 0; k < kTileK / 16; k++)
+              umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_commit_pair(&empty_bar[stage], 3);  // frees the stage in both CTAs
+          }
           if (++stage == kPairStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!ok) break;
-        umma_commit_pair(&tfull_bar[acc], 3);  // accumulator ready in both CTAs
+        if (elect_one()) umma_commit_pair(&tfull_bar[acc], 3);  // accumulator ready in both CTAs
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
@@ -325,7 +325,6 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
     const int grp = dw / kWarpsPerBlock, sub = dw - grp * kWarpsPerBlock;
     const int my_tiles = first_tile < total_tiles ? (total_tiles - first_tile + ncl - 1) / ncl : 0;
     const int total_kb = my_tiles * kb_count;
-    const uint32_t *lutl = lut + (lane & (LUTREP - 1));
     constexpr int kChunkIters = 8 / kWarpsPerBlock;
     if (grp < kPairStages) {
       const int stage = grp;
@@ -349,23 +348,39 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
             const int c = (sub * kChunkIters + i) * 32 + lane;
             const int wr = c >> 1, hf = c & 1;
             const uint4 q0 = *reinterpret_cast<const uint4 *>(rq + c * 16);
-            uint32_t sc = rq[kRawCodeBytes + c];
-            // codes come out of the table as bf16 values; times 2^(s-127), exact
-            sc = sc ? (sc << 7) : 0x0040u;  // e8m0 0 = 2^-127, a bf16 subnormal
-            const uint32_t mul = sc | (sc << 16);
+            const uint32_t sc = rq[kRawCodeBytes + c];
+            // the bit trick leaves code * 2^-126; times 2^126 * 2^(s-127) = 2^(s-1), exact,
+            // in one multiply while that factor is a bf16 (s <= 128), else in two
+            const uint32_t s1 = sc < 128u ? sc : 128u;
+            const uint32_t m1 = (s1 + 126u) << 7;
+            const uint32_t mul = m1 | (m1 << 16);
             unsigned char *row = slot + wr * 128;
             const uint32_t words[4] = {q0.x, q0.y, q0.z, q0.w};
+            uint4 o[4];
 #pragma unroll
             for (int j = 0; j < 4; j++) {  // 8 elements (one packed word) -> one 16-byte chunk
               const uint32_t w = words[j];
-              uint4 o;
-              o.x = bf16x2_mul(lutl[(w & 0xffu) * LUTREP], mul);
-              o.y = bf16x2_mul(lutl[((w >> 8) & 0xffu) * LUTREP], mul);
-              o.z = bf16x2_mul(lutl[((w >> 16) & 0xffu) * LUTREP], mul);
-              o.w = bf16x2_mul(lutl[(w >> 24) * LUTREP], mul);
-              // 128-byte swizzle: 16-byte chunk j of row r sits at chunk j ^ (r & 7)
-              *reinterpret_cast<uint4 *>(row + (((hf * 4 + j) ^ (wr & 7)) << 4)) = o;
+              const uint32_t ev = w & 0x0F0F0F0Fu, od = (w >> 4) & 0x0F0F0F0Fu;
+              // byte b of w = elements 2b (low nibble) and 2b + 1: one bf16 pair
+              o[j].x = bf16x2_mul(e2m1_pair_to_bf16x2_raw(__byte_perm(ev, od, 0x4400)), mul);
+              o[j].y = bf16x2_mul(e2m1_pair_to_bf16x2_raw(__byte_perm(ev, od, 0x5511)), mul);
+              o[j].z = bf16x2_mul(e2m1_pair_to_bf16x2_raw(__byte_perm(ev, od, 0x6622)), mul);
+              o[j].w = bf16x2_mul(e2m1_pair_to_bf16x2_raw(__byte_perm(ev, od, 0x7733)), mul);
             }
+            if (sc > 128u) {  // (never in real checkpoints) the rest of the scale
+              const uint32_t m2 = (sc - 1u) << 7, mul2 = m2 | (m2 << 16);
+#pragma unroll
+              for (int j = 0; j < 4; j++) {
+                o[j].x = bf16x2_mul(o[j].x, mul2);
+                o[j].y = bf16x2_mul(o[j].y, mul2);
+                o[j].z = bf16x2_mul(o[j].z, mul2);
+                o[j].w = bf16x2_mul(o[j].w, mul2);
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+              // 128-byte swizzle: 16-byte chunk j of row r sits at chunk j ^ (r & 7)
+              *reinterpret_cast<uint4 *>(row + (((hf * 4 + j) ^ (wr & 7)) << 4)) = o[j];
           }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -507,14 +522,14 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
   }
 }
 
-template <int EPI, int STAGES, bool MX, int TOKB, int RAWS, int LUTREP>
+template <int EPI, int STAGES, bool MX, int TOKB, int RAWS>
 static cudaError_t launch_pair_stages(int num_sms, long long *launches, const CUtensorMap &tw,
                                       const CUtensorMap *tx, const GemmArgs &g,
                                       cudaStream_t stream, bool dependent = false) {
   const size_t smem = 1024 + STAGES * (kPairOperandBytes + TOKB * kTileK * 2) + kPairBarrierBytes +
                       PairStage<EPI>::kTotalBytes +
-                      (MX ? RAWS * kRawStageBytes + 1024 * LUTREP : 0);
-  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_pair_kernel<EPI, STAGES, MX, TOKB, RAWS, LUTREP>,
+                      (MX ? RAWS * kRawStageBytes : 0);
+  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_pair_kernel<EPI, STAGES, MX, TOKB, RAWS>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg = {};
@@ -532,7 +547,7 @@ static cudaError_t launch_pair_stages(int num_sms, long long *launches, const CU
   cfg.attrs = attr;
   cfg.numAttrs = dependent ? 2 : 1;
   if (launches) ++*launches;
-  return cudaLaunchKernelEx(&cfg, grouped_gemm_pair_kernel<EPI, STAGES, MX, TOKB, RAWS, LUTREP>, tw, tx[0], tx[1], tx[2],
+  return cudaLaunchKernelEx(&cfg, grouped_gemm_pair_kernel<EPI, STAGES, MX, TOKB, RAWS>, tw, tx[0], tx[1], tx[2],
                             g);
 }
 
@@ -541,16 +556,17 @@ template <int EPI>
 static cudaError_t launch_pair(gptoss_moe *h, const CUtensorMap &tw, const CUtensorMap *tx,
                                const GemmArgs &g, cudaStream_t stream) {
   const bool dep = h->opt_dependent_launch != 0;
-  // MXFP4: the raw ring takes the room of two operand stages; decode-sized batches run
-  // with 64-token tiles, whose small token slots leave room for one code table per bank
+  // MXFP4: four operand stages, each filled by two of the eight dequantising warps; the packed
+  // weights wait in the raw ring, which is what covers HBM latency (24 x 4.25 KB per CTA with
+  // the small token slots of decode-sized batches, 12 beside full-width token slots)
   if (h->cfg.weight_format == GPTOSS_WEIGHTS_MXFP4) {
     if (h->cur_tile_rows == 64)
-      return launch_pair_stages<EPI, 6, true, 32, 12, 16>(h->num_sms, &h->launches, tx[0], tx, g,
-                                                          stream, dep);
-    return launch_pair_stages<EPI, 4, true, 128, 12, 1>(h->num_sms, &h->launches, tx[0], tx, g,
-                                                        stream, dep);
+      return launch_pair_stages<EPI, 4, true, 32, 24>(h->num_sms, &h->launches, tx[0], tx, g,
+                                                      stream, dep);
+    return launch_pair_stages<EPI, 4, true, 128, 12>(h->num_sms, &h->launches, tx[0], tx, g,
+                                                     stream, dep);
   }
-  return launch_pair_stages<EPI, 6, false, 128, 0, 1>(h->num_sms, &h->launches, tw, tx, g, stream,
+  return launch_pair_stages<EPI, 6, false, 128, 0>(h->num_sms, &h->launches, tw, tx, g, stream,
                                                       dep);
 }
 
@@ -592,8 +608,8 @@ cudaError_t launch_linear_pair(int num_sms, const CUtensorMap &tw, const CUtenso
                                const GemmArgs &g, cudaStream_t stream, long long *launches,
                                bool f32_out) {
   if (f32_out)
-    return launch_pair_stages<kEpiF32, 4, false, 128, 0, 1>(num_sms, launches, tw, tx, g, stream);
-  return launch_pair_stages<kEpiDown, 6, false, 128, 0, 1>(num_sms, launches, tw, tx, g, stream);
+    return launch_pair_stages<kEpiF32, 4, false, 128, 0>(num_sms, launches, tw, tx, g, stream);
+  return launch_pair_stages<kEpiDown, 6, false, 128, 0>(num_sms, launches, tw, tx, g, stream);
 }
 
 cudaError_t launch_down_pair(gptoss_moe *h, int layer, cudaStream_t stream) {

@@ -151,7 +151,7 @@ router_topk_kernel(const __grid_constant__ CUtensorMap tmap_t,
   const int sl = warp >> 1;  // expert slice: experts sl*NT*8 .. +NT*8-1
 
   if (warp == kRtComputeWarps) {
-    if (lane == 0) {
+    {
       int stage = 0;
       uint32_t phase = 0;
       for (int kc = kc_lo; kc < kc_hi; kc++) {
@@ -161,9 +161,11 @@ router_topk_kernel(const __grid_constant__ CUtensorMap tmap_t,
           break;
         }
         unsigned char *dst = smem + stage * kStageBytes;
-        mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
-        tma_load_2d(dst, &tmap_t, &full_bar[stage], kc * kRtKC, tok0);
-        tma_load_2d(dst + kTokBytes, &tmap_w, &full_bar[stage], kc * kRtKC, 0);
+        if (elect_one()) {
+          mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
+          tma_load_2d(dst, &tmap_t, &full_bar[stage], kc * kRtKC, tok0);
+          tma_load_2d(dst + kTokBytes, &tmap_w, &full_bar[stage], kc * kRtKC, 0);
+        }
         if (++stage == kRtStages) {
           stage = 0;
           phase ^= 1u;
@@ -453,8 +455,11 @@ router_tx_kernel(const __grid_constant__ CUtensorMap tmap_t,
   grid_dependency_wait();
   grid_launch_dependents();
 
+  // the producer and the MMA warp walk the ring whole (every lane polls the barriers) and
+  // one elected lane issues: a loop that only one lane runs makes every load and MMA several
+  // times dearer to issue
   if (warp == 0) {
-    if (lane == 0) {
+    {
       int stage = 0;
       uint32_t phase = 0;
       const uint32_t bytes = EM * kRxTileBytes + ntok * kRtRowBytes;
@@ -465,11 +470,13 @@ router_tx_kernel(const __grid_constant__ CUtensorMap tmap_t,
           break;
         }
         unsigned char *dst = smem + stage * kStageBytes;
-        mbar_arrive_expect_tx(&full_bar[stage], bytes);
-        tma_load_2d(dst + EM * kRxTileBytes, &tmap_t, &full_bar[stage], kc * kRtKC, tok0);
+        if (elect_one()) {
+          mbar_arrive_expect_tx(&full_bar[stage], bytes);
+          tma_load_2d(dst + EM * kRxTileBytes, &tmap_t, &full_bar[stage], kc * kRtKC, tok0);
 #pragma unroll
-        for (int m = 0; m < EM; m++)
-          tma_load_2d(dst + m * kRxTileBytes, &tmap_wr, &full_bar[stage], 0, (m * nk + kc) * 32);
+          for (int m = 0; m < EM; m++)
+            tma_load_2d(dst + m * kRxTileBytes, &tmap_wr, &full_bar[stage], 0, (m * nk + kc) * 32);
+        }
         if (++stage == kStages) {
           stage = 0;
           phase ^= 1u;
@@ -477,7 +484,7 @@ router_tx_kernel(const __grid_constant__ CUtensorMap tmap_t,
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {
       const uint32_t idesc = umma_idesc_bf16(128, ntok);
       int stage = 0;
       uint32_t phase = 0;
@@ -494,21 +501,23 @@ router_tx_kernel(const __grid_constant__ CUtensorMap tmap_t,
         // that wait, not the tensor pipe, sets the pace: the chunks alternate between
         // kRxAccs accumulators, added up when the logits are read
         const int a = kc % kRxAccs;
+        if (elect_one()) {
 #pragma unroll
-        for (int m = 0; m < EM; m++) {
-          const uint64_t da = umma_smem_desc_sw128(sa + m * kRxTileBytes);
+          for (int m = 0; m < EM; m++) {
+            const uint64_t da = umma_smem_desc_sw128(sa + m * kRxTileBytes);
 #pragma unroll
-          for (int k = 0; k < kRtKC / 16; k++)
-            umma_bf16(tmem_base + (a * EM + m) * kAccCols, da + 2 * k, db + 2 * k, idesc,
-                      (kc >= kRxAccs || k > 0) ? 1u : 0u);
+            for (int k = 0; k < kRtKC / 16; k++)
+              umma_bf16(tmem_base + (a * EM + m) * kAccCols, da + 2 * k, db + 2 * k, idesc,
+                        (kc >= kRxAccs || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
         }
-        umma_commit(&empty_bar[stage]);
         if (++stage == kStages) {
           stage = 0;
           phase ^= 1u;
         }
       }
-      umma_commit(tfull_bar);
+      if (elect_one()) umma_commit(tfull_bar);
     }
   } else {
     // accumulator -> logits [token][expert] in shared memory, bias added

@@ -13,7 +13,8 @@ from gpt_oss_b200 import synth
 pytestmark = pytest.mark.gpu
 
 
-def _case(pkg, oracle, T, H, IM, E, K, inactive=0, on_device=False, scale_range=(119, 123), seed=0):
+def _case(pkg, oracle, T, H, IM, E, K, inactive=0, on_device=False, scale_range=(119, 123), seed=0,
+          input_scale=0.25):
     import torch
 
     shape = synth.MoeShape("mx", T, H, IM, E, K, 7.0, 500 + seed)
@@ -25,7 +26,7 @@ def _case(pkg, oracle, T, H, IM, E, K, inactive=0, on_device=False, scale_range=
     d["w_mlp2"] = synth.mxfp4_dequant(b2, s2)
     # N(0,1) inputs against weights of magnitude up to 6 * 2^-4 make huge activations;
     # scale the inputs so pre-activations stay around the clamp
-    d["t"] = synth.bf16_round(d["t"] * np.float32(0.25))
+    d["t"] = synth.bf16_round(d["t"] * np.float32(input_scale))
     want = oracle.moe_layer(d, shape)
 
     dev = torch.device("cuda:0")
@@ -75,3 +76,9 @@ def test_mxfp4_layer_against_oracle(pkg, oracle, T, H, IM, E, K, inactive):
 def test_mxfp4_device_side_upload_and_all_scale_codes(pkg, oracle):
     # scales over a wide range, including small exponents whose values are bf16 subnormals' neighbours
     _case(pkg, oracle, 100, 128, 96, 8, 4, on_device=True, scale_range=(110, 126), seed=3)
+
+
+def test_mxfp4_scales_above_one(pkg, oracle):
+    # block scales up to 2^4 (e8m0 131): weights up to 96, past the exponent one bf16 multiply
+    # of the expansion can carry; inputs scaled down to keep the pre-activations near the clamp
+    _case(pkg, oracle, 96, 128, 96, 8, 4, scale_range=(125, 131), seed=5, input_scale=2.0 ** -8)
