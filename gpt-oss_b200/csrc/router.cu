@@ -375,16 +375,19 @@ router_topk_kernel(const __grid_constant__ CUtensorMap tmap_t,
 //
 // Warp 0 = TMA producer, warp 1 = TMEM allocation + MMA issue (tcgen05.mma M=128, N=tokens,
 // K=16, bf16 -> fp32 in TMEM).  Then warps 2-5 read the accumulator (a TMEM lane is an
-// expert, a column a token), add the bias and transpose it into shared memory, and ONE
-// THREAD PER TOKEN selects: it walks its token's row keeping the best K+1 logits sorted in
-// registers (a warp per token with shuffles, as the mma.sync kernel does it, costs about a
-// thousand dependent instructions per token and was 30 of that kernel's 45 microseconds).
+// expert, a column a token), add the bias and transpose it into shared memory, and FOUR
+// LANES PER TOKEN select: each keeps the best K+1 of its quarter of the row sorted in
+// registers by a branch-free insertion, and the four lists meet in two shuffle steps (a
+// warp per token with shuffles, as the mma.sync kernel does it, costs about a thousand
+// dependent instructions per token and was 30 of that kernel's 45 microseconds).  Measured
+// on one CTA of the 120b shape: K loop 11 us (the CTA's ingest of the router matrix from
+// L2), readout 0.9, selection 1.4.
 //
 // Exact selection: a token whose best K+1 logits contain two neighbours closer than the
 // guard lists every expert within twice the guard of its K-th value; the CTA's warps then
 // recompute the listed logits the way the reference's CPU matmul does (float products
-// summed in double), one (token, expert) pair per warp at a time, and the token's thread
-// selects again from the corrected row.  The guard is tighter than the mma.sync kernel's:
+// summed in double), one (token, expert) pair per warp at a time, and the token's lanes
+// select again from the corrected row.  The guard is tighter than the mma.sync kernel's:
 // the tensor core's fp32 accumulation was measured within 3e-6 of the reference's double
 // sums at H = 2880.
 constexpr int kRxThreads = 192;
@@ -394,7 +397,7 @@ constexpr int kRxPairs = 1024;                   // (token, expert) pairs a CTA 
 constexpr float kTieGuardTc = 3e-5f;
 constexpr int kRxAccs = 2;  // accumulators the K chunks alternate between
 
-// NT = 32-expert groups (EPAD = 32 * NT); NS = length of the sorted list a thread keeps
+// NT = 32-expert groups (EPAD = 32 * NT); NS = length of the sorted list a lane keeps
 template <int NT, int NS>
 __global__ void __launch_bounds__(kRxThreads, 1)
 router_tx_kernel(const __grid_constant__ CUtensorMap tmap_t,
@@ -405,7 +408,9 @@ router_tx_kernel(const __grid_constant__ CUtensorMap tmap_t,
                  float *__restrict__ logits_out, int exact_ties, int *status) {
   constexpr int EPAD = 32 * NT;
   constexpr int EM = EPAD > 128 ? 2 : 1;           // 128-row MMA tiles of router rows
-  constexpr int kPitch = EPAD + 1;                  // logits row pitch: a thread per row, no conflicts
+  // logits row pitch, = 4 (mod 32): the four lanes of a row and the eight rows of a warp read
+  // 32 different banks; the accumulator readout writes consecutive experts of one row
+  constexpr int kPitch = EPAD + 4;
   constexpr int kTokBytes = kRxMaxTok * kRtRowBytes;            // 8 KB slot for up to 64 tokens
   constexpr int kStageBytes = EM * kRxTileBytes + kTokBytes;
   constexpr int kStages = EM == 1 ? 8 : 4;
@@ -555,112 +560,141 @@ router_tx_kernel(const __grid_constant__ CUtensorMap tmap_t,
   }
   __syncthreads();
 
-  // ---- selection: thread `tid` owns token row `tid`
-  const int tok = tok0 + tid;
-  const bool mine = tid < ntok && tok < T;
-  const bool live = mine && !(pos && pos[tok] < 0);
+  // ---- selection: four lanes per token row, kRowsPerPass rows at a time.  Lane s of a row
+  // keeps the best NS of the logits e = s, s + 4, ... (sorted: value descending, lower index
+  // first on equal values) by branch-free insertion, then the four lists meet in two
+  // exchange steps, after which every lane of the row holds the row's best NS.
+  constexpr int kG = 4;
+  constexpr int kRowsPerPass = kRxThreads / kG;
+  constexpr int kPasses = (kRxMaxTok + kRowsPerPass - 1) / kRowsPerPass;
+  const int sub = tid & (kG - 1);
   const int rounds_chk = (K + 1 <= E) ? K + 1 : E;
-  const float *my = lg + tid * kPitch;
   float bv[NS];
   int bi[NS];
-  // the best NS logits of the row, sorted (value descending, lower index first on equal values)
-  auto scan_row = [&]() {
+  // v enters the sorted list where it belongs; all the comparisons are independent of each
+  // other and every slot is rewritten from the old list, so an insertion is three
+  // instructions deep (the list is sorted: once v beats a slot it beats the ones after it).
+  // The comparisons are combined with | and &, not || and &&: the short-circuit forms compile
+  // to a branch per slot, and the selection then takes 7 us instead of 1.4.
+  auto insert = [&](float v, int i) {
+    bool up[NS];
+#pragma unroll
+    for (int p = 0; p < NS; p++) up[p] = (v > bv[p]) | ((v == bv[p]) & (i < bi[p]));
+#pragma unroll
+    for (int p = NS - 1; p > 0; p--) {
+      bv[p] = up[p] ? (up[p - 1] ? bv[p - 1] : v) : bv[p];
+      bi[p] = up[p] ? (up[p - 1] ? bi[p - 1] : i) : bi[p];
+    }
+    bv[0] = up[0] ? v : bv[0];
+    bi[0] = up[0] ? i : bi[0];
+  };
+  auto scan_row = [&](const float *my) {
 #pragma unroll
     for (int p = 0; p < NS; p++) {
       bv[p] = -INFINITY;
       bi[p] = 0x7fffffff;
     }
-    // eight loads in flight before the first compare: the row walk is a chain of
-    // shared-memory latencies otherwise
-    for (int e0 = 0; e0 < E; e0 += 8) {
+    // eight loads in flight before the first compare
+    for (int j0 = 0; j0 * kG < E; j0 += 8) {
       float v8[8];
 #pragma unroll
-      for (int u = 0; u < 8; u++) v8[u] = e0 + u < E ? my[e0 + u] : -INFINITY;
+      for (int u = 0; u < 8; u++) {
+        const int e = sub + kG * (j0 + u);
+        v8[u] = e < E ? my[e] : -INFINITY;
+      }
 #pragma unroll
       for (int u = 0; u < 8; u++) {
-        const float v = v8[u];
-        if (v > bv[NS - 1]) {
-          float cv = v;
-          int ci = e0 + u;
-          bool carrying = false;
-#pragma unroll
-          for (int p = 0; p < NS; p++) {
-            if (carrying || cv > bv[p]) {
-              const float tv = bv[p];
-              const int ti = bi[p];
-              bv[p] = cv;
-              bi[p] = ci;
-              cv = tv;
-              ci = ti;
-              carrying = true;
-            }
-          }
-        }
+        const int e = sub + kG * (j0 + u);
+        insert(v8[u], e < E ? e : 0x7fffffff);  // (-inf, 0x7fffffff) never enters the list
       }
+    }
+#pragma unroll
+    for (int m = 1; m < kG; m <<= 1) {
+      float ov[NS];
+      int oi[NS];
+#pragma unroll
+      for (int p = 0; p < NS; p++) {
+        ov[p] = __shfl_xor_sync(0xffffffffu, bv[p], m);
+        oi[p] = __shfl_xor_sync(0xffffffffu, bi[p], m);
+      }
+#pragma unroll
+      for (int p = 0; p < NS; p++) insert(ov[p], oi[p]);
     }
   };
   // softmax over the K selected values (run.cpp:336-354) and the token's outputs
-  auto write_out = [&]() {
-    float ev[NS];
-    float sum = 0.f;
+  auto write_out = [&](int tok, const float *my) {
+    if (sub == 0) {
+      float ev[NS];
+      float sum = 0.f;
 #pragma unroll
-    for (int r = 0; r < NS; r++) {
-      if (r < K) {
-        ev[r] = expf(bv[r] - bv[0]);
-        sum += ev[r];
+      for (int r = 0; r < NS; r++) {
+        if (r < K) {
+          ev[r] = expf(bv[r] - bv[0]);
+          sum += ev[r];
+        }
       }
-    }
 #pragma unroll
-    for (int r = 0; r < NS; r++) {
-      if (r < K) {
-        topk_i[static_cast<size_t>(tok) * K + r] = bi[r];
-        topk_v[static_cast<size_t>(tok) * K + r] = ev[r] / sum;
+      for (int r = 0; r < NS; r++) {
+        if (r < K) {
+          topk_i[static_cast<size_t>(tok) * K + r] = bi[r];
+          topk_v[static_cast<size_t>(tok) * K + r] = ev[r] / sum;
+        }
       }
     }
     if (logits_out)
-      for (int e = 0; e < E; e++) logits_out[static_cast<size_t>(tok) * E + e] = my[e];
+      for (int e = sub; e < E; e += kG) logits_out[static_cast<size_t>(tok) * E + e] = my[e];
   };
 
-  bool flagged = false;
-  if (live) {
-    scan_row();
-    if (exact_ties) {
+  bool flagged[kPasses];
+#pragma unroll
+  for (int pass = 0; pass < kPasses; pass++) {
+    flagged[pass] = false;
+    if (pass * kRowsPerPass >= ntok) continue;  // (the same for the whole CTA)
+    const int row = pass * kRowsPerPass + (tid >> 2);
+    const int tok = tok0 + row;
+    const bool mine = row < ntok && tok < T;
+    const bool live = mine && !(pos && pos[tok] < 0);
+    // rows past the tile are scanned like the others (the lanes stay together for the
+    // exchanges) but from a row that exists, and nothing of theirs is kept
+    const float *my = lg + (row < kRxMaxTok ? row : kRxMaxTok - 1) * kPitch;
+    scan_row(my);
+    bool flag = false;
+    if (live && exact_ties) {
 #pragma unroll
       for (int r = 0; r + 1 < NS; r++)
-        if (r + 1 < rounds_chk && bv[r] - bv[r + 1] < kTieGuardTc) flagged = true;
+        if (r + 1 < rounds_chk && bv[r] - bv[r + 1] < kTieGuardTc) flag = true;
     }
-    if (flagged) {
-      // list the contenders: everything within twice the guard of the K-th value
-      float kth = bv[0];
+    // list the contenders of a flagged row: everything within twice the guard of the K-th
+    // value, each lane its own quarter of the row
+    float kth = bv[0];
 #pragma unroll
-      for (int r = 1; r < NS; r++)
-        if (r < K) kth = bv[r];
-      const float thr = kth - 2.f * kTieGuardTc;
-      bool full = false;
-      for (int e0 = 0; e0 < E && !full; e0 += 8) {
-        float v8[8];
-#pragma unroll
-        for (int u = 0; u < 8; u++) v8[u] = e0 + u < E ? my[e0 + u] : -INFINITY;
-#pragma unroll
-        for (int u = 0; u < 8; u++) {
-          if (v8[u] >= thr && !full) {
-            const int at = atomicAdd(n_pairs, 1);
-            if (at < kRxPairs)
-              pairs[at] = (tid << 16) | (e0 + u);
-            else
-              full = true;
-          }
+    for (int r = 1; r < NS; r++)
+      if (r < K) kth = bv[r];
+    const float thr = kth - 2.f * kTieGuardTc;
+    bool full = false;
+    if (flag) {
+      for (int e = sub; e < E && !full; e += kG) {
+        if (my[e] >= thr) {
+          const int at = atomicAdd(n_pairs, 1);
+          if (at < kRxPairs)
+            pairs[at] = (row << 16) | e;
+          else
+            full = true;
         }
       }
-      // the list is full (hundreds of near ties in one tile): this row is recomputed whole
-      if (full) whole[atomicAdd(n_whole, 1)] = tid;
-    } else {
-      write_out();
     }
-  } else if (mine) {
-    for (int r = 0; r < K; r++) {
-      topk_i[static_cast<size_t>(tok) * K + r] = -1;
-      topk_v[static_cast<size_t>(tok) * K + r] = 0.f;
+    // the list is full (hundreds of near ties in one tile): the row is recomputed whole
+#pragma unroll
+    for (int m = 1; m < kG; m <<= 1) full |= __shfl_xor_sync(0xffffffffu, full ? 1 : 0, m) != 0;
+    if (full && sub == 0) whole[atomicAdd(n_whole, 1)] = row;
+    flagged[pass] = flag;
+    if (live && !flag) {
+      write_out(tok, my);
+    } else if (mine && !live && sub == 0) {
+      for (int r = 0; r < K; r++) {
+        topk_i[static_cast<size_t>(tok) * K + r] = -1;
+        topk_v[static_cast<size_t>(tok) * K + r] = 0.f;
+      }
     }
   }
   __syncthreads();
@@ -684,9 +718,16 @@ router_tx_kernel(const __grid_constant__ CUtensorMap tmap_t,
       }
     }
     __syncthreads();
-    if (flagged) {
-      scan_row();
-      write_out();
+#pragma unroll
+    for (int pass = 0; pass < kPasses; pass++) {
+      if (pass * kRowsPerPass >= ntok) continue;
+      const int row = pass * kRowsPerPass + (tid >> 2);
+      const float *my = lg + (row < kRxMaxTok ? row : kRxMaxTok - 1) * kPitch;
+      // a warp rescans when one of its eight rows was flagged
+      if (__any_sync(0xffffffffu, flagged[pass])) {
+        scan_row(my);
+        if (flagged[pass]) write_out(tok0 + row, my);
+      }
     }
   }
 
