@@ -59,7 +59,7 @@ struct PairStage {
 };
 
 // MXFP4 weights (MX = true): a producer warp bulk-copies the packed codes (4 KB) and
-// scales (256 B) of the CTA's 128 rows x 64 k into a raw ring; eight extra warps expand
+// scales (256 B) of the CTA's 128 rows x 64 k into a raw ring; sixteen extra warps expand
 // them to bf16 straight into the operand ring, in the 128-byte-swizzled layout TMA would
 // have written, and count as arrivals on the even CTA's full barrier beside the token
 // tiles' bytes.  The expansion is register arithmetic only (a table in shared memory cost
@@ -67,14 +67,24 @@ struct PairStage {
 constexpr int kPairBarrierBytes = 1024;  // mbarriers, TMEM address holder, abort flag
 constexpr int kRawCodeBytes = 128 * 32;
 constexpr int kRawStageBytes = kRawCodeBytes + 128 * 2;
-constexpr int kDequantWarps = 8;  // two threads per weight row
+// four warps per operand stage: the expansion is bound by the integer pipe and by its own
+// latencies, and 16 warps measured 10% faster than 8 (72 registers per thread, no spills)
+constexpr int kDequantWarps = 16;
 
-// two e2m1 codes, one in bits 0-3 and one in bits 16-19 (other bits: anything) -> two bf16
+// two e2m1 codes, one in bits 0-3 and one in bits 16-19 (all other bits zero) -> two bf16
 // whose value is code * 2^-126: sign to bit 15 of its half, the three magnitude bits to
 // exponent bits 0-1 and mantissa bit 6 (magnitude code 1 becomes the bf16 subnormal
-// 2^-127, which bf16 multiplies take at full rate)
+// 2^-127, which bf16 multiplies take at full rate).  One multiply makes both shifted
+// copies (by 6 and by 12; they cannot overlap), one mask keeps the bits that matter.
 __device__ __forceinline__ uint32_t e2m1_pair_to_bf16x2_raw(uint32_t u) {
-  return ((u << 6) & 0x01C001C0u) | ((u << 12) & 0x80008000u);
+  return (u * 0x1040u) & 0x81C081C0u;
+}
+// prmt.b32: byte i of the result is byte (digit i of sel & 7) of {b, a}; a digit of 8 or more
+// copies that byte's sign bit to all eight bits instead
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
 }
 __device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
   __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162 *>(&a),
@@ -343,7 +353,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
         const unsigned char *rq = raw_ring + rs * kRawStageBytes;
         unsigned char *slot = smem + stage * kPairStageBytes;
         {
-#pragma unroll 2
+#pragma unroll
           for (int i = 0; i < kChunkIters; i++) {
             const int c = (sub * kChunkIters + i) * 32 + lane;
             const int wr = c >> 1, hf = c & 1;
@@ -354,33 +364,33 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
             const uint32_t s1 = sc < 128u ? sc : 128u;
             const uint32_t m1 = (s1 + 126u) << 7;
             const uint32_t mul = m1 | (m1 << 16);
-            unsigned char *row = slot + wr * 128;
+            // 128-byte swizzle: 16-byte chunk j of row r sits at chunk j ^ (r & 7)
+            unsigned char *row = slot + wr * 128 + (((hf * 4) ^ (wr & 4)) << 4);
+            const int x3 = wr & 3;
             const uint32_t words[4] = {q0.x, q0.y, q0.z, q0.w};
-            uint4 o[4];
+            // (a scale above 2^1 is in no real checkpoint: one vote per chunk keeps the second
+            // multiply out of the common path without a branch per lane)
+            const bool two = __any_sync(0xffffffffu, sc > 128u);
+            const uint32_t m2 = (sc > 128u ? sc - 1u : 127u) << 7, mul2 = m2 | (m2 << 16);
 #pragma unroll
             for (int j = 0; j < 4; j++) {  // 8 elements (one packed word) -> one 16-byte chunk
               const uint32_t w = words[j];
               const uint32_t ev = w & 0x0F0F0F0Fu, od = (w >> 4) & 0x0F0F0F0Fu;
-              // byte b of w = elements 2b (low nibble) and 2b + 1: one bf16 pair
-              o[j].x = bf16x2_mul(e2m1_pair_to_bf16x2_raw(__byte_perm(ev, od, 0x4400)), mul);
-              o[j].y = bf16x2_mul(e2m1_pair_to_bf16x2_raw(__byte_perm(ev, od, 0x5511)), mul);
-              o[j].z = bf16x2_mul(e2m1_pair_to_bf16x2_raw(__byte_perm(ev, od, 0x6622)), mul);
-              o[j].w = bf16x2_mul(e2m1_pair_to_bf16x2_raw(__byte_perm(ev, od, 0x7733)), mul);
-            }
-            if (sc > 128u) {  // (never in real checkpoints) the rest of the scale
-              const uint32_t m2 = (sc - 1u) << 7, mul2 = m2 | (m2 << 16);
-#pragma unroll
-              for (int j = 0; j < 4; j++) {
-                o[j].x = bf16x2_mul(o[j].x, mul2);
-                o[j].y = bf16x2_mul(o[j].y, mul2);
-                o[j].z = bf16x2_mul(o[j].z, mul2);
-                o[j].w = bf16x2_mul(o[j].w, mul2);
+              // byte b of w = elements 2b (low nibble) and 2b + 1: one bf16 pair; the selector
+              // digits 8 and up give zero bytes (the sign bit of a nibble-sized byte)
+              uint4 o;
+              o.x = bf16x2_mul(e2m1_pair_to_bf16x2_raw(prmt(ev, od, 0xC480u)), mul);
+              o.y = bf16x2_mul(e2m1_pair_to_bf16x2_raw(prmt(ev, od, 0xD591u)), mul);
+              o.z = bf16x2_mul(e2m1_pair_to_bf16x2_raw(prmt(ev, od, 0xE6A2u)), mul);
+              o.w = bf16x2_mul(e2m1_pair_to_bf16x2_raw(prmt(ev, od, 0xF7B3u)), mul);
+              if (two) {
+                o.x = bf16x2_mul(o.x, mul2);
+                o.y = bf16x2_mul(o.y, mul2);
+                o.z = bf16x2_mul(o.z, mul2);
+                o.w = bf16x2_mul(o.w, mul2);
               }
+              *reinterpret_cast<uint4 *>(row + ((j ^ x3) << 4)) = o;
             }
-#pragma unroll
-            for (int j = 0; j < 4; j++)
-              // 128-byte swizzle: 16-byte chunk j of row r sits at chunk j ^ (r & 7)
-              *reinterpret_cast<uint4 *>(row + (((hf * 4 + j) ^ (wr & 7)) << 4)) = o[j];
           }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -556,7 +566,7 @@ template <int EPI>
 static cudaError_t launch_pair(gptoss_moe *h, const CUtensorMap &tw, const CUtensorMap *tx,
                                const GemmArgs &g, cudaStream_t stream) {
   const bool dep = h->opt_dependent_launch != 0;
-  // MXFP4: four operand stages, each filled by two of the eight dequantising warps; the packed
+  // MXFP4: four operand stages, each filled by four of the sixteen dequantising warps; the packed
   // weights wait in the raw ring, which is what covers HBM latency (24 x 4.25 KB per CTA with
   // the small token slots of decode-sized batches, 12 beside full-width token slots)
   if (h->cfg.weight_format == GPTOSS_WEIGHTS_MXFP4) {
