@@ -656,8 +656,10 @@ def run_ours(args, shape):
 
 # ratio of measured DRAM traffic (ncu dram__bytes_read.sum + dram__bytes_write.sum) to the
 # algorithmic bytes of the gate_up launch, per workload the capture covers
-TRAFFIC_RATIO = {"gpt-oss-20b-moe-layer-T7168": 377.2 / 348.0,
-                 "gpt-oss-20b-moe-layer-8experts-T1792": 377.2 / 348.0}
+TRAFFIC_RATIO = {"gpt-oss-120b-moe-layer-T6144": 559.6 / 566.2,
+                 "gpt-oss-120b-moe-layer-16experts-T768": 559.6 / 566.2,
+                 "gpt-oss-20b-moe-layer-T7168": 401.6 / 348.0,
+                 "gpt-oss-20b-moe-layer-8experts-T1792": 401.6 / 348.0}
 TRAFFIC_SOURCE = ("ncu dram__bytes_read+write of the small-case capture under profiles/ scaled to "
                   "this launch by its algorithmic bytes")
 

@@ -189,26 +189,36 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
       uint32_t phase = 0;
       bool ok = true;
       int e_next = 0, tok0_next = 0, ntok_next = 0;
+      bool sib_next = false;  // the expert has a second token tile, which re-reads its weights
       int tt, wp, tt2, wp2;
-      // weights pass through L2 once: first out; token tiles are re-read by every weight-row
-      // pair of the expert: last out
-      const uint64_t pol_w = g.l2_hints ? l2_policy_evict_first() : l2_policy_normal();
+      auto has_sibling = [&](int t, int e) {
+        return (t + 1 < tt_hi && g.mtile_expert[t + 1] == e) || (t > tt_lo && g.mtile_expert[t - 1] == e);
+      };
+      // an expert's weights pass through L2 once when all its rows fit one token tile: first
+      // out (otherwise the expert's other token tiles, a few tiles further on in the same wave,
+      // read them again: no hint); token tiles are re-read by every weight-row pair of the
+      // expert: last out
+      const uint64_t pol_once = g.l2_hints ? l2_policy_evict_first() : l2_policy_normal();
+      const uint64_t pol_again = l2_policy_normal();
       const uint64_t pol_x = g.l2_hints ? l2_policy_evict_last() : l2_policy_normal();
       if (first_tile < total_tiles) {
         decode_tile(first_tile, w_pairs, tt_lo, &tt, &wp);
         e_next = g.mtile_expert[tt];
         tok0_next = g.mtile_row0[tt];
         ntok_next = g.mtile_rows[tt];
+        sib_next = has_sibling(tt, e_next);
       }
       for (int tile = first_tile; ok && tile < total_tiles; tile += ncl) {
         decode_tile(tile, w_pairs, tt_lo, &tt, &wp);
         const int e = e_next, tok0 = tok0_next, ntok = ntok_next;
+        const uint64_t pol_w = sib_next ? pol_again : pol_once;
         const int tile2 = tile + ncl;
         if (tile2 < total_tiles) {
           decode_tile(tile2, w_pairs, tt_lo, &tt2, &wp2);
           e_next = g.mtile_expert[tt2];
           tok0_next = g.mtile_row0[tt2];
           ntok_next = g.mtile_rows[tt2];
+          sib_next = has_sibling(tt2, e_next);
         }
         const int half_n = ((ntok + 15) & ~15) >> 1;  // token rows each CTA contributes
         const int wrow = e * g.n_cols + wp * 256 + static_cast<int>(rank) * 128;
