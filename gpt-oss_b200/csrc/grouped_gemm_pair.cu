@@ -63,7 +63,8 @@ struct PairStage {
 // them to bf16 straight into the operand ring, in the 128-byte-swizzled layout TMA would
 // have written, and count as arrivals on the even CTA's full barrier beside the token
 // tiles' bytes.  The expansion is register arithmetic only (a table in shared memory cost
-// more shared-memory cycles per K block than the MMAs' own operand reads).
+// more shared-memory cycles per K block than the MMAs' own operand reads): per code pair a
+// mask, a multiply, a mask and the multiply by the block scale.
 constexpr int kPairBarrierBytes = 1024;  // mbarriers, TMEM address holder, abort flag
 constexpr int kRawCodeBytes = 128 * 32;
 constexpr int kRawStageBytes = kRawCodeBytes + 128 * 2;
@@ -71,20 +72,15 @@ constexpr int kRawStageBytes = kRawCodeBytes + 128 * 2;
 // latencies, and 16 warps measured 10% faster than 8 (72 registers per thread, no spills)
 constexpr int kDequantWarps = 16;
 
-// two e2m1 codes, one in bits 0-3 and one in bits 16-19 (all other bits zero) -> two bf16
-// whose value is code * 2^-126: sign to bit 15 of its half, the three magnitude bits to
-// exponent bits 0-1 and mantissa bit 6 (magnitude code 1 becomes the bf16 subnormal
-// 2^-127, which bf16 multiplies take at full rate).  One multiply makes both shifted
-// copies (by 6 and by 12; they cannot overlap), one mask keeps the bits that matter.
+// two e2m1 codes, one in bits 0-3 and one in bits 16-19 (kLow) or in bits 4-7 and 20-23
+// (!kLow), all other bits zero -> two bf16 whose value is code * 2^-126: sign to bit 15 of
+// its half, the three magnitude bits to exponent bits 0-1 and mantissa bit 6 (magnitude
+// code 1 becomes the bf16 subnormal 2^-127, which bf16 multiplies take at full rate).  One
+// multiply makes both shifted copies (by 6 and by 12, or by 2 and by 8; they cannot overlap),
+// one mask keeps the bits that matter.
+template <bool kLow>
 __device__ __forceinline__ uint32_t e2m1_pair_to_bf16x2_raw(uint32_t u) {
-  return (u * 0x1040u) & 0x81C081C0u;
-}
-// prmt.b32: byte i of the result is byte (digit i of sel & 7) of {b, a}; a digit of 8 or more
-// copies that byte's sign bit to all eight bits instead
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-  uint32_t r;
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
-  return r;
+  return (u * (kLow ? 0x1040u : 0x104u)) & 0x81C081C0u;
 }
 __device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
   __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162 *>(&a),
@@ -384,15 +380,14 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
             const uint32_t m2 = (sc > 128u ? sc - 1u : 127u) << 7, mul2 = m2 | (m2 << 16);
 #pragma unroll
             for (int j = 0; j < 4; j++) {  // 8 elements (one packed word) -> one 16-byte chunk
-              const uint32_t w = words[j];
-              const uint32_t ev = w & 0x0F0F0F0Fu, od = (w >> 4) & 0x0F0F0F0Fu;
-              // byte b of w = elements 2b (low nibble) and 2b + 1: one bf16 pair; the selector
-              // digits 8 and up give zero bytes (the sign bit of a nibble-sized byte)
+              // the loader left the word as e0 e2 e4 e6 | e1 e3 e5 e7 (4 bits each, e0 lowest):
+              // elements 2p and 2p + 1 are 16 bits apart
+              const uint32_t w = words[j], w8 = w >> 8;
               uint4 o;
-              o.x = bf16x2_mul(e2m1_pair_to_bf16x2_raw(prmt(ev, od, 0xC480u)), mul);
-              o.y = bf16x2_mul(e2m1_pair_to_bf16x2_raw(prmt(ev, od, 0xD591u)), mul);
-              o.z = bf16x2_mul(e2m1_pair_to_bf16x2_raw(prmt(ev, od, 0xE6A2u)), mul);
-              o.w = bf16x2_mul(e2m1_pair_to_bf16x2_raw(prmt(ev, od, 0xF7B3u)), mul);
+              o.x = bf16x2_mul(e2m1_pair_to_bf16x2_raw<true>(w & 0x000F000Fu), mul);
+              o.y = bf16x2_mul(e2m1_pair_to_bf16x2_raw<false>(w & 0x00F000F0u), mul);
+              o.z = bf16x2_mul(e2m1_pair_to_bf16x2_raw<true>(w8 & 0x000F000Fu), mul);
+              o.w = bf16x2_mul(e2m1_pair_to_bf16x2_raw<false>(w8 & 0x00F000F0u), mul);
               if (two) {
                 o.x = bf16x2_mul(o.x, mul2);
                 o.y = bf16x2_mul(o.y, mul2);

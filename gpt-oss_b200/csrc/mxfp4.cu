@@ -14,6 +14,9 @@
 // CTA pair always owns two), the contraction dimension into K blocks of 64:
 //   tile[expert][block][kblock] = { codes[128 rows][32 bytes], scales[128 rows][2 bytes] }
 // i.e. 4352 contiguous bytes per (block, K block): one bulk copy per stage.
+// Inside every 32-bit word of codes the eight nibbles are reordered from e0 e1 ... e7
+// (element k at bits 4k) to e0 e2 e4 e6 | e1 e3 e5 e7: the two elements of a bf16 pair then
+// sit 16 bits apart, where one mask picks both (grouped_gemm_pair.cu expands them).
 #include "common.cuh"
 #include "engine.h"
 
@@ -43,6 +46,19 @@ mxfp4_tile_codes_kernel(uint8_t *__restrict__ q, const uint8_t *__restrict__ blo
         for (int j = 0; j < 16; j++) tmp[j] = (b0 + j < k_bytes) ? src[j] : 0;
         memcpy(&v, tmp, 16);
       }
+    }
+    {
+      uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const uint32_t x = w[j];
+        // even elements (nibbles 0, 2, 4, 6) to bits 0-15, odd ones to bits 16-31
+        const uint32_t ev = (x & 0xFu) | ((x >> 4) & 0xF0u) | ((x >> 8) & 0xF00u) | ((x >> 12) & 0xF000u);
+        const uint32_t y = x >> 4;
+        const uint32_t od = (y & 0xFu) | ((y >> 4) & 0xF0u) | ((y >> 8) & 0xF00u) | ((y >> 12) & 0xF000u);
+        w[j] = ev | (od << 16);
+      }
+      v = make_uint4(w[0], w[1], w[2], w[3]);
     }
     // 4352-byte tiles: 4096 bytes of codes, then 256 bytes of scales
     const size_t tile = i >> 8, inside = i & 255;
