@@ -132,7 +132,12 @@ struct gptoss_moe {
   int opt_ep_gather_ctas = 64;  // CTAs of that overlapped gather
   int opt_router_impl = 0;  // 0 = tcgen05 router, 1 = mma.sync router
   int opt_dependent_launch = 1;  // programmatic dependent launch between the layer's kernels
-  int opt_l2_hints = 1;     // CTA-pair GEMM: weights evict-first, token tiles evict-last
+  int opt_l2_hints = 1;
+  // peer transport: the down GEMM stores every expert output row straight into the memory of
+  // the rank whose token it belongs to (1), or leaves it here for that rank to fetch (0)
+  int opt_ep_push = 1;
+  unsigned long long *row_dst = nullptr;  // [assign_cap] destinations of the sorted rows (set per pass)
+  bool push_rows = false;                 // this pass: the down GEMM uses row_dst     // CTA-pair GEMM: weights evict-first, token tiles evict-last
   int opt_wait_limit_ms = 2000;  // longest wait for another rank's flag (peer-memory transport)
   gptoss::StageTimer timers[8];
   long long launches = 0;

@@ -19,18 +19,23 @@
 // owner waits for the N flags (acquire polls with a time limit), sorts ALL tokens
 // of all ranks by its local experts, and its gather kernel pulls the rows it needs
 // out of the home ranks' memory over NVLink into expert order - dispatch and gather
-// are one kernel.  After the owner's two GEMMs a second round of flags says "expert
-// outputs complete", and the home's combine kernel waits for them and pulls, for
-// each of a token's K slots, the weighted expert output from the owner's buffer (the
-// position from the owner's inverse permutation), adds the K rows in slot order in
-// fp32 and adds the residual - return and combine are one kernel, and the sum is the
-// single-GPU combine's, the same K rows in the same order: sharding adds no rounding
-// of its own.  (The reference's owner first sums its experts' outputs per row and rounds
-// that to bf16, expert.cpp:394-410: one more rounding per owner and one more pass over
-// the outputs, for a little less traffic.)  A rank reuses a buffer only after the flags that prove
-// its readers are done: activations and routing slots after the second flags of the
-// same layer (every peer has gathered), expert outputs and the inverse permutation
-// after the first flags of the next layer (every peer has combined).
+// are one kernel.  The owner's down GEMM then stores every weighted expert output row
+// straight into the memory of the rank its token came from (slot (t, k) of that rank's
+// receive buffer; the destination of each sorted row is worked out once per layer), so the
+// return trip runs under the GEMM's own tiles: the bulk stores of its epilogue cross
+// NVLink while the tensor cores work on the next tile.  A second round of flags says
+// "expert outputs delivered", and the home's combine kernel waits for them and adds the
+// token's K rows from its own memory, in slot order in fp32, and the residual - the sum is
+// the single-GPU combine's, the same K rows in the same order: sharding adds no rounding
+// of its own.  ("ep_push" 0 keeps the outputs at the owner and lets the home's combine
+// kernel fetch them over NVLink after the flags, the position from the owner's inverse
+// permutation: the same sum, 0.1-0.2 ms more per layer.  The reference's owner first sums
+// its experts' outputs per row and rounds that to bf16, expert.cpp:394-410: one more
+// rounding per owner and one more pass over the outputs, for a little less traffic.)
+// A rank reuses a buffer only after the flags that prove its readers or writers are done:
+// activations and routing slots after the second flags of the same layer (every peer has
+// gathered), its receive buffer is written again only after the first flags of the next
+// layer (this rank has combined before it published).
 //
 // NCCL send / recv ("ep_transport" 0, the fallback, one process per rank), per layer:
 //   1. home: mark for every token the owners it needs; counting sort of the
@@ -154,6 +159,9 @@ struct EpState {
   void *peer_t[GPTOSS_MAX_TOPK] = {};    // peers' pub_t (own entry: the local buffer)
   void *peer_out[GPTOSS_MAX_TOPK] = {};    // peers' expert outputs (their engine's ys)
   void *peer_rowof[GPTOSS_MAX_TOPK] = {};  // peers' inverse permutation (their engine's row_of)
+  bf16 *recv_out = nullptr;                // [max_t * K, H] expert outputs of this rank's tokens,
+                                           // stored here by the owners' down GEMMs (ep_push)
+  void *peer_recv[GPTOSS_MAX_TOPK] = {};   // peers' recv_out (own entry: the local buffer)
 };
 
 struct PeerRows {
@@ -247,6 +255,23 @@ ep_owner_slots_kernel(const int *all_meta, const int *flags, int round, int N, i
   stage_w[i] = mine ? __int_as_float(all_meta[static_cast<size_t>(src) * 2 * per + per + j]) : 0.f;
 }
 
+struct PeerBytes {
+  unsigned long long p[GPTOSS_MAX_TOPK];
+};
+
+// row_dst[pos] = where the expert output of sorted row pos belongs: slot (t, k) of the receive
+// buffer of the rank the token came from.  One thread per (global row, slot).
+__global__ void __launch_bounds__(256)
+ep_row_dst_kernel(const int *__restrict__ row_of, const PeerBytes recv, int N, int per, int H,
+                  int assign_cap, unsigned long long *__restrict__ row_dst) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= N * per) return;
+  const int pos = row_of[i];
+  if (pos < 0 || pos >= assign_cap) return;
+  const int src = i / per, j = i - src * per;  // j = t * K + k at the home rank
+  row_dst[pos] = recv.p[src] + static_cast<unsigned long long>(j) * H * sizeof(bf16);
+}
+
 // xs[r, :] = activations of global row sorted_row[r], read from the home rank's
 // published buffer (a peer mapping for every rank but this one); one warp per row,
 // eight 16-byte loads in flight per lane to cover the NVLink round trip.
@@ -301,11 +326,13 @@ __device__ __forceinline__ uint4 ld_peer_v4(const uint4 *p) {
 // from the owner's memory.  This is the sum the single-GPU combine makes, the same K rows
 // in the same order, so sharding the experts adds no rounding of its own.
 // One warp per token, two 16-byte columns per lane and trip.
+// recv != nullptr: the owners' down GEMMs have stored the rows into this rank's receive buffer,
+// slot (t, k) at row t * K + k: the same sum from local memory.
 __global__ void __launch_bounds__(256)
 combine_peer_kernel(bf16 *__restrict__ x, const PeerRows ys, const PeerInts rowof,
-                    const int *__restrict__ topk_i, int T, int K, int N, int rank, int max_t,
-                    int H, int assign_cap, const int *flags, int round, int *status,
-                    uint64_t limit_ns) {
+                    const bf16 *__restrict__ recv, const int *__restrict__ topk_i, int T, int K,
+                    int N, int rank, int max_t, int H, int assign_cap, const int *flags, int round,
+                    int *status, uint64_t limit_ns) {
   // every owner's outputs are complete (and every peer is done with this rank's activations);
   // a rank without tokens still takes this wait (one CTA): it is what allows it to
   // overwrite its published buffers in the next layer
@@ -321,7 +348,10 @@ combine_peer_kernel(bf16 *__restrict__ x, const PeerRows ys, const PeerInts rowo
     src[k] = nullptr;
     if (k < K) {
       const int e = topk_i[t * K + k];
-      if (e >= 0) {
+      if (e >= 0 && recv != nullptr) {
+        src[k] = recv + (static_cast<size_t>(t) * K + k) * H;
+        nvalid++;
+      } else if (e >= 0) {
         const int o = e % N;
         int pos;
         asm volatile("ld.relaxed.sys.global.b32 %0, [%1];"
@@ -588,11 +618,25 @@ static int ep_peer_owner(gptoss_moe *h, EpState *ep, int layer, const bf16 *t, c
   }
   {
     EpStageScope sc(h, 3, st);
-    EP_CUDA(h, launch_down(h, layer, st));
+    const bool push = h->opt_ep_push && h->opt_gemm_impl == GPTOSS_GEMM_PAIR && ep->recv_out;
+    if (push) {
+      // every output row goes straight to the rank its token came from
+      PeerBytes recv;
+      for (int p = 0; p < GPTOSS_MAX_TOPK; p++)
+        recv.p[p] = p < N ? reinterpret_cast<unsigned long long>(ep->peer_recv[p]) : 0ull;
+      ep_row_dst_kernel<<<(N * per + 255) / 256, 256, 0, st>>>(h->row_of, recv, N, per, H,
+                                                               h->assign_cap, h->row_dst);
+      h->launches++;
+      EP_CUDA(h, cudaGetLastError());
+    }
+    h->push_rows = push;
+    const cudaError_t e_down = launch_down(h, layer, st);
+    h->push_rows = false;
+    EP_CUDA(h, e_down);
   }
   {
-    // the homes read the expert outputs where the down GEMM left them: "my outputs are
-    // complete" goes out right behind it
+    // the homes read the expert outputs where the down GEMM left them (or find them in their
+    // own receive buffers): "my outputs are complete" goes out right behind it
     EpStageScope sc(h, 6, st);
     ep_signal_kernel<<<1, 32, 0, st>>>(ctl, N, 1, ep->rank, round);
     h->launches++;
@@ -617,7 +661,9 @@ static int ep_peer_combine(gptoss_moe *h, EpState *ep, void *x_io, int T, cudaSt
   EpStageScope sc(h, 4, st);
   const int warps = 8;
   const int grid = T > 0 ? (T + warps - 1) / warps : 1;
+  const bool pushed = h->opt_ep_push && h->opt_gemm_impl == GPTOSS_GEMM_PAIR && ep->recv_out;
   combine_peer_kernel<<<grid, warps * 32, 0, st>>>(static_cast<bf16 *>(x_io), outs, rowof,
+                                                   pushed ? ep->recv_out : nullptr,
                                                    h->topk_i, T, K, N, ep->rank, max_t, H,
                                                    h->assign_cap, ep->ctl + N, ep->round, h->status,
                                                    limit_ns);
@@ -796,7 +842,7 @@ int ep_forward(gptoss_moe *h, int layer, const void *t_in, void *x_io, int T, vo
 }
 
 struct PeerBlob {  // what a rank tells the others at start-up
-  cudaIpcMemHandle_t t, out, rowof, ctl;
+  cudaIpcMemHandle_t t, out, rowof, ctl, recv;
   int ok, max_t, hidden, pid, top_k, experts;
 };
 
@@ -811,7 +857,8 @@ static int ep_map_peers(gptoss_moe *h, EpState *ep) {
   mine.ok = cudaIpcGetMemHandle(&mine.t, ep->pub_t) == cudaSuccess &&
             cudaIpcGetMemHandle(&mine.out, h->ys) == cudaSuccess &&
             cudaIpcGetMemHandle(&mine.rowof, h->row_of) == cudaSuccess &&
-            cudaIpcGetMemHandle(&mine.ctl, ep->ctl) == cudaSuccess;
+            cudaIpcGetMemHandle(&mine.ctl, ep->ctl) == cudaSuccess &&
+            cudaIpcGetMemHandle(&mine.recv, ep->recv_out) == cudaSuccess;
   if (!mine.ok) {
     ep->peer_why = std::string("cudaIpcGetMemHandle: ") + cudaGetErrorString(cudaGetLastError());
   }
@@ -851,6 +898,7 @@ static int ep_map_peers(gptoss_moe *h, EpState *ep) {
       ep->peer_out[p] = h->ys;
       ep->peer_rowof[p] = h->row_of;
       ep->peer_ctl[p] = ep->ctl;
+      ep->peer_recv[p] = ep->recv_out;
       continue;
     }
     cudaError_t e = cudaIpcOpenMemHandle(&ep->peer_t[p], blobs[p].t, cudaIpcMemLazyEnablePeerAccess);
@@ -860,6 +908,8 @@ static int ep_map_peers(gptoss_moe *h, EpState *ep) {
       e = cudaIpcOpenMemHandle(&ep->peer_rowof[p], blobs[p].rowof, cudaIpcMemLazyEnablePeerAccess);
     if (e == cudaSuccess)
       e = cudaIpcOpenMemHandle(&ep->peer_ctl[p], blobs[p].ctl, cudaIpcMemLazyEnablePeerAccess);
+    if (e == cudaSuccess)
+      e = cudaIpcOpenMemHandle(&ep->peer_recv[p], blobs[p].recv, cudaIpcMemLazyEnablePeerAccess);
     if (e != cudaSuccess) {
       ok = false;
       ep->peer_why = std::string("cudaIpcOpenMemHandle: ") + cudaGetErrorString(e);
@@ -894,8 +944,9 @@ void ep_destroy(gptoss_moe *h) {
     if (ep->peer_out[p]) cudaIpcCloseMemHandle(ep->peer_out[p]);
     if (ep->peer_rowof[p]) cudaIpcCloseMemHandle(ep->peer_rowof[p]);
     if (ep->peer_ctl[p]) cudaIpcCloseMemHandle(ep->peer_ctl[p]);
+    if (ep->peer_recv[p]) cudaIpcCloseMemHandle(ep->peer_recv[p]);
   }
-  cudaFree(ep->pub_t); cudaFree(ep->ctl);
+  cudaFree(ep->pub_t); cudaFree(ep->ctl); cudaFree(ep->recv_out);
   if (ep->s2) cudaStreamDestroy(ep->s2);
   if (ep->ev_plan) cudaEventDestroy(ep->ev_plan);
   if (ep->ev_second) cudaEventDestroy(ep->ev_second);
@@ -934,6 +985,8 @@ static int ep_alloc_peer_side(gptoss_moe *h, EpState *ep) {
   EP_CUDA(h, ep_alloc(&ep->recv_e, (size_t)h->rows_cap * K));
   EP_CUDA(h, ep_alloc(&ep->recv_w, (size_t)h->rows_cap * K));
   EP_CUDA(h, ep_alloc(&ep->pub_t, T * H));
+  EP_CUDA(h, ep_alloc(&ep->recv_out, T * K * H));
+  if (!h->row_dst) EP_CUDA(h, ep_alloc(&h->row_dst, (size_t)h->assign_cap));
   EP_CUDA(h, ep_alloc(&ep->ctl, (size_t)kCtlHeader + (size_t)N * 2 * T * K));
   EP_CUDA(h, cudaMemset(ep->ctl, 0, sizeof(int) * kCtlHeader));
   ep->all_meta = ep->ctl + kCtlHeader;
@@ -1065,6 +1118,7 @@ extern "C" int gptoss_moe_ep_init_local(gptoss_moe_t *const *engines, int n_engi
       ep->peer_out[p] = engines[p]->ys;
       ep->peer_rowof[p] = engines[p]->row_of;
       ep->peer_ctl[p] = peer->ctl;
+      ep->peer_recv[p] = peer->recv_out;
     }
     ep->peer_ok = true;
     ep->transport = 1;

@@ -37,6 +37,9 @@ struct GemmArgs {
   const int *tile_split = nullptr;
   // (CTA-pair kernel) the loads carry L2 eviction hints: weights first out, token tiles last
   int l2_hints = 0;
+  // (CTA-pair kernel, down epilogue) where row r of the output goes instead of out + r * out_ld:
+  // the address of the row's first element, possibly in a peer GPU's memory
+  const unsigned long long *row_dst = nullptr;
 };
 
 // gate * sigmoid(alpha * gate) * (up + 1) with the reference CPU path's clamps

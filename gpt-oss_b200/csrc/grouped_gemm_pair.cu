@@ -498,8 +498,11 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
             bytes = bytes < ST::kRowBytes ? bytes : ST::kRowBytes;
             if (jt < ntok && bytes > 0) {
               unsigned char *dst =
-                  reinterpret_cast<unsigned char *>(g.out) +
-                  (static_cast<size_t>(tok0 + jt) * g.out_ld + col0) * kOutElem;
+                  (EPI == kEpiDown && g.row_dst != nullptr)
+                      ? reinterpret_cast<unsigned char *>(g.row_dst[tok0 + jt]) +
+                            static_cast<size_t>(col0) * kOutElem
+                      : reinterpret_cast<unsigned char *>(g.out) +
+                            (static_cast<size_t>(tok0 + jt) * g.out_ld + col0) * kOutElem;
               asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
                            "r"(smem_u32(tile_s + tg * ST::kPitch)), "r"(bytes)
                            : "memory");
@@ -601,6 +604,7 @@ static GemmArgs pair_args(gptoss_moe *h, bool down, const LayerWeights &lw) {
   g.status = h->status;
   g.wq = down ? lw.w2_blocks : lw.w1_blocks;
   g.l2_hints = h->opt_l2_hints;
+  g.row_dst = (down && h->push_rows) ? h->row_dst : nullptr;
   return g;
 }
 

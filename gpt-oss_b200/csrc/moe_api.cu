@@ -171,7 +171,7 @@ int gptoss_moe_destroy(gptoss_moe_t *h) {
   cudaFree(h->expert_offsets); cudaFree(h->sorted_row); cudaFree(h->sorted_weight);
   cudaFree(h->row_of); cudaFree(h->mtile_expert); cudaFree(h->mtile_row0);
   cudaFree(h->mtile_rows); cudaFree(h->num_mtiles); cudaFree(h->mtile_split); cudaFree(h->status); cudaFree(h->xs);
-  cudaFree(h->hact); cudaFree(h->ys); cudaFree(h->t_dev); cudaFree(h->x_dev);
+  cudaFree(h->hact); cudaFree(h->ys); cudaFree(h->row_dst); cudaFree(h->t_dev); cudaFree(h->x_dev);
   cudaFree(h->pos_dev);
   for (auto &sl : h->host_slots) {
     if (sl.busy) cudaEventSynchronize(sl.d2h);
@@ -654,6 +654,8 @@ int gptoss_moe_set_option(gptoss_moe_t *h, const char *name, int value) {
     h->opt_router_impl = value;
   } else if (!strcmp(name, "l2_hints")) {
     h->opt_l2_hints = value != 0;
+  } else if (!strcmp(name, "ep_push")) {
+    h->opt_ep_push = value != 0;
   } else if (!strcmp(name, "dependent_launch")) {
     h->opt_dependent_launch = value != 0;
   } else if (!strcmp(name, "wait_limit_ms")) {

@@ -203,11 +203,15 @@ int gptoss_moe_get_activations(gptoss_moe_t *h, void *act_host, size_t bytes);
  * peer-memory transport only: the owner pulls the rows of the second half of its
  * experts on a second stream while the gate_up GEMM of the first half runs;
  * "ep_gather_ctas", default 64, is the size of that second gather's grid),
+ * "ep_push" (0/1, default 1; peer-memory transport only: the owner's down GEMM
+ * stores each expert output row straight into the memory of the rank its token
+ * came from, under its own tiles; 0: the rows stay at the owner and that rank's
+ * combine kernel fetches them),
  * "time_stages" (0/1, see gptoss_moe_stage_ms), "dependent_launch" (0/1, default 1:
  * the layer's kernels are launched with programmatic stream serialization, so a
  * kernel's set-up overlaps its predecessor's tail), "l2_hints" (0/1, default 1:
- * the CTA-pair GEMM marks its weight loads evict-first and its token loads
- * evict-last in L2), "wait_limit_ms" (1..60000, default 2000: how long a
+ * the CTA-pair GEMM marks its token loads evict-last in L2 and the weight loads of
+ * experts whose rows fit one token tile evict-first), "wait_limit_ms" (1..60000, default 2000: how long a
  * kernel of the peer-memory transport waits for another rank's flag before it
  * gives up with status 106).  Every option leaves the results unchanged. */
 int gptoss_moe_set_option(gptoss_moe_t *h, const char *name, int value);
