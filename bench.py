@@ -646,19 +646,20 @@ def run_ours(args, shape):
     }
     if world > 1 and res["transport"] == 1:
         # the exchange against the link: under uniform routing (N-1)/N of the T*K rows an owner
-        # multiplies are pulled from peers inside the permute stage, and (N-1)/N of a home's
-        # T*K expert outputs inside the combine stage; the stage times also hold the local part
-        # of the same kernels, so the rates are lower bounds
+        # multiplies are pulled from peers inside the permute stage (the stage also holds the
+        # sort and the local rows, so the rate is a lower bound), and (N-1)/N of the T*K
+        # expert outputs are stored into peers' memory by the down GEMM's epilogue, under its
+        # tiles: the rate the link has to carry for that to stay hidden
         remote = (world - 1) / world * n_assign * H * 2
         line["nvlink"] = {
-            "bytes_pulled_per_rank_per_step": 2 * remote,
+            "bytes_pulled_per_rank_per_step": remote, "bytes_pushed_per_rank_per_step": remote,
             "gather_gbs_lower_bound": remote / (stage["permute"] * 1e-3) / 1e9,
-            "combine_gbs_lower_bound": remote / (stage["combine"] * 1e-3) / 1e9,
+            "push_gbs_under_down_gemm": remote / (stage["down"] * 1e-3) / 1e9,
             "peak": 770.0, "unit": "GB/s per direction per GPU",
             "peak_source": "measured peer copy on this pool (900 nominal)",
-            "exchange_floor_ms": 2 * remote / 770e9 * 1e3,
-            "exchange_ms": stage["permute"] + stage["combine"] + stage.get("dispatch", 0.0)
-                           + stage.get("return", 0.0),
+            "gather_floor_ms": remote / 770e9 * 1e3,
+            "ms_outside_the_gemms": stage["route"] + stage["permute"] + stage["combine"]
+                                    + stage.get("dispatch", 0.0) + stage.get("return", 0.0),
         }
     for key in ("strong_scaling", "nccl_send_recv", "parity"):
         if key in res:
