@@ -74,6 +74,37 @@ def read_peaks():
             "source": "fallback"}
 
 
+def nvml_handle(cuda_index):
+    """NVML handle of a CUDA device, found by its PCI address (NVML may list GPUs the process
+    cannot see, in another order); falls back to the index.  Read-only use."""
+    import pynvml
+
+    pynvml.nvmlInit()
+    try:
+        import torch
+
+        p = torch.cuda.get_device_properties(cuda_index)
+        bus = "%08x:%02x:%02x.0" % (p.pci_domain_id, p.pci_bus_id, p.pci_device_id)
+        return pynvml, pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+    except Exception:
+        return pynvml, pynvml.nvmlDeviceGetHandleByIndex(cuda_index)
+
+
+def run_near_gpu(cuda_index):
+    """Restrict this process to the CPUs NVML names as near the GPU, so that the pinned host
+    buffers it allocates from here on sit on that socket's memory.  Returns the CPU count."""
+    try:
+        nv, h = nvml_handle(cuda_index)
+        words = nv.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        near = {64 * i + b for i, w in enumerate(words) for b in range(64) if (int(w) >> b) & 1}
+        near &= os.sched_getaffinity(0)
+        if near:
+            os.sched_setaffinity(0, near)
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return None
+
+
 class ClockSampler(threading.Thread):
     """Samples SM clock and throttle reasons through NVML while the timed region runs
     (read-only queries)."""
@@ -84,12 +115,8 @@ class ClockSampler(threading.Thread):
         self.samples, self.reasons, self.stop_flag = [], set(), False
         self.max_mhz = None
         try:
-            import pynvml
-
-            pynvml.nvmlInit()
-            self.nv = pynvml
-            self.dev = pynvml.nvmlDeviceGetHandleByIndex(index)
-            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.dev, pynvml.NVML_CLOCK_SM)
+            self.nv, self.dev = nvml_handle(index)
+            self.max_mhz = self.nv.nvmlDeviceGetMaxClockInfo(self.dev, self.nv.NVML_CLOCK_SM)
         except Exception:
             self.nv = None
 
@@ -571,6 +598,8 @@ def run_ours(args, shape):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # several ranks share the host: each keeps to the CPUs (and so the memory) near its GPU
+    near_cpus = run_near_gpu(local_rank) if world > 1 else None
     pkg = entry.load_package()
     T, H, IM, E, K = (shape.n_tokens, shape.hidden_dim, shape.intermediate_dim, shape.n_experts,
                       shape.experts_per_token)
@@ -641,6 +670,7 @@ def run_ours(args, shape):
         "cpu_baseline": res.get("cpu_baseline"),
         "e2e": res["e2e"], "gpu_launches": res["launches"], "clocks": res["clocks"],
         "stage_ms": stage, "ms_per_step_with_stage_events": res["ms_per_step_with_stage_events"],
+        "host_cpus_near_gpu": near_cpus,
         "stage_timing": "the K steps run a second time with an event pair around every stage "
                         "(an event between two kernels undoes their dependent launch)",
     }
