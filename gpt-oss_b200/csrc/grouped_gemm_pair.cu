@@ -19,19 +19,25 @@
 // No TMA load uses multicast: the halves of the shared operand are loaded by the
 // CTA that holds them.
 //
-// Warp roles per CTA (320 threads): warp 0 lane 0 = TMA producer (both CTAs; the
-// odd CTA's loads complete on the even CTA's full barrier), warp 1 lane 0 of the
-// even CTA = MMA issuer, warp 1 = paired TMEM allocation, warps 2-9 = epilogue.
-// tcgen05.commit with a 2-CTA mask releases the stage / publishes the accumulator
-// in both CTAs; the odd CTA's epilogue warps release the accumulator with a
-// remote mbarrier arrive.
+// Warp roles per CTA (320 threads): warp 0 = TMA producer (both CTAs; the odd
+// CTA's loads complete on the even CTA's full barrier), warp 1 of the even CTA =
+// MMA issuer, warp 1 = paired TMEM allocation, warps 2-9 = epilogue.  The producer
+// and the issuer walk their rings with the whole warp - every lane polls the
+// barriers - and one lane picked by elect.sync inside the loop body issues.  (With
+// `if (lane == 0)` around the whole loop each TMA, MMA and commit cost the lone lane
+// 60-70 cycles to issue: a K block took 630-680 cycles whatever it contained, against
+// 450-530 this way.)  tcgen05.commit with a 2-CTA mask releases the stage / publishes
+// the accumulator in both CTAs; the odd CTA's epilogue warps release the accumulator
+// with a remote mbarrier arrive.
 //
 // Epilogue (transposed): a TMEM lane is an output feature, a column a token.  A
 // warp reads 32 lanes x 32 tokens, adds the lane's bias, pairs gate/up rows
 // (adjacent lanes) by shuffle or applies the token's routing weight, and writes
 // bf16 into a [32 tokens][row] shared tile shared by the 4 warps that cover the
-// CTA's 128 rows; the tile is then written to global memory row-wise (whole
-// 128- / 256-byte segments per token) with streaming stores.
+// CTA's 128 rows; the tile then leaves row-wise, one bulk copy per token (a whole
+// 128- / 256-byte segment), to this GPU's memory or - down GEMM under expert
+// parallelism, GemmArgs::row_dst - straight into the memory of the rank the token
+// came from.
 #include <cuda.h>
 
 #include "common.cuh"

@@ -6,9 +6,12 @@
 // fused_topk_softmax_batch_kernel (getp-csrc/utility/utility.cpp:274-365) of the
 // reference.  Bound by HBM: the only large stream is t [T,H] bf16, read once.
 //
-// Layout: a CTA owns 32 consecutive tokens.  8 warps = 2 token groups of 16 x 4
+// Two kernels: router_tx_kernel (tcgen05, further down; the default) and
+// router_topk_kernel (mma.sync, "router_impl" 1), described first.
+//
+// Layout of router_topk_kernel: a CTA owns 32 consecutive tokens.  8 warps = 2 token groups of 16 x 4
 // expert slices; bf16 tensor-core MMAs (m16n8k16, fp32 accumulate) over K chunks
-// of 64.  A ninth warp is the producer: one thread issues two TMA tile loads per
+// of 64.  A ninth warp is the producer: an elected lane issues two TMA tile loads per
 // chunk (32 token rows, all expert rows; 128-byte swizzle, rows past T or E read
 // as zeros) into a ring of 3 to 8 stages guarded by full / empty mbarriers, so the
 // compute warps spend their instructions on ldmatrix and MMAs only.  The fp32 logits
