@@ -136,6 +136,7 @@ struct gptoss_moe {
   // peer transport: the down GEMM stores every expert output row straight into the memory of
   // the rank whose token it belongs to (1), or leaves it here for that rank to fetch (0)
   int opt_ep_push = 1;
+  int opt_ep_dedup = 1;  // peer transport: a remote token with several experts here is fetched once
   unsigned long long *row_dst = nullptr;  // [assign_cap] destinations of the sorted rows (set per pass)
   bool push_rows = false;                 // this pass: the down GEMM uses row_dst     // CTA-pair GEMM: weights evict-first, token tiles evict-last
   int opt_wait_limit_ms = 2000;  // longest wait for another rank's flag (peer-memory transport)

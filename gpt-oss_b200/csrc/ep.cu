@@ -19,7 +19,7 @@
 // owner waits for the N flags (acquire polls with a time limit), sorts ALL tokens
 // of all ranks by its local experts, and its gather kernel pulls the rows it needs
 // out of the home ranks' memory over NVLink into expert order - dispatch and gather
-// are one kernel.  The owner's down GEMM then stores every weighted expert output row
+// are one kernel; a token with several experts on this owner crosses the link once.  The owner's down GEMM then stores every weighted expert output row
 // straight into the memory of the rank its token came from (slot (t, k) of that rank's
 // receive buffer; the destination of each sorted row is worked out once per layer), so the
 // return trip runs under the GEMM's own tiles: the bulk stores of its epilogue cross
@@ -275,10 +275,16 @@ ep_row_dst_kernel(const int *__restrict__ row_of, const PeerBytes recv, int N, i
 // xs[r, :] = activations of global row sorted_row[r], read from the home rank's
 // published buffer (a peer mapping for every rank but this one); one warp per row,
 // eight 16-byte loads in flight per lane to cover the NVLink round trip.
+// A token that has several of its experts on this rank crosses the link once: pass 0
+// fetches, of a remote token's slots here, only the first (and every slot of a local
+// token); pass 1 copies the others from that first row, which by then is in xs
+// (row_of, [R, K] = sorted position of every (row, slot) or -1, says which is which).
+// dedup == 0: one pass, every row from its home.
 __global__ void __launch_bounds__(256)
-gather_rows_peer_kernel(bf16 *__restrict__ xs, const PeerRows src, int max_t,
+gather_rows_peer_kernel(bf16 *xs, const PeerRows src, int max_t,
                         const int *__restrict__ sorted_row,
                         const int *__restrict__ expert_offsets, int e_lo, int e_hi, int H, int R,
+                        const int *__restrict__ row_of, int K, int rank, int dedup, int pass,
                         int *status) {
   // the rows of experts e_lo .. e_hi-1
   const int first = expert_offsets[e_lo], total = expert_offsets[e_hi];
@@ -289,17 +295,27 @@ gather_rows_peer_kernel(bf16 *__restrict__ xs, const PeerRows src, int max_t,
        r += nwarps) {
     const int g = sorted_row[r];
     if (g < 0 || g >= R) {
-      set_status(status, kStatusBadIndex);
+      if (pass == 0) set_status(status, kStatusBadIndex);
       continue;
     }
     const int home = g / max_t, tok = g - home * max_t;
     const uint4 *s4 = reinterpret_cast<const uint4 *>(src.p[home] + static_cast<size_t>(tok) * H);
+    if (dedup && home != rank) {
+      // the first of this token's slots that landed on this rank
+      int lead = -1;
+      for (int k = 0; k < K && lead < 0; k++) lead = row_of[static_cast<size_t>(g) * K + k];
+      const bool is_lead = lead == r || lead < 0;
+      if (is_lead != (pass == 0)) continue;
+      if (!is_lead) s4 = reinterpret_cast<const uint4 *>(xs + static_cast<size_t>(lead) * H);
+    } else if (pass != 0) {
+      continue;
+    }
     uint4 *d4 = reinterpret_cast<uint4 *>(xs + static_cast<size_t>(r) * H);
     for (int p0 = lane; p0 < n4; p0 += 256) {
       uint4 v[8];
 #pragma unroll
       for (int u = 0; u < 8; u++)
-        if (p0 + u * 32 < n4) v[u] = __ldg(s4 + p0 + u * 32);
+        if (p0 + u * 32 < n4) v[u] = s4[p0 + u * 32];  // (pass 1 reads xs itself: plain loads)
 #pragma unroll
       for (int u = 0; u < 8; u++)
         if (p0 + u * 32 < n4) d4[p0 + u * 32] = v[u];
@@ -591,18 +607,31 @@ static int ep_peer_owner(gptoss_moe *h, EpState *ep, int layer, const bf16 *t, c
     EpStageScope sc(h, 1, st);
     EP_CUDA(h, launch_permute_plan_only(h, st));
     if (halves) EP_CUDA(h, launch_mtile_split(h, e_mid, st));
+    // (the copies of pass 1 read rows that pass 0 wrote, possibly for the other half of the
+    // experts: no second pass when the gather is split)
+    const int dedup = (h->opt_ep_dedup && !halves && K > 1) ? 1 : 0;
     gather_rows_peer_kernel<<<h->num_sms * 4, 256, 0, st>>>(h->xs, src, max_t, h->sorted_row,
                                                             h->expert_offsets, 0, e_mid, H, R,
+                                                            h->row_of, K, ep->rank, dedup, 0,
                                                             h->status);
     h->launches++;
     EP_CUDA(h, cudaGetLastError());
+    if (dedup) {
+      gather_rows_peer_kernel<<<h->num_sms * 2, 256, 0, st>>>(h->xs, src, max_t, h->sorted_row,
+                                                              h->expert_offsets, 0, e_mid, H, R,
+                                                              h->row_of, K, ep->rank, dedup, 1,
+                                                              h->status);
+      h->launches++;
+      EP_CUDA(h, cudaGetLastError());
+    }
     if (halves) {
       // the second half starts when the first has the links to itself no longer
       EP_CUDA(h, cudaEventRecord(ep->ev_plan, st));
       EP_CUDA(h, cudaStreamWaitEvent(ep->s2, ep->ev_plan, 0));
       // few CTAs: the copy has to keep the links busy, not the SMs, which the GEMM needs
       gather_rows_peer_kernel<<<h->opt_ep_gather_ctas, 256, 0, ep->s2>>>(
-          h->xs, src, max_t, h->sorted_row, h->expert_offsets, e_mid, h->El, H, R, h->status);
+          h->xs, src, max_t, h->sorted_row, h->expert_offsets, e_mid, h->El, H, R, h->row_of, K,
+          ep->rank, 0, 0, h->status);
       EP_CUDA(h, cudaGetLastError());
       EP_CUDA(h, cudaEventRecord(ep->ev_second, ep->s2));
       h->launches++;

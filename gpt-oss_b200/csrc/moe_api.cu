@@ -654,6 +654,8 @@ int gptoss_moe_set_option(gptoss_moe_t *h, const char *name, int value) {
     h->opt_router_impl = value;
   } else if (!strcmp(name, "l2_hints")) {
     h->opt_l2_hints = value != 0;
+  } else if (!strcmp(name, "ep_dedup")) {
+    h->opt_ep_dedup = value != 0;
   } else if (!strcmp(name, "ep_push")) {
     h->opt_ep_push = value != 0;
   } else if (!strcmp(name, "dependent_launch")) {

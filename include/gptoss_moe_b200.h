@@ -203,6 +203,9 @@ int gptoss_moe_get_activations(gptoss_moe_t *h, void *act_host, size_t bytes);
  * peer-memory transport only: the owner pulls the rows of the second half of its
  * experts on a second stream while the gate_up GEMM of the first half runs;
  * "ep_gather_ctas", default 64, is the size of that second gather's grid),
+ * "ep_dedup" (0/1, default 1; peer-memory transport only: a remote token that
+ * has several of its experts on this rank crosses the link once and is copied
+ * locally for the others),
  * "ep_push" (0/1, default 1; peer-memory transport only: the owner's down GEMM
  * stores each expert output row straight into the memory of the rank its token
  * came from, under its own tiles; 0: the rows stay at the owner and that rank's
