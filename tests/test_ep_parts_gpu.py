@@ -133,6 +133,40 @@ def test_zero_residual_block_output_under_expert_parallelism(pkg, oracle):
             eng.close()
 
 
+def test_pushed_return_and_single_fetch_leave_the_results_unchanged(pkg):
+    """The down GEMM storing its rows into the homes' memory (ep_push) and the single fetch of
+    a token with several experts on one owner (ep_dedup) move the same bits as the plain
+    fetch-everything path."""
+    import torch
+
+    dev = torch.device("cuda:0")
+    world, H, IM, E, K, T = 4, 256, 192, 16, 4, 150
+    weights = synth.make_layer(synth.MoeShape("ep", 8, H, IM, E, K, 7.0, 77))
+    engs = _engines(pkg, world, H, IM, E, K, T, weights)
+    stream = torch.cuda.current_stream().cuda_stream
+    try:
+        ins = [_make_rank_inputs(r, T, H, 5) for r in range(world)]
+        ts = [helpers.to_dev_bf16(i[0], dev) for i in ins]
+        poss = [torch.from_numpy(i[2]).to(dev) for i in ins]
+        outs = {}
+        for push, dedup in ((1, 1), (0, 0), (1, 0), (0, 1)):
+            for eng in engs:
+                eng.set_option("ep_push", push)
+                eng.set_option("ep_dedup", dedup)
+            xs = [helpers.to_dev_bf16(i[1], dev) for i in ins]
+            _layer_in_parts(engs, ts, xs, poss, [T] * world, stream)
+            torch.cuda.synchronize()
+            assert all(e.device_status() == 0 for e in engs)
+            outs[(push, dedup)] = [x.cpu() for x in xs]
+        for key, got in outs.items():
+            for r in range(world):
+                assert torch.equal(got[r], outs[(1, 1)][r]), f"options {key}, rank {r}"
+    finally:
+        torch.cuda.synchronize()
+        for eng in engs:
+            eng.close()
+
+
 def test_engines_that_disagree_are_refused(pkg):
     a = pkg.MoeEngine(128, 64, 8, 4, max_tokens=64, ep_rank=0, ep_size=2, device=0)
     b = pkg.MoeEngine(128, 64, 8, 4, max_tokens=96, ep_rank=1, ep_size=2, device=0)
