@@ -48,6 +48,9 @@
 namespace gptoss {
 
 constexpr int kPairThreads = 320;
+// nanoseconds between polls in the two roles that wait long by design (the producer runs a
+// whole ring ahead, an epilogue warp waits for most of a tile's K loop)
+constexpr uint32_t kEpiloguePollNs = 200, kProducerPollNs = 100;
 constexpr int kPairOperandBytes = 128 * kTileK * 2;          // 16 KB: 128 rows x 64 k
 constexpr int kPairEpiWarps = kPairThreads / 32 - 2;
 constexpr int kAccColsPair = 256;  // TMEM columns per accumulator (up to 256 tokens), two of them
@@ -231,7 +234,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
         const uint32_t tok_bytes =
             (half_n <= 8 ? 8 : ((half_n <= 32 || TOKB == 32) ? 32 : 128)) * kTileK * 2;
         for (int kb = 0; kb < kb_count; kb++) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, kProducerPollNs)) {
             set_status(g.status, kStatusWaitTimeoutProducer);
             *abort_flag = 1;
             ok = false;
@@ -434,7 +437,10 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
       const float bias_v = (g.bias != nullptr && n_lane < g.n_cols)
                                ? __ldg(g.bias + static_cast<size_t>(e) * g.n_cols + n_lane)
                                : 0.f;
-      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) {
+      // (a long wait by design - most of a tile's K loop: sleeping between polls leaves the
+      // issue slots and the power of eight idle warps to the working ones, 1 % of the step
+      // under the power cap)
+      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, kEpiloguePollNs)) {
         set_status(g.status, kStatusWaitTimeoutEpilogue);
         *abort_flag = 1;
         break;
