@@ -681,13 +681,16 @@ def run_ours(args, shape):
         # expert outputs are stored into peers' memory by the down GEMM's epilogue, under its
         # tiles: the rate the link has to carry for that to stay hidden
         remote = (world - 1) / world * n_assign * H * 2
+        # a token with several experts on one owner is pulled once: under uniform routing each
+        # of the other ranks' tokens needs this owner with probability 1 - (1 - 1/N)^K
+        pulled = (world - 1) * T * (1.0 - (1.0 - 1.0 / world) ** K) * H * 2
         line["nvlink"] = {
-            "bytes_pulled_per_rank_per_step": remote, "bytes_pushed_per_rank_per_step": remote,
-            "gather_gbs_lower_bound": remote / (stage["permute"] * 1e-3) / 1e9,
+            "bytes_pulled_per_rank_per_step": pulled, "bytes_pushed_per_rank_per_step": remote,
+            "gather_gbs_lower_bound": pulled / (stage["permute"] * 1e-3) / 1e9,
             "push_gbs_under_down_gemm": remote / (stage["down"] * 1e-3) / 1e9,
             "peak": 770.0, "unit": "GB/s per direction per GPU",
             "peak_source": "measured peer copy on this pool (900 nominal)",
-            "gather_floor_ms": remote / 770e9 * 1e3,
+            "gather_floor_ms": pulled / 770e9 * 1e3,
             "ms_outside_the_gemms": stage["route"] + stage["permute"] + stage["combine"]
                                     + stage.get("dispatch", 0.0) + stage.get("return", 0.0),
         }
