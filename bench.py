@@ -858,7 +858,8 @@ def run_decode_120b(args):
     vocabulary 201088), random-init weights generated on the device, 6144 sequences split
     over the GPUs, each with 512 positions of synthetic KV context; experts sharded over
     the ranks (16 per GPU at 8).  Needs at least 2 GPUs: the bf16 experts alone are 229 GB.
-    GPTOSS_C5_LAYERS cuts the layer count for development runs (reported in the line)."""
+    GPTOSS_C5_LAYERS / GPTOSS_C5_SEQS cut the layer / sequence count for development runs
+    (reported in the line)."""
     import torch
     import torch.distributed as dist
 
@@ -875,7 +876,7 @@ def run_decode_120b(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     pkg = entry.load_package()
-    ctx, total_seqs = 512, 6144
+    ctx, total_seqs = 512, int(os.environ.get("GPTOSS_C5_SEQS", "6144"))
     B = total_seqs // world
     steps, warmup = args.steps, args.warmup
     cfg = dict(vocab_size=201088, hidden_dim=2880, n_experts=128, experts_per_token=4,

@@ -68,7 +68,7 @@ struct PairStage {
 };
 
 // MXFP4 weights (MX = true): a producer warp bulk-copies the packed codes (4 KB) and
-// scales (256 B) of the CTA's 128 rows x 64 k into a raw ring; sixteen extra warps expand
+// scales (256 B) of the CTA's 128 rows x 64 k into a raw ring; twelve or sixteen extra warps expand
 // them to bf16 straight into the operand ring, in the 128-byte-swizzled layout TMA would
 // have written, and count as arrivals on the even CTA's full barrier beside the token
 // tiles' bytes.  The expansion is register arithmetic only (a table in shared memory cost
@@ -77,9 +77,14 @@ struct PairStage {
 constexpr int kPairBarrierBytes = 1024;  // mbarriers, TMEM address holder, abort flag
 constexpr int kRawCodeBytes = 128 * 32;
 constexpr int kRawStageBytes = kRawCodeBytes + 128 * 2;
-// four warps per operand stage: the expansion is bound by the integer pipe and by its own
-// latencies, and 16 warps measured 10% faster than 8 (72 registers per thread, no spills)
-constexpr int kDequantWarps = 16;
+// Expanding warps: groups of four; group j takes the K blocks n = j, j + G, j + 2G, ... of
+// the CTA's sequence (G groups).  With up to four operand stages there is a group per stage;
+// with six, three groups alternate between two stages each (n % 6), so a group starts on its
+// next block while the MMAs still read its last one - otherwise the stage's round trip
+// (expand, MMAs, commit, wake-up) sets the pace, not the expansion.
+constexpr int kDqGroupWarps = 4;
+constexpr int dq_groups(int stages) { return stages > 4 ? stages / 2 : stages; }
+constexpr int dq_warps(int stages) { return dq_groups(stages) * kDqGroupWarps; }
 
 // two e2m1 codes, one in bits 0-3 and one in bits 16-19 (kLow) or in bits 4-7 and 20-23
 // (!kLow), all other bits zero -> two bf16 whose value is code * 2^-126: sign to bit 15 of
@@ -110,7 +115,7 @@ __device__ __forceinline__ void decode_tile(int tile, int w_pairs, int tt_lo, in
 // tiles of up to 64 for decode-sized batches, which buys a deeper ring)
 // kRawStages = depth of the raw (packed) weight ring, 0 without MX
 template <int EPI, int kPairStages, bool MX, int TOKB, int kRawStages>
-__global__ void __launch_bounds__(kPairThreads + (MX ? (kDequantWarps + 1) * 32 : 0), 1)
+__global__ void __launch_bounds__(kPairThreads + (MX ? (dq_warps(kPairStages) + 1) * 32 : 0), 1)
 grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
                          const __grid_constant__ CUtensorMap tmap_x,
                          const __grid_constant__ CUtensorMap tmap_x32,
@@ -138,8 +143,9 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
   // and a raw stage always drained by the same ones: every warp then meets the phases of
   // its barriers one by one, in order, and a parity wait can never be a whole turn of
   // the ring ahead of the barrier it polls
-  constexpr int kWarpsPerBlock = MX ? (kDequantWarps / kPairStages > 0 ? kDequantWarps / kPairStages : 1) : 1;
-  static_assert(!MX || (kRawStages % kPairStages == 0 && kWarpsPerBlock * kPairStages <= kDequantWarps &&
+  constexpr int kDequantWarps = dq_warps(kPairStages), kGroups = dq_groups(kPairStages);
+  constexpr int kWarpsPerBlock = MX ? kDqGroupWarps : 1;
+  static_assert(!MX || (kRawStages % kPairStages == 0 && kPairStages % kGroups == 0 &&
                         8 % kWarpsPerBlock == 0),
                 "dequantising warps must map to fixed ring stages");
 
@@ -341,23 +347,23 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
       }
     }
   } else if (MX && warp >= kPairThreads / 32) {
-    // dequantising warps: group j = dw / kWarpsPerBlock expands the K blocks n = j, j + S,
-    // j + 2S, ... of the CTA's sequence (S = operand stages) into operand stage j, each
-    // warp of the group a share of the block's 16-byte chunks, so that the waits, the
-    // fence and the arrivals of one block overlap the table lookups of the others.  Chunk
-    // c = half (c & 1) of weight row c >> 1: 32 codes under one scale byte.
+    // dequantising warps: group j = dw / kWarpsPerBlock expands the K blocks n = j, j + G,
+    // j + 2G, ... of the CTA's sequence into operand stage n % S, each warp of the group a
+    // share of the block's 16-byte chunks.  Chunk c = half (c & 1) of weight row c >> 1:
+    // 32 codes under one scale byte.
     const int dw = warp - kPairThreads / 32;
     const int grp = dw / kWarpsPerBlock, sub = dw - grp * kWarpsPerBlock;
     const int my_tiles = first_tile < total_tiles ? (total_tiles - first_tile + ncl - 1) / ncl : 0;
     const int total_kb = my_tiles * kb_count;
     constexpr int kChunkIters = 8 / kWarpsPerBlock;
-    if (grp < kPairStages) {
-      const int stage = grp;
-      uint32_t phase = 0;
-      for (int n = grp; n < total_kb; n += kPairStages, phase ^= 1u) {
+    if (grp < kGroups) {
+      for (int n = grp; n < total_kb; n += kGroups) {
         constexpr int kRawDiv = kRawStages > 0 ? kRawStages : 1;  // (no raw ring without MX)
         const int rs = n % kRawDiv;
         const uint32_t rphase = (n / kRawDiv) & 1;
+        // a stage (and a raw slot) always meets the same group: n % S determines n % G
+        const int stage = n % kPairStages;
+        const uint32_t phase = (n / kPairStages) & 1;
         if (!mbar_wait(&raw_full[rs], rphase, abort_flag) ||
             !mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
           set_status(g.status, kStatusWaitTimeoutProducer);
@@ -564,7 +570,7 @@ static cudaError_t launch_pair_stages(int num_sms, long long *launches, const CU
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(num_sms & ~1));
-  cfg.blockDim = dim3(kPairThreads + (MX ? (kDequantWarps + 1) * 32 : 0));
+  cfg.blockDim = dim3(kPairThreads + (MX ? (dq_warps(STAGES) + 1) * 32 : 0));
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -586,12 +592,12 @@ template <int EPI>
 static cudaError_t launch_pair(gptoss_moe *h, const CUtensorMap &tw, const CUtensorMap *tx,
                                const GemmArgs &g, cudaStream_t stream) {
   const bool dep = h->opt_dependent_launch != 0;
-  // MXFP4: four operand stages, each filled by four of the sixteen dequantising warps; the packed
-  // weights wait in the raw ring, which is what covers HBM latency (24 x 4.25 KB per CTA with
-  // the small token slots of decode-sized batches, 12 beside full-width token slots)
+  // MXFP4: the packed weights wait in the raw ring, which is what covers HBM latency (12 x 4.25 KB
+  // per CTA); decode-sized batches have small token slots and room for six operand stages,
+  // two per group of expanding warps, full-width token slots for four, one per group
   if (h->cfg.weight_format == GPTOSS_WEIGHTS_MXFP4) {
     if (h->cur_tile_rows == 64)
-      return launch_pair_stages<EPI, 4, true, 32, 24>(h->num_sms, &h->launches, tx[0], tx, g,
+      return launch_pair_stages<EPI, 6, true, 32, 12>(h->num_sms, &h->launches, tx[0], tx, g,
                                                       stream, dep);
     return launch_pair_stages<EPI, 4, true, 128, 12>(h->num_sms, &h->launches, tx[0], tx, g,
                                                      stream, dep);
