@@ -91,9 +91,8 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 // Bounded wait.  Returns false when the limit ran out or another role of the
 // CTA already gave up (*abort_flag != 0).
-// backoff_ns > 0: sleep that long between polls (for waits that are long by design).
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity,
-                                          volatile int *abort_flag, uint32_t backoff_ns = 0) {
+                                          volatile int *abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
   // the global timer is slow to read: first look at it after 1024 failed polls, so that
   // the short waits of a running pipeline never pay for it
@@ -101,7 +100,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity,
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (backoff_ns) __nanosleep(backoff_ns);
     if ((++spins & 0x3ff) == 0) {
       if (*abort_flag) return false;
       const uint64_t now = global_timer_ns();

@@ -48,9 +48,6 @@
 namespace gptoss {
 
 constexpr int kPairThreads = 320;
-// nanoseconds between polls in the two roles that wait long by design (the producer runs a
-// whole ring ahead, an epilogue warp waits for most of a tile's K loop)
-constexpr uint32_t kEpiloguePollNs = 200, kProducerPollNs = 100;
 constexpr int kPairOperandBytes = 128 * kTileK * 2;          // 16 KB: 128 rows x 64 k
 constexpr int kPairEpiWarps = kPairThreads / 32 - 2;
 constexpr int kAccColsPair = 256;  // TMEM columns per accumulator (up to 256 tokens), two of them
@@ -68,7 +65,7 @@ struct PairStage {
 };
 
 // MXFP4 weights (MX = true): a producer warp bulk-copies the packed codes (4 KB) and
-// scales (256 B) of the CTA's 128 rows x 64 k into a raw ring; twelve or sixteen extra warps expand
+// scales (256 B) of the CTA's 128 rows x 64 k into a raw ring; sixteen extra warps expand
 // them to bf16 straight into the operand ring, in the 128-byte-swizzled layout TMA would
 // have written, and count as arrivals on the even CTA's full barrier beside the token
 // tiles' bytes.  The expansion is register arithmetic only (a table in shared memory cost
@@ -83,8 +80,8 @@ constexpr int kRawStageBytes = kRawCodeBytes + 128 * 2;
 // next block while the MMAs still read its last one - otherwise the stage's round trip
 // (expand, MMAs, commit, wake-up) sets the pace, not the expansion.
 constexpr int kDqGroupWarps = 4;
-constexpr int dq_groups(int stages) { return stages > 4 ? stages / 2 : stages; }
-constexpr int dq_warps(int stages) { return dq_groups(stages) * kDqGroupWarps; }
+__host__ __device__ constexpr int dq_groups(int stages) { return stages > 4 ? stages / 2 : stages; }
+__host__ __device__ constexpr int dq_warps(int stages) { return dq_groups(stages) * kDqGroupWarps; }
 
 // two e2m1 codes, one in bits 0-3 and one in bits 16-19 (kLow) or in bits 4-7 and 20-23
 // (!kLow), all other bits zero -> two bf16 whose value is code * 2^-126: sign to bit 15 of
@@ -240,7 +237,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
         const uint32_t tok_bytes =
             (half_n <= 8 ? 8 : ((half_n <= 32 || TOKB == 32) ? 32 : 128)) * kTileK * 2;
         for (int kb = 0; kb < kb_count; kb++) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, kProducerPollNs)) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
             set_status(g.status, kStatusWaitTimeoutProducer);
             *abort_flag = 1;
             ok = false;
@@ -443,10 +440,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
       const float bias_v = (g.bias != nullptr && n_lane < g.n_cols)
                                ? __ldg(g.bias + static_cast<size_t>(e) * g.n_cols + n_lane)
                                : 0.f;
-      // (a long wait by design - most of a tile's K loop: sleeping between polls leaves the
-      // issue slots and the power of eight idle warps to the working ones, 1 % of the step
-      // under the power cap)
-      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, kEpiloguePollNs)) {
+      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) {
         set_status(g.status, kStatusWaitTimeoutEpilogue);
         *abort_flag = 1;
         break;
@@ -592,12 +586,14 @@ template <int EPI>
 static cudaError_t launch_pair(gptoss_moe *h, const CUtensorMap &tw, const CUtensorMap *tx,
                                const GemmArgs &g, cudaStream_t stream) {
   const bool dep = h->opt_dependent_launch != 0;
-  // MXFP4: the packed weights wait in the raw ring, which is what covers HBM latency (12 x 4.25 KB
-  // per CTA); decode-sized batches have small token slots and room for six operand stages,
-  // two per group of expanding warps, full-width token slots for four, one per group
+  // MXFP4: four operand stages, one per group of four expanding warps; the packed weights wait
+  // in the raw ring, which is what covers HBM latency (24 x 4.25 KB per CTA beside the small
+  // token slots of decode-sized batches, 12 beside full-width ones).  Six operand stages with
+  // three groups that alternate between two stages each (<EPI, 6, true, 32, 12>) measured the
+  // same: the expansion's instruction throughput is the bound, not the stage's round trip.
   if (h->cfg.weight_format == GPTOSS_WEIGHTS_MXFP4) {
     if (h->cur_tile_rows == 64)
-      return launch_pair_stages<EPI, 6, true, 32, 12>(h->num_sms, &h->launches, tx[0], tx, g,
+      return launch_pair_stages<EPI, 4, true, 32, 24>(h->num_sms, &h->launches, tx[0], tx, g,
                                                       stream, dep);
     return launch_pair_stages<EPI, 4, true, 128, 12>(h->num_sms, &h->launches, tx[0], tx, g,
                                                      stream, dep);

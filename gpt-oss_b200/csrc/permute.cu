@@ -244,15 +244,16 @@ gather_rows_kernel(bf16 *__restrict__ xs, const bf16 *__restrict__ rows,
     }
     const uint4 *s4 = reinterpret_cast<const uint4 *>(rows + static_cast<size_t>(src) * H);
     uint4 *d4 = reinterpret_cast<uint4 *>(xs + static_cast<size_t>(r) * H);
-    // four loads in flight per lane before the first store
-    for (int p0 = lane; p0 < n4; p0 += 128) {
-      uint4 v[4];
+    // eight loads in flight per lane before the first store; the copy is written once and
+    // read once by the next kernel: streaming stores
+    for (int p0 = lane; p0 < n4; p0 += 256) {
+      uint4 v[8];
 #pragma unroll
-      for (int u = 0; u < 4; u++)
+      for (int u = 0; u < 8; u++)
         if (p0 + u * 32 < n4) v[u] = __ldg(s4 + p0 + u * 32);
 #pragma unroll
-      for (int u = 0; u < 4; u++)
-        if (p0 + u * 32 < n4) d4[p0 + u * 32] = v[u];
+      for (int u = 0; u < 8; u++)
+        if (p0 + u * 32 < n4) __stcs(d4 + p0 + u * 32, v[u]);
     }
   }
 }

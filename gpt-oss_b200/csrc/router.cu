@@ -529,7 +529,7 @@ router_tx_kernel(const __grid_constant__ CUtensorMap tmap_t,
     }
   } else {
     // accumulator -> logits [token][expert] in shared memory, bias added
-    if (!mbar_wait(tfull_bar, 0, abort_flag, 200)) {  // the whole K loop: sleep between polls
+    if (!mbar_wait(tfull_bar, 0, abort_flag)) {
       set_status(status, kStatusWaitTimeoutEpilogue);
       *abort_flag = 1;
     }
