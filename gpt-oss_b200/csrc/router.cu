@@ -668,14 +668,30 @@ router_tx_kernel(const __grid_constant__ CUtensorMap tmap_t,
         if (r + 1 < rounds_chk && bv[r] - bv[r + 1] < kTieGuardTc) flag = true;
     }
     // list the contenders of a flagged row: everything within twice the guard of the K-th
-    // value, each lane its own quarter of the row
+    // value
     float kth = bv[0];
 #pragma unroll
     for (int r = 1; r < NS; r++)
       if (r < K) kth = bv[r];
     const float thr = kth - 2.f * kTieGuardTc;
     bool full = false;
-    if (flag) {
+    if (flag && bv[NS - 1] < thr) {
+      // the usual case: the band ends inside the kept list, which then names every contender
+      // (walking the row again for them cost a CTA with a near tie 4.5 us)
+      if (sub == 0) {
+#pragma unroll
+        for (int p = 0; p < NS; p++) {
+          if (bv[p] >= thr) {
+            const int at = atomicAdd(n_pairs, 1);
+            if (at < kRxPairs)
+              pairs[at] = (row << 16) | bi[p];
+            else
+              full = true;
+          }
+        }
+      }
+    } else if (flag) {
+      // even the last kept value is inside the band: there may be more beyond the list
       for (int e = sub; e < E && !full; e += kG) {
         if (my[e] >= thr) {
           const int at = atomicAdd(n_pairs, 1);
