@@ -111,13 +111,23 @@ __device__ __forceinline__ void decode_tile(int tile, int w_pairs, int tt_lo, in
 // TOKB = token rows a CTA's operand slot holds (128: token tiles of up to 256; 32:
 // tiles of up to 64 for decode-sized batches, which buys a deeper ring)
 // kRawStages = depth of the raw (packed) weight ring, 0 without MX
-template <int EPI, int kPairStages, bool MX, int TOKB, int kRawStages>
+// TA = the expanded weights go to tensor memory, not to the operand ring (MX, decode-sized
+// token tiles): see the dequantising warps below
+template <int EPI, int kPairStages, bool MX, int TOKB, int kRawStages, bool TA>
 __global__ void __launch_bounds__(kPairThreads + (MX ? (dq_warps(kPairStages) + 1) * 32 : 0), 1)
 grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
                          const __grid_constant__ CUtensorMap tmap_x,
                          const __grid_constant__ CUtensorMap tmap_x32,
                          const __grid_constant__ CUtensorMap tmap_x8, const GemmArgs g) {
-  constexpr int kPairStageBytes = kPairOperandBytes + TOKB * kTileK * 2;  // weights + token half
+  constexpr int kTokOff = TA ? 0 : kPairOperandBytes;           // token half within a stage
+  constexpr int kPairStageBytes = kTokOff + TOKB * kTileK * 2;  // weights (unless TA) + token half
+  // TMEM columns: two accumulators of up to 256 token columns; with TA the token tiles have
+  // at most 64 rows, the accumulators sit 64 columns apart and the weight operand takes 32
+  // columns (64 k as bf16 pairs) per stage from column 128 on
+  constexpr int kAccStride = TA ? 64 : kAccColsPair;
+  constexpr int kTmemACol0 = 128;
+  static_assert(!TA || (MX && TOKB == 32 && kTmemACol0 + kPairStages * 32 <= 512),
+                "the TMEM-resident weight operand needs MX, 64-row token tiles and room in TMEM");
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   unsigned char *smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
@@ -253,8 +263,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
               // the weights arrive through the raw ring and the dequantising warps
               mbar_arrive_expect_tx(&full_bar[stage], 2 * tok_bytes);
             }
-            tma_load_2d_pair_hint(sa + kPairOperandBytes, tx, &full_bar[stage], kb * kTileK, trow,
-                                  pol_x);
+            tma_load_2d_pair_hint(sa + kTokOff, tx, &full_bar[stage], kb * kTileK, trow, pol_x);
           }
           if (++stage == kPairStages) {
             stage = 0;
@@ -314,7 +323,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * kAccColsPair;
+        const uint32_t d_tmem = tmem_base + acc * kAccStride;
         for (int kb = 0; kb < kb_count; kb++) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
             set_status(g.status, kStatusWaitTimeoutMma);
@@ -325,11 +334,16 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * kPairStageBytes);
           const uint64_t da = umma_smem_desc_sw128(sa);
-          const uint64_t db = umma_smem_desc_sw128(sa + kPairOperandBytes);
+          const uint64_t db = umma_smem_desc_sw128(sa + kTokOff);
           if (elect_one()) {
 #pragma unroll
-            for (int k = 0; k < kTileK / 16; k++)
-              umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < kTileK / 16; k++) {
+              if (TA)  // 16 k = 8 columns of the stage's 32
+                umma_bf16_pair_ta(d_tmem, tmem_base + kTmemACol0 + stage * 32 + k * 8, db + 2 * k,
+                                  idesc, (kb | k) != 0 ? 1u : 0u);
+              else
+                umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
             umma_commit_pair(&empty_bar[stage], 3);  // frees the stage in both CTAs
           }
           if (++stage == kPairStages) {
@@ -370,7 +384,44 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
         tc_fence_after();  // the MMAs that read this operand slot are done
         const unsigned char *rq = raw_ring + rs * kRawStageBytes;
         unsigned char *slot = smem + stage * kPairStageBytes;
-        {
+        if (TA) {
+          // A lane expands one whole weight row of the block (64 codes, two scales) and
+          // stores it into its own TMEM lane: the warp's quarter of TMEM (warp index % 4)
+          // decides which 32 rows it takes.  Column 16 h + 4 j + p of the stage holds
+          // elements 32 h + 8 j + 2 p and + 1 of the row, the layout the MMA reads its M
+          // operand in.  Nothing of the weights touches shared memory after the raw tile.
+          const int qrow = (warp & 3) * 32 + lane;
+          const uint32_t sc2 = *reinterpret_cast<const unsigned short *>(rq + kRawCodeBytes + 2 * qrow);
+          const uint32_t taddr_a = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) +
+                                   kTmemACol0 + stage * 32;
+#pragma unroll
+          for (int hf = 0; hf < 2; hf++) {
+            const uint4 q0 = *reinterpret_cast<const uint4 *>(rq + (2 * qrow + hf) * 16);
+            const uint32_t sc = (sc2 >> (8 * hf)) & 0xFFu;
+            const uint32_t s1 = sc < 128u ? sc : 128u;
+            const uint32_t m1 = (s1 + 126u) << 7;
+            const uint32_t mul = m1 | (m1 << 16);
+            const bool two = __any_sync(0xffffffffu, sc > 128u);
+            const uint32_t m2 = (sc > 128u ? sc - 1u : 127u) << 7, mul2 = m2 | (m2 << 16);
+            const uint32_t words[4] = {q0.x, q0.y, q0.z, q0.w};
+            uint32_t o[16];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              const uint32_t w = words[j], w8 = w >> 8;
+              o[4 * j + 0] = bf16x2_mul(e2m1_pair_to_bf16x2_raw<true>(w & 0x000F000Fu), mul);
+              o[4 * j + 1] = bf16x2_mul(e2m1_pair_to_bf16x2_raw<false>(w & 0x00F000F0u), mul);
+              o[4 * j + 2] = bf16x2_mul(e2m1_pair_to_bf16x2_raw<true>(w8 & 0x000F000Fu), mul);
+              o[4 * j + 3] = bf16x2_mul(e2m1_pair_to_bf16x2_raw<false>(w8 & 0x00F000F0u), mul);
+            }
+            if (two) {
+#pragma unroll
+              for (int j = 0; j < 16; j++) o[j] = bf16x2_mul(o[j], mul2);
+            }
+            tmem_st16(taddr_a + 16 * hf, o);
+          }
+          tmem_st_wait();
+          tc_fence_before();
+        } else {
 #pragma unroll
           for (int i = 0; i < kChunkIters; i++) {
             const int c = (sub * kChunkIters + i) * 32 + lane;
@@ -410,7 +461,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
             }
           }
         }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (!TA) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) {
           mbar_arrive(&raw_empty[rs]);
@@ -447,7 +498,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
       }
       tc_fence_after();
       const uint32_t taddr =
-          tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kAccColsPair;
+          tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kAccStride;
       const int n_chunks = (ntok + 31) >> 5;
       {
         for (int c = half; c < n_chunks; c += 2) {
@@ -552,14 +603,15 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
   }
 }
 
-template <int EPI, int STAGES, bool MX, int TOKB, int RAWS>
+template <int EPI, int STAGES, bool MX, int TOKB, int RAWS, bool TA = false>
 static cudaError_t launch_pair_stages(int num_sms, long long *launches, const CUtensorMap &tw,
                                       const CUtensorMap *tx, const GemmArgs &g,
                                       cudaStream_t stream, bool dependent = false) {
-  const size_t smem = 1024 + STAGES * (kPairOperandBytes + TOKB * kTileK * 2) + kPairBarrierBytes +
+  const size_t smem = 1024 + STAGES * ((TA ? 0 : kPairOperandBytes) + TOKB * kTileK * 2) +
+                      kPairBarrierBytes +
                       PairStage<EPI>::kTotalBytes +
                       (MX ? RAWS * kRawStageBytes : 0);
-  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_pair_kernel<EPI, STAGES, MX, TOKB, RAWS>,
+  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_pair_kernel<EPI, STAGES, MX, TOKB, RAWS, TA>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg = {};
@@ -577,8 +629,8 @@ static cudaError_t launch_pair_stages(int num_sms, long long *launches, const CU
   cfg.attrs = attr;
   cfg.numAttrs = dependent ? 2 : 1;
   if (launches) ++*launches;
-  return cudaLaunchKernelEx(&cfg, grouped_gemm_pair_kernel<EPI, STAGES, MX, TOKB, RAWS>, tw, tx[0], tx[1], tx[2],
-                            g);
+  return cudaLaunchKernelEx(&cfg, grouped_gemm_pair_kernel<EPI, STAGES, MX, TOKB, RAWS, TA>, tw,
+                            tx[0], tx[1], tx[2], g);
 }
 
 template <int EPI>
@@ -592,9 +644,13 @@ static cudaError_t launch_pair(gptoss_moe *h, const CUtensorMap &tw, const CUten
   // three groups that alternate between two stages each (<EPI, 6, true, 32, 12>) measured the
   // same: the expansion's instruction throughput is the bound, not the stage's round trip.
   if (h->cfg.weight_format == GPTOSS_WEIGHTS_MXFP4) {
-    if (h->cur_tile_rows == 64)
+    if (h->cur_tile_rows == 64) {
+      if (h->opt_mx_tmem)
+        return launch_pair_stages<EPI, 8, true, 32, 32, true>(h->num_sms, &h->launches, tx[0], tx,
+                                                              g, stream, dep);
       return launch_pair_stages<EPI, 4, true, 32, 24>(h->num_sms, &h->launches, tx[0], tx, g,
                                                       stream, dep);
+    }
     return launch_pair_stages<EPI, 4, true, 128, 12>(h->num_sms, &h->launches, tx[0], tx, g,
                                                      stream, dep);
   }

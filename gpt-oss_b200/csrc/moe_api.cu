@@ -654,6 +654,8 @@ int gptoss_moe_set_option(gptoss_moe_t *h, const char *name, int value) {
     h->opt_router_impl = value;
   } else if (!strcmp(name, "l2_hints")) {
     h->opt_l2_hints = value != 0;
+  } else if (!strcmp(name, "mx_tmem")) {
+    h->opt_mx_tmem = value != 0;
   } else if (!strcmp(name, "ep_dedup")) {
     h->opt_ep_dedup = value != 0;
   } else if (!strcmp(name, "ep_push")) {

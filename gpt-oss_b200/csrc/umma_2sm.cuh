@@ -72,6 +72,20 @@ __device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a,
       : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same with the M operand in tensor memory (lane = row, 32-bit column = two consecutive
+// k): each CTA's 128 rows sit at the same address of its own TMEM.
+__device__ __forceinline__ void umma_bf16_pair_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b,
+                                                  uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "}"
+      :
+      : "r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Arrive on the mbarrier at this offset in every CTA of `cta_mask` once all MMAs
 // issued so far are done.
 __device__ __forceinline__ void umma_commit_pair(uint64_t *bar, uint16_t cta_mask) {

@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 
 
 def _case(pkg, oracle, T, H, IM, E, K, inactive=0, on_device=False, scale_range=(119, 123), seed=0,
-          input_scale=0.25):
+          input_scale=0.25, mx_tmem=None):
     import torch
 
     shape = synth.MoeShape("mx", T, H, IM, E, K, 7.0, 500 + seed)
@@ -42,6 +42,8 @@ def _case(pkg, oracle, T, H, IM, E, K, inactive=0, on_device=False, scale_range=
             eng.load_layer_mxfp4(0, *[np.ascontiguousarray(a) for a in args], on_device=False)
         with pytest.raises(pkg.MoeError):
             eng.set_option("gemm_impl", pkg.GEMM_TCGEN05)
+        if mx_tmem is not None:
+            eng.set_option("mx_tmem", mx_tmem)
         t = helpers.to_dev_bf16(d["t"], dev)
         x = helpers.to_dev_bf16(np.zeros_like(d["x"]), dev)
         pos = torch.from_numpy(d["pos"]).to(dev)
@@ -73,6 +75,16 @@ def test_mxfp4_layer_against_oracle(pkg, oracle, T, H, IM, E, K, inactive):
     _case(pkg, oracle, T, H, IM, E, K, inactive)
 
 
+@pytest.mark.parametrize("T,H,IM,E,K", [
+    (64, 96, 160, 8, 2),
+    (40, 2880, 2880, 4, 2),
+])
+def test_mxfp4_decode_tiles_expanded_into_tensor_memory(pkg, oracle, T, H, IM, E, K):
+    # decode-sized batches: the variant that stores the expanded weights into tensor memory
+    # (the MMA's M operand read from there) instead of the shared-memory operand ring
+    _case(pkg, oracle, T, H, IM, E, K, mx_tmem=1)
+
+
 def test_mxfp4_device_side_upload_and_all_scale_codes(pkg, oracle):
     # scales over a wide range, including small exponents whose values are bf16 subnormals' neighbours
     _case(pkg, oracle, 100, 128, 96, 8, 4, on_device=True, scale_range=(110, 126), seed=3)
@@ -82,3 +94,5 @@ def test_mxfp4_scales_above_one(pkg, oracle):
     # block scales up to 2^4 (e8m0 131): weights up to 96, past the exponent one bf16 multiply
     # of the expansion can carry; inputs scaled down to keep the pre-activations near the clamp
     _case(pkg, oracle, 96, 128, 96, 8, 4, scale_range=(125, 131), seed=5, input_scale=2.0 ** -8)
+    _case(pkg, oracle, 96, 128, 96, 8, 4, scale_range=(125, 131), seed=5, input_scale=2.0 ** -8,
+          mx_tmem=1)
