@@ -133,7 +133,7 @@ struct gptoss_moe {
   int opt_router_impl = 0;  // 0 = tcgen05 router, 1 = mma.sync router
   int opt_dependent_launch = 1;  // programmatic dependent launch between the layer's kernels
   int opt_l2_hints = 1;
-  int opt_mx_tmem = 0;  // MXFP4, decode-sized tiles: expanded weights go to TMEM, not shared memory
+  int opt_mx_tmem = 1;  // MXFP4, decode-sized tiles: three K blocks per stage, expanded weights in TMEM
   // peer transport: the down GEMM stores every expert output row straight into the memory of
   // the rank whose token it belongs to (1), or leaves it here for that rank to fetch (0)
   int opt_ep_push = 1;

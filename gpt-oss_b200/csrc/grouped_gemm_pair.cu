@@ -71,6 +71,18 @@ struct PairStage {
 // tiles' bytes.  The expansion is register arithmetic only (a table in shared memory cost
 // more shared-memory cycles per K block than the MMAs' own operand reads): per code pair a
 // mask, a multiply, a mask and the multiply by the block scale.
+//
+// Decode-sized batches (token tiles of at most 64 rows, template flag TA) go one step
+// further.  With so few tokens a K block holds little work of any kind and the hand-shakes
+// around it - four rings, each with a wait, an issue and an arrival or a commit per K
+// block - are most of its time: with the expansion's arithmetic, the MMAs, the token loads
+// and even the weight loads from HBM all switched off, a launch still took 0.72 of its
+// full time.  So (1) a ring stage carries kTaKbs = 3 K blocks: one raw copy, one round of
+// waits and one commit per 192 k; (2) the expanded weights go to tensor memory, not to
+// shared memory: a lane expands one weight row and stores it into its own TMEM lane
+// (tcgen05.st), and the MMA takes its M operand from there.  The accumulators need only
+// 2 x 64 columns, which leaves 384 for four stages of 3 x 32 columns of weights; shared
+// memory holds the raw ring and the token tiles only.
 constexpr int kPairBarrierBytes = 1024;  // mbarriers, TMEM address holder, abort flag
 constexpr int kRawCodeBytes = 128 * 32;
 constexpr int kRawStageBytes = kRawCodeBytes + 128 * 2;
@@ -80,6 +92,7 @@ constexpr int kRawStageBytes = kRawCodeBytes + 128 * 2;
 // next block while the MMAs still read its last one - otherwise the stage's round trip
 // (expand, MMAs, commit, wake-up) sets the pace, not the expansion.
 constexpr int kDqGroupWarps = 4;
+constexpr int kTaKbs = 3;  // K blocks per ring stage when the weights go to TMEM (TA)
 __host__ __device__ constexpr int dq_groups(int stages) { return stages > 4 ? stages / 2 : stages; }
 __host__ __device__ constexpr int dq_warps(int stages) { return dq_groups(stages) * kDqGroupWarps; }
 
@@ -119,14 +132,22 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
                          const __grid_constant__ CUtensorMap tmap_x,
                          const __grid_constant__ CUtensorMap tmap_x32,
                          const __grid_constant__ CUtensorMap tmap_x8, const GemmArgs g) {
-  constexpr int kTokOff = TA ? 0 : kPairOperandBytes;           // token half within a stage
-  constexpr int kPairStageBytes = kTokOff + TOKB * kTileK * 2;  // weights (unless TA) + token half
+  // K blocks per ring stage, i.e. per round of barrier hand-shakes.  With TA the hand-shakes
+  // themselves (wait, issue, commit, wake-up on four rings) are most of a K block's time at
+  // decode sizes, so a stage carries two K blocks: one raw copy, one wait and one commit per
+  // 128 k (the last stage of an odd count carries one)
+  constexpr int kKbs = TA ? kTaKbs : 1;
+  constexpr int kTokOff = TA ? 0 : kPairOperandBytes;  // token half within a stage
+  constexpr int kTokBytes = TOKB * kTileK * 2;          // one K block of the CTA's token half
+  constexpr int kPairStageBytes = kTokOff + kKbs * kTokBytes;  // weights (unless TA) + tokens
+  constexpr int kRawSlotBytes = kKbs * kRawStageBytes;
   // TMEM columns: two accumulators of up to 256 token columns; with TA the token tiles have
   // at most 64 rows, the accumulators sit 64 columns apart and the weight operand takes 32
-  // columns (64 k as bf16 pairs) per stage from column 128 on
+  // columns (64 k as bf16 pairs) per K block from column 128 on
   constexpr int kAccStride = TA ? 64 : kAccColsPair;
   constexpr int kTmemACol0 = 128;
-  static_assert(!TA || (MX && TOKB == 32 && kTmemACol0 + kPairStages * 32 <= 512),
+  constexpr int kTmemAStageCols = kKbs * 32;
+  static_assert(!TA || (MX && TOKB == 32 && kTmemACol0 + kPairStages * kTmemAStageCols <= 512),
                 "the TMEM-resident weight operand needs MX, 64-row token tiles and room in TMEM");
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -199,6 +220,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
   const int first_tile = blockIdx.x >> 1;
   const int total_tiles = n_tt * w_pairs;
   const int kb_count = (g.k_dim + kTileK - 1) / kTileK;
+  const int sb_count = (kb_count + kKbs - 1) / kKbs;  // ring stages per tile
   const int ncl = gridDim.x >> 1;  // clusters of the launch; a cluster strides over the tiles
 
   if (warp == 0) {
@@ -246,7 +268,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
             half_n <= 8 ? &tmap_x8 : ((half_n <= 32 || TOKB == 32) ? &tmap_x32 : &tmap_x);
         const uint32_t tok_bytes =
             (half_n <= 8 ? 8 : ((half_n <= 32 || TOKB == 32) ? 32 : 128)) * kTileK * 2;
-        for (int kb = 0; kb < kb_count; kb++) {
+        for (int sb = 0; sb < sb_count; sb++) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
             set_status(g.status, kStatusWaitTimeoutProducer);
             *abort_flag = 1;
@@ -254,6 +276,8 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
             break;
           }
           unsigned char *sa = smem + stage * kPairStageBytes;
+          const int kb = sb * kKbs;
+          const int nkb = kb_count - kb < kKbs ? kb_count - kb : kKbs;
           if (elect_one()) {
             if (!MX) {
               if (rank == 0)
@@ -261,9 +285,11 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
               tma_load_2d_pair_hint(sa, &tmap_w, &full_bar[stage], kb * kTileK, wrow, pol_w);
             } else if (rank == 0) {
               // the weights arrive through the raw ring and the dequantising warps
-              mbar_arrive_expect_tx(&full_bar[stage], 2 * tok_bytes);
+              mbar_arrive_expect_tx(&full_bar[stage], 2 * tok_bytes * nkb);
             }
-            tma_load_2d_pair_hint(sa + kTokOff, tx, &full_bar[stage], kb * kTileK, trow, pol_x);
+            for (int j = 0; j < nkb; j++)
+              tma_load_2d_pair_hint(sa + kTokOff + j * kTokBytes, tx, &full_bar[stage],
+                                    (kb + j) * kTileK, trow, pol_x);
           }
           if (++stage == kPairStages) {
             stage = 0;
@@ -285,17 +311,19 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
         const int e = g.mtile_expert[tt];
         const size_t blk0 =
             (static_cast<size_t>(e) * (2 * w_pairs) + 2 * wp + rank) * kb_count;
-        for (int kb = 0; kb < kb_count; kb++) {
+        for (int sb = 0; sb < sb_count; sb++) {
           if (!mbar_wait(&raw_empty[rs], rphase ^ 1u, abort_flag)) {
             set_status(g.status, kStatusWaitTimeoutProducer);
             *abort_flag = 1;
             ok = false;
             break;
           }
-          if (elect_one()) {
-            mbar_arrive_expect_tx(&raw_full[rs], kRawStageBytes);
-            bulk_load(raw_ring + rs * kRawStageBytes, g.wq + (blk0 + kb) * kRawStageBytes,
-                      kRawStageBytes, &raw_full[rs]);
+          const int kb = sb * kKbs;
+          const int nkb = kb_count - kb < kKbs ? kb_count - kb : kKbs;
+          if (elect_one()) {  // the K blocks of a tile follow each other in memory
+            mbar_arrive_expect_tx(&raw_full[rs], nkb * kRawStageBytes);
+            bulk_load(raw_ring + rs * kRawSlotBytes, g.wq + (blk0 + kb) * kRawStageBytes,
+                      nkb * kRawStageBytes, &raw_full[rs]);
           }
           if (++rs == kRawStages) {
             rs = 0;
@@ -324,7 +352,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kAccStride;
-        for (int kb = 0; kb < kb_count; kb++) {
+        for (int sb = 0; sb < sb_count; sb++) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
             set_status(g.status, kStatusWaitTimeoutMma);
             *abort_flag = 1;
@@ -334,15 +362,19 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * kPairStageBytes);
           const uint64_t da = umma_smem_desc_sw128(sa);
-          const uint64_t db = umma_smem_desc_sw128(sa + kTokOff);
+          const int nkb = kb_count - sb * kKbs < kKbs ? kb_count - sb * kKbs : kKbs;
           if (elect_one()) {
+            for (int j = 0; j < nkb; j++) {
+              const uint64_t db = umma_smem_desc_sw128(sa + kTokOff + j * kTokBytes);
+              const uint32_t ta = tmem_base + kTmemACol0 + stage * kTmemAStageCols + j * 32;
 #pragma unroll
-            for (int k = 0; k < kTileK / 16; k++) {
-              if (TA)  // 16 k = 8 columns of the stage's 32
-                umma_bf16_pair_ta(d_tmem, tmem_base + kTmemACol0 + stage * 32 + k * 8, db + 2 * k,
-                                  idesc, (kb | k) != 0 ? 1u : 0u);
-              else
-                umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+              for (int k = 0; k < kTileK / 16; k++) {
+                if (TA)  // 16 k = 8 columns of the K block's 32
+                  umma_bf16_pair_ta(d_tmem, ta + k * 8, db + 2 * k, idesc,
+                                    (sb | j | k) != 0 ? 1u : 0u);
+                else
+                  umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (sb | k) != 0 ? 1u : 0u);
+              }
             }
             umma_commit_pair(&empty_bar[stage], 3);  // frees the stage in both CTAs
           }
@@ -365,9 +397,10 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
     const int dw = warp - kPairThreads / 32;
     const int grp = dw / kWarpsPerBlock, sub = dw - grp * kWarpsPerBlock;
     const int my_tiles = first_tile < total_tiles ? (total_tiles - first_tile + ncl - 1) / ncl : 0;
-    const int total_kb = my_tiles * kb_count;
+    const int total_kb = my_tiles * sb_count;  // ring stages this CTA passes through
     constexpr int kChunkIters = 8 / kWarpsPerBlock;
     if (grp < kGroups) {
+      int sb = grp % sb_count;  // the stage's place within its tile
       for (int n = grp; n < total_kb; n += kGroups) {
         constexpr int kRawDiv = kRawStages > 0 ? kRawStages : 1;  // (no raw ring without MX)
         const int rs = n % kRawDiv;
@@ -382,8 +415,11 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
           break;
         }
         tc_fence_after();  // the MMAs that read this operand slot are done
-        const unsigned char *rq = raw_ring + rs * kRawStageBytes;
+        const unsigned char *rq = raw_ring + rs * kRawSlotBytes;
         unsigned char *slot = smem + stage * kPairStageBytes;
+        const int nkb = kb_count - sb * kKbs < kKbs ? kb_count - sb * kKbs : kKbs;
+        sb += kGroups;
+        while (sb >= sb_count) sb -= sb_count;
         if (TA) {
           // A lane expands one whole weight row of the block (64 codes, two scales) and
           // stores it into its own TMEM lane: the warp's quarter of TMEM (warp index % 4)
@@ -391,12 +427,15 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
           // elements 32 h + 8 j + 2 p and + 1 of the row, the layout the MMA reads its M
           // operand in.  Nothing of the weights touches shared memory after the raw tile.
           const int qrow = (warp & 3) * 32 + lane;
-          const uint32_t sc2 = *reinterpret_cast<const unsigned short *>(rq + kRawCodeBytes + 2 * qrow);
+          for (int jb = 0; jb < nkb; jb++) {
+          const unsigned char *rqb = rq + jb * kRawStageBytes;
+          const uint32_t sc2 =
+              *reinterpret_cast<const unsigned short *>(rqb + kRawCodeBytes + 2 * qrow);
           const uint32_t taddr_a = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) +
-                                   kTmemACol0 + stage * 32;
+                                   kTmemACol0 + stage * kTmemAStageCols + jb * 32;
 #pragma unroll
           for (int hf = 0; hf < 2; hf++) {
-            const uint4 q0 = *reinterpret_cast<const uint4 *>(rq + (2 * qrow + hf) * 16);
+            const uint4 q0 = *reinterpret_cast<const uint4 *>(rqb + (2 * qrow + hf) * 16);
             const uint32_t sc = (sc2 >> (8 * hf)) & 0xFFu;
             const uint32_t s1 = sc < 128u ? sc : 128u;
             const uint32_t m1 = (s1 + 126u) << 7;
@@ -418,6 +457,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w,
               for (int j = 0; j < 16; j++) o[j] = bf16x2_mul(o[j], mul2);
             }
             tmem_st16(taddr_a + 16 * hf, o);
+          }
           }
           tmem_st_wait();
           tc_fence_before();
@@ -607,10 +647,11 @@ template <int EPI, int STAGES, bool MX, int TOKB, int RAWS, bool TA = false>
 static cudaError_t launch_pair_stages(int num_sms, long long *launches, const CUtensorMap &tw,
                                       const CUtensorMap *tx, const GemmArgs &g,
                                       cudaStream_t stream, bool dependent = false) {
-  const size_t smem = 1024 + STAGES * ((TA ? 0 : kPairOperandBytes) + TOKB * kTileK * 2) +
+  constexpr int kbs = TA ? kTaKbs : 1;  // K blocks per ring stage
+  const size_t smem = 1024 + STAGES * ((TA ? 0 : kPairOperandBytes) + kbs * TOKB * kTileK * 2) +
                       kPairBarrierBytes +
                       PairStage<EPI>::kTotalBytes +
-                      (MX ? RAWS * kRawStageBytes : 0);
+                      (MX ? RAWS * kbs * kRawStageBytes : 0);
   cudaError_t e = cudaFuncSetAttribute(grouped_gemm_pair_kernel<EPI, STAGES, MX, TOKB, RAWS, TA>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
@@ -639,14 +680,17 @@ static cudaError_t launch_pair(gptoss_moe *h, const CUtensorMap &tw, const CUten
                                const GemmArgs &g, cudaStream_t stream) {
   const bool dep = h->opt_dependent_launch != 0;
   // MXFP4: four operand stages, one per group of four expanding warps; the packed weights wait
-  // in the raw ring, which is what covers HBM latency (24 x 4.25 KB per CTA beside the small
-  // token slots of decode-sized batches, 12 beside full-width ones).  Six operand stages with
-  // three groups that alternate between two stages each (<EPI, 6, true, 32, 12>) measured the
-  // same: the expansion's instruction throughput is the bound, not the stage's round trip.
+  // in the raw ring, which is what covers HBM latency (24 K blocks of 4.25 KB per CTA beside
+  // the small token slots of decode-sized batches, 12 beside full-width ones).  Decode-sized
+  // batches take the variant with three K blocks per stage and the expanded weights in TMEM
+  // (18-30 % less time per layer at 64-1024 tokens than with one K block per stage and the
+  // weights expanded into shared memory, which "mx_tmem" = 0 still selects).  Neither more
+  // stages (six, with three groups alternating between two each; five with five groups)
+  // nor the TMEM operand alone (2 %) changed the one-K-block form: its hand-shakes set the pace.
   if (h->cfg.weight_format == GPTOSS_WEIGHTS_MXFP4) {
     if (h->cur_tile_rows == 64) {
       if (h->opt_mx_tmem)
-        return launch_pair_stages<EPI, 8, true, 32, 32, true>(h->num_sms, &h->launches, tx[0], tx,
+        return launch_pair_stages<EPI, 4, true, 32, 8, true>(h->num_sms, &h->launches, tx[0], tx,
                                                               g, stream, dep);
       return launch_pair_stages<EPI, 4, true, 32, 24>(h->num_sms, &h->launches, tx[0], tx, g,
                                                       stream, dep);

@@ -214,9 +214,10 @@ int gptoss_moe_get_activations(gptoss_moe_t *h, void *act_host, size_t bytes);
  * the layer's kernels are launched with programmatic stream serialization, so a
  * kernel's set-up overlaps its predecessor's tail), "l2_hints" (0/1, default 1:
  * the CTA-pair GEMM marks its token loads evict-last in L2 and the weight loads of
- * experts whose rows fit one token tile evict-first), "mx_tmem" (0/1, default 0;
- * MXFP4 weights, decode-sized batches: the expanded weights are stored into tensor
- * memory and the MMA reads them there, instead of into the shared-memory operand ring),
+ * experts whose rows fit one token tile evict-first), "mx_tmem" (0/1, default 1;
+ * MXFP4 weights, decode-sized batches: a pipeline stage carries three K blocks and the
+ * expanded weights are stored into tensor memory, where the MMA reads them; 0: one K
+ * block per stage, expanded into the shared-memory operand ring),
  * "wait_limit_ms" (1..60000, default 2000: how long a
  * kernel of the peer-memory transport waits for another rank's flag before it
  * gives up with status 106).  Every option leaves the results unchanged. */

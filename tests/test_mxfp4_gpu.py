@@ -79,10 +79,11 @@ def test_mxfp4_layer_against_oracle(pkg, oracle, T, H, IM, E, K, inactive):
     (64, 96, 160, 8, 2),
     (40, 2880, 2880, 4, 2),
 ])
-def test_mxfp4_decode_tiles_expanded_into_tensor_memory(pkg, oracle, T, H, IM, E, K):
-    # decode-sized batches: the variant that stores the expanded weights into tensor memory
-    # (the MMA's M operand read from there) instead of the shared-memory operand ring
-    _case(pkg, oracle, T, H, IM, E, K, mx_tmem=1)
+def test_mxfp4_decode_tiles_expanded_into_shared_memory(pkg, oracle, T, H, IM, E, K):
+    # decode-sized batches expand the weights into tensor memory, three K blocks per pipeline
+    # stage, by default (every other case of this file); the variant with one K block per
+    # stage and the weights expanded into the shared-memory operand ring stays selectable
+    _case(pkg, oracle, T, H, IM, E, K, mx_tmem=0)
 
 
 def test_mxfp4_device_side_upload_and_all_scale_codes(pkg, oracle):
@@ -95,4 +96,4 @@ def test_mxfp4_scales_above_one(pkg, oracle):
     # of the expansion can carry; inputs scaled down to keep the pre-activations near the clamp
     _case(pkg, oracle, 96, 128, 96, 8, 4, scale_range=(125, 131), seed=5, input_scale=2.0 ** -8)
     _case(pkg, oracle, 96, 128, 96, 8, 4, scale_range=(125, 131), seed=5, input_scale=2.0 ** -8,
-          mx_tmem=1)
+          mx_tmem=0)
