@@ -793,7 +793,8 @@ def measure_decode_mxfp4(args, pkg, dev):
         torch.cuda.synchronize()
         if eng.device_status() != 0:
             raise SystemExit("device status non-zero")
-        eng.set_option("time_stages", 1)
+        # the step time without events between the stages (they keep a kernel's set-up from
+        # overlapping its predecessor's tail), the stage times from a second pass with them
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record()
         for _ in range(args.steps):
@@ -801,6 +802,14 @@ def measure_decode_mxfp4(args, pkg, dev):
         ev1.record()
         torch.cuda.synchronize()
         ms = ev0.elapsed_time(ev1) / args.steps
+        eng.set_option("time_stages", 1)
+        ev2, ev3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev2.record()
+        for _ in range(args.steps):
+            eng.forward(0, t, x, None, T, stream)
+        ev3.record()
+        torch.cuda.synchronize()
+        ms_staged = ev2.elapsed_time(ev3) / args.steps
         stage_ms = {s: eng.stage_ms(s) for s in ("route", "permute", "gate_up", "down", "combine")}
         eng.set_option("time_stages", 0)
         r = eng.get_routing(T)
@@ -809,7 +818,8 @@ def measure_decode_mxfp4(args, pkg, dev):
         gemm_ms = stage_ms["gate_up"] + stage_ms["down"]
         gbs = touched * per_expert_bytes / (gemm_ms * 1e-3) / 1e9
         results[str(T)] = {
-            "tokens_per_s": T / (ms * 1e-3), "ms_per_step": ms, "stage_ms": stage_ms,
+            "tokens_per_s": T / (ms * 1e-3), "ms_per_step": ms,
+            "ms_per_step_with_stage_events": ms_staged, "stage_ms": stage_ms,
             "experts_touched": touched, "busiest_expert_share": float(counts.max() / counts.sum()),
             "roofline": {"kernel": "grouped_gemm_pair_kernel<*, mxfp4> (gate_up + down)",
                          "bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
